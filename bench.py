@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Mini-batch throughput of the sampling-server hot path on seeded synthetic graphs.
+
+    python bench.py --gpus N --steps K --warmup W            # CUDA path (this repository)
+    python bench.py --impl reference --steps K --warmup W     # CPU pipeline on the host cores
+
+A step is one mini-batch per GPU: seeds -> neighbour sampling (all hops) -> dedup / relabel ->
+cache lookup -> feature gather, outputs left in the double-buffered hand-off buffers.
+`value` = batches of all ranks / device time (CUDA events on the runner's streams, max over ranks)
+with all inputs resident; `e2e` = the same batches through the host-buffer C-ABI call, seeds copied
+in from pinned host memory and the block structure copied back inside the timed region.
+One JSON line on stdout (rank 0).
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # products-shaped (BASELINE.json configs[0]); whole table cached
+    "c1": dict(name="products-shaped RMAT", n_nodes=2449029, n_pairs=34000000, feat_len=100, classes=47,
+               train_frac=0.08, batch=800, fanout=[25, 10], cache_frac=1.0),
+    # paper100M-shaped (configs[1]): the configuration the metric is quoted on
+    "c2": dict(name="paper100M-shaped RMAT", n_nodes=111059956, n_pairs=900000000, feat_len=128, classes=172,
+               train_frac=0.011, batch=8000, fanout=[25, 10], cache_frac=0.2),
+    # reduced copy of c2 for checking the harness itself on small machines (never the default)
+    "tiny": dict(name="tiny RMAT (harness check)", n_nodes=200000, n_pairs=2000000, feat_len=128, classes=172,
+                 train_frac=0.2, batch=2000, fanout=[25, 10], cache_frac=0.2),
+}
+
+
+def load_pkg():
+    import __graft_entry__ as ge
+    return ge._package()
+
+
+def load_oracle():
+    import __graft_entry__ as ge
+    return ge._oracle()
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm = sorted(float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit())
+        mx = [float(r[2]) for r in self.rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = set()
+        for r in self.rows:
+            if len(r) > 8:
+                for i, nm in enumerate(names):
+                    if r[5 + i].lower().startswith("active"):
+                        reasons.add(nm)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_graph(cfg, device, seed=0):
+    from legion_ibp_b200 import synth
+    return synth.rmat_csr(cfg["n_nodes"], cfg["n_pairs"], seed=seed, device=device)
+
+
+def host_table(cfg, shared_name=None, rank=0, world=1, pinned=True):
+    """[N, F] fp32 table in host memory, filled by rank 0; pinned / registered for zero-copy reads."""
+    import torch
+    from legion_ibp_b200 import synth
+    n, f = cfg["n_nodes"], cfg["feat_len"]
+    if world == 1:
+        t = torch.empty((n, f), dtype=torch.float32, pin_memory=pinned)
+        synth.features_into(t, seed=0)
+        return t
+    import torch.distributed as dist
+    path = "/dev/shm/" + shared_name
+    if rank == 0:
+        t = torch.from_file(path, shared=True, size=n * f, dtype=torch.float32).view(n, f)
+        synth.features_into(t, seed=0)
+    dist.barrier()
+    if rank != 0:
+        t = torch.from_file(path, shared=True, size=n * f, dtype=torch.float32).view(n, f)
+    err = torch.cuda.cudart().cudaHostRegister(t.data_ptr(), t.numel() * 4, 0)
+    assert int(err) == 0, "cudaHostRegister failed: %s" % err
+    dist.barrier()
+    if rank == 0:
+        os.unlink(path)  # the mappings stay valid
+    return t
+
+
+def bounds(batch, fanout):
+    nodes, edges = batch, 0
+    for k in fanout:
+        e = nodes * k
+        edges += e
+        nodes += e
+    return nodes, edges
+
+
+def run_reference(args, cfg):
+    """CPU arm: the DGL CPU pipeline restated in oracle/ (sample -> relabel -> gather), one batch
+    per host thread, on the same synthetic workload."""
+    import numpy as np
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    O = load_oracle()
+    load_pkg()
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    ip, ix = make_graph(cfg, dev)
+    indptr, indices = ip.cpu().numpy(), ix.cpu().numpy()
+    del ip, ix
+    from legion_ibp_b200 import synth
+    labels, train, _, _ = synth.labels_and_split(cfg["n_nodes"], cfg["classes"], cfg["train_frac"], device=dev)
+    train = train.cpu().numpy()
+    tl = labels.cpu().numpy()[train]
+    table = torch.empty((cfg["n_nodes"], cfg["feat_len"]), dtype=torch.float32)
+    synth.features_into(table, seed=0)
+    table = table.numpy()
+    if dev == "cuda":
+        torch.cuda.empty_cache()
+    cores = O.num_threads()
+    batch, fanout = cfg["batch"], cfg["fanout"]
+    per_step = cores  # one batch per thread and step
+    n_iters = (len(train) - 1) // batch
+    it = 0
+    for _ in range(args.warmup):
+        O.cpu_pipeline(indptr, indices, train, tl, batch, it % max(1, n_iters - per_step), per_step, fanout, 1, table, cores)
+        it += per_step
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.cpu_pipeline(indptr, indices, train, tl, batch, it % max(1, n_iters - per_step), per_step, fanout, 1, table, cores)
+        it += per_step
+    dt = time.perf_counter() - t0
+    value = args.steps * per_step / dt
+    line = {"impl": "reference", "metric": "sampled+gathered mini-batches/sec", "value": value, "unit": "batches/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(cfg, args.gpus),
+            "cpu_baseline": {"value": value, "unit": "batches/s", "cores": cores, "kind": "port",
+                             "sample": "%d batches per step (one per thread), %d steps" % (per_step, args.steps)},
+            "e2e": {"value": value, "unit": "batches/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, n_gpus):
+    return {"workload": "%s: %d nodes, fp32 dim %d, batch %d, fanout %s, static degree-ordered cache %d%% of the "
+                        "table per GPU, misses by zero-copy from pinned host memory" %
+                        (cfg["name"], cfg["n_nodes"], cfg["feat_len"], cfg["batch"], cfg["fanout"],
+                         int(cfg["cache_frac"] * 100)),
+            "batch_per_gpu": cfg["batch"], "fanout": cfg["fanout"], "feat_len": cfg["feat_len"],
+            "parallelism": "dp%d, cache striped over %d GPU(s)" % (n_gpus, n_gpus),
+            "l2": "inputs larger than L2 (topology, cache partition and host table are each GBs)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--cpu-sample-batches", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args, cfg)
+        return
+
+    import numpy as np
+    import torch
+    L = load_pkg()
+    L.lib()  # fails loudly when the CUDA library is missing
+    from legion_ibp_b200 import synth
+    assert torch.cuda.is_available(), "bench.py needs a GPU (use --impl reference for the CPU arm)"
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, "--gpus must equal the number of launched ranks"
+    torch.cuda.set_device(local_rank)
+    dev = local_rank
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    t_setup = time.perf_counter()
+
+    # ---- synthetic inputs -------------------------------------------------------------------
+    indptr, indices = make_graph(cfg, "cuda")
+    torch.cuda.empty_cache()
+    n, f = cfg["n_nodes"], cfg["feat_len"]
+    row_bytes = f * 4
+    n_edges = int(indices.numel())
+    labels, train, _, _ = synth.labels_and_split(n, cfg["classes"], cfg["train_frac"], device="cuda")
+    mine = train[(train % world) == rank].contiguous()  # id % ngpu split, storage_management.cu:214-250
+    mine_labels = labels[mine.long()].contiguous()
+    table = host_table(cfg, "legion_b200_bench_features", rank, world)
+
+    # ---- storage, cache, pool, runner ------------------------------------------------------------
+    g = L.GraphStorage(dev, indptr, indices)
+    fs = L.FeatureStorage(dev, n, row_bytes, table)
+    fs.set_split(L.TRAINMODE, mine, mine_labels)
+    order = torch.empty(n, dtype=torch.int32, device="cuda")
+    L.UnifiedCache.degree_order(dev, indptr, order)
+    cap = min(n, int(n * cfg["cache_frac"]))
+    if cap * world >= n:
+        cap = (n + world - 1) // world
+    cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank)
+    cache.fill_static(order, table)
+    del order
+    if world > 1:
+        exchange_partitions(L, cache, rank, world, dist)
+    pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, 2)
+    pool.set_rng(0x5EED + rank, 64)
+    runner = L.Runner(dev, g, fs, cache, pool, None)
+    n_iters = (int(mine.numel()) - 1) // cfg["batch"]
+    torch.cuda.synchronize()
+    setup_s = time.perf_counter() - t_setup
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- value: inputs resident, device-timed ----------------------------------------------------
+    step = 0
+    for _ in range(args.warmup):
+        runner.enqueue(step, L.TRAINMODE, step % n_iters)
+        step += 1
+    runner.sync()
+    stats0 = cache.stats()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.steps):
+        runner.enqueue(step, L.TRAINMODE, step % n_iters)
+        step += 1
+    runner.sync()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    tm = runner.timing()
+    stats1 = cache.stats()
+    ms_total = max_over_ranks(tm["batch_ms"])
+    value = args.steps * world / (ms_total * 1e-3)
+    assert pool.device_error() == 0, "device-side error flag set"
+
+    # ---- roofline of the gather ---------------------------------------------------------------------
+    d = {k: stats1[k] - stats0[k] for k in stats0}
+    rows = d["local_hits"] + d["peer_hits"] + d["misses"]
+    gather_launches = args.steps * (len(cfg["fanout"]) + 1)
+    gather_bytes = rows * (2 * row_bytes + 8)            # row read + row written + id + table entry
+    gather_s = tm["gather_ms"] * 1e-3
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = gather_bytes / gather_s / 1e9 if gather_s > 0 else 0.0
+    roofline = {"bound": "hbm", "kernel": "gather_vec_kernel (lookup + gather, all sources)",
+                "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s",
+                "traffic": None,
+                "avg_launch_ms": tm["gather_ms"] / max(1, gather_launches),
+                "rows_per_batch": rows / args.steps,
+                "source_split": {k: d[k] / max(1, rows) for k in ("local_hits", "peer_hits", "misses")},
+                "host_link_GBps": d["misses"] * row_bytes / gather_s / 1e9 if gather_s > 0 else 0.0}
+
+    # ---- e2e: host buffers through the C ABI --------------------------------------------------------
+    max_nodes, max_edges = bounds(cfg["batch"], cfg["fanout"])
+    seeds_h = mine.cpu().numpy()
+    labels_h = mine_labels.cpu().numpy()
+    ids_o = torch.empty(max_nodes, dtype=torch.int32).pin_memory().numpy()
+    lab_o = np.empty(cfg["batch"], np.int32)
+    src_o = torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy()
+    dst_o = torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy()
+    nc_o, ec_o = np.zeros(16, np.int32), np.zeros(16, np.int32)
+    b = cfg["batch"]
+
+    def host_step(i):
+        it = i % n_iters
+        pool.set_batch(it, L.TRAINMODE, i % 2, i)
+        return L.run_batch_host(g, fs, cache, pool, dev, seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b],
+                                ids_o, lab_o, src_o, dst_o, nc_o, ec_o, None)
+
+    for i in range(3):
+        host_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    d2h = 0
+    for i in range(args.steps):
+        nn, ne = host_step(100 + i)
+        d2h += 4 * nn + 8 * ne + 4 * b + 128
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    e2e = {"value": args.steps * world / e2e_s, "unit": "batches/s", "h2d_bytes_per_step": 8 * b,
+           "d2h_bytes_per_step": d2h // args.steps,
+           "note": "seeds+labels copied in, ids/labels/edge lists/counters copied out; gathered rows stay in the "
+                   "device hand-off buffer where the trainer reads them; missed rows cross the host link inside "
+                   "the gather"}
+
+    # ---- CPU baseline on this box's cores (rank 0, N=1 only) ----------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        O = load_oracle()
+        cores = O.num_threads()
+        nb = args.cpu_sample_batches or 2 * cores
+        h_indptr, h_indices = indptr.cpu().numpy(), indices.cpu().numpy()
+        tnp = table.numpy()
+        O.cpu_pipeline(h_indptr, h_indices, seeds_h, labels_h, b, 0, cores, cfg["fanout"], 1, tnp, cores)
+        t0 = time.perf_counter()
+        O.cpu_pipeline(h_indptr, h_indices, seeds_h, labels_h, b, cores, nb, cfg["fanout"], 1, tnp, cores)
+        dt = time.perf_counter() - t0
+        cpu = {"value": nb / dt, "unit": "batches/s", "cores": cores, "kind": "port",
+               "sample": "%d batches of the same workload (sample + relabel + gather), %d threads, %.1f s" %
+                         (nb, cores, dt)}
+
+    if rank == 0:
+        hops = len(cfg["fanout"])
+        line = {"metric": "sampled+gathered mini-batches/sec", "value": value, "unit": "batches/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, world),
+                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + (hops + 1)),
+                "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+                "graph": {"nodes": n, "directed_edges": n_edges, "train_seeds_this_rank": int(mine.numel()),
+                          "cache_rows_per_gpu": cap}, "setup_s": setup_s}
+        print(json.dumps(line), flush=True)
+    runner.Finalize()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def exchange_partitions(L, cache, rank, world, dist):
+    """Every rank publishes its cache partition as a CUDA IPC handle and maps the others'
+    (the pointer table d_float_feature_cache_ptr_ of the reference, cache/cache.cu:601-622, across
+    processes instead of threads).  Peers are then read by plain loads over NVLink."""
+    import ctypes as C
+    import torch
+    ptr, nbytes = cache.partition()
+    handle = (C.c_char * 64)()
+    rc = L.lib().legion_ipc_get_handle(C.c_void_p(ptr), handle)
+    assert rc == 0, L.lib().legion_last_error()
+    mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device="cuda")
+    allh = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    for k in range(world):
+        if k == rank:
+            continue
+        raw = bytes(allh[k].cpu().tolist())
+        p = C.c_void_p()
+        rc = L.lib().legion_ipc_open_handle(raw, C.byref(p))
+        assert rc == 0, L.lib().legion_last_error()
+        cache.set_peer(k, p.value)
+
+
+if __name__ == "__main__":
+    main()

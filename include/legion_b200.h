@@ -1,0 +1,246 @@
+/*
+ * legion_b200.h -- C ABI of the B200 sampling-server hot path.
+ *
+ * Plain pointers and sizes only; no C++ or torch types cross this boundary.  Every entry
+ * point names the reference interface it replaces (paths relative to the reference
+ * repository root).  All functions return 0 on success or a negative LEGION_E_* code and
+ * leave a message for legion_last_error(); nothing here calls exit().  The five operator
+ * entry points also exist under the reference's own symbol names (BatchGenerate,
+ * RandomSample, FeatureCacheLookup, IOSubmit, IOComplete) in legion_b200_compat.h.
+ *
+ * Threading: one host thread per device, as in GPURunner (engine/server.cu:330-331).
+ * Streams are passed as void* (a cudaStream_t).
+ */
+#ifndef LEGION_B200_H
+#define LEGION_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LEGION_OK 0
+#define LEGION_E_ARG (-1)     /* bad argument */
+#define LEGION_E_CUDA (-2)    /* a CUDA call failed */
+#define LEGION_E_NOMEM (-3)   /* allocation failed */
+#define LEGION_E_LIMIT (-4)   /* size above a documented limit */
+#define LEGION_E_STATE (-5)   /* call out of order */
+#define LEGION_E_SYS (-6)     /* shm / semaphore failure */
+#define LEGION_E_TIMEOUT (-7) /* peer did not answer in time */
+
+#define LEGION_MAX_DEVICE 8      /* include/system_config.cuh:50 */
+#define LEGION_INTERBATCH_CON 2  /* include/system_config.cuh:47 */
+#define LEGION_INTRABATCH_CON 3  /* include/system_config.cuh:48 */
+#define LEGION_MEMORY_USAGE 7    /* include/system_config.cuh:51 */
+#define LEGION_TRAINMODE 0
+#define LEGION_VALIDMODE 1
+#define LEGION_TESTMODE 2
+#define LEGION_CACHEMISS_FLAG (-2) /* include/system_config.cuh:56 */
+#define LEGION_MAX_FANOUT 32       /* engine/operator_impl.cu:504 */
+#define LEGION_MAX_HOPS 3          /* counter slots 9+h / 12+h, engine/operator_impl.cu:80-82 */
+
+#define LEGION_CODEC_RAW 0
+#define LEGION_CODEC_INT8 1
+#define LEGION_CODEC_E4M3 2
+
+typedef struct LegionGraph LegionGraph;       /* GraphStorage,   storage/graph_storage.cuh:7-24 */
+typedef struct LegionFeatures LegionFeatures; /* FeatureStorage, storage/feature_storage.cuh:6-34 */
+typedef struct LegionCache LegionCache;       /* UnifiedCache,   cache/cache.cuh:66-188 */
+typedef struct LegionPool LegionPool;         /* MemoryPool,     engine/memorypool.cuh:20-221 */
+typedef struct LegionIpcEnv LegionIpcEnv;     /* IPCEnv,         engine/ipc_service.h:6-35 */
+typedef struct LegionRunner LegionRunner;     /* Runner,         engine/server.h:23-34 */
+
+const char *legion_last_error(void);
+int legion_abi_version(void);
+/* Blocking copy between raw pointers, for callers without a CUDA binding of their own (the
+ * reference's alloc/copy helpers, engine/server_imp.cuh:1-51).  kind: 1 host->device,
+ * 2 device->host, 3 device->device. */
+int legion_copy(void *dst, const void *src, int64_t bytes, int32_t kind);
+
+/* ---- storage --------------------------------------------------------------------- */
+
+/* NewCompleteGraphStorage + Build (storage/graph_storage.cu:12-74).  indptr/indices must be
+ * readable from device dev_id: device memory or mapped pinned host memory (UVA), as the
+ * reference keeps them (storage/storage_management.cu:114-115).  Not owned. */
+int legion_graph_create(LegionGraph **out, int32_t dev_id, int64_t n_nodes, int64_t n_edges,
+                        const int64_t *indptr, const int32_t *indices);
+int legion_graph_destroy(LegionGraph *g);
+
+/* NewCompleteFeatureStorage + Build (storage/feature_storage.cu:18-90).  host_table is the
+ * full feature table in mapped pinned host memory (row i at i*row_bytes), or NULL when every
+ * row is cached.  row_bytes = feature_len * element size; rows are opaque bytes. */
+int legion_features_create(LegionFeatures **out, int32_t dev_id, int64_t n_nodes, int32_t row_bytes,
+                           const void *host_table);
+/* This GPU's seed list of one mode (GetTrainingSetIds/Labels..., feature_storage.cuh:12-29):
+ * device arrays of `count` int32, not owned. */
+int legion_features_set_split(LegionFeatures *f, int32_t mode, const int32_t *ids_dev,
+                              const int32_t *labels_dev, int32_t count);
+int legion_features_destroy(LegionFeatures *f);
+
+/* ---- cache ----------------------------------------------------------------------- */
+
+/* UnifiedCache::Initialize + the allocation half of FillUp (cache/cache.cu:559-600).
+ * Static cache striped over a clique of kg GPUs, this GPU being member ki; `capacity` rows
+ * per GPU.  codec RAW keeps rows as they are; INT8 / E4M3 keep feature_len codes plus one
+ * fp32 scale per row (row_bytes must then be feature_len*4).  Allocates the lookup table
+ * (one int32 per node) and this GPU's partition. */
+int legion_cache_create(LegionCache **out, int32_t dev_id, int64_t n_nodes, int32_t row_bytes,
+                        int32_t kg, int32_t ki, int32_t capacity, int32_t codec);
+/* Descending-degree order of all nodes, ties by ascending id; the ranking that
+ * CandidateSelection produces from presampled hotness (cache/cache.cu:405-440), with degree as
+ * the key.  order_dev: n_nodes int32 in device memory. */
+int legion_cache_degree_order(int32_t dev_id, const int64_t *indptr, int64_t n_nodes,
+                              int32_t *order_dev, void *stream);
+/* InitPair + Insert + FeatFillUp (cache/cache_impl.cuh:104-109,183-188; cache/cache.cu:74-141):
+ * rank t of `order` lives on GPU t % kg at row t / kg.  Builds the whole lookup table and copies
+ * (and encodes) this GPU's rows from host_table. */
+int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n_order,
+                             const void *host_table, void *stream);
+/* Pointer tables of the clique (d_float_feature_cache_ptr_, cache/cache.cu:601-622). */
+int legion_cache_partition(LegionCache *c, void **ptr, int64_t *bytes);
+int legion_cache_set_peer(LegionCache *c, int32_t k, const void *partition_ptr);
+int legion_cache_lut(LegionCache *c, int32_t **lut_dev);
+/* Table that serves the misses (cpu_float_features_, cache/cache.cu:771-776); set by
+ * legion_cache_fill_static, or here for a cache that is filled some other way. */
+int legion_cache_set_host_table(LegionCache *c, const void *host_table);
+/* Per-GPU set-associative cache with LRU replacement: sets*ways rows.  Addressing follows
+ * comp_cache/static_cache_kernel.cuh:6-29; lookup = retrieve_and_touch, the insertion of missed
+ * rows runs in legion_io_complete (comp_cache/tests/test_cache.cu:57-58 names the calls). */
+int legion_cache_create_lru(LegionCache **out, int32_t dev_id, int64_t n_nodes, int32_t row_bytes,
+                            int64_t sets, int32_t ways);
+int legion_cache_lru_state(LegionCache *c, int32_t **keys_dev, int32_t **stamps_dev, void **rows_dev);
+/* Batch clock used for the stamps: 1 at creation, +1 at every legion_io_complete. */
+int legion_cache_lru_clock(LegionCache *c, int32_t *clock);
+/* counters since creation: [0] local hits, [1] peer hits, [2] misses, [3] lru inserts */
+int legion_cache_stats(LegionCache *c, int64_t stats[4], void *stream);
+int legion_cache_destroy(LegionCache *c);
+
+/* ---- memory pool ------------------------------------------------------------------- */
+
+/* MemoryPool + GPURunner::Initialize buffer allocation + IPCEnv::Initialize{Samples,Features}Buffer
+ * (engine/server.cu:204-265, engine/ipc_service.cu:134-206).  Buffers are sized for the true
+ * worst case of the fanout list.  `pipes` output sets (INTERBATCH_CON).  row_bytes_out is the
+ * size of one gathered row. */
+int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batch_size, int32_t hop_num,
+                       const int32_t *fanout, int32_t row_bytes_out, int32_t pipes);
+int legion_pool_destroy(LegionPool *p);
+#define LEGION_BUF_IDS 0          /* slot order of engine/ipc_service.cu:163-169 */
+#define LEGION_BUF_FEATURES 1
+#define LEGION_BUF_LABELS 2
+#define LEGION_BUF_AGG_SRC 3
+#define LEGION_BUF_AGG_DST 4
+#define LEGION_BUF_NODE_COUNTER 5
+#define LEGION_BUF_EDGE_COUNTER 6
+#define LEGION_BUF_CACHE_INDEX 7  /* cache_search_buffer, engine/server.cu:238 (shared by pipes) */
+#define LEGION_BUF_SRC_GLOBAL 8   /* agg_src_ids, engine/server.cu:244 (shared by pipes) */
+int legion_pool_buffer(LegionPool *p, int32_t which, int32_t pipe, void **ptr, int64_t *bytes);
+int legion_pool_limits(LegionPool *p, int64_t *max_nodes, int64_t *max_edges);
+/* SetIter / SetCurrentMode / SetCurrentPipe (engine/memorypool.cuh) plus the number of the batch
+ * in the whole run, which seeds the sampler's counter RNG. */
+int legion_pool_set_batch(LegionPool *p, int32_t iter, int32_t mode, int32_t pipe, uint32_t global_batch);
+int legion_pool_set_rng(LegionPool *p, uint64_t seed, int32_t max_rounds);
+/* First error raised on the device since the last reset (the reference prints and exits,
+ * engine/operator_impl.cu:17-25): 0 none, 1 id map full, 2 edge buffer overflow, 3 node buffer
+ * overflow.  Synchronises `stream`. */
+int legion_pool_device_error(LegionPool *p, void *stream, int32_t *err, int32_t reset);
+
+/* ---- the five operators (engine/operator_impl.cuh:11-69) ---------------------------- */
+
+/* BatchGenerate, engine/operator_impl.cu:93-175 (same argument order; `counter` is the batch
+ * number within the mode's seed list). */
+int legion_batch_generate(void *stream, LegionFeatures *feature, LegionCache *cache, LegionPool *pool,
+                          int32_t batch_size, int32_t counter, int32_t part_id, int32_t dev_id,
+                          int32_t mode, int32_t is_presc, int32_t hop_num, int32_t dyn_cache);
+/* RandomSample, engine/operator_impl.cu:439-553: one hop (op_id = 3, 6, 9) of sampling,
+ * dedup, relabel and counter bookkeeping; `count` is the fanout. */
+int legion_random_sample(void *stream, LegionGraph *graph, LegionCache *cache, LegionPool *pool,
+                         int32_t count, int32_t dev_id, int32_t op_id, int32_t is_presc, int32_t dyn_cache);
+/* FeatureCacheLookup, engine/operator_impl.cu:555-575: cache lookup + feature gather of the
+ * current node segment (op_id = 1, 4, 7, 10). */
+int legion_feature_cache_lookup(void *stream, LegionCache *cache, LegionPool *pool, int32_t op_id,
+                                int32_t dev_id, int32_t dyn_cache);
+/* IOSubmit, engine/operator_impl.cu:577-595: a no-op in the reference, kept for the op list. */
+int legion_io_submit(void *stream, LegionFeatures *feature, LegionPool *pool, int32_t op_id, int32_t dev_id);
+/* IOComplete, engine/operator_impl.cu:606-636: end-of-batch maintenance (the reference clears
+ * position_map; here the LRU insertion phase runs). */
+int legion_io_complete(void *stream, LegionCache *cache, LegionPool *pool, int32_t dev_id, int32_t mode);
+
+/* ---- whole batch --------------------------------------------------------------------- */
+
+/* The op list of GPURunner::RunOnce (engine/server.cu:342-351) for one batch on one stream set.
+ * Seeds come from the mode's device-resident seed list. */
+int legion_run_batch(void *stream, LegionGraph *graph, LegionFeatures *feature, LegionCache *cache,
+                     LegionPool *pool, int32_t dev_id);
+/* Same batch with HOST buffers: seeds and labels are copied in from host memory, and the block
+ * structure (ids, labels, edge lists, both counters) is copied back; `features_out` may be NULL,
+ * in which case gathered rows stay in the pool's feature buffer on the device, where the trainer
+ * reads them (training_backend/ipc_cuda_kernel.cu:205-211).  Blocks until done. */
+int legion_run_batch_host(LegionGraph *graph, LegionFeatures *feature, LegionCache *cache, LegionPool *pool,
+                          int32_t dev_id, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                          int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out, int32_t *agg_dst_out,
+                          int32_t node_counter_out[16], int32_t edge_counter_out[16], void *features_out);
+
+/* ---- server <-> trainer hand-off (engine/ipc_service.h:6-35) --------------------------- */
+
+/* NewIPCEnv (engine/ipc_service.cu:35-58): creates and zero-fills the POSIX shared segment
+ * "simpleIPCshm" (steps[3] + cudaIpcMemHandle_t[8][2][7]).  shm_name NULL = that default. */
+int legion_ipc_create(LegionIpcEnv **out, int32_t device_count, const char *shm_name);
+/* Coordinate (engine/ipc_service.cu:60-128): step counts and per-device batch sizes. */
+int legion_ipc_coordinate(LegionIpcEnv *e, const int32_t *train_num, const int32_t *valid_num,
+                          const int32_t *test_num, int32_t partition_count, int32_t raw_batch_size,
+                          int32_t epochs);
+int legion_ipc_steps(LegionIpcEnv *e, int32_t steps[3]);
+int legion_ipc_max_step(LegionIpcEnv *e);                                           /* GetMaxStep */
+int legion_ipc_current_mode(LegionIpcEnv *e, int32_t global_batch_id);               /* GetCurrentMode */
+int legion_ipc_local_batch_id(LegionIpcEnv *e, int32_t global_batch_id);             /* GetLocalBatchId */
+int legion_ipc_current_batchsize(LegionIpcEnv *e, int32_t dev_id, int32_t mode);     /* GetCurrentBatchsize */
+/* InitializeSamplesBuffer + InitializeFeaturesBuffer (engine/ipc_service.cu:134-206): publishes
+ * the pool's output buffers as CUDA IPC handles and opens sem_r_<dev>_<pipe> / sem_w_<dev>_<pipe>. */
+int legion_ipc_publish_pool(LegionIpcEnv *e, LegionPool *pool, int32_t dev_id);
+/* Same, for a process without a GPU (tests): opens the semaphores only. */
+int legion_ipc_open_semaphores(LegionIpcEnv *e, int32_t dev_id, int32_t pipes);
+/* IPCWait / IPCPost (engine/ipc_service.cu:283-291).  timeout_ms < 0 blocks for ever like the
+ * reference; otherwise LEGION_E_TIMEOUT is returned when the trainer does not answer. */
+int legion_ipc_wait(LegionIpcEnv *e, int32_t dev_id, int32_t pipe, int32_t timeout_ms);
+int legion_ipc_post(LegionIpcEnv *e, int32_t dev_id, int32_t pipe);
+/* Finalize (engine/ipc_service.cu:293-320): closes and unlinks semaphores and the segment. */
+int legion_ipc_destroy(LegionIpcEnv *e);
+/* Byte layout of the shared segment, for consumers written in other languages. */
+int legion_ipc_layout(int64_t *segment_bytes, int64_t *handle_bytes, int64_t *handles_offset);
+/* Trainer side of one buffer (GPUIPCEnv::Initialize / Finalize, training_backend/ipc_cuda_kernel.cu:62-68,
+ * 143-149): map / unmap a 64-byte handle taken from the segment.  Must run in another process than
+ * the one that published the buffer. */
+int legion_ipc_open_handle(const void *handle_bytes, void **dev_ptr);
+/* Handle of one cudaMalloc allocation (cudaIpcGetMemHandle, engine/ipc_service.cu:163-169); also used
+ * to share cache partitions between one-process-per-GPU ranks. */
+int legion_ipc_get_handle(const void *dev_ptr, void *handle_bytes_out);
+int legion_ipc_close_handle(void *dev_ptr);
+
+/* ---- runner (engine/server.h:23-34, engine/server.cu:176-416) ---------------------------- */
+
+/* GPURunner::Initialize: binds storage, cache, pool and (optionally) an IPC environment. */
+int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGraph *graph, LegionFeatures *feature,
+                         LegionCache *cache, LegionPool *pool, LegionIpcEnv *env);
+/* GPURunner::RunOnce: wait for a free slot, run batch `global_batch_id`, post it, rotate the pipe.
+ * Without an IPC environment the slot is considered free at once. */
+int legion_runner_run_once(LegionRunner *r, int32_t global_batch_id, int32_t mode, int32_t local_batch_id,
+                           int32_t timeout_ms);
+/* Enqueue without waiting for completion (keeps INTERBATCH_CON batches in flight);
+ * legion_runner_sync waits for everything enqueued. */
+int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, int32_t mode, int32_t local_batch_id);
+int legion_runner_sync(LegionRunner *r);
+int legion_runner_current_pipe(LegionRunner *r);
+/* Device time of the batches enqueued between the last two legion_runner_sync calls, measured
+ * with CUDA events on the runner's streams (ms); gather_ms is the sum over the feature gather
+ * launches of that window. */
+int legion_runner_timing(LegionRunner *r, float *batch_ms, float *gather_ms, int32_t *n_batches);
+/* The serving loop of GPUServer (engine/server.cu:39-44,124-143) for `count` batches starting at
+ * first_global_batch, with mode and local batch number taken from the IPC environment. */
+int legion_runner_serve(LegionRunner *r, int32_t first_global_batch, int32_t count, int32_t timeout_ms);
+int legion_runner_destroy(LegionRunner *r);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,368 @@
+"""Host-side mirror of the sampling server's operator / runner / IPC interface over the C ABI.
+
+The classes keep the reference's names for this path (GraphStorage, FeatureStorage,
+UnifiedCache, MemoryPool, IPCEnv, Runner; sampling_server/src/engine/server.h,
+engine/operator_impl.cuh, cache/cache.cuh) and call ``liblegion_b200.so`` through ctypes.
+There is no CPU fallback: importing works anywhere, but every call needs the CUDA library
+and a GPU, and :func:`lib` raises when the library has not been built.
+
+torch is used by callers for device memory and streams only; nothing here computes with it.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liblegion_b200.so")
+
+TRAINMODE, VALIDMODE, TESTMODE = 0, 1, 2
+CACHEMISS_FLAG = -2
+CODEC_RAW, CODEC_INT8, CODEC_E4M3 = 0, 1, 2
+(BUF_IDS, BUF_FEATURES, BUF_LABELS, BUF_AGG_SRC, BUF_AGG_DST, BUF_NODE_COUNTER, BUF_EDGE_COUNTER,
+ BUF_CACHE_INDEX, BUF_SRC_GLOBAL) = range(9)
+INTRABATCH_CON = 3
+
+_lib = None
+
+
+class LegionError(RuntimeError):
+    pass
+
+
+def build(verbose=False):
+    """Compile the CUDA library in-tree for sm_100a (nvcc cross-compiles without a GPU)."""
+    import subprocess
+    cmd = ["make", "-C", os.path.join(_HERE, "csrc"), "-j8"]
+    if not verbose:
+        cmd.append("-s")
+    subprocess.check_call(cmd)
+    return LIB_PATH
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LegionError("liblegion_b200.so is missing: build it with `make -C legion-ibp_b200/csrc` "
+                              "(there is no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.legion_last_error.restype = C.c_char_p
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise LegionError("legion error %d: %s" % (rc, lib().legion_last_error().decode()))
+
+
+def _ptr(t):
+    """Device or host address of a torch tensor / numpy array / int."""
+    if t is None:
+        return C.c_void_p(0)
+    if isinstance(t, int):
+        return C.c_void_p(t)
+    if hasattr(t, "data_ptr"):
+        return C.c_void_p(t.data_ptr())
+    return C.c_void_p(t.ctypes.data)
+
+
+def _stream(s):
+    if s is None:
+        return C.c_void_p(0)
+    if isinstance(s, int):
+        return C.c_void_p(s)
+    return C.c_void_p(s.cuda_stream)
+
+
+class GraphStorage:
+    """CSR topology readable from the device (GraphStorage, storage/graph_storage.cuh:7-24)."""
+
+    def __init__(self, dev_id, indptr, indices):
+        self._keep = (indptr, indices)
+        self.n_nodes = int(indptr.numel()) - 1
+        self.n_edges = int(indices.numel())
+        self.h = C.c_void_p()
+        _check(lib().legion_graph_create(C.byref(self.h), C.c_int32(dev_id), C.c_int64(self.n_nodes),
+                                         C.c_int64(self.n_edges), _ptr(indptr), _ptr(indices)))
+
+    def close(self):
+        if self.h:
+            lib().legion_graph_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class FeatureStorage:
+    """Feature table in pinned host memory and this GPU's seed lists (storage/feature_storage.cuh:6-34)."""
+
+    def __init__(self, dev_id, n_nodes, row_bytes, host_table=None):
+        self._keep = [host_table]
+        self.n_nodes, self.row_bytes = int(n_nodes), int(row_bytes)
+        self.h = C.c_void_p()
+        _check(lib().legion_features_create(C.byref(self.h), C.c_int32(dev_id), C.c_int64(n_nodes),
+                                            C.c_int32(row_bytes), _ptr(host_table)))
+
+    def set_split(self, mode, ids_dev, labels_dev):
+        self._keep += [ids_dev, labels_dev]
+        _check(lib().legion_features_set_split(self.h, C.c_int32(mode), _ptr(ids_dev), _ptr(labels_dev),
+                                               C.c_int32(ids_dev.numel())))
+
+    def close(self):
+        if self.h:
+            lib().legion_features_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class UnifiedCache:
+    """Static (clique-striped, optionally compressed) or LRU feature cache (cache/cache.cuh:66-188)."""
+
+    def __init__(self, dev_id, n_nodes, row_bytes, capacity, kg=1, ki=0, codec=CODEC_RAW, lru=None):
+        self.dev_id, self.n_nodes, self.row_bytes = dev_id, int(n_nodes), int(row_bytes)
+        self.kg, self.ki, self.capacity, self.codec = kg, ki, int(capacity), codec
+        self._keep = []
+        self.h = C.c_void_p()
+        self.lru = lru
+        if lru is None:
+            _check(lib().legion_cache_create(C.byref(self.h), C.c_int32(dev_id), C.c_int64(n_nodes),
+                                             C.c_int32(row_bytes), C.c_int32(kg), C.c_int32(ki),
+                                             C.c_int32(capacity), C.c_int32(codec)))
+        else:
+            sets, ways = lru
+            _check(lib().legion_cache_create_lru(C.byref(self.h), C.c_int32(dev_id), C.c_int64(n_nodes),
+                                                 C.c_int32(row_bytes), C.c_int64(sets), C.c_int32(ways)))
+
+    @staticmethod
+    def degree_order(dev_id, indptr, order_out, stream=None):
+        _check(lib().legion_cache_degree_order(C.c_int32(dev_id), _ptr(indptr), C.c_int64(indptr.numel() - 1),
+                                               _ptr(order_out), _stream(stream)))
+
+    def fill_static(self, order_dev, host_table, stream=None):
+        self._keep += [host_table]
+        _check(lib().legion_cache_fill_static(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()),
+                                              _ptr(host_table), _stream(stream)))
+
+    def set_host_table(self, host_table):
+        self._keep += [host_table]
+        _check(lib().legion_cache_set_host_table(self.h, _ptr(host_table)))
+
+    def partition(self):
+        p, b = C.c_void_p(), C.c_int64()
+        _check(lib().legion_cache_partition(self.h, C.byref(p), C.byref(b)))
+        return p.value or 0, b.value
+
+    def set_peer(self, k, ptr):
+        _check(lib().legion_cache_set_peer(self.h, C.c_int32(k), C.c_void_p(ptr)))
+
+    def lut_ptr(self):
+        p = C.c_void_p()
+        _check(lib().legion_cache_lut(self.h, C.byref(p)))
+        return p.value
+
+    def lru_state(self):
+        k, s, r = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        _check(lib().legion_cache_lru_state(self.h, C.byref(k), C.byref(s), C.byref(r)))
+        return k.value, s.value, r.value
+
+    def lru_clock(self):
+        c = C.c_int32()
+        _check(lib().legion_cache_lru_clock(self.h, C.byref(c)))
+        return c.value
+
+    def stats(self, stream=None):
+        a = (C.c_int64 * 4)()
+        _check(lib().legion_cache_stats(self.h, a, _stream(stream)))
+        return dict(local_hits=a[0], peer_hits=a[1], misses=a[2], lru_inserts=a[3])
+
+    def close(self):
+        if self.h:
+            lib().legion_cache_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class MemoryPool:
+    """Scratch and double-buffered outputs of one GPU (engine/memorypool.cuh:20-221)."""
+
+    def __init__(self, dev_id, batch_size, fanout, row_bytes_out, pipes=2):
+        self.dev_id, self.batch_size, self.fanout = dev_id, int(batch_size), list(fanout)
+        self.row_bytes_out, self.pipes = int(row_bytes_out), pipes
+        fan = (C.c_int32 * max(1, len(fanout)))(*fanout)
+        self.h = C.c_void_p()
+        _check(lib().legion_pool_create(C.byref(self.h), C.c_int32(dev_id), C.c_int32(batch_size),
+                                        C.c_int32(len(fanout)), fan, C.c_int32(row_bytes_out), C.c_int32(pipes)))
+        mn, me = C.c_int64(), C.c_int64()
+        _check(lib().legion_pool_limits(self.h, C.byref(mn), C.byref(me)))
+        self.max_nodes, self.max_edges = mn.value, me.value
+
+    def buffer(self, which, pipe=0):
+        p, b = C.c_void_p(), C.c_int64()
+        _check(lib().legion_pool_buffer(self.h, C.c_int32(which), C.c_int32(pipe), C.byref(p), C.byref(b)))
+        return p.value, b.value
+
+    def set_batch(self, it, mode=TRAINMODE, pipe=0, global_batch=0):
+        _check(lib().legion_pool_set_batch(self.h, C.c_int32(it), C.c_int32(mode), C.c_int32(pipe),
+                                           C.c_uint32(global_batch)))
+
+    def set_rng(self, seed, max_rounds=64):
+        _check(lib().legion_pool_set_rng(self.h, C.c_uint64(seed), C.c_int32(max_rounds)))
+
+    def device_error(self, stream=None, reset=True):
+        e = C.c_int32()
+        _check(lib().legion_pool_device_error(self.h, _stream(stream), C.byref(e), C.c_int32(1 if reset else 0)))
+        return e.value
+
+    def read(self, which, pipe, count, dtype):
+        """Copy `count` elements of an output buffer to a numpy array (tests and checks)."""
+        import numpy as np
+        import torch
+        p, b = self.buffer(which, pipe)
+        out = np.empty(count, dtype=dtype)
+        nbytes = out.nbytes
+        assert nbytes <= b, (nbytes, b)
+        if nbytes:
+            torch.cuda.synchronize()
+            _check(lib().legion_copy(C.c_void_p(out.ctypes.data), C.c_void_p(p), C.c_int64(nbytes), C.c_int32(2)))
+        return out
+
+    def close(self):
+        if self.h:
+            lib().legion_pool_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+# ---- the five operators, argument for argument (engine/operator_impl.cuh:11-69) ------------------
+
+def BatchGenerate(stream, feature, cache, memorypool, batch_size, counter, part_id, dev_id, mode, is_presc,
+                  hop_num, dyn_cache=0):
+    _check(lib().legion_batch_generate(_stream(stream), feature.h, cache.h if cache else None, memorypool.h,
+                                       C.c_int32(batch_size), C.c_int32(counter), C.c_int32(part_id),
+                                       C.c_int32(dev_id), C.c_int32(mode), C.c_int32(int(is_presc)),
+                                       C.c_int32(hop_num), C.c_int32(dyn_cache)))
+
+
+def RandomSample(stream, graph, cache, memorypool, count, dev_id, op_id, is_presc=False, dyn_cache=0):
+    _check(lib().legion_random_sample(_stream(stream), graph.h, cache.h if cache else None, memorypool.h,
+                                      C.c_int32(count), C.c_int32(dev_id), C.c_int32(op_id),
+                                      C.c_int32(int(is_presc)), C.c_int32(dyn_cache)))
+
+
+def FeatureCacheLookup(stream, cache, memorypool, op_id, dev_id, dyn_cache=0):
+    _check(lib().legion_feature_cache_lookup(_stream(stream), cache.h if cache else None, memorypool.h,
+                                             C.c_int32(op_id), C.c_int32(dev_id), C.c_int32(dyn_cache)))
+
+
+def IOSubmit(stream, feature, memorypool, op_id, dev_id):
+    _check(lib().legion_io_submit(_stream(stream), feature.h, memorypool.h, C.c_int32(op_id), C.c_int32(dev_id)))
+
+
+def IOComplete(stream, cache, memorypool, dev_id, mode):
+    _check(lib().legion_io_complete(_stream(stream), cache.h if cache else None, memorypool.h, C.c_int32(dev_id),
+                                    C.c_int32(mode)))
+
+
+def run_batch(stream, graph, feature, cache, pool, dev_id):
+    _check(lib().legion_run_batch(_stream(stream), graph.h, feature.h, cache.h if cache else None, pool.h,
+                                  C.c_int32(dev_id)))
+
+
+def run_batch_host(graph, feature, cache, pool, dev_id, seeds, labels, ids_out, labels_out, agg_src_out,
+                   agg_dst_out, nc_out, ec_out, features_out=None):
+    """Host-buffer call: numpy int32 arrays in and out; returns (n_nodes, n_edges)."""
+    _check(lib().legion_run_batch_host(graph.h, feature.h if feature else None, cache.h if cache else None, pool.h,
+                                       C.c_int32(dev_id), _ptr(seeds), _ptr(labels), C.c_int32(len(seeds)),
+                                       _ptr(ids_out), _ptr(labels_out), _ptr(agg_src_out), _ptr(agg_dst_out),
+                                       _ptr(nc_out), _ptr(ec_out), _ptr(features_out)))
+    hops = int(nc_out[INTRABATCH_CON * 3 - 1])
+    return int(nc_out[INTRABATCH_CON * 3 + hops]), int(ec_out[0] + ec_out[1])
+
+
+class IPCEnv:
+    """Shared segment + semaphores of the server <-> trainer hand-off (engine/ipc_service.h:6-35)."""
+
+    def __init__(self, device_count, shm_name=None):
+        self.h = C.c_void_p()
+        name = shm_name.encode() if shm_name else None
+        _check(lib().legion_ipc_create(C.byref(self.h), C.c_int32(device_count), name))
+
+    def Coordinate(self, train_num, valid_num, test_num, raw_batch_size, epochs):
+        n = len(train_num)
+        arr = lambda v: (C.c_int32 * n)(*v)
+        _check(lib().legion_ipc_coordinate(self.h, arr(train_num), arr(valid_num), arr(test_num), C.c_int32(n),
+                                           C.c_int32(raw_batch_size), C.c_int32(epochs)))
+
+    def steps(self):
+        a = (C.c_int32 * 3)()
+        _check(lib().legion_ipc_steps(self.h, a))
+        return list(a)
+
+    def GetMaxStep(self):
+        return lib().legion_ipc_max_step(self.h)
+
+    def GetCurrentMode(self, global_batch_id):
+        return lib().legion_ipc_current_mode(self.h, C.c_int32(global_batch_id))
+
+    def GetLocalBatchId(self, global_batch_id):
+        return lib().legion_ipc_local_batch_id(self.h, C.c_int32(global_batch_id))
+
+    def GetCurrentBatchsize(self, dev_id, mode):
+        return lib().legion_ipc_current_batchsize(self.h, C.c_int32(dev_id), C.c_int32(mode))
+
+    def publish_pool(self, pool, dev_id):
+        _check(lib().legion_ipc_publish_pool(self.h, pool.h, C.c_int32(dev_id)))
+
+    def open_semaphores(self, dev_id, pipes=2):
+        _check(lib().legion_ipc_open_semaphores(self.h, C.c_int32(dev_id), C.c_int32(pipes)))
+
+    def IPCWait(self, dev_id, pipe, timeout_ms=-1):
+        _check(lib().legion_ipc_wait(self.h, C.c_int32(dev_id), C.c_int32(pipe), C.c_int32(timeout_ms)))
+
+    def IPCPost(self, dev_id, pipe):
+        _check(lib().legion_ipc_post(self.h, C.c_int32(dev_id), C.c_int32(pipe)))
+
+    def Finalize(self):
+        if self.h:
+            lib().legion_ipc_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+def ipc_layout():
+    a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
+    _check(lib().legion_ipc_layout(C.byref(a), C.byref(b), C.byref(c)))
+    return dict(segment_bytes=a.value, handle_bytes=b.value, handles_offset=c.value)
+
+
+class Runner:
+    """GPURunner (engine/server.cu:176-416): runs batches, rotates pipes, hands them off."""
+
+    def __init__(self, dev_id, graph, feature, cache, pool, env=None):
+        self.dev_id = dev_id
+        self._keep = (graph, feature, cache, pool, env)
+        self.h = C.c_void_p()
+        _check(lib().legion_runner_create(C.byref(self.h), C.c_int32(dev_id), graph.h, feature.h,
+                                          cache.h if cache else None, pool.h, env.h if env else None))
+
+    def RunOnce(self, global_batch_id, mode=TRAINMODE, local_batch_id=None, timeout_ms=-1):
+        lb = global_batch_id if local_batch_id is None else local_batch_id
+        _check(lib().legion_runner_run_once(self.h, C.c_int32(global_batch_id), C.c_int32(mode), C.c_int32(lb),
+                                            C.c_int32(timeout_ms)))
+
+    def enqueue(self, global_batch_id, mode=TRAINMODE, local_batch_id=None):
+        lb = global_batch_id if local_batch_id is None else local_batch_id
+        _check(lib().legion_runner_enqueue(self.h, C.c_int32(global_batch_id), C.c_int32(mode), C.c_int32(lb)))
+
+    def sync(self):
+        _check(lib().legion_runner_sync(self.h))
+
+    def serve(self, first_global_batch, count, timeout_ms=-1):
+        _check(lib().legion_runner_serve(self.h, C.c_int32(first_global_batch), C.c_int32(count),
+                                         C.c_int32(timeout_ms)))
+
+    def current_pipe(self):
+        return lib().legion_runner_current_pipe(self.h)
+
+    def timing(self):
+        a, b, n = C.c_float(), C.c_float(), C.c_int32()
+        _check(lib().legion_runner_timing(self.h, C.byref(a), C.byref(b), C.byref(n)))
+        return dict(batch_ms=a.value, gather_ms=b.value, batches=n.value)
+
+    def Finalize(self):
+        if self.h:
+            lib().legion_runner_destroy(self.h)
+            self.h = C.c_void_p()

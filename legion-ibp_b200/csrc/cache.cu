@@ -1,0 +1,350 @@
+// Feature-cache construction: ranking, placement over the clique, fill (with optional
+// int8 / fp8 encoding), and the state of the set-associative LRU cache.
+//
+// Replaces UnifiedCache::CandidateSelection / FillUp and their kernels
+// (sampling_server/src/cache/cache.cu:354-447,559-656; cache/cache_impl.cuh:72-109,183-188) and
+// StaticCache::init_cache (comp_cache/static_cache.cu:20-114).  The bucketed cuckoo table of
+// the reference (include/hashmap/bcht.hpp) becomes a direct table with one int32 per node:
+// one 4-byte read per lookup instead of up to three 128-byte bucket probes.
+#include "common.cuh"
+
+#include <cub/device/device_radix_sort.cuh>
+#include <cuda_fp8.h>
+
+namespace legion {
+
+static constexpr unsigned kFull = 0xFFFFFFFFu;
+
+__global__ void fill_i32_kernel(int32_t *a, int64_t n, int32_t v)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        a[i] = v;
+}
+
+__global__ void fill_u64_kernel(unsigned long long *a, int64_t n, unsigned long long v)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        a[i] = v;
+}
+
+__global__ void degree_keys_kernel(const int64_t *__restrict__ indptr, int64_t n, uint32_t *deg, int32_t *id)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        deg[i] = (uint32_t)(indptr[i + 1] - indptr[i]);
+        id[i] = (int32_t)i;
+    }
+}
+
+// rank t -> GPU t % kg, row t / kg (InitPair, cache_impl.cuh:104-109)
+__global__ void static_place_kernel(const int32_t *__restrict__ order, int64_t n_cached, int32_t capacity, int32_t kg,
+                                    int32_t *lut)
+{
+    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < n_cached; t += (int64_t)gridDim.x * blockDim.x)
+        lut[order[t]] = (int32_t)((t % kg) * (int64_t)capacity + t / kg);
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(kFull, v, d));
+    return v;
+}
+
+// One warp per cached row: row s of GPU ki <- host row order[s*kg + ki] (FeatFillUp, cache_impl.cuh:183-188).
+// CODEC 0 copies bytes; 1 / 2 store feature_len codes + one fp32 scale, zero padded to slot_bytes.
+template <int CODEC>
+__global__ void __launch_bounds__(256)
+static_fill_kernel(const int32_t *__restrict__ order, int64_t n_order, int32_t capacity, int32_t kg, int32_t ki,
+                   const uint8_t *__restrict__ host, int32_t row_bytes, uint8_t *part, int32_t slot_bytes)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t s = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < capacity; s += n_warps) {
+        int64_t t = s * kg + ki;
+        if (t >= n_order) break;
+        const uint8_t *src = host + (int64_t)order[t] * row_bytes;
+        uint8_t *dst = part + s * (int64_t)slot_bytes;
+        if (CODEC == LEGION_CODEC_RAW) {
+            if ((row_bytes & 15) == 0) {
+                for (int q = lane; q < (row_bytes >> 4); q += 32)
+                    reinterpret_cast<uint4 *>(dst)[q] = reinterpret_cast<const uint4 *>(src)[q];
+            } else {
+                for (int q = lane; q < (row_bytes >> 2); q += 32)
+                    reinterpret_cast<uint32_t *>(dst)[q] = reinterpret_cast<const uint32_t *>(src)[q];
+            }
+        } else {
+            const int f = row_bytes >> 2;
+            const float *x = reinterpret_cast<const float *>(src);
+            float a = 0.0f;
+            for (int i = lane; i < f; i += 32) a = fmaxf(a, fabsf(x[i]));
+            a = warp_max(a);
+            const float top = (CODEC == LEGION_CODEC_INT8) ? 127.0f : 448.0f;
+            const float inv = a > 0.0f ? __fdiv_rn(top, a) : 0.0f;
+            const float scale = __fdiv_rn(a, top);
+            for (int i = lane; i < f; i += 32) {
+                float prod = __fmul_rn(x[i], inv);
+                uint8_t code;
+                if (CODEC == LEGION_CODEC_INT8) {
+                    int q = __float2int_rn(prod);
+                    q = max(-127, min(127, q));
+                    code = (uint8_t)(int8_t)q;
+                } else {
+                    code = (uint8_t)__nv_cvt_float_to_fp8(prod, __NV_SATFINITE, __NV_E4M3);
+                }
+                dst[i] = code;
+            }
+            if (lane == 0) *reinterpret_cast<float *>(dst + f) = scale;
+            for (int i = f + 4 + lane; i < slot_bytes; i += 32) dst[i] = 0;
+        }
+    }
+}
+
+static int grid_stride(int64_t n, int sm_count)
+{
+    int64_t g = (n + 255) / 256;
+    int64_t cap = (int64_t)sm_count * 16;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+static int sm_count_of(int dev)
+{
+    int n = 148;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+}
+
+}  // namespace legion
+
+using namespace legion;
+
+extern "C" int legion_cache_create(LegionCache **out, int32_t dev_id, int64_t n_nodes, int32_t row_bytes,
+                                   int32_t kg, int32_t ki, int32_t capacity, int32_t codec)
+{
+    LG_ARG(out != nullptr, "out is NULL");
+    LG_ARG(n_nodes > 0 && n_nodes < (1ll << 31), "n_nodes must fit int32");
+    LG_ARG(row_bytes > 0 && row_bytes % 4 == 0, "row_bytes must be a positive multiple of 4");
+    LG_ARG(kg >= 1 && kg <= LEGION_MAX_DEVICE && ki >= 0 && ki < kg, "bad clique size or member index");
+    LG_ARG(capacity >= 0 && (int64_t)capacity * kg < (1ll << 31), "capacity * kg must fit int32");
+    LG_ARG(codec >= LEGION_CODEC_RAW && codec <= LEGION_CODEC_E4M3, "unknown codec");
+    if (codec != LEGION_CODEC_RAW) LG_ARG((row_bytes / 4) % 4 == 0, "compressed rows need feature_len % 4 == 0");
+    LG_CUDA(cudaSetDevice(dev_id));
+    LegionCache *c = new LegionCache();
+    memset(c, 0, sizeof(*c));
+    c->dev_id = dev_id;
+    c->n_nodes = n_nodes;
+    c->row_bytes = row_bytes;
+    c->codec = codec;
+    c->kind = 0;
+    c->kg = kg;
+    c->ki = ki;
+    c->capacity = capacity;
+    c->slot_bytes = codec == LEGION_CODEC_RAW ? row_bytes : (row_bytes / 4 + 4 + 15) / 16 * 16;
+    cudaError_t e = cudaMalloc(&c->lut, sizeof(int32_t) * n_nodes);
+    if (e == cudaSuccess && capacity > 0) e = cudaMalloc(&c->part[ki], (int64_t)capacity * c->slot_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&c->stats, sizeof(unsigned long long) * 4);
+    if (e != cudaSuccess) {
+        set_error("legion_cache_create: cudaMalloc failed: %s", cudaGetErrorString(e));
+        cudaFree(c->lut); cudaFree(c->part[ki]); cudaFree(c->stats);
+        delete c;
+        return LEGION_E_NOMEM;
+    }
+    int sms = sm_count_of(dev_id);
+    fill_i32_kernel<<<grid_stride(n_nodes, sms), 256>>>(c->lut, n_nodes, LEGION_CACHEMISS_FLAG);
+    LG_LAUNCH_CHECK();
+    LG_CUDA(cudaMemset(c->stats, 0, sizeof(unsigned long long) * 4));
+    LG_CUDA(cudaDeviceSynchronize());
+    *out = c;
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_degree_order(int32_t dev_id, const int64_t *indptr, int64_t n_nodes,
+                                         int32_t *order_dev, void *stream)
+{
+    LG_ARG(indptr != nullptr && order_dev != nullptr, "NULL pointer");
+    LG_ARG(n_nodes > 0 && n_nodes < (1ll << 31), "n_nodes must fit int32");
+    LG_CUDA(cudaSetDevice(dev_id));
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t *deg_in = nullptr, *deg_out = nullptr;
+    int32_t *id_in = nullptr;
+    void *tmp = nullptr;
+    size_t tmp_bytes = 0;
+    int rc = LEGION_OK;
+    cudaError_t e = cudaMalloc(&deg_in, sizeof(uint32_t) * n_nodes);
+    if (e == cudaSuccess) e = cudaMalloc(&deg_out, sizeof(uint32_t) * n_nodes);
+    if (e == cudaSuccess) e = cudaMalloc(&id_in, sizeof(int32_t) * n_nodes);
+    if (e == cudaSuccess)
+        e = cub::DeviceRadixSort::SortPairsDescending(nullptr, tmp_bytes, deg_in, deg_out, id_in, order_dev,
+                                                      (int)n_nodes, 0, 32, s);
+    if (e == cudaSuccess) e = cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1);
+    if (e == cudaSuccess) {
+        degree_keys_kernel<<<grid_stride(n_nodes, sm_count_of(dev_id)), 256, 0, s>>>(indptr, n_nodes, deg_in, id_in);
+        e = cudaGetLastError();
+    }
+    // LSD radix sort is stable: equal degrees keep ascending id order
+    if (e == cudaSuccess)
+        e = cub::DeviceRadixSort::SortPairsDescending(tmp, tmp_bytes, deg_in, deg_out, id_in, order_dev,
+                                                      (int)n_nodes, 0, 32, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        set_error("legion_cache_degree_order: %s", cudaGetErrorString(e));
+        rc = LEGION_E_CUDA;
+    }
+    cudaFree(deg_in); cudaFree(deg_out); cudaFree(id_in); cudaFree(tmp);
+    return rc;
+}
+
+extern "C" int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n_order,
+                                        const void *host_table, void *stream)
+{
+    LG_ARG(c != nullptr && c->kind == 0, "not a static cache");
+    LG_ARG(order_dev != nullptr && n_order >= 0 && n_order <= c->n_nodes, "bad order");
+    LG_CUDA(cudaSetDevice(c->dev_id));
+    cudaStream_t s = (cudaStream_t)stream;
+    c->host_table = host_table;
+    int sms = sm_count_of(c->dev_id);
+    int64_t n_cached = (int64_t)c->capacity * c->kg;
+    if (n_cached > n_order) n_cached = n_order;
+    fill_i32_kernel<<<grid_stride(c->n_nodes, sms), 256, 0, s>>>(c->lut, c->n_nodes, LEGION_CACHEMISS_FLAG);
+    LG_LAUNCH_CHECK();
+    if (n_cached > 0) {
+        static_place_kernel<<<grid_stride(n_cached, sms), 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->lut);
+        LG_LAUNCH_CHECK();
+        LG_ARG(host_table != nullptr, "host_table is NULL");
+        int64_t warps = c->capacity;
+        int64_t g = (warps + 7) / 8;
+        int grid = (int)(g > (int64_t)sms * 16 ? (int64_t)sms * 16 : (g < 1 ? 1 : g));
+        uint8_t *part = (uint8_t *)c->part[c->ki];
+        const uint8_t *host = (const uint8_t *)host_table;
+        if (c->codec == LEGION_CODEC_RAW)
+            static_fill_kernel<LEGION_CODEC_RAW><<<grid, 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->ki,
+                                                                     host, c->row_bytes, part, c->slot_bytes);
+        else if (c->codec == LEGION_CODEC_INT8)
+            static_fill_kernel<LEGION_CODEC_INT8><<<grid, 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->ki,
+                                                                      host, c->row_bytes, part, c->slot_bytes);
+        else
+            static_fill_kernel<LEGION_CODEC_E4M3><<<grid, 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->ki,
+                                                                      host, c->row_bytes, part, c->slot_bytes);
+        LG_LAUNCH_CHECK();
+    }
+    LG_CUDA(cudaStreamSynchronize(s));
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_set_host_table(LegionCache *c, const void *host_table)
+{
+    LG_ARG(c != nullptr, "cache is NULL");
+    c->host_table = host_table;
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_partition(LegionCache *c, void **ptr, int64_t *bytes)
+{
+    LG_ARG(c != nullptr && c->kind == 0, "not a static cache");
+    if (ptr) *ptr = c->part[c->ki];
+    if (bytes) *bytes = (int64_t)c->capacity * c->slot_bytes;
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_set_peer(LegionCache *c, int32_t k, const void *partition_ptr)
+{
+    LG_ARG(c != nullptr && c->kind == 0, "not a static cache");
+    LG_ARG(k >= 0 && k < c->kg && k != c->ki, "k must name another member of the clique");
+    c->part[k] = const_cast<void *>(partition_ptr);
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_lut(LegionCache *c, int32_t **lut_dev)
+{
+    LG_ARG(c != nullptr && c->kind == 0 && lut_dev != nullptr, "not a static cache");
+    *lut_dev = c->lut;
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_create_lru(LegionCache **out, int32_t dev_id, int64_t n_nodes, int32_t row_bytes,
+                                       int64_t sets, int32_t ways)
+{
+    LG_ARG(out != nullptr, "out is NULL");
+    LG_ARG(n_nodes > 0 && n_nodes < (1ll << 31), "n_nodes must fit int32");
+    LG_ARG(row_bytes > 0 && row_bytes % 16 == 0 && row_bytes <= 2048, "row_bytes must be a multiple of 16, at most 2048");
+    LG_ARG(sets > 0, "sets must be positive");
+    LG_ARG(ways >= 1 && ways <= 32 && (ways & (ways - 1)) == 0, "ways must be a power of two, at most 32");
+    LG_CUDA(cudaSetDevice(dev_id));
+    LegionCache *c = new LegionCache();
+    memset(c, 0, sizeof(*c));
+    c->dev_id = dev_id;
+    c->n_nodes = n_nodes;
+    c->row_bytes = row_bytes;
+    c->slot_bytes = row_bytes;
+    c->kind = 1;
+    c->kg = 1;
+    c->sets = sets;
+    c->ways = ways;
+    c->clock = 1;
+    int64_t slots = sets * ways;
+    cudaError_t e = cudaMalloc(&c->keys, sizeof(int32_t) * slots);
+    if (e == cudaSuccess) e = cudaMalloc(&c->stamps, sizeof(int32_t) * slots);
+    if (e == cudaSuccess) e = cudaMalloc(&c->claim, sizeof(int64_t) * slots);
+    if (e == cudaSuccess) e = cudaMalloc(&c->rows, slots * (int64_t)row_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&c->stats, sizeof(unsigned long long) * 4);
+    if (e != cudaSuccess) {
+        set_error("legion_cache_create_lru: cudaMalloc failed: %s", cudaGetErrorString(e));
+        cudaFree(c->keys); cudaFree(c->stamps); cudaFree(c->claim); cudaFree(c->rows); cudaFree(c->stats);
+        delete c;
+        return LEGION_E_NOMEM;
+    }
+    int sms = sm_count_of(dev_id);
+    fill_i32_kernel<<<grid_stride(slots, sms), 256>>>(c->keys, slots, -1);
+    LG_LAUNCH_CHECK();
+    fill_i32_kernel<<<grid_stride(slots, sms), 256>>>(c->stamps, slots, 0);
+    LG_LAUNCH_CHECK();
+    fill_u64_kernel<<<grid_stride(slots, sms), 256>>>(reinterpret_cast<unsigned long long *>(c->claim), slots, ~0ull);
+    LG_LAUNCH_CHECK();
+    LG_CUDA(cudaMemset(c->stats, 0, sizeof(unsigned long long) * 4));
+    LG_CUDA(cudaDeviceSynchronize());
+    *out = c;
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_lru_state(LegionCache *c, int32_t **keys_dev, int32_t **stamps_dev, void **rows_dev)
+{
+    LG_ARG(c != nullptr && c->kind == 1, "not an lru cache");
+    if (keys_dev) *keys_dev = c->keys;
+    if (stamps_dev) *stamps_dev = c->stamps;
+    if (rows_dev) *rows_dev = c->rows;
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_lru_clock(LegionCache *c, int32_t *clock)
+{
+    LG_ARG(c != nullptr && c->kind == 1 && clock != nullptr, "not an lru cache");
+    *clock = c->clock;
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_stats(LegionCache *c, int64_t stats[4], void *stream)
+{
+    LG_ARG(c != nullptr && stats != nullptr, "NULL pointer");
+    LG_CUDA(cudaSetDevice(c->dev_id));
+    unsigned long long h[4];
+    LG_CUDA(cudaMemcpyAsync(h, c->stats, sizeof(h), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    LG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    for (int i = 0; i < 4; ++i) stats[i] = (int64_t)h[i];
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_destroy(LegionCache *c)
+{
+    if (c == nullptr) return LEGION_OK;
+    cudaSetDevice(c->dev_id);
+    if (c->kind == 0) {
+        cudaFree(c->lut);
+        cudaFree(c->part[c->ki]);
+    } else {
+        cudaFree(c->keys); cudaFree(c->stamps); cudaFree(c->claim); cudaFree(c->rows);
+    }
+    cudaFree(c->stats);
+    delete c;
+    return LEGION_OK;
+}

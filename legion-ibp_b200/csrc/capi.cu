@@ -1,0 +1,409 @@
+// C ABI: storage handles, the memory pool, the five operators and the whole-batch calls.
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <string.h>
+
+namespace legion {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+static int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+template <typename T>
+static cudaError_t dmalloc(T **p, int64_t count)
+{
+    return cudaMalloc(reinterpret_cast<void **>(p), sizeof(T) * (size_t)(count > 0 ? count : 1));
+}
+
+}  // namespace legion
+
+using namespace legion;
+
+extern "C" const char *legion_last_error(void) { return g_error; }
+extern "C" int legion_abi_version(void) { return 1; }
+
+// ---- storage ---------------------------------------------------------------------------------------
+
+extern "C" int legion_graph_create(LegionGraph **out, int32_t dev_id, int64_t n_nodes, int64_t n_edges,
+                                   const int64_t *indptr, const int32_t *indices)
+{
+    LG_ARG(out != nullptr && indptr != nullptr, "NULL pointer");
+    LG_ARG(indices != nullptr || n_edges == 0, "indices is NULL");
+    LG_ARG(n_nodes > 0 && n_nodes < (1ll << 31), "n_nodes must fit int32");
+    LegionGraph *g = new LegionGraph();
+    g->dev_id = dev_id;
+    g->n_nodes = n_nodes;
+    g->n_edges = n_edges;
+    g->indptr = indptr;
+    g->indices = indices;
+    *out = g;
+    return LEGION_OK;
+}
+
+extern "C" int legion_graph_destroy(LegionGraph *g)
+{
+    delete g;
+    return LEGION_OK;
+}
+
+extern "C" int legion_features_create(LegionFeatures **out, int32_t dev_id, int64_t n_nodes, int32_t row_bytes,
+                                      const void *host_table)
+{
+    LG_ARG(out != nullptr, "out is NULL");
+    LG_ARG(n_nodes > 0 && n_nodes < (1ll << 31), "n_nodes must fit int32");
+    LG_ARG(row_bytes > 0 && row_bytes % 4 == 0, "row_bytes must be a positive multiple of 4");
+    LegionFeatures *f = new LegionFeatures();
+    memset(f, 0, sizeof(*f));
+    f->dev_id = dev_id;
+    f->n_nodes = n_nodes;
+    f->row_bytes = row_bytes;
+    f->host_table = host_table;
+    *out = f;
+    return LEGION_OK;
+}
+
+extern "C" int legion_features_set_split(LegionFeatures *f, int32_t mode, const int32_t *ids_dev,
+                                         const int32_t *labels_dev, int32_t count)
+{
+    LG_ARG(f != nullptr, "features is NULL");
+    LG_ARG(mode >= 0 && mode <= 2, "mode must be 0 (train), 1 (valid) or 2 (test)");
+    LG_ARG(count >= 0 && (count == 0 || (ids_dev != nullptr && labels_dev != nullptr)), "NULL seed list");
+    f->ids[mode] = ids_dev;
+    f->labels[mode] = labels_dev;
+    f->count[mode] = count;
+    return LEGION_OK;
+}
+
+extern "C" int legion_features_destroy(LegionFeatures *f)
+{
+    delete f;
+    return LEGION_OK;
+}
+
+// ---- memory pool -----------------------------------------------------------------------------------
+
+extern "C" int legion_pool_destroy(LegionPool *p)
+{
+    if (p == nullptr) return LEGION_OK;
+    cudaSetDevice(p->dev_id);
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+        cudaFree(p->ids[i]); cudaFree(p->features[i]); cudaFree(p->labels[i]); cudaFree(p->agg_src[i]);
+        cudaFree(p->agg_dst[i]); cudaFree(p->node_counter[i]); cudaFree(p->edge_counter[i]);
+    }
+    cudaFree(p->cache_index); cudaFree(p->src_global); cudaFree(p->map); cudaFree(p->node_rec);
+    cudaFree(p->tile_sum); cudaFree(p->tile_off); cudaFree(p->eslot); cudaFree(p->erank);
+    cudaFree(p->lru_victim); cudaFree(p->ctl); cudaFree(p->seed_stage); cudaFree(p->label_stage);
+    if (p->h_stage) cudaFreeHost(p->h_stage);
+    delete p;
+    return LEGION_OK;
+}
+
+extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batch_size, int32_t hop_num,
+                                  const int32_t *fanout, int32_t row_bytes_out, int32_t pipes)
+{
+    LG_ARG(out != nullptr, "out is NULL");
+    LG_ARG(batch_size > 0, "batch_size must be positive");
+    LG_ARG(hop_num >= 0 && hop_num <= LEGION_MAX_HOPS, "hop_num must be 0..3");
+    LG_ARG(hop_num == 0 || fanout != nullptr, "fanout is NULL");
+    LG_ARG(row_bytes_out > 0 && row_bytes_out % 4 == 0, "row_bytes_out must be a positive multiple of 4");
+    LG_ARG(pipes >= 1 && pipes <= LEGION_INTERBATCH_CON, "pipes must be 1 or 2");
+    for (int h = 0; h < hop_num; ++h)
+        LG_ARG(fanout[h] >= 1 && fanout[h] <= LEGION_MAX_FANOUT, "fanout must be 1..32");
+    LG_CUDA(cudaSetDevice(dev_id));
+
+    LegionPool *p = new LegionPool();
+    memset(p, 0, sizeof(*p));
+    p->dev_id = dev_id;
+    p->batch_size = batch_size;
+    p->hop_num = hop_num;
+    p->row_bytes_out = row_bytes_out;
+    p->pipes = pipes;
+    // True worst case: every hop samples all nodes found so far (the reference sizes its buffers
+    // as B*(1+f1+f1*f2), engine/server.cu:204-216, which is below it).
+    int64_t nodes = batch_size, edges = 0, max_hop_edges = 0, max_inputs = batch_size;
+    for (int h = 0; h < hop_num; ++h) {
+        p->fanout[h] = fanout[h];
+        int64_t e = nodes * fanout[h];
+        if (nodes > max_inputs) max_inputs = nodes;
+        if (e > max_hop_edges) max_hop_edges = e;
+        edges += e;
+        nodes += e;
+    }
+    if (nodes >= kNewBase || edges >= kNewBase) {
+        set_error("legion_pool_create: batch of up to %lld nodes / %lld edges is above the 2^30 limit",
+                  (long long)nodes, (long long)edges);
+        delete p;
+        return LEGION_E_LIMIT;
+    }
+    p->max_nodes = nodes;
+    p->max_edges = edges;
+    p->max_hop_edges = max_hop_edges;
+    p->max_inputs = max_inputs;
+    p->feat_rows = nodes;
+    p->rng_seed = 0;
+    p->max_rounds = 64;
+    p->sm_count = 148;
+    cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, dev_id);
+    if (p->sm_count <= 0) p->sm_count = 148;
+
+    uint32_t cap = 1024;
+    while ((int64_t)cap * 5 < nodes * 8) cap <<= 1;  // load factor <= 0.625 in the worst case
+    p->map_mask = cap - 1;
+
+    const int64_t pad_nodes = round_up(nodes, kTile) + kTile;
+    const int64_t pad_edges = round_up(edges > 0 ? edges : 1, kTile) + kTile;
+    const int64_t pad_hop_edges = round_up(max_hop_edges > 0 ? max_hop_edges : 1, kTile) + kTile;
+    const int64_t tiles = max_inputs / kTile + 2 + max_hop_edges / kTile + 2;
+
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < pipes && e == cudaSuccess; ++i) {
+        e = dmalloc(&p->ids[i], pad_nodes);
+        if (e == cudaSuccess) e = cudaMalloc(&p->features[i], (size_t)(nodes * (int64_t)row_bytes_out));
+        if (e == cudaSuccess) e = dmalloc(&p->labels[i], batch_size);
+        if (e == cudaSuccess) e = dmalloc(&p->agg_src[i], pad_edges);
+        if (e == cudaSuccess) e = dmalloc(&p->agg_dst[i], pad_edges);
+        if (e == cudaSuccess) e = dmalloc(&p->node_counter[i], 16);
+        if (e == cudaSuccess) e = dmalloc(&p->edge_counter[i], 16);
+        if (e == cudaSuccess) e = cudaMemset(p->node_counter[i], 0, 64);
+        if (e == cudaSuccess) e = cudaMemset(p->edge_counter[i], 0, 64);
+        if (e == cudaSuccess) e = cudaMemset(p->ids[i], 0xFF, sizeof(int32_t) * pad_nodes);
+    }
+    if (e == cudaSuccess) e = dmalloc(&p->cache_index, pad_nodes);
+    if (e == cudaSuccess) e = dmalloc(&p->src_global, pad_edges);
+    if (e == cudaSuccess) e = dmalloc(&p->map, (int64_t)cap);
+    if (e == cudaSuccess) e = dmalloc(&p->node_rec, pad_nodes);
+    if (e == cudaSuccess) e = dmalloc(&p->tile_sum, tiles);
+    if (e == cudaSuccess) e = dmalloc(&p->tile_off, tiles);
+    if (e == cudaSuccess) e = dmalloc(&p->eslot, pad_hop_edges);
+    if (e == cudaSuccess) e = dmalloc(&p->erank, pad_hop_edges);
+    if (e == cudaSuccess) e = dmalloc(&p->lru_victim, pad_nodes);
+    if (e == cudaSuccess) e = dmalloc(&p->ctl, CTL_WORDS);
+    if (e == cudaSuccess) e = dmalloc(&p->seed_stage, batch_size);
+    if (e == cudaSuccess) e = dmalloc(&p->label_stage, batch_size);
+    if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void **>(&p->h_stage), sizeof(int32_t) * (2 * (size_t)batch_size + 32));
+    if (e == cudaSuccess) e = cudaMemset(p->ctl, 0, sizeof(int32_t) * CTL_WORDS);
+    if (e == cudaSuccess) e = cudaMemset(p->eslot, 0, sizeof(int32_t) * pad_hop_edges);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        set_error("legion_pool_create: %s", cudaGetErrorString(e));
+        legion_pool_destroy(p);
+        return LEGION_E_NOMEM;
+    }
+    *out = p;
+    return LEGION_OK;
+}
+
+extern "C" int legion_pool_buffer(LegionPool *p, int32_t which, int32_t pipe, void **ptr, int64_t *bytes)
+{
+    LG_ARG(p != nullptr && ptr != nullptr, "NULL pointer");
+    LG_ARG(pipe >= 0 && pipe < p->pipes, "pipe out of range");
+    int64_t b = 0;
+    void *q = nullptr;
+    switch (which) {
+    case LEGION_BUF_IDS: q = p->ids[pipe]; b = p->max_nodes * 4; break;
+    case LEGION_BUF_FEATURES: q = p->features[pipe]; b = p->feat_rows * (int64_t)p->row_bytes_out; break;
+    case LEGION_BUF_LABELS: q = p->labels[pipe]; b = (int64_t)p->batch_size * 4; break;
+    case LEGION_BUF_AGG_SRC: q = p->agg_src[pipe]; b = p->max_edges * 4; break;
+    case LEGION_BUF_AGG_DST: q = p->agg_dst[pipe]; b = p->max_edges * 4; break;
+    case LEGION_BUF_NODE_COUNTER: q = p->node_counter[pipe]; b = 64; break;
+    case LEGION_BUF_EDGE_COUNTER: q = p->edge_counter[pipe]; b = 64; break;
+    case LEGION_BUF_CACHE_INDEX: q = p->cache_index; b = p->max_nodes * 8; break;
+    case LEGION_BUF_SRC_GLOBAL: q = p->src_global; b = p->max_edges * 4; break;
+    default: LG_ARG(false, "unknown buffer");
+    }
+    *ptr = q;
+    if (bytes) *bytes = b;
+    return LEGION_OK;
+}
+
+extern "C" int legion_pool_limits(LegionPool *p, int64_t *max_nodes, int64_t *max_edges)
+{
+    LG_ARG(p != nullptr, "pool is NULL");
+    if (max_nodes) *max_nodes = p->max_nodes;
+    if (max_edges) *max_edges = p->max_edges;
+    return LEGION_OK;
+}
+
+extern "C" int legion_pool_set_batch(LegionPool *p, int32_t iter, int32_t mode, int32_t pipe, uint32_t global_batch)
+{
+    LG_ARG(p != nullptr, "pool is NULL");
+    LG_ARG(pipe >= 0 && pipe < p->pipes, "pipe out of range");
+    LG_ARG(mode >= 0 && mode <= 2, "mode must be 0, 1 or 2");
+    p->iter = iter;
+    p->mode = mode;
+    p->pipe = pipe;
+    p->global_batch = global_batch;
+    return LEGION_OK;
+}
+
+extern "C" int legion_pool_set_rng(LegionPool *p, uint64_t seed, int32_t max_rounds)
+{
+    LG_ARG(p != nullptr, "pool is NULL");
+    LG_ARG(max_rounds >= 1 && max_rounds <= 1024, "max_rounds must be 1..1024");
+    p->rng_seed = seed;
+    p->max_rounds = max_rounds;
+    return LEGION_OK;
+}
+
+// First error raised by a kernel of this pool since the last reset (0 = none): 1 id map full,
+// 2 edge buffer overflow, 3 node buffer overflow.  Synchronises the stream.
+extern "C" int legion_pool_device_error(LegionPool *p, void *stream, int32_t *err, int32_t reset)
+{
+    LG_ARG(p != nullptr && err != nullptr, "NULL pointer");
+    LG_CUDA(cudaSetDevice(p->dev_id));
+    LG_CUDA(cudaMemcpyAsync(err, p->ctl + CTL_ERROR, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    LG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (reset && *err != 0) LG_CUDA(cudaMemsetAsync(p->ctl + CTL_ERROR, 0, 4, (cudaStream_t)stream));
+    return LEGION_OK;
+}
+
+// ---- operators ---------------------------------------------------------------------------------------
+
+extern "C" int legion_batch_generate(void *stream, LegionFeatures *feature, LegionCache *cache, LegionPool *pool,
+                                     int32_t batch_size, int32_t counter, int32_t part_id, int32_t dev_id,
+                                     int32_t mode, int32_t is_presc, int32_t hop_num, int32_t dyn_cache)
+{
+    (void)cache; (void)part_id; (void)is_presc; (void)dyn_cache;
+    LG_ARG(feature != nullptr && pool != nullptr, "NULL handle");
+    LG_ARG(mode >= 0 && mode <= 2, "invalid mode");
+    LG_ARG(batch_size > 0 && batch_size <= pool->batch_size, "batch_size above the pool's");
+    LG_ARG(hop_num == pool->hop_num, "hop_num differs from the pool's");
+    LG_ARG(counter >= 0, "negative batch counter");
+    const int32_t *all_ids = feature->ids[mode];
+    const int32_t *all_labels = feature->labels[mode];
+    int32_t total_cap = feature->count[mode];
+    LG_ARG(all_ids != nullptr && all_labels != nullptr && total_cap > 0, "no seed list for this mode");
+    LG_CUDA(cudaSetDevice(dev_id));
+    int64_t first = (int64_t)batch_size * counter;
+    // tail batch is shortened, operator_impl.cu:162
+    int64_t size = ((int64_t)batch_size * (counter + 1) >= total_cap) ? (total_cap - first) : batch_size;
+    if (size < 0) size = 0;
+    return launch_batch_generate((cudaStream_t)stream, pool, all_ids, all_labels, total_cap, first, (int32_t)size,
+                                 hop_num);
+}
+
+extern "C" int legion_random_sample(void *stream, LegionGraph *graph, LegionCache *cache, LegionPool *pool,
+                                    int32_t count, int32_t dev_id, int32_t op_id, int32_t is_presc, int32_t dyn_cache)
+{
+    (void)cache; (void)is_presc; (void)dyn_cache;
+    LG_ARG(graph != nullptr && pool != nullptr, "NULL handle");
+    LG_ARG(op_id > 0 && op_id % LEGION_INTRABATCH_CON == 0 && op_id / LEGION_INTRABATCH_CON <= pool->hop_num,
+           "op_id must be 3, 6 or 9 and within the pool's hop count");
+    const int hop = op_id / LEGION_INTRABATCH_CON - 1;
+    LG_ARG(count >= 1 && count <= LEGION_MAX_FANOUT, "Neighbor count must be at most 32");
+    LG_ARG(count == pool->fanout[hop], "fanout differs from the pool's");
+    LG_CUDA(cudaSetDevice(dev_id));
+    return launch_sample_hop((cudaStream_t)stream, pool, graph, count, hop, op_id);
+}
+
+extern "C" int legion_feature_cache_lookup(void *stream, LegionCache *cache, LegionPool *pool, int32_t op_id,
+                                           int32_t dev_id, int32_t dyn_cache)
+{
+    (void)dyn_cache;
+    LG_ARG(pool != nullptr, "NULL handle");
+    LG_ARG(op_id > 0 && op_id % LEGION_INTRABATCH_CON == 1 && op_id / LEGION_INTRABATCH_CON <= pool->hop_num,
+           "op_id must be 1, 4, 7 or 10 and within the pool's hop count");
+    if (cache != nullptr) LG_ARG(cache->row_bytes == pool->row_bytes_out, "cache and pool disagree on the row size");
+    LG_CUDA(cudaSetDevice(dev_id));
+    return launch_gather((cudaStream_t)stream, pool, cache, op_id);
+}
+
+extern "C" int legion_io_submit(void *stream, LegionFeatures *feature, LegionPool *pool, int32_t op_id, int32_t dev_id)
+{
+    (void)stream; (void)feature; (void)pool; (void)op_id; (void)dev_id;
+    return LEGION_OK;
+}
+
+extern "C" int legion_io_complete(void *stream, LegionCache *cache, LegionPool *pool, int32_t dev_id, int32_t mode)
+{
+    (void)mode;
+    LG_ARG(pool != nullptr, "NULL handle");
+    LG_CUDA(cudaSetDevice(dev_id));
+    return launch_lru_insert((cudaStream_t)stream, pool, cache);
+}
+
+// ---- whole batch ---------------------------------------------------------------------------------------
+
+static int run_ops(cudaStream_t s, LegionGraph *graph, LegionCache *cache, LegionPool *pool, int32_t dev_id)
+{
+    int rc = legion_feature_cache_lookup(s, cache, pool, 1, dev_id, 0);
+    for (int h = 0; h < pool->hop_num && rc == LEGION_OK; ++h) {
+        int op = LEGION_INTRABATCH_CON * (h + 1);
+        rc = legion_random_sample(s, graph, cache, pool, pool->fanout[h], dev_id, op, 0, 0);
+        if (rc == LEGION_OK) rc = legion_feature_cache_lookup(s, cache, pool, op + 1, dev_id, 0);
+    }
+    if (rc == LEGION_OK) rc = legion_io_complete(s, cache, pool, dev_id, pool->mode);
+    return rc;
+}
+
+extern "C" int legion_run_batch(void *stream, LegionGraph *graph, LegionFeatures *feature, LegionCache *cache,
+                                LegionPool *pool, int32_t dev_id)
+{
+    LG_ARG(graph != nullptr && feature != nullptr && pool != nullptr, "NULL handle");
+    int rc = legion_batch_generate(stream, feature, cache, pool, pool->batch_size, pool->iter, dev_id, dev_id,
+                                   pool->mode, 0, pool->hop_num, 0);
+    if (rc != LEGION_OK) return rc;
+    return run_ops((cudaStream_t)stream, graph, cache, pool, dev_id);
+}
+
+extern "C" int legion_run_batch_host(LegionGraph *graph, LegionFeatures *feature, LegionCache *cache, LegionPool *pool,
+                                     int32_t dev_id, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                                     int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out, int32_t *agg_dst_out,
+                                     int32_t node_counter_out[16], int32_t edge_counter_out[16], void *features_out)
+{
+    (void)feature;
+    LG_ARG(graph != nullptr && pool != nullptr && seeds != nullptr && labels != nullptr, "NULL pointer");
+    LG_ARG(n_seeds > 0 && n_seeds <= pool->batch_size, "n_seeds above the pool's batch size");
+    LG_ARG(node_counter_out != nullptr && edge_counter_out != nullptr, "NULL counter output");
+    LG_CUDA(cudaSetDevice(dev_id));
+    cudaStream_t s = 0;
+    const int pipe = pool->pipe;
+    // inputs: host -> pinned staging -> device
+    memcpy(pool->h_stage, seeds, sizeof(int32_t) * n_seeds);
+    memcpy(pool->h_stage + pool->batch_size, labels, sizeof(int32_t) * n_seeds);
+    LG_CUDA(cudaMemcpyAsync(pool->seed_stage, pool->h_stage, sizeof(int32_t) * n_seeds, cudaMemcpyHostToDevice, s));
+    LG_CUDA(cudaMemcpyAsync(pool->label_stage, pool->h_stage + pool->batch_size, sizeof(int32_t) * n_seeds,
+                            cudaMemcpyHostToDevice, s));
+    int rc = launch_batch_generate(s, pool, pool->seed_stage, pool->label_stage, n_seeds, 0, n_seeds, pool->hop_num);
+    if (rc != LEGION_OK) return rc;
+    rc = run_ops(s, graph, cache, pool, dev_id);
+    if (rc != LEGION_OK) return rc;
+    int32_t *hc = pool->h_stage + 2 * (size_t)pool->batch_size;
+    LG_CUDA(cudaMemcpyAsync(hc, pool->node_counter[pipe], 64, cudaMemcpyDeviceToHost, s));
+    LG_CUDA(cudaMemcpyAsync(hc + 16, pool->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, s));
+    LG_CUDA(cudaStreamSynchronize(s));
+    memcpy(node_counter_out, hc, 64);
+    memcpy(edge_counter_out, hc + 16, 64);
+    const int hops = hc[LEGION_INTRABATCH_CON * 3 - 1];
+    const int64_t n_nodes = hc[LEGION_INTRABATCH_CON * 3 + hops];
+    const int64_t n_edges = (int64_t)hc[16] + hc[17];
+    if (ids_out) LG_CUDA(cudaMemcpyAsync(ids_out, pool->ids[pipe], 4 * n_nodes, cudaMemcpyDeviceToHost, s));
+    if (labels_out) LG_CUDA(cudaMemcpyAsync(labels_out, pool->labels[pipe], 4 * (int64_t)n_seeds, cudaMemcpyDeviceToHost, s));
+    if (agg_src_out) LG_CUDA(cudaMemcpyAsync(agg_src_out, pool->agg_src[pipe], 4 * n_edges, cudaMemcpyDeviceToHost, s));
+    if (agg_dst_out) LG_CUDA(cudaMemcpyAsync(agg_dst_out, pool->agg_dst[pipe], 4 * n_edges, cudaMemcpyDeviceToHost, s));
+    if (features_out)
+        LG_CUDA(cudaMemcpyAsync(features_out, pool->features[pipe], n_nodes * (int64_t)pool->row_bytes_out,
+                                cudaMemcpyDeviceToHost, s));
+    LG_CUDA(cudaStreamSynchronize(s));
+    return LEGION_OK;
+}
+
+// Plain copies for callers that hold raw pointers only (tests, consumers without a CUDA binding).
+// kind: 1 host->device, 2 device->host, 3 device->device.  Blocking.
+extern "C" int legion_copy(void *dst, const void *src, int64_t bytes, int32_t kind)
+{
+    LG_ARG(bytes >= 0 && (bytes == 0 || (dst != nullptr && src != nullptr)), "NULL pointer");
+    LG_ARG(kind >= 1 && kind <= 3, "kind must be 1, 2 or 3");
+    if (bytes == 0) return LEGION_OK;
+    LG_CUDA(cudaMemcpy(dst, src, (size_t)bytes, (cudaMemcpyKind)kind));
+    return LEGION_OK;
+}

@@ -1,0 +1,161 @@
+// Internal definitions shared by the kernels and the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+
+#include "../../include/legion_b200.h"
+
+namespace legion {
+
+// ---- error reporting -------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+
+#define LG_CUDA(call)                                                                      \
+    do {                                                                                   \
+        cudaError_t _e = (call);                                                           \
+        if (_e != cudaSuccess) {                                                           \
+            legion::set_error("%s:%d: %s -> %s", __FILE__, __LINE__, #call,                \
+                              cudaGetErrorString(_e));                                     \
+            return LEGION_E_CUDA;                                                          \
+        }                                                                                  \
+    } while (0)
+
+#define LG_ARG(cond, msg)                                                                  \
+    do {                                                                                   \
+        if (!(cond)) {                                                                     \
+            legion::set_error("%s:%d: %s", __FILE__, __LINE__, msg);                       \
+            return LEGION_E_ARG;                                                           \
+        }                                                                                  \
+    } while (0)
+
+#define LG_LAUNCH_CHECK() LG_CUDA(cudaGetLastError())
+
+// ---- device-side batch state --------------------------------------------------------------
+// Tile = number of items (nodes or edges) one CTA scans at a time.
+constexpr int kTile = 1024;
+constexpr int kScanThreads = 256;  // kTile / 4 items per thread
+
+// Values stored in the batch-local id map while a hop is in flight: a node that is new in
+// this hop carries kNewBase + (index of the first edge that reached it) until it gets its
+// local id.  Local ids stay below kNewBase.
+constexpr int32_t kNewBase = 0x40000000;
+constexpr int32_t kEmptyKey = -1;
+constexpr int32_t kEmptyVal = 0x7FFFFFFF;
+
+// ctl[] words (device scratch, one int32 each)
+enum Ctl {
+    CTL_N_NODES = 0,   // nodes known so far (== nc[0] + nc[1])
+    CTL_E_TOTAL = 1,   // edges of the hops already finished
+    CTL_E_HOP = 2,     // edges of the hop in flight
+    CTL_C_HOP = 3,     // new nodes of the hop in flight
+    CTL_TICKET_A = 4,  // "last CTA done" tickets, one per kernel that needs one
+    CTL_TICKET_B = 5,
+    CTL_TICKET_C = 6,
+    CTL_ERROR = 7,     // first error raised by a kernel (0 = none)
+    CTL_MISS_COUNT = 8,
+    CTL_WORDS = 16
+};
+
+enum DeviceError { DERR_NONE = 0, DERR_MAP_FULL = 1, DERR_EDGE_OVERFLOW = 2, DERR_NODE_OVERFLOW = 3 };
+
+struct NodeRec {  // per input node of a hop, written by the count kernel
+    int64_t start;  // first CSR position of the adjacency list
+    int32_t loff;   // exclusive prefix of min(deg, fanout) inside the node's tile
+    int32_t deg;
+};
+static_assert(sizeof(NodeRec) == 16, "NodeRec is read and written as one 16-byte vector");
+
+struct MapSlot {
+    int32_t key;
+    int32_t val;
+};
+
+}  // namespace legion
+
+// ---- handle structs (opaque in the C ABI) ------------------------------------------------------
+struct LegionGraph {
+    int32_t dev_id;
+    int64_t n_nodes, n_edges;
+    const int64_t *indptr;
+    const int32_t *indices;
+};
+
+struct LegionFeatures {
+    int32_t dev_id;
+    int64_t n_nodes;
+    int32_t row_bytes;
+    const void *host_table;
+    const int32_t *ids[3];
+    const int32_t *labels[3];
+    int32_t count[3];
+};
+
+struct LegionCache {
+    int32_t dev_id;
+    int64_t n_nodes;
+    int32_t row_bytes;   // bytes of one source (and output) row
+    int32_t slot_bytes;  // bytes of one cached row (== row_bytes for RAW)
+    int32_t codec;
+    int32_t kind;  // 0 static, 1 lru
+    // static
+    int32_t kg, ki, capacity;
+    int32_t *lut;                      // n_nodes entries, global index or CACHEMISS
+    void *part[LEGION_MAX_DEVICE];     // part[ki] is owned
+    // lru
+    int64_t sets;
+    int32_t ways;
+    int32_t *keys, *stamps;
+    int64_t *claim;
+    void *rows;
+    int32_t clock;
+    const void *host_table;
+    unsigned long long *stats;  // 4 counters on the device
+};
+
+struct LegionPool {
+    int32_t dev_id;
+    int32_t batch_size, hop_num;
+    int32_t fanout[LEGION_MAX_HOPS];
+    int32_t row_bytes_out;
+    int32_t pipes;
+    int64_t max_nodes, max_edges, max_hop_edges, max_inputs;
+    int64_t feat_rows;
+    // per pipe outputs
+    int32_t *ids[LEGION_INTERBATCH_CON];
+    void *features[LEGION_INTERBATCH_CON];
+    int32_t *labels[LEGION_INTERBATCH_CON];
+    int32_t *agg_src[LEGION_INTERBATCH_CON];
+    int32_t *agg_dst[LEGION_INTERBATCH_CON];
+    int32_t *node_counter[LEGION_INTERBATCH_CON];
+    int32_t *edge_counter[LEGION_INTERBATCH_CON];
+    // shared scratch
+    int64_t *cache_index;      // one entry per node of the batch
+    int32_t *src_global;       // sampled neighbour ids, all hops
+    legion::MapSlot *map;      // batch-local id map
+    uint32_t map_mask;
+    legion::NodeRec *node_rec;
+    int32_t *tile_sum, *tile_off;
+    int32_t *eslot, *erank;
+    int64_t *lru_victim;       // per node: way chosen for insertion, or -1
+    int32_t *ctl;
+    int32_t *seed_stage, *label_stage;  // device staging for host-provided seeds
+    int32_t *h_stage;                   // pinned host staging
+    // batch state
+    int32_t iter, mode, pipe;
+    uint32_t global_batch;
+    uint64_t rng_seed;
+    int32_t max_rounds;
+    int32_t sm_count;
+};
+
+namespace legion {
+// kernel launchers (defined in sample.cu / gather.cu / cache.cu)
+int launch_batch_generate(cudaStream_t s, LegionPool *p, const int32_t *all_ids, const int32_t *all_labels,
+                          int32_t total_cap, int64_t first, int32_t size, int32_t hop_num);
+int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32_t fanout, int32_t hop,
+                      int32_t op_id);
+int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
+int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c);
+}  // namespace legion

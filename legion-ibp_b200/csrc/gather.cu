@@ -1,0 +1,507 @@
+// Cache lookup fused with the feature gather.
+//
+// One warp owns 32 consecutive rows of the segment: every lane looks up one id (one coalesced id
+// load, one 4-byte table read), turns the answer into a source pointer (this GPU's partition, a
+// peer's partition reached by plain loads over NVLink, or the pinned host table reached by
+// zero-copy loads), and the warp then copies the rows four at a time with 16-byte loads so that
+// 4 x 512 B per warp are in flight before the first store.  Stores are streaming (the trainer
+// reads the rows once).  Hit / miss sets leave the kernel in cache_index exactly as FindFeat
+// would have written them.
+//
+// Replaces bght::bcht::find + multiGPU_feat_cache_lookup (sampling_server/src/cache/cache.cu:157-192,
+// 743-781; cache/cache_impl.cuh:239-303: thread-per-float, 4-byte loads, 32-64 CTAs) and
+// static_retrieve_kernel + static_transfer_kernel (comp_cache/static_cache_kernel.cuh:185-266).
+#include "common.cuh"
+
+#include <cuda_fp8.h>
+
+namespace legion {
+
+static constexpr unsigned kFull = 0xFFFFFFFFu;
+
+struct GatherParams {
+    const int32_t *ids;
+    int32_t *nc;  // node_counter of the pipe
+    int32_t op_id;
+    const int32_t *lut;
+    int32_t capacity, kg, ki;
+    const uint8_t *part[LEGION_MAX_DEVICE];
+    const uint8_t *host;
+    int64_t n_nodes;
+    uint8_t *dst;
+    int32_t *cache_index;
+    unsigned long long *stats;
+    int32_t row_bytes;   // bytes of one output row
+    int32_t slot_bytes;  // bytes of one cached row
+    int32_t feature_len; // elements per row (quantised codecs)
+};
+
+__device__ __forceinline__ const uint8_t *shfl_ptr(const uint8_t *p, int src)
+{
+    unsigned long long v = (unsigned long long)p;
+    unsigned lo = __shfl_sync(kFull, (unsigned)v, src);
+    unsigned hi = __shfl_sync(kFull, (unsigned)(v >> 32), src);
+    return (const uint8_t *)(((unsigned long long)hi << 32) | lo);
+}
+
+// Segment of a lookup op: the seeds (op 1) or the nodes found by hop h (op 3h+1).  Taken from
+// the cumulative counts nc[9+h], which are written once per batch, so that a gather may overlap
+// the sampling of the next hop on another stream.  Block 0 also leaves the (offset, size)
+// snapshot that counter_update writes for a lookup op (operator_impl.cu:85-87).
+__device__ __forceinline__ void segment_of(int32_t *nc, int op_id, int &off, int &n)
+{
+    const int h = op_id / LEGION_INTRABATCH_CON;
+    off = h > 0 ? nc[LEGION_INTRABATCH_CON * 3 + h - 1] : 0;
+    n = nc[LEGION_INTRABATCH_CON * 3 + h] - off;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        nc[(op_id % LEGION_INTRABATCH_CON) * 2] = off;
+        nc[(op_id % LEGION_INTRABATCH_CON) * 2 + 1] = n;
+    }
+}
+
+// Looks one id up and resolves it to a source row.  `where`: 0 local, 1 peer, 2 host, 3 none.
+__device__ __forceinline__ const uint8_t *resolve(const GatherParams &p, int32_t id, int32_t &gidx, int &where)
+{
+    gidx = LEGION_CACHEMISS_FLAG;
+    where = 3;
+    if (id < 0) return nullptr;
+    if (p.lut != nullptr) gidx = __ldg(&p.lut[id]);
+    if (gidx >= 0) {
+        int d = gidx / p.capacity;
+        int row = gidx - d * p.capacity;
+        where = (d == p.ki) ? 0 : 1;
+        return p.part[d] + (int64_t)row * p.slot_bytes;
+    }
+    if (p.host != nullptr) {
+        where = 2;
+        return p.host + ((int64_t)id % p.n_nodes) * (int64_t)p.row_bytes;
+    }
+    return nullptr;
+}
+
+__device__ __forceinline__ void add_stats(unsigned long long *stats, int where, int lane)
+{
+    unsigned m0 = __ballot_sync(kFull, where == 0);
+    unsigned m1 = __ballot_sync(kFull, where == 1);
+    unsigned m2 = __ballot_sync(kFull, where == 2);
+    if (stats != nullptr && lane == 0) {
+        if (m0) atomicAdd(&stats[0], (unsigned long long)__popc(m0));
+        if (m1) atomicAdd(&stats[1], (unsigned long long)__popc(m1));
+        if (m2) atomicAdd(&stats[2], (unsigned long long)__popc(m2));
+    }
+}
+
+// Rows whose size is a multiple of 16 bytes.  VPL = 16-byte vectors per lane per row,
+// R = rows copied together.
+template <int VPL, int R>
+__global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
+{
+    int off, n;
+    segment_of(p.nc, p.op_id, off, n);
+    const int lane = threadIdx.x & 31;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    const int row_vec = p.row_bytes >> 4;
+    for (int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; c * 32 < n; c += n_warps) {
+        const int r = c * 32 + lane;
+        int32_t id = (r < n) ? __ldg(&p.ids[off + r]) : -1;
+        int32_t gidx;
+        int where;
+        const uint8_t *src = resolve(p, id, gidx, where);
+        if (r < n) p.cache_index[off + r] = gidx;
+        add_stats(p.stats, where, lane);
+        const int rows_here = min(32, n - c * 32);
+        uint8_t *dst_base = p.dst + (int64_t)(off + c * 32) * p.row_bytes;
+        for (int j0 = 0; j0 < rows_here; j0 += R) {
+            uint4 v[R][VPL];
+            const uint8_t *sp[R];
+#pragma unroll
+            for (int jj = 0; jj < R; ++jj) {
+                sp[jj] = shfl_ptr(src, (j0 + jj) & 31);
+                if (j0 + jj >= rows_here) sp[jj] = nullptr;
+            }
+#pragma unroll
+            for (int jj = 0; jj < R; ++jj) {
+#pragma unroll
+                for (int q = 0; q < VPL; ++q) {
+                    int idx = lane + 32 * q;
+                    if (sp[jj] != nullptr && idx < row_vec)
+                        v[jj][q] = *reinterpret_cast<const uint4 *>(sp[jj] + idx * 16);
+                }
+            }
+#pragma unroll
+            for (int jj = 0; jj < R; ++jj) {
+#pragma unroll
+                for (int q = 0; q < VPL; ++q) {
+                    int idx = lane + 32 * q;
+                    if (sp[jj] != nullptr && idx < row_vec)
+                        __stcs(reinterpret_cast<uint4 *>(dst_base + (int64_t)(j0 + jj) * p.row_bytes + idx * 16),
+                               v[jj][q]);
+                }
+            }
+        }
+    }
+}
+
+// Any row size that is a multiple of 4 bytes (rows of F floats with F odd, ...).
+__global__ void __launch_bounds__(256) gather_word_kernel(GatherParams p)
+{
+    int off, n;
+    segment_of(p.nc, p.op_id, off, n);
+    const int lane = threadIdx.x & 31;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    const int row_words = p.row_bytes >> 2;
+    for (int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; c * 32 < n; c += n_warps) {
+        const int r = c * 32 + lane;
+        int32_t id = (r < n) ? __ldg(&p.ids[off + r]) : -1;
+        int32_t gidx;
+        int where;
+        const uint8_t *src = resolve(p, id, gidx, where);
+        if (r < n) p.cache_index[off + r] = gidx;
+        add_stats(p.stats, where, lane);
+        const int rows_here = min(32, n - c * 32);
+        uint32_t *dst_base = reinterpret_cast<uint32_t *>(p.dst + (int64_t)(off + c * 32) * p.row_bytes);
+        for (int j = 0; j < rows_here; ++j) {
+            const uint32_t *sp = reinterpret_cast<const uint32_t *>(shfl_ptr(src, j));
+            if (sp == nullptr) continue;
+            for (int w = lane; w < row_words; w += 32) __stcs(&dst_base[(int64_t)j * row_words + w], sp[w]);
+        }
+    }
+}
+
+// Compressed cache: a hit row holds feature_len one-byte codes followed by an fp32 scale
+// and is expanded to fp32 here; a miss row is a plain fp32 row of the host table.
+// x^ = float(code) * scale, one multiplication, so the host replay is exact.
+template <int CODEC>
+__device__ __forceinline__ float decode_code(uint8_t b)
+{
+    if (CODEC == LEGION_CODEC_INT8) return (float)(int8_t)b;
+    __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+    return __half2float(__half(h));
+}
+
+template <int CODEC>
+__global__ void __launch_bounds__(256) gather_quant_kernel(GatherParams p)
+{
+    int off, n;
+    segment_of(p.nc, p.op_id, off, n);
+    const int lane = threadIdx.x & 31;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    const int f = p.feature_len;
+    for (int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; c * 32 < n; c += n_warps) {
+        const int r = c * 32 + lane;
+        int32_t id = (r < n) ? __ldg(&p.ids[off + r]) : -1;
+        int32_t gidx;
+        int where;
+        const uint8_t *src = resolve(p, id, gidx, where);
+        if (r < n) p.cache_index[off + r] = gidx;
+        add_stats(p.stats, where, lane);
+        const int rows_here = min(32, n - c * 32);
+        float *dst_base = reinterpret_cast<float *>(p.dst + (int64_t)(off + c * 32) * p.row_bytes);
+        for (int j = 0; j < rows_here; ++j) {
+            const uint8_t *sp = shfl_ptr(src, j);
+            const int wj = __shfl_sync(kFull, where, j);
+            if (sp == nullptr) continue;
+            float *drow = dst_base + (int64_t)j * f;
+            if (wj == 2) {  // raw fp32 row from the host table
+                const uint32_t *s32 = reinterpret_cast<const uint32_t *>(sp);
+                for (int w = lane; w < f; w += 32) __stcs(reinterpret_cast<uint32_t *>(drow) + w, s32[w]);
+            } else {
+                const float scale = *reinterpret_cast<const float *>(sp + f);  // f is a multiple of 4
+                const int groups = f >> 2;
+                for (int g = lane; g < groups; g += 32) {
+                    uint32_t packed = *reinterpret_cast<const uint32_t *>(sp + g * 4);
+                    float4 o;
+                    o.x = __fmul_rn(decode_code<CODEC>((uint8_t)(packed)), scale);
+                    o.y = __fmul_rn(decode_code<CODEC>((uint8_t)(packed >> 8)), scale);
+                    o.z = __fmul_rn(decode_code<CODEC>((uint8_t)(packed >> 16)), scale);
+                    o.w = __fmul_rn(decode_code<CODEC>((uint8_t)(packed >> 24)), scale);
+                    __stcs(reinterpret_cast<float4 *>(drow) + g, o);
+                }
+            }
+        }
+    }
+}
+
+// ---- set-associative LRU cache ----------------------------------------------------------------------
+// Lookup ("retrieve_and_touch"): `ways` consecutive lanes probe one set; a hit stamps the way
+// with the batch clock.  Addressing: set = id % sets (one GPU), slot = set * ways + way.
+struct LruParams {
+    const int32_t *ids;
+    int32_t *nc;
+    int32_t op_id;
+    int32_t *keys, *stamps;
+    int64_t sets;
+    int32_t ways, clock;
+    const uint8_t *rows;
+    const uint8_t *host;
+    int64_t n_nodes;
+    uint8_t *dst;
+    int64_t *cache_index;
+    unsigned long long *stats;
+    int32_t row_bytes;
+};
+
+template <int VPL, int R>
+__global__ void __launch_bounds__(256) gather_lru_kernel(LruParams p)
+{
+    int off, n;
+    segment_of(p.nc, p.op_id, off, n);
+    const int lane = threadIdx.x & 31;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    const int row_vec = p.row_bytes >> 4;
+    const int ways = p.ways;              // power of two, <= 32
+    const int per_pass = 32 / ways;       // ids probed together by one warp
+    const int sub = lane / ways, way = lane % ways;
+    for (int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; c * 32 < n; c += n_warps) {
+        const int r = c * 32 + lane;
+        const int32_t my_id = (r < n) ? __ldg(&p.ids[off + r]) : -1;
+        int64_t my_slot = -1;
+        for (int pass = 0; pass < 32; pass += per_pass) {
+            const int owner = pass + sub;  // lane whose id this group of `ways` lanes probes
+            const int32_t id = __shfl_sync(kFull, my_id, owner);
+            int64_t set = id >= 0 ? (int64_t)id % p.sets : 0;
+            int32_t key = id >= 0 ? __ldcg(&p.keys[set * ways + way]) : -1;
+            unsigned hitmask = __ballot_sync(kFull, id >= 0 && key == id);
+            unsigned group = (ways == 32) ? hitmask : ((hitmask >> (sub * ways)) & ((1u << ways) - 1u));
+            int hit_way = __ffs(group) - 1;
+            if (hit_way == way && id >= 0) p.stamps[set * ways + way] = p.clock;
+            // hand the answer to the owning lane
+            int64_t slot = hit_way >= 0 ? set * ways + hit_way : -1;
+#pragma unroll 1
+            for (int g = 0; g < per_pass; ++g) {
+                long long s_g = __shfl_sync(kFull, (long long)slot, g * ways);
+                if (lane == pass + g) my_slot = s_g;
+            }
+        }
+        if (r < n) p.cache_index[off + r] = my_slot;
+        int where = 3;
+        const uint8_t *src = nullptr;
+        if (my_id >= 0) {
+            if (my_slot >= 0) { where = 0; src = p.rows + my_slot * (int64_t)p.row_bytes; }
+            else if (p.host != nullptr) { where = 2; src = p.host + ((int64_t)my_id % p.n_nodes) * (int64_t)p.row_bytes; }
+        }
+        add_stats(p.stats, where, lane);
+        const int rows_here = min(32, n - c * 32);
+        uint8_t *dst_base = p.dst + (int64_t)(off + c * 32) * p.row_bytes;
+        for (int j0 = 0; j0 < rows_here; j0 += R) {
+            uint4 v[R][VPL];
+            const uint8_t *sp[R];
+#pragma unroll
+            for (int jj = 0; jj < R; ++jj) {
+                sp[jj] = shfl_ptr(src, (j0 + jj) & 31);
+                if (j0 + jj >= rows_here) sp[jj] = nullptr;
+            }
+#pragma unroll
+            for (int jj = 0; jj < R; ++jj) {
+#pragma unroll
+                for (int q = 0; q < VPL; ++q) {
+                    int idx = lane + 32 * q;
+                    if (sp[jj] != nullptr && idx < row_vec)
+                        v[jj][q] = *reinterpret_cast<const uint4 *>(sp[jj] + idx * 16);
+                }
+            }
+#pragma unroll
+            for (int jj = 0; jj < R; ++jj) {
+#pragma unroll
+                for (int q = 0; q < VPL; ++q) {
+                    int idx = lane + 32 * q;
+                    if (sp[jj] != nullptr && idx < row_vec)
+                        __stcs(reinterpret_cast<uint4 *>(dst_base + (int64_t)(j0 + jj) * p.row_bytes + idx * 16),
+                               v[jj][q]);
+                }
+            }
+        }
+    }
+}
+
+// Insertion phase, run once per batch after every gather (two launches):
+//  claim : every missed id picks the way of its set with the smallest stamp (empty ways count
+//          as -1, ways stamped in this batch are excluded, lowest way on ties) and bids for it
+//          with its position in the id list (atomicMin);
+//  commit: the lowest bidder writes key and stamp and copies its row from the batch's feature
+//          buffer (already gathered) into the slot.
+__global__ void lru_claim_kernel(const int32_t *__restrict__ ids, const int64_t *__restrict__ cache_index,
+                                 const int32_t *__restrict__ nc, const int32_t *__restrict__ keys,
+                                 const int32_t *__restrict__ stamps, int64_t sets, int ways, int clock,
+                                 unsigned long long *claim, int64_t *victim /* per row: chosen slot or -1 */)
+{
+    const int n = nc[LEGION_INTRABATCH_CON * 3 + nc[LEGION_INTRABATCH_CON * 3 - 1]];  // all nodes of the batch
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
+        int64_t v = -1;
+        int32_t id = ids[r];
+        if (id >= 0 && cache_index[r] < 0) {
+            int64_t set = (int64_t)id % sets;
+            int best = -1, best_stamp = 0;
+            for (int w = 0; w < ways; ++w) {
+                int32_t key = keys[set * ways + w];
+                int32_t st = key == -1 ? -1 : stamps[set * ways + w];
+                if (st == clock) continue;
+                if (best < 0 || st < best_stamp) { best = w; best_stamp = st; }
+            }
+            if (best >= 0) {
+                v = set * ways + best;
+                atomicMin(&claim[v], (unsigned long long)r);
+            }
+        }
+        victim[r] = v;
+    }
+}
+
+__global__ void lru_commit_kernel(const int32_t *__restrict__ ids, const int32_t *__restrict__ nc, int32_t *keys,
+                                  int32_t *stamps, int clock, const unsigned long long *__restrict__ claim,
+                                  const int64_t *__restrict__ victim, const uint8_t *__restrict__ features,
+                                  uint8_t *rows, int row_bytes, unsigned long long *stats)
+{
+    const int n = nc[LEGION_INTRABATCH_CON * 3 + nc[LEGION_INTRABATCH_CON * 3 - 1]];  // all nodes of the batch
+    const int lane = threadIdx.x & 31;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    const int row_vec = row_bytes >> 4;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n; r += n_warps) {
+        int64_t v = victim[r];
+        if (v < 0) continue;
+        if (claim[v] != (unsigned long long)r) continue;  // a lower position won the way
+        const uint4 *s = reinterpret_cast<const uint4 *>(features + (int64_t)r * row_bytes);
+        uint4 *d = reinterpret_cast<uint4 *>(rows + v * (int64_t)row_bytes);
+        for (int q = lane; q < row_vec; q += 32) d[q] = s[q];
+        if (lane == 0) {
+            keys[v] = ids[r];
+            stamps[v] = clock;
+            if (stats != nullptr) atomicAdd(&stats[3], 1ull);
+        }
+    }
+}
+
+__global__ void lru_claim_reset_kernel(const int64_t *__restrict__ victim, const int32_t *__restrict__ nc,
+                                       unsigned long long *claim)
+{
+    const int n = nc[LEGION_INTRABATCH_CON * 3 + nc[LEGION_INTRABATCH_CON * 3 - 1]];  // all nodes of the batch
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
+        int64_t v = victim[r];
+        if (v >= 0) claim[v] = ~0ull;
+    }
+}
+
+// ---- launchers ------------------------------------------------------------------------------------------
+
+template <int VPL, int R>
+static void launch_vec(int grid, cudaStream_t s, const GatherParams &gp)
+{
+    gather_vec_kernel<VPL, R><<<grid, 256, 0, s>>>(gp);
+}
+template <int VPL, int R>
+static void launch_lru(int grid, cudaStream_t s, const LruParams &lp)
+{
+    gather_lru_kernel<VPL, R><<<grid, 256, 0, s>>>(lp);
+}
+
+int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id)
+{
+    const int pipe = p->pipe;
+    // worst-case rows of this segment: the seeds, or the new nodes of hop (op_id / 3)
+    int hop = op_id / LEGION_INTRABATCH_CON;  // 0 = seeds
+    int64_t rows = p->batch_size;
+    {
+        int64_t nodes = p->batch_size;
+        for (int h = 0; h < hop; ++h) { rows = nodes * p->fanout[h]; nodes += rows; }
+    }
+    int64_t chunks = (rows + 31) / 32;
+    int64_t g64 = (chunks + 7) / 8;
+    int cap = p->sm_count * 8;
+    int grid = (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
+    const int row_bytes = p->row_bytes_out;
+
+    if (c != nullptr && c->kind == 1) {
+        LG_ARG(c->row_bytes == row_bytes && row_bytes % 16 == 0, "lru cache rows must be a multiple of 16 bytes");
+        LruParams lp;
+        lp.ids = p->ids[pipe];
+        lp.nc = p->node_counter[pipe];
+        lp.op_id = op_id;
+        lp.keys = c->keys;
+        lp.stamps = c->stamps;
+        lp.sets = c->sets;
+        lp.ways = c->ways;
+        lp.clock = c->clock;
+        lp.rows = (const uint8_t *)c->rows;
+        lp.host = (const uint8_t *)c->host_table;
+        lp.n_nodes = c->n_nodes;
+        lp.dst = (uint8_t *)p->features[pipe];
+        lp.cache_index = p->cache_index;
+        lp.stats = c->stats;
+        lp.row_bytes = row_bytes;
+        int vpl = (row_bytes / 16 + 31) / 32;
+        LG_ARG(vpl >= 1 && vpl <= 4, "row size above 2048 bytes is not supported by the lru gather");
+        switch (vpl) {
+        case 1: launch_lru<1, 4>(grid, s, lp); break;
+        case 2: launch_lru<2, 2>(grid, s, lp); break;
+        case 3: launch_lru<3, 2>(grid, s, lp); break;
+        default: launch_lru<4, 2>(grid, s, lp); break;
+        }
+        LG_LAUNCH_CHECK();
+        return LEGION_OK;
+    }
+
+    GatherParams gp;
+    gp.ids = p->ids[pipe];
+    gp.nc = p->node_counter[pipe];
+    gp.op_id = op_id;
+    gp.lut = c ? c->lut : nullptr;
+    gp.capacity = c ? (c->capacity > 0 ? c->capacity : 1) : 1;
+    gp.kg = c ? c->kg : 1;
+    gp.ki = c ? c->ki : 0;
+    for (int k = 0; k < LEGION_MAX_DEVICE; ++k) gp.part[k] = c ? (const uint8_t *)c->part[k] : nullptr;
+    gp.host = c ? (const uint8_t *)c->host_table : nullptr;
+    gp.n_nodes = c ? c->n_nodes : 1;
+    gp.dst = (uint8_t *)p->features[pipe];
+    gp.cache_index = reinterpret_cast<int32_t *>(p->cache_index);
+    gp.stats = c ? c->stats : nullptr;
+    gp.row_bytes = row_bytes;
+    gp.slot_bytes = c ? c->slot_bytes : row_bytes;
+    gp.feature_len = row_bytes / 4;
+
+    if (c != nullptr && c->codec != LEGION_CODEC_RAW) {
+        LG_ARG(gp.feature_len % 4 == 0, "compressed rows need a feature length that is a multiple of 4");
+        if (c->codec == LEGION_CODEC_INT8) gather_quant_kernel<LEGION_CODEC_INT8><<<grid, 256, 0, s>>>(gp);
+        else gather_quant_kernel<LEGION_CODEC_E4M3><<<grid, 256, 0, s>>>(gp);
+        LG_LAUNCH_CHECK();
+        return LEGION_OK;
+    }
+    if (row_bytes % 16 == 0 && row_bytes <= 2048) {
+        int vpl = (row_bytes / 16 + 31) / 32;
+        switch (vpl) {
+        case 1: launch_vec<1, 4>(grid, s, gp); break;
+        case 2: launch_vec<2, 2>(grid, s, gp); break;
+        case 3: launch_vec<3, 2>(grid, s, gp); break;
+        default: launch_vec<4, 2>(grid, s, gp); break;
+        }
+    } else {
+        LG_ARG(row_bytes % 4 == 0, "row size must be a multiple of 4 bytes");
+        gather_word_kernel<<<grid, 256, 0, s>>>(gp);
+    }
+    LG_LAUNCH_CHECK();
+    return LEGION_OK;
+}
+
+int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c)
+{
+    if (c == nullptr || c->kind != 1) return LEGION_OK;
+    const int pipe = p->pipe;
+    const int cap = p->sm_count * 8;
+    int64_t g_thread = (p->max_nodes + 255) / 256;
+    int64_t g_warp = (p->max_nodes + 7) / 8;
+    int grid_t = (int)(g_thread > cap ? cap : g_thread);
+    int grid_w = (int)(g_warp > cap ? cap : g_warp);
+    unsigned long long *claim = reinterpret_cast<unsigned long long *>(c->claim);
+    lru_claim_kernel<<<grid_t, 256, 0, s>>>(p->ids[pipe], p->cache_index, p->node_counter[pipe], c->keys, c->stamps, c->sets,
+                                            c->ways, c->clock, claim, p->lru_victim);
+    LG_LAUNCH_CHECK();
+    lru_commit_kernel<<<grid_w, 256, 0, s>>>(p->ids[pipe], p->node_counter[pipe], c->keys, c->stamps, c->clock, claim,
+                                             p->lru_victim, (const uint8_t *)p->features[pipe],
+                                             (uint8_t *)c->rows, c->row_bytes, c->stats);
+    LG_LAUNCH_CHECK();
+    lru_claim_reset_kernel<<<grid_t, 256, 0, s>>>(p->lru_victim, p->node_counter[pipe], claim);
+    LG_LAUNCH_CHECK();
+    c->clock += 1;
+    return LEGION_OK;
+}
+
+}  // namespace legion

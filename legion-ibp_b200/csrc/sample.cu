@@ -1,0 +1,488 @@
+// Seed batch generation, neighbour sampling, per-hop dedup and relabel.
+//
+// One hop is five launches on one stream, with every size kept on the device:
+//   hop_count   : per input node degree, CSR start and its edge offset inside a 1024-node tile;
+//                 the last CTA to finish turns the tile sums into tile offsets (no host sync)
+//   hop_sample  : one warp per input node draws the neighbours (Philox4x32-10 counter RNG),
+//                 writes the edges at their final positions and enters every neighbour into the
+//                 batch-local id map with atomicMin(first edge index)
+//   hop_flag    : marks the edge that reached a new node first, ranks the marks per tile
+//   hop_assign  : gives new nodes their local ids in order of first appearance
+//   hop_relabel : writes local source ids; the last CTA advances the counters
+// The edge order (input after input, slot after slot) and the node order (first appearance in
+// that edge order) do not depend on scheduling, so a host replay reproduces them bit for bit.
+//
+// Replaces batch_generate / random_sample / construct_graph / counter_update / ClearPosMap of
+// sampling_server/src/engine/operator_impl.cu:28-91,178-317,598-604: the O(N) bitmap and
+// position_map become a batch-local open-addressing map that stays in L2, the fixed <<<16,512>>>
+// grid becomes a grid sized from the SM count, and the blocking counter read-backs disappear.
+#include "common.cuh"
+
+namespace legion {
+
+static constexpr unsigned kFull = 0xFFFFFFFFu;
+
+__device__ __forceinline__ uint32_t mix32(uint32_t h)
+{
+    h ^= h >> 16; h *= 0x85EBCA6Bu; h ^= h >> 13; h *= 0xC2B2AE35u; h ^= h >> 16;
+    return h;
+}
+
+// Enters `key` and lowers its value to `cand`; returns the slot.  Keys never change once
+// written during a batch, so a stale read can only show "empty", which the CAS then corrects.
+__device__ __forceinline__ int32_t map_insert_min(MapSlot *map, uint32_t mask, int32_t key, int32_t cand,
+                                                  int32_t *ctl)
+{
+    uint32_t s = mix32((uint32_t)key) & mask;
+    for (uint32_t probe = 0; probe <= mask; ++probe) {
+        int32_t k = __ldcg(&map[s].key);
+        if (k == kEmptyKey) {
+            int32_t old = atomicCAS(&map[s].key, kEmptyKey, key);
+            k = (old == kEmptyKey) ? key : old;
+        }
+        if (k == key) {
+            atomicMin(&map[s].val, cand);
+            return (int32_t)s;
+        }
+        s = (s + 1) & mask;
+    }
+    atomicCAS(&ctl[CTL_ERROR], DERR_NONE, DERR_MAP_FULL);
+    return 0;
+}
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                              uint32_t k0, uint32_t k1, uint32_t &o0, uint32_t &o1)
+{
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        uint32_t n0 = hi1 ^ c1 ^ k0;
+        uint32_t n2 = hi0 ^ c3 ^ k1;
+        c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    o0 = c0; o1 = c1;
+}
+
+// one bounded draw in [0, n): 64 random bits times n, high half
+__device__ __forceinline__ uint32_t draw_below(uint32_t input_index, uint32_t lane, uint32_t round,
+                                               uint32_t hop, uint32_t batch_id, uint32_t k0, uint32_t k1,
+                                               uint32_t n)
+{
+    uint32_t w0, w1;
+    philox4x32_10(input_index, round * 32u + lane, hop, batch_id, k0, k1, w0, w1);
+    unsigned long long r64 = ((unsigned long long)w1 << 32) | w0;
+    return (uint32_t)__umul64hi(r64, (unsigned long long)n);
+}
+
+// m distinct values of [0, n) in lanes 0..m-1 (m <= 32 < n).  All 32 lanes take part; lanes
+// >= m hold a dummy that can never compare equal.  A lane keeps its draw unless a lane that
+// already holds the value, or a lower lane that drew it in the same round, exists.
+__device__ __forceinline__ uint32_t draw_distinct(int m, uint32_t n, uint32_t input_index, uint32_t hop,
+                                                  uint32_t batch_id, uint32_t k0, uint32_t k1,
+                                                  int max_rounds, int lane)
+{
+    bool kept = lane >= m;
+    uint32_t x = 0x80000000u | (uint32_t)lane;
+    for (int r = 0; r < max_rounds; ++r) {
+        unsigned keptmask = __ballot_sync(kFull, kept);
+        if (keptmask == kFull) break;
+        if (!kept) x = draw_below(input_index, (uint32_t)lane, (uint32_t)r, hop, batch_id, k0, k1, n);
+        unsigned peers = __match_any_sync(kFull, x);
+        if (!kept) kept = ((peers & keptmask) == 0u) && ((__ffs(peers) - 1) == lane);
+    }
+    // Lanes still without a value after max_rounds take the next free value, in lane order.
+    unsigned keptmask = __ballot_sync(kFull, kept);
+    for (int guard = 0; guard < 32 && keptmask != kFull; ++guard) {
+        int l = __ffs(~keptmask) - 1;
+        uint32_t cand = __shfl_sync(kFull, x, l);
+        for (int it = 0; it < 64; ++it) {
+            unsigned clash = __ballot_sync(kFull, kept && lane < m && x == cand);
+            if (!clash) break;
+            cand = (cand + 1u) % n;
+        }
+        if (lane == l) { x = cand; kept = true; }
+        keptmask = __ballot_sync(kFull, kept);
+    }
+    return x;
+}
+
+// exclusive scan over the CTA (kScanThreads threads); smem holds 8 ints
+__device__ __forceinline__ int block_excl_scan(int x, int *total, int *smem)
+{
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = x;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int t = __shfl_up_sync(kFull, incl, d);
+        if (lane >= d) incl += t;
+    }
+    if (lane == 31) smem[warp] = incl;
+    __syncthreads();
+    int wo = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < kScanThreads / 32; ++w) {
+        int s = smem[w];
+        if (w < warp) wo += s;
+        tot += s;
+    }
+    __syncthreads();
+    *total = tot;
+    return wo + incl - x;
+}
+
+// The CTA that takes the last ticket turns tile sums into exclusive tile offsets and
+// returns the grand total through *out_total (valid in thread 0 of that CTA only).
+__device__ __forceinline__ bool last_cta_scan(int32_t *ticket, const int32_t *tile_sum, int32_t *tile_off,
+                                              int n_tiles, int *smem, int *s_flag, int *out_total)
+{
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = atomicAdd(ticket, 1);
+        *s_flag = (t == (int)gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!*s_flag) return false;
+    __threadfence();
+    int running = 0;
+    for (int c0 = 0; c0 < n_tiles; c0 += kScanThreads) {
+        int idx = c0 + threadIdx.x;
+        int x = idx < n_tiles ? __ldcg(&tile_sum[idx]) : 0;
+        int tot;
+        int ex = block_excl_scan(x, &tot, smem);
+        if (idx < n_tiles) tile_off[idx] = running + ex;
+        running += tot;
+    }
+    if (threadIdx.x == 0) {
+        *ticket = 0;
+        *out_total = running;
+    }
+    return true;
+}
+
+// literal restatement of counter_update (operator_impl.cu:58-91), executed by one thread
+__device__ __forceinline__ void counter_update(int32_t *nc, int32_t *ec, int op_id, int size, int hop_num)
+{
+    const int C = LEGION_INTRABATCH_CON;
+    if (op_id == 0) {
+        nc[0] = 0;
+        nc[1] = size;
+        nc[C * 3] = size;
+        nc[C * 3 - 1] = hop_num;
+    } else if (op_id % C == 0) {
+        nc[0] = nc[0] + nc[1];
+        nc[1] = nc[C * 2];
+        nc[C * 2] = 0;
+        nc[C * 2 + 1] = nc[0] + nc[1];
+        ec[0] = ec[0] + ec[1];
+        ec[1] = ec[2];
+        ec[2] = 0;
+        nc[C * 3 + op_id / C] = nc[0] + nc[1];
+        ec[C * 3 + op_id / C] = ec[1];
+        ec[C * 4 + op_id / C] = ec[0];
+    } else {
+        nc[(op_id % C) * 2] = nc[0];
+        nc[(op_id % C) * 2 + 1] = nc[1];
+    }
+}
+
+// ---- batch start -----------------------------------------------------------------------------
+
+__global__ void map_clear_kernel(uint4 *slots2, int64_t n_pairs, int32_t *ctl, int32_t *nc, int32_t *ec)
+{
+    const uint4 empty = make_uint4((uint32_t)kEmptyKey, (uint32_t)kEmptyVal, (uint32_t)kEmptyKey,
+                                   (uint32_t)kEmptyVal);
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_pairs;
+         i += (int64_t)gridDim.x * blockDim.x)
+        slots2[i] = empty;
+    if (blockIdx.x == 0 && threadIdx.x < 16) {
+        if (threadIdx.x != CTL_ERROR) ctl[threadIdx.x] = 0;  // the error word is sticky
+        nc[threadIdx.x] = 0;  // cudaMemsetAsync of both counters, operator_impl.cu:158-159
+        ec[threadIdx.x] = 0;
+    }
+}
+
+__global__ void batch_generate_kernel(const int32_t *__restrict__ all_ids, const int32_t *__restrict__ all_labels,
+                                      int32_t total_cap, int64_t first, int32_t size, int32_t hop_num,
+                                      int32_t *ids, int32_t *labels, MapSlot *map, uint32_t mask, int32_t *ctl,
+                                      int32_t *nc, int32_t *ec)
+{
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < size) {
+        int64_t pos = first + idx;
+        if (pos >= total_cap) {  // operator_impl.cu:41-43
+            ids[idx] = -1;
+            labels[idx] = -1;
+        } else {
+            int32_t id = all_ids[pos % total_cap];
+            ids[idx] = id;
+            labels[idx] = all_labels[pos % total_cap];
+            if (id >= 0) map_insert_min(map, mask, id, idx, ctl);
+        }
+    }
+    if (idx == 0) {
+        counter_update(nc, ec, 0, size, hop_num);
+        ctl[CTL_N_NODES] = size;
+        ctl[CTL_E_TOTAL] = 0;
+    }
+}
+
+// ---- one hop -----------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(kScanThreads)
+hop_count_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict__ ids, int32_t fanout,
+                 NodeRec *rec, int32_t *tile_sum, int32_t *tile_off, int32_t *ctl, int64_t max_edges)
+{
+    __shared__ int smem[kScanThreads / 32];
+    __shared__ int s_flag;
+    const int n = ctl[CTL_N_NODES];
+    const int n_tiles = (n + kTile - 1) / kTile;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int base = tile * kTile + threadIdx.x * 4;
+        int4 v4 = *reinterpret_cast<const int4 *>(ids + base);  // ids is padded to a whole tile
+        int32_t v[4] = { v4.x, v4.y, v4.z, v4.w };
+        int64_t start[4];
+        int32_t deg[4], cnt[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            start[j] = 0; deg[j] = 0; cnt[j] = 0;
+            if (base + j < n && v[j] >= 0) {
+                int64_t s = indptr[v[j]];
+                int64_t e = indptr[v[j] + 1];
+                start[j] = s;
+                deg[j] = (int32_t)(e - s);
+                cnt[j] = min(deg[j], fanout);
+            }
+        }
+        int tsum = cnt[0] + cnt[1] + cnt[2] + cnt[3];
+        int total;
+        int ex = block_excl_scan(tsum, &total, smem);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (base + j < n) {
+                NodeRec r;
+                r.start = start[j];
+                r.loff = ex;
+                r.deg = deg[j];
+                *reinterpret_cast<int4 *>(&rec[base + j]) = *reinterpret_cast<int4 *>(&r);
+            }
+            ex += cnt[j];
+        }
+        if (threadIdx.x == 0) tile_sum[tile] = total;
+    }
+    int grand;
+    if (last_cta_scan(&ctl[CTL_TICKET_A], tile_sum, tile_off, n_tiles, smem, &s_flag, &grand)) {
+        if (threadIdx.x == 0) {
+            ctl[CTL_E_HOP] = grand;
+            if ((int64_t)ctl[CTL_E_TOTAL] + grand > max_edges) atomicCAS(&ctl[CTL_ERROR], DERR_NONE, DERR_EDGE_OVERFLOW);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+hop_sample_kernel(const int32_t *__restrict__ indices, const NodeRec *__restrict__ rec,
+                  const int32_t *__restrict__ tile_off, int32_t fanout, uint32_t hop, uint32_t batch_id,
+                  uint32_t k0, uint32_t k1, int max_rounds, int32_t *src_global, int32_t *agg_dst,
+                  int32_t *eslot, MapSlot *map, uint32_t mask, int32_t *ctl)
+{
+    if (ctl[CTL_ERROR] != DERR_NONE) return;
+    const int n = ctl[CTL_N_NODES];
+    const int e_base = ctl[CTL_E_TOTAL];
+    const int lane = threadIdx.x & 31;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    const uint32_t k = (uint32_t)fanout;
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < n; i += n_warps) {
+        int4 raw = __ldg(reinterpret_cast<const int4 *>(&rec[i]));
+        NodeRec r = *reinterpret_cast<NodeRec *>(&raw);
+        const uint32_t deg = (uint32_t)r.deg;
+        if (deg == 0) continue;
+        const int eh0 = __ldg(&tile_off[i >> 10]) + r.loff;
+        int out_slot = -1;   // slot of this lane's first edge, second edge in out_slot2
+        int out_slot2 = -1;
+        int64_t pos = 0, pos2 = 0;
+        if (deg <= k) {
+            if ((uint32_t)lane < deg) { out_slot = lane; pos = lane; }
+        } else if (deg >= 2 * k) {
+            uint32_t x = draw_distinct((int)k, deg, (uint32_t)i, hop, batch_id, k0, k1, max_rounds, lane);
+            if ((uint32_t)lane < k) { out_slot = lane; pos = x; }
+        } else {
+            const int m = (int)(deg - k);
+            uint32_t x = draw_distinct(m, deg, (uint32_t)i, hop, batch_id, k0, k1, max_rounds, lane);
+            uint32_t mylo = (lane < m && x < 32u) ? (1u << x) : 0u;
+            uint32_t myhi = (lane < m && x >= 32u) ? (1u << (x - 32u)) : 0u;
+            uint32_t exlo = __reduce_or_sync(kFull, mylo);
+            uint32_t exhi = __reduce_or_sync(kFull, myhi);
+            uint32_t validlo = deg >= 32u ? 0xFFFFFFFFu : ((1u << deg) - 1u);
+            uint32_t validhi = deg <= 32u ? 0u : (deg >= 64u ? 0xFFFFFFFFu : ((1u << (deg - 32u)) - 1u));
+            uint32_t keeplo = ~exlo & validlo;
+            uint32_t keephi = ~exhi & validhi;
+            uint32_t below = (1u << lane) - 1u;
+            if ((keeplo >> lane) & 1u) { out_slot = __popc(keeplo & below); pos = lane; }
+            if ((keephi >> lane) & 1u) { out_slot2 = __popc(keeplo) + __popc(keephi & below); pos2 = lane + 32; }
+        }
+        if (out_slot >= 0) {
+            int32_t u = __ldg(&indices[r.start + pos]);
+            int eh = eh0 + out_slot;
+            src_global[e_base + eh] = u;
+            agg_dst[e_base + eh] = i;
+            eslot[eh] = map_insert_min(map, mask, u, kNewBase + eh, ctl);
+        }
+        if (out_slot2 >= 0) {
+            int32_t u = __ldg(&indices[r.start + pos2]);
+            int eh = eh0 + out_slot2;
+            src_global[e_base + eh] = u;
+            agg_dst[e_base + eh] = i;
+            eslot[eh] = map_insert_min(map, mask, u, kNewBase + eh, ctl);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+hop_flag_kernel(const int32_t *__restrict__ eslot, const MapSlot *map, int32_t *erank, int32_t *tile_sum,
+                int32_t *tile_off, int32_t *ctl, int64_t max_nodes)
+{
+    __shared__ int smem[kScanThreads / 32];
+    __shared__ int s_flag;
+    const int n_edges = ctl[CTL_E_HOP];
+    const int n_tiles = (n_edges + kTile - 1) / kTile;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int base = tile * kTile + threadIdx.x * 4;
+        int4 s4 = *reinterpret_cast<const int4 *>(eslot + base);  // eslot is padded to a whole tile
+        int32_t s[4] = { s4.x, s4.y, s4.z, s4.w };
+        int f[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            f[j] = 0;
+            if (base + j < n_edges) f[j] = (__ldcg(&map[s[j]].val) == kNewBase + base + j) ? 1 : 0;
+        }
+        int total;
+        int ex = block_excl_scan(f[0] + f[1] + f[2] + f[3], &total, smem);
+        int4 out;
+        out.x = f[0] ? ex : -1; ex += f[0];
+        out.y = f[1] ? ex : -1; ex += f[1];
+        out.z = f[2] ? ex : -1; ex += f[2];
+        out.w = f[3] ? ex : -1;
+        *reinterpret_cast<int4 *>(erank + base) = out;  // erank is padded to a whole tile
+        if (threadIdx.x == 0) tile_sum[tile] = total;
+    }
+    int grand;
+    if (last_cta_scan(&ctl[CTL_TICKET_B], tile_sum, tile_off, n_tiles, smem, &s_flag, &grand)) {
+        if (threadIdx.x == 0) {
+            ctl[CTL_C_HOP] = grand;
+            if ((int64_t)ctl[CTL_N_NODES] + grand > max_nodes) atomicCAS(&ctl[CTL_ERROR], DERR_NONE, DERR_NODE_OVERFLOW);
+        }
+    }
+}
+
+__global__ void hop_assign_kernel(const int32_t *__restrict__ erank, const int32_t *__restrict__ tile_off,
+                                  const int32_t *__restrict__ eslot, const int32_t *__restrict__ src_global,
+                                  int32_t *ids, MapSlot *map, const int32_t *ctl)
+{
+    if (ctl[CTL_ERROR] != DERR_NONE) return;
+    const int n_edges = ctl[CTL_E_HOP];
+    const int n0 = ctl[CTL_N_NODES];
+    const int e_base = ctl[CTL_E_TOTAL];
+    for (int eh = blockIdx.x * blockDim.x + threadIdx.x; eh < n_edges; eh += gridDim.x * blockDim.x) {
+        int r = erank[eh];
+        if (r >= 0) {
+            int nid = n0 + tile_off[eh >> 10] + r;
+            ids[nid] = src_global[e_base + eh];
+            map[eslot[eh]].val = nid;
+        }
+    }
+}
+
+__global__ void hop_relabel_kernel(const int32_t *__restrict__ eslot, const MapSlot *map, int32_t *agg_src,
+                                   int32_t *ctl, int32_t *nc, int32_t *ec, int op_id)
+{
+    __shared__ int s_flag;
+    const int n_edges = ctl[CTL_E_HOP];
+    const int e_base = ctl[CTL_E_TOTAL];
+    const bool ok = ctl[CTL_ERROR] == DERR_NONE;
+    if (ok) {
+        for (int eh = blockIdx.x * blockDim.x + threadIdx.x; eh < n_edges; eh += gridDim.x * blockDim.x)
+            agg_src[e_base + eh] = __ldcg(&map[eslot[eh]].val);
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = atomicAdd(&ctl[CTL_TICKET_C], 1);
+        s_flag = (t == (int)gridDim.x - 1);
+    }
+    __syncthreads();
+    if (s_flag && threadIdx.x == 0) {
+        // every other CTA has read ctl by now
+        int c = ok ? ctl[CTL_C_HOP] : 0;
+        int e = ok ? n_edges : 0;
+        nc[LEGION_INTRABATCH_CON * 2] += c;  // operator_impl.cu:281
+        ec[2] += e;                          // operator_impl.cu:282
+        counter_update(nc, ec, op_id, 0, 0);
+        ctl[CTL_N_NODES] = ctl[CTL_N_NODES] + c;
+        ctl[CTL_E_TOTAL] = e_base + e;
+        ctl[CTL_E_HOP] = 0;
+        ctl[CTL_C_HOP] = 0;
+        ctl[CTL_TICKET_C] = 0;
+    }
+}
+
+// ---- launchers -----------------------------------------------------------------------------------
+
+static inline int grid_for(int64_t items, int per_cta, int cap)
+{
+    int64_t g = (items + per_cta - 1) / per_cta;
+    if (g < 1) g = 1;
+    if (g > cap) g = cap;
+    return (int)g;
+}
+
+int launch_batch_generate(cudaStream_t s, LegionPool *p, const int32_t *all_ids, const int32_t *all_labels,
+                          int32_t total_cap, int64_t first, int32_t size, int32_t hop_num)
+{
+    const int pipe = p->pipe;
+    int64_t n_pairs = ((int64_t)p->map_mask + 1) / 2;
+    map_clear_kernel<<<grid_for(n_pairs, 256 * 4, p->sm_count * 8), 256, 0, s>>>(
+        reinterpret_cast<uint4 *>(p->map), n_pairs, p->ctl, p->node_counter[pipe], p->edge_counter[pipe]);
+    LG_LAUNCH_CHECK();
+    batch_generate_kernel<<<grid_for(size, 256, 1 << 20), 256, 0, s>>>(
+        all_ids, all_labels, total_cap, first, size, hop_num, p->ids[pipe], p->labels[pipe], p->map,
+        p->map_mask, p->ctl, p->node_counter[pipe], p->edge_counter[pipe]);
+    LG_LAUNCH_CHECK();
+    return LEGION_OK;
+}
+
+int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32_t fanout, int32_t hop,
+                      int32_t op_id)
+{
+    const int pipe = p->pipe;
+    const int cap = p->sm_count * 8;
+    // worst-case sizes of this hop: inputs = all nodes so far, edges = inputs * fanout
+    int64_t inputs = p->batch_size;
+    for (int h = 0; h < hop; ++h) inputs += inputs * p->fanout[h];
+    int64_t edges = inputs * fanout;
+    hop_count_kernel<<<grid_for(inputs, kTile, cap), kScanThreads, 0, s>>>(
+        g->indptr, p->ids[pipe], fanout, p->node_rec, p->tile_sum, p->tile_off, p->ctl, p->max_edges);
+    LG_LAUNCH_CHECK();
+    hop_sample_kernel<<<grid_for(inputs, 8, cap), 256, 0, s>>>(
+        g->indices, p->node_rec, p->tile_off, fanout, (uint32_t)hop, p->global_batch, (uint32_t)p->rng_seed,
+        (uint32_t)(p->rng_seed >> 32), p->max_rounds, p->src_global, p->agg_dst[pipe], p->eslot, p->map,
+        p->map_mask, p->ctl);
+    LG_LAUNCH_CHECK();
+    int32_t *tile_sum2 = p->tile_sum + p->max_inputs / kTile + 2;
+    int32_t *tile_off2 = p->tile_off + p->max_inputs / kTile + 2;
+    hop_flag_kernel<<<grid_for(edges, kTile, cap), kScanThreads, 0, s>>>(p->eslot, p->map, p->erank, tile_sum2,
+                                                                         tile_off2, p->ctl, p->max_nodes);
+    LG_LAUNCH_CHECK();
+    hop_assign_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->erank, tile_off2, p->eslot, p->src_global,
+                                                                   p->ids[pipe], p->map, p->ctl);
+    LG_LAUNCH_CHECK();
+    hop_relabel_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->eslot, p->map, p->agg_src[pipe], p->ctl,
+                                                                    p->node_counter[pipe], p->edge_counter[pipe],
+                                                                    op_id);
+    LG_LAUNCH_CHECK();
+    return LEGION_OK;
+}
+
+}  // namespace legion

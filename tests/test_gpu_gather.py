@@ -1,0 +1,258 @@
+"""Cache build, cache lookup and feature gather parity against the CPU checker.
+
+Gathered rows and hit / miss sets are bit-exact; dequantised rows of the compressed caches are
+bit-exact against the host dequantiser and within the stated tolerance of the fp32 rows.
+"""
+import numpy as np
+import pytest
+
+import legion_ibp_b200 as L
+from conftest import small_graph
+
+pytestmark = pytest.mark.gpu
+
+
+def _pinned(arr):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(arr)).pin_memory()
+    return t
+
+
+class Rig:
+    """One GPU's storage objects around a host table, with the id list as the seed list (0 hops)."""
+
+    def __init__(self, table, ids_list, batch, lru=None, capacity=0, kg=1, ki=0, codec=L.CODEC_RAW, order=None,
+                 out_row_bytes=None):
+        import torch
+        self.table = table
+        self.n = table.shape[0]
+        self.row_bytes = table.strides[0]
+        self.h_table = _pinned(table)
+        self.ids = torch.from_numpy(ids_list.astype(np.int32)).cuda()
+        self.lab = torch.zeros_like(self.ids)
+        self.f = L.FeatureStorage(0, self.n, self.row_bytes, self.h_table)
+        self.f.set_split(L.TRAINMODE, self.ids, self.lab)
+        self.pool = L.MemoryPool(0, batch, [], out_row_bytes or self.row_bytes, 2)
+        if lru is not None:
+            self.cache = L.UnifiedCache(0, self.n, self.row_bytes, 0, lru=lru)
+            self.cache.set_host_table(self.h_table)
+        else:
+            self.cache = L.UnifiedCache(0, self.n, self.row_bytes, capacity, kg, ki, codec)
+            if order is not None:
+                self.order = torch.from_numpy(order.astype(np.int32)).cuda()
+                self.cache.fill_static(self.order, self.h_table)
+        self.batch = batch
+
+    def gather(self, it, pipe=0):
+        self.pool.set_batch(it, L.TRAINMODE, pipe, it)
+        L.BatchGenerate(None, self.f, self.cache, self.pool, self.batch, it, 0, 0, L.TRAINMODE, False, 0)
+        L.FeatureCacheLookup(None, self.cache, self.pool, 1, 0)
+        L.IOComplete(None, self.cache, self.pool, 0, L.TRAINMODE)
+        nc = self.pool.read(L.BUF_NODE_COUNTER, pipe, 16, np.int32)
+        n = int(nc[9])
+        feat = self.pool.read(L.BUF_FEATURES, pipe, n * self.pool.row_bytes_out, np.uint8)
+        return n, feat.reshape(n, self.pool.row_bytes_out), nc
+
+    def close(self):
+        self.pool.close(); self.cache.close(); self.f.close()
+
+
+@pytest.mark.parametrize("feat_len,dtype", [(100, np.float32), (128, np.float32), (768, np.float16),
+                                            (3, np.float32), (602, np.float32), (512, np.float32), (1, np.float32)])
+@pytest.mark.parametrize("cached_frac", [0.0, 0.2, 1.0])
+def test_static_cache_gather(oracle_mod, feat_len, dtype, cached_frac):
+    rng = np.random.default_rng(feat_len)
+    indptr, _ = small_graph(4000, 50000, 3)
+    n = len(indptr) - 1
+    table = rng.standard_normal((n, feat_len)).astype(dtype)
+    ids_list = rng.integers(0, n, 5000).astype(np.int32)
+    cap = int(n * cached_frac)
+    order = oracle_mod.degree_order(indptr)
+    rig = Rig(table, ids_list, 1237, capacity=cap, order=order)
+    lut = oracle_mod.static_cache_lut(order, cap, 1)
+    part = oracle_mod.static_cache_fill(order, cap, 1, 0, table)
+    got_lut = np.empty(n, np.int32)
+    L._check(L.lib().legion_copy(got_lut.ctypes.data_as(L.C.c_void_p), L.C.c_void_p(rig.cache.lut_ptr()),
+                                 L.C.c_int64(n * 4), L.C.c_int32(2)))
+    np.testing.assert_array_equal(got_lut, lut)
+    if cap:
+        p, b = rig.cache.partition()
+        got_part = np.empty(b, np.uint8)
+        L._check(L.lib().legion_copy(got_part.ctypes.data_as(L.C.c_void_p), L.C.c_void_p(p), L.C.c_int64(b),
+                                     L.C.c_int32(2)))
+        np.testing.assert_array_equal(got_part, part.view(np.uint8).reshape(-1))
+    for it in range(5):  # 4 full batches and the tail
+        cnt, feat, nc = rig.gather(it)
+        ids = ids_list[it * 1237: it * 1237 + cnt]
+        assert cnt == len(ids)
+        ci = oracle_mod.find_feat(ids, lut)
+        ref = oracle_mod.gather(ids, ci, cap, [part], table)
+        np.testing.assert_array_equal(feat, ref.view(np.uint8).reshape(cnt, -1))
+        got_ci = rig.pool.read(L.BUF_CACHE_INDEX, 0, cnt, np.int32)
+        np.testing.assert_array_equal(got_ci, ci)
+        assert nc[2] == 0 and nc[3] == cnt
+    st = rig.cache.stats()
+    assert st["local_hits"] + st["misses"] == 5000 and st["peer_hits"] == 0
+    rig.close()
+
+
+def test_degree_order_matches(oracle_mod):
+    import torch
+    for seed, n, pairs in ((0, 5000, 60000), (1, 70000, 200000)):
+        indptr, _ = small_graph(n, pairs, seed)
+        d = torch.from_numpy(indptr).cuda()
+        out = torch.empty(n, dtype=torch.int32, device="cuda")
+        L.UnifiedCache.degree_order(0, d, out)
+        np.testing.assert_array_equal(out.cpu().numpy(), oracle_mod.degree_order(indptr))
+
+
+@pytest.mark.parametrize("kg", [2, 4, 8])
+def test_clique_striped_cache_on_one_device(oracle_mod, kg):
+    """The kg members of a clique emulated on one GPU: every member holds its stripe, the others'
+    stripes are reached through the partition pointer table exactly as peer memory would be."""
+    rng = np.random.default_rng(kg)
+    indptr, _ = small_graph(6000, 80000, 5)
+    n = len(indptr) - 1
+    table = rng.standard_normal((n, 128)).astype(np.float32)
+    ids_list = rng.integers(0, n, 3000).astype(np.int32)
+    cap = n // (kg * 2)  # half of the table cached over the clique
+    order = oracle_mod.degree_order(indptr)
+    rigs = [Rig(table, ids_list, 3000, capacity=cap, kg=kg, ki=ki, order=order) for ki in range(kg)]
+    for a in range(kg):
+        for b in range(kg):
+            if a != b:
+                rigs[a].cache.set_peer(b, rigs[b].cache.partition()[0])
+    lut = oracle_mod.static_cache_lut(order, cap, kg)
+    parts = [oracle_mod.static_cache_fill(order, cap, kg, ki, table) for ki in range(kg)]
+    ci = oracle_mod.find_feat(ids_list, lut)
+    ref = oracle_mod.gather(ids_list, ci, cap, parts, table)
+    for ki in (0, kg - 1):
+        cnt, feat, _ = rigs[ki].gather(0)
+        np.testing.assert_array_equal(feat.view(np.float32), ref)
+        np.testing.assert_array_equal(rigs[ki].pool.read(L.BUF_CACHE_INDEX, 0, cnt, np.int32), ci)
+        st = rigs[ki].cache.stats()
+        owner = ci[ci >= 0] // cap
+        assert st["local_hits"] == int((owner == ki).sum())
+        assert st["peer_hits"] == int((owner != ki).sum())
+        assert st["misses"] == int((ci < 0).sum())
+    for r in rigs:
+        r.close()
+
+
+@pytest.mark.parametrize("codec", [L.CODEC_INT8, L.CODEC_E4M3])
+@pytest.mark.parametrize("feat_len", [100, 128])
+def test_compressed_cache(oracle_mod, codec, feat_len):
+    rng = np.random.default_rng(codec * 10 + feat_len)
+    indptr, _ = small_graph(3000, 40000, 9)
+    n = len(indptr) - 1
+    table = rng.standard_normal((n, feat_len)).astype(np.float32)
+    table[5] = 0.0                      # an all-zero row: scale 0
+    table[6, 0] = 1e-30                 # tiny values next to a large one
+    table[6, 1] = 300.0
+    ids_list = rng.integers(0, n, 4000).astype(np.int32)
+    ids_list[:8] = np.arange(8)
+    cap = n // 2
+    order = np.arange(n, dtype=np.int32)  # rows 0..cap-1 cached
+    rig = Rig(table, ids_list, 4000, capacity=cap, codec=codec, order=order)
+    rq = oracle_mod.quant_row_bytes(feat_len)
+    part = oracle_mod.quant_rows(table[:cap], codec)
+    p, b = rig.cache.partition()
+    assert b == cap * rq
+    got_part = np.empty(b, np.uint8)
+    L._check(L.lib().legion_copy(got_part.ctypes.data_as(L.C.c_void_p), L.C.c_void_p(p), L.C.c_int64(b), L.C.c_int32(2)))
+    np.testing.assert_array_equal(got_part.reshape(cap, rq), part)
+    lut = oracle_mod.static_cache_lut(order, cap, 1)
+    ci = oracle_mod.find_feat(ids_list, lut)
+    ref = oracle_mod.gather_quant(ids_list, ci, cap, [part], table, codec)
+    cnt, feat, _ = rig.gather(0)
+    got = feat.view(np.float32).reshape(cnt, feat_len)
+    np.testing.assert_array_equal(got.view(np.uint32), ref.view(np.uint32))
+    # stated tolerance against the fp32 rows
+    exact = table[ids_list]
+    absmax = np.abs(exact).max(axis=1, keepdims=True)
+    if codec == L.CODEC_INT8:
+        tol = absmax / 254.0 + absmax * 2.0 ** -22 + 1e-30   # half a quantisation step + fp32 rounding
+    else:
+        tol = np.maximum(np.abs(exact) * 2.0 ** -4, absmax / 448.0 * 2.0 ** -10) * (1 + 1e-5) + 1e-30  # half ulp of e4m3
+    assert (np.abs(got - exact) <= tol).all()
+    hit = ci >= 0
+    np.testing.assert_array_equal(got[~hit], exact[~hit])  # misses are raw fp32 rows
+    rig.close()
+
+
+@pytest.mark.parametrize("ways,sets,feat_len", [(8, 64, 128), (4, 100, 32), (32, 7, 128), (1, 50, 4), (16, 33, 384)])
+def test_lru_cache_sequence(oracle_mod, ways, sets, feat_len):
+    """Hot-set workload of the reference's stale dynamic-cache smoke test (1000 nodes, 130 hot ids
+    hit 90% of the time): per-batch hit / miss sets, cache state and rows follow the host replay."""
+    rng = np.random.default_rng(ways)
+    n = 1000
+    table = rng.standard_normal((n, feat_len)).astype(np.float32)
+    hot = rng.integers(0, n, 130)
+    batches = []
+    for _ in range(30):
+        pick = np.where(rng.random(128) < 0.9, hot[rng.integers(0, 130, 128)], rng.integers(0, n, 128))
+        batches.append(np.unique(pick).astype(np.int32)[:128])  # ids of a batch are unique after dedup
+    bsz = 128
+    flat = np.full(30 * bsz, -1, np.int32)
+    for i, b in enumerate(batches):
+        flat[i * bsz: i * bsz + len(b)] = rng.permutation(b)
+    rig = Rig(table, flat, bsz, lru=(sets, ways))
+    ref = oracle_mod.LruCache(sets, ways)
+    rows_ref = np.zeros((sets * ways, feat_len), np.float32)
+    total_inserts = 0
+    for it in range(30):
+        ids = flat[it * bsz:(it + 1) * bsz]
+        clock = rig.cache.lru_clock()
+        assert clock == it + 1
+        cnt, feat, _ = rig.gather(it, pipe=it % 2)
+        assert cnt == bsz
+        ci = ref.lookup(ids, clock)
+        got_ci = rig.pool.read(L.BUF_CACHE_INDEX, 0, cnt, np.int64)
+        np.testing.assert_array_equal(got_ci, ci)
+        valid = ids >= 0
+        got = feat.view(np.float32).reshape(cnt, feat_len)
+        np.testing.assert_array_equal(got[valid], table[ids[valid]])
+        n_ins, slot = ref.insert(ids, ci, clock)
+        total_inserts += n_ins
+        for r in np.nonzero(slot >= 0)[0]:
+            rows_ref[slot[r]] = table[ids[r]]
+        k, s, rw = rig.cache.lru_state()
+        keys = np.empty(sets * ways, np.int32); stamps = np.empty(sets * ways, np.int32)
+        rows = np.empty((sets * ways, feat_len), np.float32)
+        for dst, src in ((keys, k), (stamps, s), (rows, rw)):
+            L._check(L.lib().legion_copy(dst.ctypes.data_as(L.C.c_void_p), L.C.c_void_p(src), L.C.c_int64(dst.nbytes),
+                                         L.C.c_int32(2)))
+        np.testing.assert_array_equal(keys, ref.keys)
+        np.testing.assert_array_equal(stamps, ref.stamps)
+        live = ref.keys >= 0
+        np.testing.assert_array_equal(rows[live], rows_ref[live])
+        np.testing.assert_array_equal(rows[live], table[ref.keys[live]])
+    st = rig.cache.stats()
+    assert st["lru_inserts"] == total_inserts
+    assert st["local_hits"] > 0 and st["misses"] > 0
+    rig.close()
+
+
+def test_gather_full_size_rows_roundtrip(oracle_mod):
+    """Paper100M-sized batch (2.3 M rows of 512 B, cache at 20%): every output row equals its
+    source row, checked through a per-row checksum computed on both sides."""
+    import torch
+    rng = np.random.default_rng(0)
+    n = 400000
+    table = rng.integers(-2**31, 2**31 - 1, (n, 128), dtype=np.int64).astype(np.int32)
+    ids_list = rng.integers(0, n, 2288000).astype(np.int32)
+    indptr, _ = small_graph(n, 2000000, 13)
+    order = oracle_mod.degree_order(indptr)
+    cap = n // 5
+    rig = Rig(table, ids_list, len(ids_list), capacity=cap, order=order)
+    cnt, feat, _ = rig.gather(0)
+    assert cnt == len(ids_list)
+    got_sum = feat.view(np.int32).reshape(cnt, 128).astype(np.int64).sum(axis=1)
+    ref_sum = table.astype(np.int64).sum(axis=1)[ids_list]
+    np.testing.assert_array_equal(got_sum, ref_sum)
+    sample = rng.integers(0, cnt, 5000)
+    np.testing.assert_array_equal(feat.view(np.int32).reshape(cnt, 128)[sample], table[ids_list[sample]])
+    st = rig.cache.stats()
+    lut = oracle_mod.static_cache_lut(order, cap, 1)
+    assert st["local_hits"] == int((lut[ids_list] >= 0).sum())
+    rig.close()

@@ -1,0 +1,223 @@
+"""Whole-batch paths: the two-stream runner with batches in flight, the host-buffer call, and the
+hand-off to a trainer process over CUDA IPC + semaphores."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import legion_ibp_b200 as L
+from conftest import ROOT, small_graph
+
+pytestmark = pytest.mark.gpu
+
+
+def _world(oracle_mod, n=5000, pairs=70000, feat_len=128, batch=96, fanout=(25, 10), cached_frac=0.3, seed=0):
+    import torch
+    rng = np.random.default_rng(seed)
+    indptr, indices = small_graph(n, pairs, seed)
+    table = rng.standard_normal((n, feat_len)).astype(np.float32)
+    train = rng.permutation(n)[: batch * 6 + 5].astype(np.int32)
+    labels = rng.integers(0, 47, len(train)).astype(np.int32)
+    w = dict(indptr=indptr, indices=indices, table=table, train=train, labels=labels, batch=batch,
+             fanout=list(fanout), n=n)
+    w["d_indptr"] = torch.from_numpy(indptr).cuda()
+    w["d_indices"] = torch.from_numpy(indices).cuda()
+    w["h_table"] = torch.from_numpy(table).pin_memory()
+    w["g"] = L.GraphStorage(0, w["d_indptr"], w["d_indices"])
+    w["f"] = L.FeatureStorage(0, n, feat_len * 4, w["h_table"])
+    w["d_train"] = torch.from_numpy(train).cuda()
+    w["d_labels"] = torch.from_numpy(labels).cuda()
+    w["f"].set_split(L.TRAINMODE, w["d_train"], w["d_labels"])
+    cap = int(n * cached_frac)
+    order = oracle_mod.degree_order(indptr)
+    w["cache"] = L.UnifiedCache(0, n, feat_len * 4, cap)
+    w["d_order"] = torch.from_numpy(order).cuda()
+    w["cache"].fill_static(w["d_order"], w["h_table"])
+    w["pool"] = L.MemoryPool(0, batch, list(fanout), feat_len * 4, 2)
+    w["pool"].set_rng(99, 64)
+    return w
+
+
+def _check_pipe(oracle_mod, w, pipe, it, global_batch):
+    pool = w["pool"]
+    ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], w["batch"], it, w["fanout"],
+                               global_batch, 99)
+    nc = pool.read(L.BUF_NODE_COUNTER, pipe, 16, np.int32)
+    ec = pool.read(L.BUF_EDGE_COUNTER, pipe, 16, np.int32)
+    np.testing.assert_array_equal(nc, ref["node_counter"])
+    np.testing.assert_array_equal(ec, ref["edge_counter"])
+    n_nodes, n_edges = len(ref["ids"]), len(ref["agg_src"])
+    np.testing.assert_array_equal(pool.read(L.BUF_IDS, pipe, n_nodes, np.int32), ref["ids"])
+    np.testing.assert_array_equal(pool.read(L.BUF_AGG_SRC, pipe, n_edges, np.int32), ref["agg_src"])
+    np.testing.assert_array_equal(pool.read(L.BUF_AGG_DST, pipe, n_edges, np.int32), ref["agg_dst"])
+    np.testing.assert_array_equal(pool.read(L.BUF_LABELS, pipe, int(nc[9]), np.int32), ref["labels"])
+    feat = pool.read(L.BUF_FEATURES, pipe, n_nodes * w["table"].shape[1], np.float32).reshape(n_nodes, -1)
+    np.testing.assert_array_equal(feat, w["table"][ref["ids"]])
+
+
+def test_runner_two_batches_in_flight(oracle_mod):
+    w = _world(oracle_mod)
+    r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], None)
+    # pairs of batches are enqueued back to back, then both pipes are checked
+    for it in range(0, 6, 2):
+        r.enqueue(it, L.TRAINMODE, it)
+        r.enqueue(it + 1, L.TRAINMODE, it + 1)
+        r.sync()
+        _check_pipe(oracle_mod, w, 0, it, it)
+        _check_pipe(oracle_mod, w, 1, it + 1, it + 1)
+        t = r.timing()
+        assert t["batches"] == 2 and t["batch_ms"] > 0 and t["gather_ms"] > 0
+    # many batches without a sync in between: only the last two survive in the pipes
+    for it in range(6):
+        r.enqueue(10 + it, L.TRAINMODE, it)
+    r.sync()
+    _check_pipe(oracle_mod, w, 0, 4, 14)
+    _check_pipe(oracle_mod, w, 1, 5, 15)
+    assert w["pool"].device_error() == 0
+    r.RunOnce(20, L.TRAINMODE, 2)
+    _check_pipe(oracle_mod, w, 0, 2, 20)
+    r.Finalize()
+
+
+def test_run_batch_host_buffers(oracle_mod):
+    w = _world(oracle_mod, seed=3)
+    pool = w["pool"]
+    ids = np.empty(pool.max_nodes, np.int32); lab = np.empty(w["batch"], np.int32)
+    src = np.empty(pool.max_edges, np.int32); dst = np.empty(pool.max_edges, np.int32)
+    nc = np.zeros(16, np.int32); ec = np.zeros(16, np.int32)
+    feat = np.empty((pool.max_nodes, w["table"].shape[1]), np.float32)
+    for it in range(3):
+        seeds = w["train"][it * w["batch"]:(it + 1) * w["batch"]]
+        labels = w["labels"][it * w["batch"]:(it + 1) * w["batch"]]
+        pool.set_batch(it, L.TRAINMODE, it % 2, 40 + it)
+        n_nodes, n_edges = L.run_batch_host(w["g"], w["f"], w["cache"], pool, 0, seeds, labels, ids, lab, src, dst,
+                                            nc, ec, feat)
+        ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], w["batch"], it, w["fanout"],
+                                   40 + it, 99)
+        assert n_nodes == len(ref["ids"]) and n_edges == len(ref["agg_src"])
+        np.testing.assert_array_equal(nc, ref["node_counter"])
+        np.testing.assert_array_equal(ec, ref["edge_counter"])
+        np.testing.assert_array_equal(ids[:n_nodes], ref["ids"])
+        np.testing.assert_array_equal(src[:n_edges], ref["agg_src"])
+        np.testing.assert_array_equal(dst[:n_edges], ref["agg_dst"])
+        np.testing.assert_array_equal(lab[:len(seeds)], ref["labels"])
+        np.testing.assert_array_equal(feat[:n_nodes], w["table"][ref["ids"]])
+
+
+CONSUMER = r'''
+import ctypes as C, sys, os, mmap, numpy as np
+sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+import conftest
+import legion_ibp_b200 as L
+# Trainer side, as training_backend/ipc_cuda_kernel.cu:37-106,177-243 does it: open the segment,
+# open the 7 handles of each pipe for device 0, post sem_r once per pipe, then per batch
+# wait sem_w, read both counters, slice ids / labels / edge lists / features, post sem_r.
+shm_name, n_batches, feat_len, out_path = sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
+lay = L.ipc_layout()
+lib = L.lib()
+fd = os.open("/dev/shm/" + shm_name, os.O_RDWR)
+seg = mmap.mmap(fd, lay["segment_bytes"])
+steps = np.frombuffer(seg, dtype=np.int32, count=3).copy()
+class Handle(C.Structure):
+    _fields_ = [("reserved", C.c_char * 64)]
+ptrs = []
+for pipe in range(2):
+    row = []
+    for k in range(7):
+        off = lay["handles_offset"] + ((0 * 2 + pipe) * 7 + k) * 64
+        h = Handle.from_buffer_copy(seg[off:off + 64])
+        p = C.c_void_p()
+        err = lib.legion_ipc_open_handle(C.byref(h), C.byref(p))
+        assert err == 0, ("legion_ipc_open_handle", err, pipe, k, lib.legion_last_error())
+        row.append(p.value)
+    ptrs.append(row)
+libc = C.CDLL("libc.so.6", use_errno=True)
+libc.sem_open.restype = C.c_void_p
+libc.sem_open.argtypes = [C.c_char_p, C.c_int, C.c_uint, C.c_uint]
+libc.sem_wait.argtypes = [C.c_void_p]; libc.sem_post.argtypes = [C.c_void_p]
+prefix = "" if shm_name == "simpleIPCshm" else shm_name + "_"
+semr = [libc.sem_open((prefix + "sem_r_0_%d" % i).encode(), os.O_CREAT | os.O_RDWR, 0o666, 0) for i in range(2)]
+semw = [libc.sem_open((prefix + "sem_w_0_%d" % i).encode(), os.O_CREAT | os.O_RDWR, 0o666, 0) for i in range(2)]
+for i in range(2):
+    libc.sem_post(semr[i])
+def d2h(ptr, count, dtype):
+    out = np.empty(count, dtype)
+    if out.nbytes:
+        assert lib.legion_copy(C.c_void_p(out.ctypes.data), C.c_void_p(ptr), C.c_int64(out.nbytes), C.c_int32(2)) == 0
+    return out
+res = {"steps": steps}
+pipe = 0
+for b in range(n_batches):
+    libc.sem_wait(semw[pipe])
+    nc = d2h(ptrs[pipe][5], 16, np.int32); ec = d2h(ptrs[pipe][6], 16, np.int32)
+    hops = int(nc[8]); n = int(nc[9 + hops])
+    res["nc%d" % b] = nc; res["ec%d" % b] = ec
+    res["ids%d" % b] = d2h(ptrs[pipe][0], n, np.int32)
+    res["feat%d" % b] = d2h(ptrs[pipe][1], n * feat_len, np.float32)
+    res["labels%d" % b] = d2h(ptrs[pipe][2], int(nc[9]), np.int32)
+    for i in range(hops, 0, -1):
+        eo, en = int(ec[12 + i]), int(ec[9 + i])
+        res["src%d_%d" % (b, i)] = d2h(ptrs[pipe][3] + 4 * eo, en, np.int32)
+        res["dst%d_%d" % (b, i)] = d2h(ptrs[pipe][4] + 4 * eo, en, np.int32)
+    res["blocks%d" % b] = np.array([[nc[9 + i], nc[9 + i - 1]] for i in range(hops, 0, -1)], np.int32)
+    libc.sem_post(semr[pipe])
+    pipe = (pipe + 1) % 2
+for row in ptrs:
+    for p in row:
+        lib.legion_ipc_close_handle(C.c_void_p(p))
+np.savez(out_path, **res)
+'''
+
+
+def test_ipc_handoff_to_trainer_process(oracle_mod, tmp_path):
+    """A second process plays the trainer extension; the server serves 5 batches through the
+    shared segment and the semaphores, with a bounded wait so that a lost trainer cannot hang it."""
+    w = _world(oracle_mod, seed=5)
+    shm = "legion_b200_test_%d" % os.getpid()
+    env = L.IPCEnv(1, shm)
+    env.Coordinate([len(w["train"])], [1], [1], w["batch"], 1)
+    steps = env.steps()
+    assert steps[0] == (len(w["train"]) - 1) // w["batch"]
+    env.publish_pool(w["pool"], 0)
+    script = tmp_path / "consumer.py"
+    script.write_text(CONSUMER)
+    out = tmp_path / "consumer.npz"
+    n_batches = 5
+    proc = subprocess.Popen([sys.executable, str(script), ROOT, shm, str(n_batches), str(w["table"].shape[1]), str(out)],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], env)
+    try:
+        r.serve(0, n_batches, timeout_ms=120000)
+        stdout, _ = proc.communicate(timeout=120)
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    assert proc.returncode == 0, stdout.decode()[-2000:]
+    got = np.load(out)
+    np.testing.assert_array_equal(got["steps"], steps)
+    for b in range(n_batches):
+        ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], w["batch"], b, w["fanout"], b, 99)
+        np.testing.assert_array_equal(got["nc%d" % b], ref["node_counter"])
+        np.testing.assert_array_equal(got["ec%d" % b], ref["edge_counter"])
+        np.testing.assert_array_equal(got["ids%d" % b], ref["ids"])
+        np.testing.assert_array_equal(got["labels%d" % b], ref["labels"])
+        np.testing.assert_array_equal(got["feat%d" % b].reshape(len(ref["ids"]), -1), w["table"][ref["ids"]])
+        ec = ref["edge_counter"]
+        for i in (2, 1):
+            lo, cnt = int(ec[12 + i]), int(ec[9 + i])
+            np.testing.assert_array_equal(got["src%d_%d" % (b, i)], ref["agg_src"][lo:lo + cnt])
+            np.testing.assert_array_equal(got["dst%d_%d" % (b, i)], ref["agg_dst"][lo:lo + cnt])
+        # DGL block convention: dst nodes are a prefix of src nodes
+        blocks = got["blocks%d" % b]
+        assert blocks[0][1] == blocks[1][0] and blocks[1][1] == w["batch"]
+        assert got["src%d_2" % b].max() < blocks[0][0] and got["dst%d_2" % b].max() < blocks[0][1]
+    # the trainer is gone now: the next wait must time out instead of blocking for ever
+    with pytest.raises(L.LegionError, match="did not release"):
+        r.RunOnce(n_batches, L.TRAINMODE, 0, timeout_ms=300)
+        r.RunOnce(n_batches + 1, L.TRAINMODE, 1, timeout_ms=300)
+        r.RunOnce(n_batches + 2, L.TRAINMODE, 1, timeout_ms=300)
+    r.Finalize()
+    env.Finalize()
+    assert not os.path.exists("/dev/shm/" + shm)
