@@ -30,6 +30,9 @@ CONFIGS = {
     # paper100M-shaped (configs[1]): the configuration the metric is quoted on
     "c2": dict(name="paper100M-shaped RMAT", n_nodes=111059956, n_pairs=900000000, feat_len=128, classes=172,
                train_frac=0.011, batch=8000, fanout=[25, 10], cache_frac=0.2),
+    # c2 scaled down to a few GB (inputs still larger than L2) for profiler captures
+    "mid": dict(name="mid RMAT (profiler capture)", n_nodes=8000000, n_pairs=64000000, feat_len=128, classes=172,
+                train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2),
     # reduced copy of c2 for checking the harness itself on small machines (never the default)
     "tiny": dict(name="tiny RMAT (harness check)", n_nodes=200000, n_pairs=2000000, feat_len=128, classes=172,
                  train_frac=0.2, batch=2000, fanout=[25, 10], cache_frac=0.2),
@@ -121,6 +124,24 @@ def host_table(cfg, shared_name=None, rank=0, world=1, pinned=True):
     return t
 
 
+def host_link_peak(table):
+    """GB/s of a plain pinned host -> device copy, the ceiling for zero-copy reads of the host table."""
+    import torch
+    n = min(table.numel(), 1 << 28)  # 1 GiB of fp32
+    src = table.view(-1)[:n]
+    dst = torch.empty(n, dtype=table.dtype, device="cuda")
+    for _ in range(2):
+        dst.copy_(src, non_blocking=True)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(3):
+        dst.copy_(src, non_blocking=True)
+    b.record()
+    torch.cuda.synchronize()
+    return 3 * n * 4 / (a.elapsed_time(b) * 1e-3) / 1e9
+
+
 def bounds(batch, fanout):
     nodes, edges = batch, 0
     for k in fanout:
@@ -196,6 +217,8 @@ def main():
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--cpu-sample-batches", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-only", action="store_true",
+                    help="set-up, warm-up and the timed steps only (for runs under a profiler); prints no bench line")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     if args.warmup < 3:
@@ -288,28 +311,52 @@ def main():
     ms_total = max_over_ranks(tm["batch_ms"])
     value = args.steps * world / (ms_total * 1e-3)
     assert pool.device_error() == 0, "device-side error flag set"
+    if args.profile_only:
+        if rank == 0:
+            print(json.dumps({"profile_only": True, "ms_per_step": ms_total / args.steps, "value": value}), flush=True)
+        runner.Finalize()
+        return
 
     # ---- roofline of the gather ---------------------------------------------------------------------
+    # Algorithmic bytes per gathered row: the row read from its source + the row written + 4 B id +
+    # 4 B lookup-table entry.  Rows served from GPU memory are moved by the hit kernel (HBM bound);
+    # rows that miss the cache are moved by the miss kernel over the host link, for which the hit
+    # kernel still reads id + table entry and writes a 4-byte list entry.
     d = {k: stats1[k] - stats0[k] for k in stats0}
-    rows = d["local_hits"] + d["peer_hits"] + d["misses"]
+    hits = d["local_hits"] + d["peer_hits"]
+    rows = hits + d["misses"]
     gather_launches = args.steps * (len(cfg["fanout"]) + 1)
-    gather_bytes = rows * (2 * row_bytes + 8)            # row read + row written + id + table entry
+    hit_bytes = hits * (2 * row_bytes + 8) + d["misses"] * 12
+    miss_bytes = d["misses"] * (2 * row_bytes + 8)
     gather_s = tm["gather_ms"] * 1e-3
+    miss_s = tm["miss_ms"] * 1e-3
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except Exception:
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-    achieved = gather_bytes / gather_s / 1e9 if gather_s > 0 else 0.0
-    roofline = {"bound": "hbm", "kernel": "gather_vec_kernel (lookup + gather, all sources)",
+    achieved = hit_bytes / gather_s / 1e9 if gather_s > 0 else 0.0
+    roofline = {"bound": "hbm", "kernel": "gather_vec_kernel (cache lookup + gather of rows held in GPU memory)",
                 "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s",
-                "traffic": None,
+                "peak_source": "of measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "of fallback 6650 GB/s",
+                "traffic": None, "launches": gather_launches,
                 "avg_launch_ms": tm["gather_ms"] / max(1, gather_launches),
                 "rows_per_batch": rows / args.steps,
-                "source_split": {k: d[k] / max(1, rows) for k in ("local_hits", "peer_hits", "misses")},
-                "host_link_GBps": d["misses"] * row_bytes / gather_s / 1e9 if gather_s > 0 else 0.0}
+                "source_split": {k: d[k] / max(1, rows) for k in ("local_hits", "peer_hits", "misses")}}
+    link_peak = host_link_peak(table)
+    link_achieved = d["misses"] * row_bytes / miss_s / 1e9 if miss_s > 0 else 0.0
+    roofline_host = {"bound": "host_link", "kernel": "gather_miss_kernel (zero-copy fetch of missed rows)",
+                     "achieved": link_achieved, "peak": link_peak, "unit": "GB/s",
+                     "frac": link_achieved / link_peak if link_peak else None,
+                     "peak_source": "pinned host->device cudaMemcpy of 1 GiB measured in this run",
+                     "avg_launch_ms": tm["miss_ms"] / max(1, gather_launches),
+                     "rows_per_batch": d["misses"] / args.steps, "algorithmic_bytes": miss_bytes}
+    # lower bound of the whole gather step: the slower of the HBM side and the host-link side
+    t_lb = max(hit_bytes / (hbm_peak * 1e9), d["misses"] * row_bytes / (link_peak * 1e9) if link_peak else 0.0)
+    roofline_path = {"lower_bound_ms_per_batch": t_lb / args.steps * 1e3,
+                     "gather_ms_per_batch": (tm["gather_ms"] + tm["miss_ms"]) / args.steps,
+                     "batch_ms": ms_total / args.steps}
 
     # ---- e2e: host buffers through the C ABI --------------------------------------------------------
     max_nodes, max_edges = bounds(cfg["batch"], cfg["fanout"])
@@ -367,8 +414,9 @@ def main():
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, world),
-                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + (hops + 1)),
-                "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + 2 * (hops + 1)),
+                "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
+                "cpu_baseline": cpu, "clocks": clocks,
                 "graph": {"nodes": n, "directed_edges": n_edges, "train_seeds_this_rank": int(mine.numel()),
                           "cache_rows_per_gpu": cap}, "setup_s": setup_s}
         print(json.dumps(line), flush=True)

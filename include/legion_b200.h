@@ -232,9 +232,10 @@ int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, int32_t mode
 int legion_runner_sync(LegionRunner *r);
 int legion_runner_current_pipe(LegionRunner *r);
 /* Device time of the batches enqueued between the last two legion_runner_sync calls, measured
- * with CUDA events on the runner's streams (ms); gather_ms is the sum over the feature gather
- * launches of that window. */
-int legion_runner_timing(LegionRunner *r, float *batch_ms, float *gather_ms, int32_t *n_batches);
+ * with CUDA events on the runner's streams (ms); gather_ms is the sum over the launches that
+ * gather cached rows (HBM / peer memory), miss_ms the sum over the launches that fetch missed rows
+ * from pinned host memory, each timed on the stream it runs on. */
+int legion_runner_timing(LegionRunner *r, float *batch_ms, float *gather_ms, float *miss_ms, int32_t *n_batches);
 /* The serving loop of GPUServer (engine/server.cu:39-44,124-143) for `count` batches starting at
  * first_global_batch, with mode and local batch number taken from the IPC environment. */
 int legion_runner_serve(LegionRunner *r, int32_t first_global_batch, int32_t count, int32_t timeout_ms);

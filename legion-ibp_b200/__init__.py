@@ -358,9 +358,9 @@ class Runner:
         return lib().legion_runner_current_pipe(self.h)
 
     def timing(self):
-        a, b, n = C.c_float(), C.c_float(), C.c_int32()
-        _check(lib().legion_runner_timing(self.h, C.byref(a), C.byref(b), C.byref(n)))
-        return dict(batch_ms=a.value, gather_ms=b.value, batches=n.value)
+        a, b, m, n = C.c_float(), C.c_float(), C.c_float(), C.c_int32()
+        _check(lib().legion_runner_timing(self.h, C.byref(a), C.byref(b), C.byref(m), C.byref(n)))
+        return dict(batch_ms=a.value, gather_ms=b.value, miss_ms=m.value, batches=n.value)
 
     def Finalize(self):
         if self.h:

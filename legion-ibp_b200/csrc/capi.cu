@@ -98,6 +98,7 @@ extern "C" int legion_pool_destroy(LegionPool *p)
     for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
         cudaFree(p->ids[i]); cudaFree(p->features[i]); cudaFree(p->labels[i]); cudaFree(p->agg_src[i]);
         cudaFree(p->agg_dst[i]); cudaFree(p->node_counter[i]); cudaFree(p->edge_counter[i]);
+        cudaFree(p->miss_rows[i]); cudaFree(p->miss_count[i]);
     }
     cudaFree(p->cache_index); cudaFree(p->src_global); cudaFree(p->map); cudaFree(p->node_rec);
     cudaFree(p->tile_sum); cudaFree(p->tile_off); cudaFree(p->eslot); cudaFree(p->erank);
@@ -176,6 +177,9 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
         if (e == cudaSuccess) e = cudaMemset(p->node_counter[i], 0, 64);
         if (e == cudaSuccess) e = cudaMemset(p->edge_counter[i], 0, 64);
         if (e == cudaSuccess) e = cudaMemset(p->ids[i], 0xFF, sizeof(int32_t) * pad_nodes);
+        if (e == cudaSuccess) e = dmalloc(&p->miss_rows[i], pad_nodes);
+        if (e == cudaSuccess) e = dmalloc(&p->miss_count[i], 8);
+        if (e == cudaSuccess) e = cudaMemset(p->miss_count[i], 0, 32);
     }
     if (e == cudaSuccess) e = dmalloc(&p->cache_index, pad_nodes);
     if (e == cudaSuccess) e = dmalloc(&p->src_global, pad_edges);

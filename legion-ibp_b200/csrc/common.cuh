@@ -139,6 +139,8 @@ struct LegionPool {
     int32_t *tile_sum, *tile_off;
     int32_t *eslot, *erank;
     int64_t *lru_victim;       // per node: way chosen for insertion, or -1
+    int32_t *miss_rows[LEGION_INTERBATCH_CON];   // per pipe: rows to fetch from the host table, by segment
+    int32_t *miss_count[LEGION_INTERBATCH_CON];  // per pipe: [0..3] entries per segment, [4] ticket
     int32_t *ctl;
     int32_t *seed_stage, *label_stage;  // device staging for host-provided seeds
     int32_t *h_stage;                   // pinned host staging
@@ -157,5 +159,7 @@ int launch_batch_generate(cudaStream_t s, LegionPool *p, const int32_t *all_ids,
 int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32_t fanout, int32_t hop,
                       int32_t op_id);
 int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
+int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
+int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
 int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c);
 }  // namespace legion

@@ -34,6 +34,8 @@ struct GatherParams {
     int32_t row_bytes;   // bytes of one output row
     int32_t slot_bytes;  // bytes of one cached row
     int32_t feature_len; // elements per row (quantised codecs)
+    int32_t *miss_rows;  // rows (positions in ids) whose source is the host table, per segment
+    int32_t *miss_count; // [segment] number of entries
 };
 
 __device__ __forceinline__ const uint8_t *shfl_ptr(const uint8_t *p, int src)
@@ -79,6 +81,23 @@ __device__ __forceinline__ const uint8_t *resolve(const GatherParams &p, int32_t
     return nullptr;
 }
 
+// Rows served by the host table are not copied by the hit kernels: the warp appends them to the
+// segment's miss list (one atomicAdd per warp, ranks by ballot) and clears their source pointer.
+// The list of segment h starts at the segment's node offset, so lists never overlap.
+__device__ __forceinline__ void defer_misses(int32_t *miss_rows, int32_t *miss_count, int seg, int off, int row,
+                                             int where, const uint8_t *&src, int lane)
+{
+    unsigned m = __ballot_sync(kFull, where == 2);
+    if (m == 0u) return;
+    int base = 0;
+    if (lane == 0) base = atomicAdd(&miss_count[seg], __popc(m));
+    base = __shfl_sync(kFull, base, 0);
+    if (where == 2) {
+        miss_rows[off + base + __popc(m & ((1u << lane) - 1u))] = row;
+        src = nullptr;
+    }
+}
+
 __device__ __forceinline__ void add_stats(unsigned long long *stats, int where, int lane)
 {
     unsigned m0 = __ballot_sync(kFull, where == 0);
@@ -109,6 +128,7 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
         const uint8_t *src = resolve(p, id, gidx, where);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
+        defer_misses(p.miss_rows, p.miss_count, p.op_id / LEGION_INTRABATCH_CON, off, off + r, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         uint8_t *dst_base = p.dst + (int64_t)(off + c * 32) * p.row_bytes;
         for (int j0 = 0; j0 < rows_here; j0 += R) {
@@ -158,6 +178,7 @@ __global__ void __launch_bounds__(256) gather_word_kernel(GatherParams p)
         const uint8_t *src = resolve(p, id, gidx, where);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
+        defer_misses(p.miss_rows, p.miss_count, p.op_id / LEGION_INTRABATCH_CON, off, off + r, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         uint32_t *dst_base = reinterpret_cast<uint32_t *>(p.dst + (int64_t)(off + c * 32) * p.row_bytes);
         for (int j = 0; j < rows_here; ++j) {
@@ -195,17 +216,14 @@ __global__ void __launch_bounds__(256) gather_quant_kernel(GatherParams p)
         const uint8_t *src = resolve(p, id, gidx, where);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
+        defer_misses(p.miss_rows, p.miss_count, p.op_id / LEGION_INTRABATCH_CON, off, off + r, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         float *dst_base = reinterpret_cast<float *>(p.dst + (int64_t)(off + c * 32) * p.row_bytes);
         for (int j = 0; j < rows_here; ++j) {
             const uint8_t *sp = shfl_ptr(src, j);
-            const int wj = __shfl_sync(kFull, where, j);
-            if (sp == nullptr) continue;
+            if (sp == nullptr) continue;  // invalid id, or a miss left to the miss kernel (raw fp32 row)
             float *drow = dst_base + (int64_t)j * f;
-            if (wj == 2) {  // raw fp32 row from the host table
-                const uint32_t *s32 = reinterpret_cast<const uint32_t *>(sp);
-                for (int w = lane; w < f; w += 32) __stcs(reinterpret_cast<uint32_t *>(drow) + w, s32[w]);
-            } else {
+            {
                 const float scale = *reinterpret_cast<const float *>(sp + f);  // f is a multiple of 4
                 const int groups = f >> 2;
                 for (int g = lane; g < groups; g += 32) {
@@ -218,6 +236,81 @@ __global__ void __launch_bounds__(256) gather_quant_kernel(GatherParams p)
                     __stcs(reinterpret_cast<float4 *>(drow) + g, o);
                 }
             }
+        }
+    }
+}
+
+// Rows that miss the cache: one warp copies `R` rows of the segment's miss list at a time from the
+// pinned host table by zero-copy loads (16 bytes per lane, so a 512-byte row is four 128-byte
+// reads on the host link).  Runs on its own stream with a grid of its own so that the link always
+// has thousands of reads in flight while the HBM-bound kernels carry on.  The last CTA clears
+// the segment's counter for the next batch.
+struct MissParams {
+    const int32_t *ids;
+    const int32_t *miss_rows;
+    int32_t *miss_count;
+    int32_t *ticket;
+    const int32_t *nc;
+    int32_t seg;
+    const uint8_t *host;
+    int64_t n_nodes;
+    uint8_t *dst;
+    int32_t row_bytes;
+};
+
+template <int R>
+__global__ void __launch_bounds__(256) gather_miss_kernel(MissParams p)
+{
+    __shared__ int s_last;
+    const int seg_off = p.seg > 0 ? p.nc[LEGION_INTRABATCH_CON * 3 + p.seg - 1] : 0;
+    const int n = p.miss_count[p.seg];
+    const int lane = threadIdx.x & 31;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    const int32_t *list = p.miss_rows + seg_off;
+    if ((p.row_bytes & 15) == 0) {
+        const int row_vec = p.row_bytes >> 4;
+        for (int m0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * R; m0 < n; m0 += n_warps * R) {
+            const uint8_t *sp[R];
+            uint8_t *dp[R];
+#pragma unroll
+            for (int jj = 0; jj < R; ++jj) {
+                sp[jj] = nullptr;
+                dp[jj] = nullptr;
+                if (m0 + jj < n) {
+                    int row = __ldg(&list[m0 + jj]);
+                    int32_t id = __ldg(&p.ids[row]);
+                    sp[jj] = p.host + ((int64_t)id % p.n_nodes) * (int64_t)p.row_bytes;
+                    dp[jj] = p.dst + (int64_t)row * p.row_bytes;
+                }
+            }
+            for (int q0 = 0; q0 < row_vec; q0 += 32) {
+                uint4 v[R];
+                const int idx = q0 + lane;
+#pragma unroll
+                for (int jj = 0; jj < R; ++jj)
+                    if (sp[jj] != nullptr && idx < row_vec) v[jj] = *reinterpret_cast<const uint4 *>(sp[jj] + idx * 16);
+#pragma unroll
+                for (int jj = 0; jj < R; ++jj)
+                    if (sp[jj] != nullptr && idx < row_vec) __stcs(reinterpret_cast<uint4 *>(dp[jj] + idx * 16), v[jj]);
+            }
+        }
+    } else {
+        const int row_words = p.row_bytes >> 2;
+        for (int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; m < n; m += n_warps) {
+            int row = __ldg(&list[m]);
+            int32_t id = __ldg(&p.ids[row]);
+            const uint32_t *sp = reinterpret_cast<const uint32_t *>(p.host + ((int64_t)id % p.n_nodes) * (int64_t)p.row_bytes);
+            uint32_t *dp = reinterpret_cast<uint32_t *>(p.dst + (int64_t)row * p.row_bytes);
+            for (int w = lane; w < row_words; w += 32) __stcs(&dp[w], sp[w]);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = atomicAdd(p.ticket, 1);
+        s_last = (t == (int)gridDim.x - 1);
+        if (s_last) {  // every CTA has read its count by now
+            p.miss_count[p.seg] = 0;
+            *p.ticket = 0;
         }
     }
 }
@@ -239,6 +332,8 @@ struct LruParams {
     int64_t *cache_index;
     unsigned long long *stats;
     int32_t row_bytes;
+    int32_t *miss_rows;
+    int32_t *miss_count;
 };
 
 template <int VPL, int R>
@@ -281,6 +376,7 @@ __global__ void __launch_bounds__(256) gather_lru_kernel(LruParams p)
             else if (p.host != nullptr) { where = 2; src = p.host + ((int64_t)my_id % p.n_nodes) * (int64_t)p.row_bytes; }
         }
         add_stats(p.stats, where, lane);
+        defer_misses(p.miss_rows, p.miss_count, p.op_id / LEGION_INTRABATCH_CON, off, off + r, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         uint8_t *dst_base = p.dst + (int64_t)(off + c * 32) * p.row_bytes;
         for (int j0 = 0; j0 < rows_here; j0 += R) {
@@ -394,20 +490,26 @@ static void launch_lru(int grid, cudaStream_t s, const LruParams &lp)
     gather_lru_kernel<VPL, R><<<grid, 256, 0, s>>>(lp);
 }
 
-int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id)
+static int segment_grid(const LegionPool *p, int32_t op_id, int64_t *rows_out)
 {
-    const int pipe = p->pipe;
     // worst-case rows of this segment: the seeds, or the new nodes of hop (op_id / 3)
     int hop = op_id / LEGION_INTRABATCH_CON;  // 0 = seeds
     int64_t rows = p->batch_size;
-    {
-        int64_t nodes = p->batch_size;
-        for (int h = 0; h < hop; ++h) { rows = nodes * p->fanout[h]; nodes += rows; }
-    }
+    int64_t nodes = p->batch_size;
+    for (int h = 0; h < hop; ++h) { rows = nodes * p->fanout[h]; nodes += rows; }
+    if (rows_out) *rows_out = rows;
     int64_t chunks = (rows + 31) / 32;
     int64_t g64 = (chunks + 7) / 8;
     int cap = p->sm_count * 8;
-    int grid = (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
+    return (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
+}
+
+// Lookup + gather of every row that is served from GPU memory; rows served by the host table
+// are listed for launch_gather_misses.
+int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id)
+{
+    const int pipe = p->pipe;
+    const int grid = segment_grid(p, op_id, nullptr);
     const int row_bytes = p->row_bytes_out;
 
     if (c != nullptr && c->kind == 1) {
@@ -428,6 +530,8 @@ int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id)
         lp.cache_index = p->cache_index;
         lp.stats = c->stats;
         lp.row_bytes = row_bytes;
+        lp.miss_rows = p->miss_rows[pipe];
+        lp.miss_count = p->miss_count[pipe];
         int vpl = (row_bytes / 16 + 31) / 32;
         LG_ARG(vpl >= 1 && vpl <= 4, "row size above 2048 bytes is not supported by the lru gather");
         switch (vpl) {
@@ -457,6 +561,8 @@ int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id)
     gp.row_bytes = row_bytes;
     gp.slot_bytes = c ? c->slot_bytes : row_bytes;
     gp.feature_len = row_bytes / 4;
+    gp.miss_rows = p->miss_rows[pipe];
+    gp.miss_count = p->miss_count[pipe];
 
     if (c != nullptr && c->codec != LEGION_CODEC_RAW) {
         LG_ARG(gp.feature_len % 4 == 0, "compressed rows need a feature length that is a multiple of 4");
@@ -479,6 +585,40 @@ int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id)
     }
     LG_LAUNCH_CHECK();
     return LEGION_OK;
+}
+
+// The rows the hit kernel listed, fetched from the pinned host table.  No-op without a host table.
+int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id)
+{
+    if (c == nullptr || c->host_table == nullptr) return LEGION_OK;
+    const int pipe = p->pipe;
+    MissParams mp;
+    mp.ids = p->ids[pipe];
+    mp.miss_rows = p->miss_rows[pipe];
+    mp.miss_count = p->miss_count[pipe];
+    mp.ticket = p->miss_count[pipe] + 4;
+    mp.nc = p->node_counter[pipe];
+    mp.seg = op_id / LEGION_INTRABATCH_CON;
+    mp.host = (const uint8_t *)c->host_table;
+    mp.n_nodes = c->n_nodes;
+    mp.dst = (uint8_t *)p->features[pipe];
+    mp.row_bytes = p->row_bytes_out;
+    int64_t rows = 0;
+    segment_grid(p, op_id, &rows);
+    // 4 rows per warp and pass; at most two CTAs per SM so that HBM-bound kernels keep their share
+    int64_t g64 = (rows + 31) / 32;
+    int cap = p->sm_count * 2;
+    int grid = (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
+    gather_miss_kernel<4><<<grid, 256, 0, s>>>(mp);
+    LG_LAUNCH_CHECK();
+    return LEGION_OK;
+}
+
+int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id)
+{
+    int rc = launch_gather_hits(s, p, c, op_id);
+    if (rc != LEGION_OK) return rc;
+    return launch_gather_misses(s, p, c, op_id);
 }
 
 int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c)

@@ -1,0 +1,142 @@
+"""One rank of the sampling server: the Server interface of the reference
+(sampling_server/src/engine/server.h:5-21: Initialize / PreSc / Run / Finalize) for one process per GPU.
+
+The reference runs one host thread per GPU inside one process (engine/server.cu:46-170) and shares
+raw pointers between the threads; here every GPU has its own process, so the two things the threads
+shared travel through ``torch.distributed`` once at start-up:
+  * the per-GPU seed counts that the step arithmetic needs (IPCEnv::Coordinate), and
+  * the CUDA IPC handles of the cache partitions, from which each rank builds the pointer table that
+    its gather kernel reads peers through (plain loads over NVLink; no collective on the data path).
+"""
+import ctypes as C
+
+import torch
+
+from . import (CODEC_RAW, TRAINMODE, VALIDMODE, TESTMODE, FeatureStorage, GraphStorage, IPCEnv, LegionError,
+               MemoryPool, Runner, UnifiedCache, lib)
+
+
+def split_seeds(ids, world, rank):
+    """Seeds of one GPU: ``id % ngpu`` (storage/storage_management.cu:214-250, no partition file)."""
+    return ids[(ids % world) == rank].contiguous()
+
+
+def plan_cache_rows(n_nodes, per_gpu_rows, world):
+    """Rows each clique member holds: the requested budget, capped so that the clique never holds
+    more rows than the table has (rank t lives on GPU t % world at row t // world)."""
+    per_gpu_rows = max(0, min(int(per_gpu_rows), int(n_nodes)))
+    if per_gpu_rows * world >= n_nodes:
+        per_gpu_rows = (n_nodes + world - 1) // world
+    return per_gpu_rows
+
+
+def all_gather_ints(values, dist, device="cpu"):
+    """[[values of rank 0], [values of rank 1], ...]; works with gloo (cpu) and nccl (cuda)."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return [list(values)]
+    t = torch.tensor(list(values), dtype=torch.int64, device=device)
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t)
+    return [[int(v) for v in o.cpu().tolist()] for o in out]
+
+
+def all_gather_bytes(blob, dist, device="cpu"):
+    """Every rank's fixed-size byte string, in rank order."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return [bytes(blob)]
+    t = torch.tensor(list(blob), dtype=torch.uint8, device=device)
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t)
+    return [bytes(o.cpu().tolist()) for o in out]
+
+
+def exchange_partitions(cache, rank, world, dist, device="cuda"):
+    """Publishes this rank's cache partition and maps the peers' (the pointer table
+    d_float_feature_cache_ptr_ of cache/cache.cu:601-622, across processes)."""
+    ptr, _ = cache.partition()
+    handle = (C.c_char * 64)()
+    if ptr:
+        rc = lib().legion_ipc_get_handle(C.c_void_p(ptr), handle)
+        if rc != 0:
+            raise LegionError(lib().legion_last_error().decode())
+    blobs = all_gather_bytes(handle.raw, dist, device)
+    for k in range(world):
+        if k == rank or not ptr:
+            continue
+        p = C.c_void_p()
+        rc = lib().legion_ipc_open_handle(blobs[k], C.byref(p))
+        if rc != 0:
+            raise LegionError(lib().legion_last_error().decode())
+        cache.set_peer(k, p.value)
+    return blobs
+
+
+class Server:
+    """Builds and runs one rank.  Arguments mirror what GPUServer::Initialize pulls out of
+    ``meta_config`` and argv (engine/server.cu:48-92, storage/storage_management.cu:33-68)."""
+
+    def __init__(self, dist=None):
+        self.dist = dist
+        self.rank = dist.get_rank() if dist is not None and dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist is not None and dist.is_initialized() else 1
+        self.runner = None
+
+    def Initialize(self, dev_id, indptr, indices, host_table, row_bytes, train_ids, labels, batch_size, fanout,
+                   cache_rows_per_gpu, valid_ids=None, test_ids=None, epochs=1, codec=CODEC_RAW, use_ipc=False,
+                   shm_name=None, rng_seed=0):
+        self.dev_id = dev_id
+        n = int(indptr.numel()) - 1
+        self.graph = GraphStorage(dev_id, indptr, indices)
+        self.feature = FeatureStorage(dev_id, n, row_bytes, host_table)
+        self.splits = {}
+        counts = []
+        for mode, ids in ((TRAINMODE, train_ids), (VALIDMODE, valid_ids), (TESTMODE, test_ids)):
+            if ids is None or ids.numel() == 0:
+                counts.append(1)
+                continue
+            mine = split_seeds(ids, self.world, self.rank)
+            mine_labels = labels[mine.long()].contiguous()
+            self.feature.set_split(mode, mine, mine_labels)
+            self.splits[mode] = (mine, mine_labels)
+            counts.append(int(mine.numel()))
+        dev = "cuda" if indptr.is_cuda else "cpu"
+        per_rank = all_gather_ints(counts, self.dist, dev)
+        self.env = None
+        if use_ipc:
+            self.env = IPCEnv(self.world, shm_name)
+            self.env.Coordinate([c[0] for c in per_rank], [c[1] for c in per_rank], [c[2] for c in per_rank],
+                                batch_size, epochs)
+        self.train_step = (min(c[0] for c in per_rank) - 1) // batch_size
+        cap = plan_cache_rows(n, cache_rows_per_gpu, self.world)
+        self.cache = UnifiedCache(dev_id, n, row_bytes, cap, kg=self.world, ki=self.rank, codec=codec)
+        return cap
+
+    def PreSc(self, indptr, host_table):
+        """Cache build.  The reference presamples an epoch to rank nodes by hotness
+        (engine/server.cu:94-122, cache/cache.cu:354-447); here the ranking is by degree."""
+        n = int(indptr.numel()) - 1
+        order = torch.empty(n, dtype=torch.int32, device=indptr.device)
+        UnifiedCache.degree_order(self.dev_id, indptr, order)
+        self.cache.fill_static(order, host_table)
+        del order
+        if self.world > 1:
+            exchange_partitions(self.cache, self.rank, self.world, self.dist)
+        print("System is ready for serving", flush=True)  # engine/server.cu:121, scripts/wait_file.sh:3
+
+    def make_runner(self, batch_size, fanout, row_bytes_out, rng_seed=0):
+        self.pool = MemoryPool(self.dev_id, batch_size, fanout, row_bytes_out, 2)
+        self.pool.set_rng(rng_seed, 64)
+        if self.env is not None:
+            self.env.publish_pool(self.pool, self.dev_id)
+        self.runner = Runner(self.dev_id, self.graph, self.feature, self.cache, self.pool, self.env)
+        return self.runner
+
+    def Run(self, timeout_ms=-1):
+        """Serves every batch of the schedule (engine/server.cu:124-143)."""
+        self.runner.serve(0, self.env.GetMaxStep(), timeout_ms)
+
+    def Finalize(self):
+        if self.runner is not None:
+            self.runner.Finalize()
+        if self.env is not None:
+            self.env.Finalize()
