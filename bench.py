@@ -295,7 +295,6 @@ def main():
         runner.enqueue(step, L.TRAINMODE, step % n_iters)
         step += 1
     runner.sync()
-    stats0 = cache.stats()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -306,11 +305,28 @@ def main():
     runner.sync()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
-    tm = runner.timing()
-    stats1 = cache.stats()
-    ms_total = max_over_ranks(tm["batch_ms"])
+    ms_total = max_over_ranks(runner.timing()["batch_ms"])
     value = args.steps * world / (ms_total * 1e-3)
     assert pool.device_error() == 0, "device-side error flag set"
+
+    # ---- kernel durations: the same graph replay with CUDA events around the gather launches, one
+    # batch at a time (the events of a pipe's graph are overwritten by its next launch) ----------------
+    runner.set_options(use_graph=True, time_kernels=True)
+    for _ in range(2):
+        runner.enqueue(step, L.TRAINMODE, step % n_iters)
+        step += 1
+    runner.sync()
+    stats0 = cache.stats()
+    tm = {"gather_ms": 0.0, "miss_ms": 0.0, "timed": 0}
+    for _ in range(args.steps):
+        runner.enqueue(step, L.TRAINMODE, step % n_iters)
+        step += 1
+        runner.sync()
+        t1 = runner.timing()
+        for k in tm:
+            tm[k] += t1[k]
+    stats1 = cache.stats()
+    runner.set_options(use_graph=True, time_kernels=False)
     if args.profile_only:
         if rank == 0:
             print(json.dumps({"profile_only": True, "ms_per_step": ms_total / args.steps, "value": value}), flush=True)
@@ -325,7 +341,8 @@ def main():
     d = {k: stats1[k] - stats0[k] for k in stats0}
     hits = d["local_hits"] + d["peer_hits"]
     rows = hits + d["misses"]
-    gather_launches = args.steps * (len(cfg["fanout"]) + 1)
+    gather_launches = tm["timed"] * (len(cfg["fanout"]) + 1)
+    timed_frac = tm["timed"] / float(args.steps)
     hit_bytes = hits * (2 * row_bytes + 8) + d["misses"] * 12
     miss_bytes = d["misses"] * (2 * row_bytes + 8)
     gather_s = tm["gather_ms"] * 1e-3
@@ -343,7 +360,9 @@ def main():
                 "traffic": None, "launches": gather_launches,
                 "avg_launch_ms": tm["gather_ms"] / max(1, gather_launches),
                 "rows_per_batch": rows / args.steps,
-                "source_split": {k: d[k] / max(1, rows) for k in ("local_hits", "peer_hits", "misses")}}
+                "source_split": {k: d[k] / max(1, rows) for k in ("local_hits", "peer_hits", "misses")},
+                "measured": "CUDA events around each launch on its stream, graph replay, %d batches run one at a "
+                            "time right after the timed region" % tm["timed"]}
     link_peak = host_link_peak(table)
     link_achieved = d["misses"] * row_bytes / miss_s / 1e9 if miss_s > 0 else 0.0
     roofline_host = {"bound": "host_link", "kernel": "gather_miss_kernel (zero-copy fetch of missed rows)",
@@ -355,7 +374,7 @@ def main():
     # lower bound of the whole gather step: the slower of the HBM side and the host-link side
     t_lb = max(hit_bytes / (hbm_peak * 1e9), d["misses"] * row_bytes / (link_peak * 1e9) if link_peak else 0.0)
     roofline_path = {"lower_bound_ms_per_batch": t_lb / args.steps * 1e3,
-                     "gather_ms_per_batch": (tm["gather_ms"] + tm["miss_ms"]) / args.steps,
+                     "gather_ms_per_batch": (tm["gather_ms"] + tm["miss_ms"]) / max(1, tm["timed"]),
                      "batch_ms": ms_total / args.steps}
 
     # ---- e2e: host buffers through the C ABI --------------------------------------------------------
@@ -369,28 +388,38 @@ def main():
     nc_o, ec_o = np.zeros(16, np.int32), np.zeros(16, np.int32)
     b = cfg["batch"]
 
-    def host_step(i):
+    def submit(i):
         it = i % n_iters
-        pool.set_batch(it, L.TRAINMODE, i % 2, i)
-        return L.run_batch_host(g, fs, cache, pool, dev, seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b],
-                                ids_o, lab_o, src_o, dst_o, nc_o, ec_o, None)
+        runner.submit_host(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i)
 
-    for i in range(3):
-        host_step(i)
+    def collect():
+        return runner.collect_host(ids_o, lab_o, src_o, dst_o, nc_o, ec_o, None)
+
+    # two batches in flight: the copies of batch k overlap the device work of batch k+1
+    submit(0)
+    for i in range(1, 4):
+        submit(i)
+        collect()
+    collect()
     barrier()
     t0 = time.perf_counter()
     d2h = 0
-    for i in range(args.steps):
-        nn, ne = host_step(100 + i)
+    submit(100)
+    for i in range(1, args.steps):
+        submit(100 + i)
+        nn, ne = collect()
         d2h += 4 * nn + 8 * ne + 4 * b + 128
+    nn, ne = collect()
+    d2h += 4 * nn + 8 * ne + 4 * b + 128
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
     e2e = {"value": args.steps * world / e2e_s, "unit": "batches/s", "h2d_bytes_per_step": 8 * b,
            "d2h_bytes_per_step": d2h // args.steps,
-           "note": "seeds+labels copied in, ids/labels/edge lists/counters copied out; gathered rows stay in the "
-                   "device hand-off buffer where the trainer reads them; missed rows cross the host link inside "
-                   "the gather"}
+           "api": "legion_runner_submit_host / legion_runner_collect_host, two batches in flight",
+           "note": "seeds+labels copied in from host memory, ids/labels/edge lists/counters copied out to host "
+                   "memory every step; gathered rows stay in the device hand-off buffer where the trainer reads "
+                   "them; missed rows cross the host link inside the gather"}
 
     # ---- CPU baseline on this box's cores (rank 0, N=1 only) ----------------------------------------
     cpu = None

@@ -132,8 +132,8 @@ int legion_pool_destroy(LegionPool *p);
 #define LEGION_BUF_AGG_DST 4
 #define LEGION_BUF_NODE_COUNTER 5
 #define LEGION_BUF_EDGE_COUNTER 6
-#define LEGION_BUF_CACHE_INDEX 7  /* cache_search_buffer, engine/server.cu:238 (shared by pipes) */
-#define LEGION_BUF_SRC_GLOBAL 8   /* agg_src_ids, engine/server.cu:244 (shared by pipes) */
+#define LEGION_BUF_CACHE_INDEX 7  /* cache_search_buffer, engine/server.cu:238 (scratch, one per pipe here) */
+#define LEGION_BUF_SRC_GLOBAL 8   /* agg_src_ids, engine/server.cu:244 (scratch, one per pipe here) */
 int legion_pool_buffer(LegionPool *p, int32_t which, int32_t pipe, void **ptr, int64_t *bytes);
 int legion_pool_limits(LegionPool *p, int64_t *max_nodes, int64_t *max_edges);
 /* SetIter / SetCurrentMode / SetCurrentPipe (engine/memorypool.cuh) plus the number of the batch
@@ -230,12 +230,29 @@ int legion_runner_run_once(LegionRunner *r, int32_t global_batch_id, int32_t mod
  * legion_runner_sync waits for everything enqueued. */
 int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, int32_t mode, int32_t local_batch_id);
 int legion_runner_sync(LegionRunner *r);
+/* The batch interface with HOST buffers and batches in flight: submit copies `n_seeds` seeds and
+ * labels in from host memory and starts the batch; collect waits for the oldest submitted batch and
+ * copies ids, labels, both edge lists and both counter arrays out (features_out may be NULL: the
+ * gathered rows then stay in the device hand-off buffer, where the trainer reads them,
+ * training_backend/ipc_cuda_kernel.cu:205-211).  At most `pipes` batches may be in flight;
+ * LEGION_E_STATE otherwise.  Pinned output buffers make the copies asynchronous. */
+int legion_runner_submit_host(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                              int32_t global_batch_id);
+int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
+                               int32_t *agg_dst_out, int32_t node_counter_out[16], int32_t edge_counter_out[16],
+                               void *features_out);
 int legion_runner_current_pipe(LegionRunner *r);
+/* use_graph (default 1): replay every batch as one CUDA graph per pipe instead of ~25 launches and
+ * ~20 event calls from the host.  time_kernels (default 0): bracket the gather launches with CUDA
+ * events on the streams they run on.  Call between batches; waits for the device. */
+int legion_runner_set_options(LegionRunner *r, int32_t use_graph, int32_t time_kernels);
 /* Device time of the batches enqueued between the last two legion_runner_sync calls, measured
- * with CUDA events on the runner's streams (ms); gather_ms is the sum over the launches that
- * gather cached rows (HBM / peer memory), miss_ms the sum over the launches that fetch missed rows
- * from pinned host memory, each timed on the stream it runs on. */
-int legion_runner_timing(LegionRunner *r, float *batch_ms, float *gather_ms, float *miss_ms, int32_t *n_batches);
+ * with CUDA events (ms).  With time_kernels: gather_ms is the sum over the launches that gather
+ * cached rows (HBM / peer memory), miss_ms the sum over the launches that fetch missed rows from
+ * pinned host memory, over n_timed batches (all batches of the window when launching one by one;
+ * the last batch of each pipe when replaying graphs, whose events are overwritten per launch). */
+int legion_runner_timing(LegionRunner *r, float *batch_ms, float *gather_ms, float *miss_ms, int32_t *n_batches,
+                         int32_t *n_timed);
 /* The serving loop of GPUServer (engine/server.cu:39-44,124-143) for `count` batches starting at
  * first_global_batch, with mode and local batch number taken from the IPC environment. */
 int legion_runner_serve(LegionRunner *r, int32_t first_global_batch, int32_t count, int32_t timeout_ms);

@@ -350,6 +350,18 @@ class Runner:
     def sync(self):
         _check(lib().legion_runner_sync(self.h))
 
+    def submit_host(self, seeds, labels, global_batch_id):
+        """Start one batch from host seed / label arrays (numpy int32)."""
+        _check(lib().legion_runner_submit_host(self.h, _ptr(seeds), _ptr(labels), C.c_int32(len(seeds)),
+                                               C.c_int32(global_batch_id)))
+
+    def collect_host(self, ids_out, labels_out, agg_src_out, agg_dst_out, nc_out, ec_out, features_out=None):
+        """Wait for the oldest submitted batch and copy it out; returns (n_nodes, n_edges)."""
+        _check(lib().legion_runner_collect_host(self.h, _ptr(ids_out), _ptr(labels_out), _ptr(agg_src_out),
+                                                _ptr(agg_dst_out), _ptr(nc_out), _ptr(ec_out), _ptr(features_out)))
+        hops = int(nc_out[INTRABATCH_CON * 3 - 1])
+        return int(nc_out[INTRABATCH_CON * 3 + hops]), int(ec_out[0] + ec_out[1])
+
     def serve(self, first_global_batch, count, timeout_ms=-1):
         _check(lib().legion_runner_serve(self.h, C.c_int32(first_global_batch), C.c_int32(count),
                                          C.c_int32(timeout_ms)))
@@ -358,9 +370,12 @@ class Runner:
         return lib().legion_runner_current_pipe(self.h)
 
     def timing(self):
-        a, b, m, n = C.c_float(), C.c_float(), C.c_float(), C.c_int32()
-        _check(lib().legion_runner_timing(self.h, C.byref(a), C.byref(b), C.byref(m), C.byref(n)))
-        return dict(batch_ms=a.value, gather_ms=b.value, miss_ms=m.value, batches=n.value)
+        a, b, m, n, t = C.c_float(), C.c_float(), C.c_float(), C.c_int32(), C.c_int32()
+        _check(lib().legion_runner_timing(self.h, C.byref(a), C.byref(b), C.byref(m), C.byref(n), C.byref(t)))
+        return dict(batch_ms=a.value, gather_ms=b.value, miss_ms=m.value, batches=n.value, timed=t.value)
+
+    def set_options(self, use_graph=True, time_kernels=False):
+        _check(lib().legion_runner_set_options(self.h, C.c_int32(int(use_graph)), C.c_int32(int(time_kernels))))
 
     def Finalize(self):
         if self.h:

@@ -99,11 +99,12 @@ extern "C" int legion_pool_destroy(LegionPool *p)
         cudaFree(p->ids[i]); cudaFree(p->features[i]); cudaFree(p->labels[i]); cudaFree(p->agg_src[i]);
         cudaFree(p->agg_dst[i]); cudaFree(p->node_counter[i]); cudaFree(p->edge_counter[i]);
         cudaFree(p->miss_rows[i]); cudaFree(p->miss_count[i]);
+        cudaFree(p->cache_index[i]); cudaFree(p->src_global[i]); cudaFree(p->map[i]); cudaFree(p->node_rec[i]);
+        cudaFree(p->tile_sum[i]); cudaFree(p->tile_off[i]); cudaFree(p->eslot[i]); cudaFree(p->erank[i]);
+        cudaFree(p->lru_victim[i]); cudaFree(p->ctl[i]); cudaFree(p->bctl[i]);
+        cudaFree(p->seed_stage[i]); cudaFree(p->label_stage[i]);
+        if (p->h_stage[i]) cudaFreeHost(p->h_stage[i]);
     }
-    cudaFree(p->cache_index); cudaFree(p->src_global); cudaFree(p->map); cudaFree(p->node_rec);
-    cudaFree(p->tile_sum); cudaFree(p->tile_off); cudaFree(p->eslot); cudaFree(p->erank);
-    cudaFree(p->lru_victim); cudaFree(p->ctl); cudaFree(p->seed_stage); cudaFree(p->label_stage);
-    if (p->h_stage) cudaFreeHost(p->h_stage);
     delete p;
     return LEGION_OK;
 }
@@ -180,22 +181,25 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
         if (e == cudaSuccess) e = dmalloc(&p->miss_rows[i], pad_nodes);
         if (e == cudaSuccess) e = dmalloc(&p->miss_count[i], 8);
         if (e == cudaSuccess) e = cudaMemset(p->miss_count[i], 0, 32);
+        if (e == cudaSuccess) e = dmalloc(&p->cache_index[i], pad_nodes);
+        if (e == cudaSuccess) e = dmalloc(&p->src_global[i], pad_edges);
+        if (e == cudaSuccess) e = dmalloc(&p->map[i], (int64_t)cap);
+        if (e == cudaSuccess) e = dmalloc(&p->node_rec[i], pad_nodes);
+        if (e == cudaSuccess) e = dmalloc(&p->tile_sum[i], tiles);
+        if (e == cudaSuccess) e = dmalloc(&p->tile_off[i], tiles);
+        if (e == cudaSuccess) e = dmalloc(&p->eslot[i], pad_hop_edges);
+        if (e == cudaSuccess) e = dmalloc(&p->erank[i], pad_hop_edges);
+        if (e == cudaSuccess) e = dmalloc(&p->lru_victim[i], pad_nodes);
+        if (e == cudaSuccess) e = dmalloc(&p->ctl[i], CTL_WORDS);
+        if (e == cudaSuccess) e = dmalloc(&p->bctl[i], 1);
+        if (e == cudaSuccess) e = cudaMemset(p->ctl[i], 0, sizeof(int32_t) * CTL_WORDS);
+        if (e == cudaSuccess) e = cudaMemset(p->bctl[i], 0, sizeof(BatchCtl));
+        if (e == cudaSuccess) e = cudaMemset(p->eslot[i], 0, sizeof(int32_t) * pad_hop_edges);
+        if (e == cudaSuccess) e = dmalloc(&p->seed_stage[i], batch_size);
+        if (e == cudaSuccess) e = dmalloc(&p->label_stage[i], batch_size);
+        if (e == cudaSuccess)
+            e = cudaMallocHost(reinterpret_cast<void **>(&p->h_stage[i]), sizeof(int32_t) * (2 * (size_t)batch_size + 32));
     }
-    if (e == cudaSuccess) e = dmalloc(&p->cache_index, pad_nodes);
-    if (e == cudaSuccess) e = dmalloc(&p->src_global, pad_edges);
-    if (e == cudaSuccess) e = dmalloc(&p->map, (int64_t)cap);
-    if (e == cudaSuccess) e = dmalloc(&p->node_rec, pad_nodes);
-    if (e == cudaSuccess) e = dmalloc(&p->tile_sum, tiles);
-    if (e == cudaSuccess) e = dmalloc(&p->tile_off, tiles);
-    if (e == cudaSuccess) e = dmalloc(&p->eslot, pad_hop_edges);
-    if (e == cudaSuccess) e = dmalloc(&p->erank, pad_hop_edges);
-    if (e == cudaSuccess) e = dmalloc(&p->lru_victim, pad_nodes);
-    if (e == cudaSuccess) e = dmalloc(&p->ctl, CTL_WORDS);
-    if (e == cudaSuccess) e = dmalloc(&p->seed_stage, batch_size);
-    if (e == cudaSuccess) e = dmalloc(&p->label_stage, batch_size);
-    if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void **>(&p->h_stage), sizeof(int32_t) * (2 * (size_t)batch_size + 32));
-    if (e == cudaSuccess) e = cudaMemset(p->ctl, 0, sizeof(int32_t) * CTL_WORDS);
-    if (e == cudaSuccess) e = cudaMemset(p->eslot, 0, sizeof(int32_t) * pad_hop_edges);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
         set_error("legion_pool_create: %s", cudaGetErrorString(e));
@@ -220,8 +224,8 @@ extern "C" int legion_pool_buffer(LegionPool *p, int32_t which, int32_t pipe, vo
     case LEGION_BUF_AGG_DST: q = p->agg_dst[pipe]; b = p->max_edges * 4; break;
     case LEGION_BUF_NODE_COUNTER: q = p->node_counter[pipe]; b = 64; break;
     case LEGION_BUF_EDGE_COUNTER: q = p->edge_counter[pipe]; b = 64; break;
-    case LEGION_BUF_CACHE_INDEX: q = p->cache_index; b = p->max_nodes * 8; break;
-    case LEGION_BUF_SRC_GLOBAL: q = p->src_global; b = p->max_edges * 4; break;
+    case LEGION_BUF_CACHE_INDEX: q = p->cache_index[pipe]; b = p->max_nodes * 8; break;
+    case LEGION_BUF_SRC_GLOBAL: q = p->src_global[pipe]; b = p->max_edges * 4; break;
     default: LG_ARG(false, "unknown buffer");
     }
     *ptr = q;
@@ -264,9 +268,14 @@ extern "C" int legion_pool_device_error(LegionPool *p, void *stream, int32_t *er
 {
     LG_ARG(p != nullptr && err != nullptr, "NULL pointer");
     LG_CUDA(cudaSetDevice(p->dev_id));
-    LG_CUDA(cudaMemcpyAsync(err, p->ctl + CTL_ERROR, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
-    LG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    if (reset && *err != 0) LG_CUDA(cudaMemsetAsync(p->ctl + CTL_ERROR, 0, 4, (cudaStream_t)stream));
+    *err = 0;
+    for (int i = 0; i < p->pipes; ++i) {
+        int32_t e = 0;
+        LG_CUDA(cudaMemcpyAsync(&e, p->ctl[i] + CTL_ERROR, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+        LG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+        if (e != 0 && *err == 0) *err = e;
+        if (reset && e != 0) LG_CUDA(cudaMemsetAsync(p->ctl[i] + CTL_ERROR, 0, 4, (cudaStream_t)stream));
+    }
     return LEGION_OK;
 }
 
@@ -276,7 +285,7 @@ extern "C" int legion_batch_generate(void *stream, LegionFeatures *feature, Legi
                                      int32_t batch_size, int32_t counter, int32_t part_id, int32_t dev_id,
                                      int32_t mode, int32_t is_presc, int32_t hop_num, int32_t dyn_cache)
 {
-    (void)cache; (void)part_id; (void)is_presc; (void)dyn_cache;
+    (void)part_id; (void)is_presc; (void)dyn_cache;
     LG_ARG(feature != nullptr && pool != nullptr, "NULL handle");
     LG_ARG(mode >= 0 && mode <= 2, "invalid mode");
     LG_ARG(batch_size > 0 && batch_size <= pool->batch_size, "batch_size above the pool's");
@@ -291,8 +300,8 @@ extern "C" int legion_batch_generate(void *stream, LegionFeatures *feature, Legi
     // tail batch is shortened, operator_impl.cu:162
     int64_t size = ((int64_t)batch_size * (counter + 1) >= total_cap) ? (total_cap - first) : batch_size;
     if (size < 0) size = 0;
-    return launch_batch_generate((cudaStream_t)stream, pool, all_ids, all_labels, total_cap, first, (int32_t)size,
-                                 hop_num);
+    return launch_batch_generate((cudaStream_t)stream, pool,
+                                 make_batch_ctl(pool, cache, all_ids, all_labels, total_cap, first, (int32_t)size));
 }
 
 extern "C" int legion_random_sample(void *stream, LegionGraph *graph, LegionCache *cache, LegionPool *pool,
@@ -332,7 +341,9 @@ extern "C" int legion_io_complete(void *stream, LegionCache *cache, LegionPool *
     (void)mode;
     LG_ARG(pool != nullptr, "NULL handle");
     LG_CUDA(cudaSetDevice(dev_id));
-    return launch_lru_insert((cudaStream_t)stream, pool, cache);
+    int rc = launch_lru_insert((cudaStream_t)stream, pool, cache);
+    if (rc == LEGION_OK && cache != nullptr && cache->kind == 1) cache->clock += 1;  // next batch, next stamp
+    return rc;
 }
 
 // ---- whole batch ---------------------------------------------------------------------------------------
@@ -371,17 +382,19 @@ extern "C" int legion_run_batch_host(LegionGraph *graph, LegionFeatures *feature
     LG_CUDA(cudaSetDevice(dev_id));
     cudaStream_t s = 0;
     const int pipe = pool->pipe;
+    int32_t *hs = pool->h_stage[pipe];
     // inputs: host -> pinned staging -> device
-    memcpy(pool->h_stage, seeds, sizeof(int32_t) * n_seeds);
-    memcpy(pool->h_stage + pool->batch_size, labels, sizeof(int32_t) * n_seeds);
-    LG_CUDA(cudaMemcpyAsync(pool->seed_stage, pool->h_stage, sizeof(int32_t) * n_seeds, cudaMemcpyHostToDevice, s));
-    LG_CUDA(cudaMemcpyAsync(pool->label_stage, pool->h_stage + pool->batch_size, sizeof(int32_t) * n_seeds,
+    memcpy(hs, seeds, sizeof(int32_t) * n_seeds);
+    memcpy(hs + pool->batch_size, labels, sizeof(int32_t) * n_seeds);
+    LG_CUDA(cudaMemcpyAsync(pool->seed_stage[pipe], hs, sizeof(int32_t) * n_seeds, cudaMemcpyHostToDevice, s));
+    LG_CUDA(cudaMemcpyAsync(pool->label_stage[pipe], hs + pool->batch_size, sizeof(int32_t) * n_seeds,
                             cudaMemcpyHostToDevice, s));
-    int rc = launch_batch_generate(s, pool, pool->seed_stage, pool->label_stage, n_seeds, 0, n_seeds, pool->hop_num);
+    int rc = launch_batch_generate(s, pool, make_batch_ctl(pool, cache, pool->seed_stage[pipe], pool->label_stage[pipe],
+                                                            n_seeds, 0, n_seeds));
     if (rc != LEGION_OK) return rc;
     rc = run_ops(s, graph, cache, pool, dev_id);
     if (rc != LEGION_OK) return rc;
-    int32_t *hc = pool->h_stage + 2 * (size_t)pool->batch_size;
+    int32_t *hc = hs + 2 * (size_t)pool->batch_size;
     LG_CUDA(cudaMemcpyAsync(hc, pool->node_counter[pipe], 64, cudaMemcpyDeviceToHost, s));
     LG_CUDA(cudaMemcpyAsync(hc + 16, pool->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, s));
     LG_CUDA(cudaStreamSynchronize(s));

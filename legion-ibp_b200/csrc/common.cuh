@@ -72,6 +72,22 @@ struct MapSlot {
     int32_t val;
 };
 
+// Per-batch parameters, kept in device memory (one copy per pipe) so that the launch sequence of a
+// batch does not depend on them and can be replayed as a CUDA graph: only the kernel that writes
+// this struct takes them by value.
+struct BatchCtl {
+    const int32_t *all_ids;     // seed list of the batch's mode
+    const int32_t *all_labels;
+    int64_t first;              // position of the batch's first seed in the list
+    int32_t total_cap;          // length of the list
+    int32_t size;               // seeds in this batch (the tail batch is shorter)
+    int32_t hop_num;
+    uint32_t global_batch;      // counter word of the sampler's RNG
+    uint32_t k0, k1;            // RNG key
+    int32_t max_rounds;
+    int32_t clock;              // LRU batch clock
+};
+
 }  // namespace legion
 
 // ---- handle structs (opaque in the C ABI) ------------------------------------------------------
@@ -130,20 +146,21 @@ struct LegionPool {
     int32_t *agg_dst[LEGION_INTERBATCH_CON];
     int32_t *node_counter[LEGION_INTERBATCH_CON];
     int32_t *edge_counter[LEGION_INTERBATCH_CON];
-    // shared scratch
-    int64_t *cache_index;      // one entry per node of the batch
-    int32_t *src_global;       // sampled neighbour ids, all hops
-    legion::MapSlot *map;      // batch-local id map
+    // per pipe scratch (two batches may be in flight)
+    int64_t *cache_index[LEGION_INTERBATCH_CON];      // one entry per node of the batch
+    int32_t *src_global[LEGION_INTERBATCH_CON];       // sampled neighbour ids, all hops
+    legion::MapSlot *map[LEGION_INTERBATCH_CON];      // batch-local id map
     uint32_t map_mask;
-    legion::NodeRec *node_rec;
-    int32_t *tile_sum, *tile_off;
-    int32_t *eslot, *erank;
-    int64_t *lru_victim;       // per node: way chosen for insertion, or -1
-    int32_t *miss_rows[LEGION_INTERBATCH_CON];   // per pipe: rows to fetch from the host table, by segment
-    int32_t *miss_count[LEGION_INTERBATCH_CON];  // per pipe: [0..3] entries per segment, [4] ticket
-    int32_t *ctl;
-    int32_t *seed_stage, *label_stage;  // device staging for host-provided seeds
-    int32_t *h_stage;                   // pinned host staging
+    legion::NodeRec *node_rec[LEGION_INTERBATCH_CON];
+    int32_t *tile_sum[LEGION_INTERBATCH_CON], *tile_off[LEGION_INTERBATCH_CON];
+    int32_t *eslot[LEGION_INTERBATCH_CON], *erank[LEGION_INTERBATCH_CON];
+    int64_t *lru_victim[LEGION_INTERBATCH_CON];       // per node: way chosen for insertion, or -1
+    int32_t *miss_rows[LEGION_INTERBATCH_CON];        // rows to fetch from the host table, by segment
+    int32_t *miss_count[LEGION_INTERBATCH_CON];       // [0..3] entries per segment, [4] ticket
+    int32_t *ctl[LEGION_INTERBATCH_CON];
+    legion::BatchCtl *bctl[LEGION_INTERBATCH_CON];
+    int32_t *seed_stage[LEGION_INTERBATCH_CON], *label_stage[LEGION_INTERBATCH_CON];  // device staging for host-provided seeds
+    int32_t *h_stage[LEGION_INTERBATCH_CON];  // pinned host staging: seeds, labels, then both counter arrays
     // batch state
     int32_t iter, mode, pipe;
     uint32_t global_batch;
@@ -154,8 +171,10 @@ struct LegionPool {
 
 namespace legion {
 // kernel launchers (defined in sample.cu / gather.cu / cache.cu)
-int launch_batch_generate(cudaStream_t s, LegionPool *p, const int32_t *all_ids, const int32_t *all_labels,
-                          int32_t total_cap, int64_t first, int32_t size, int32_t hop_num);
+int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &ctl);
+BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t *all_ids, const int32_t *all_labels,
+                        int32_t total_cap, int64_t first, int32_t size);
+const void *map_clear_kernel_address();
 int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32_t fanout, int32_t hop,
                       int32_t op_id);
 int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);

@@ -324,7 +324,8 @@ struct LruParams {
     int32_t op_id;
     int32_t *keys, *stamps;
     int64_t sets;
-    int32_t ways, clock;
+    int32_t ways;
+    const BatchCtl *bctl;  // clock of the batch
     const uint8_t *rows;
     const uint8_t *host;
     int64_t n_nodes;
@@ -344,6 +345,7 @@ __global__ void __launch_bounds__(256) gather_lru_kernel(LruParams p)
     const int lane = threadIdx.x & 31;
     const int n_warps = (gridDim.x * blockDim.x) >> 5;
     const int row_vec = p.row_bytes >> 4;
+    const int clock = p.bctl->clock;
     const int ways = p.ways;              // power of two, <= 32
     const int per_pass = 32 / ways;       // ids probed together by one warp
     const int sub = lane / ways, way = lane % ways;
@@ -359,7 +361,7 @@ __global__ void __launch_bounds__(256) gather_lru_kernel(LruParams p)
             unsigned hitmask = __ballot_sync(kFull, id >= 0 && key == id);
             unsigned group = (ways == 32) ? hitmask : ((hitmask >> (sub * ways)) & ((1u << ways) - 1u));
             int hit_way = __ffs(group) - 1;
-            if (hit_way == way && id >= 0) p.stamps[set * ways + way] = p.clock;
+            if (hit_way == way && id >= 0) p.stamps[set * ways + way] = clock;
             // hand the answer to the owning lane
             int64_t slot = hit_way >= 0 ? set * ways + hit_way : -1;
 #pragma unroll 1
@@ -418,9 +420,11 @@ __global__ void __launch_bounds__(256) gather_lru_kernel(LruParams p)
 //          buffer (already gathered) into the slot.
 __global__ void lru_claim_kernel(const int32_t *__restrict__ ids, const int64_t *__restrict__ cache_index,
                                  const int32_t *__restrict__ nc, const int32_t *__restrict__ keys,
-                                 const int32_t *__restrict__ stamps, int64_t sets, int ways, int clock,
-                                 unsigned long long *claim, int64_t *victim /* per row: chosen slot or -1 */)
+                                 const int32_t *__restrict__ stamps, int64_t sets, int ways,
+                                 const BatchCtl *__restrict__ bctl, unsigned long long *claim,
+                                 int64_t *victim /* per row: chosen slot or -1 */)
 {
+    const int clock = bctl->clock;
     const int n = nc[LEGION_INTRABATCH_CON * 3 + nc[LEGION_INTRABATCH_CON * 3 - 1]];  // all nodes of the batch
     for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
         int64_t v = -1;
@@ -444,10 +448,12 @@ __global__ void lru_claim_kernel(const int32_t *__restrict__ ids, const int64_t 
 }
 
 __global__ void lru_commit_kernel(const int32_t *__restrict__ ids, const int32_t *__restrict__ nc, int32_t *keys,
-                                  int32_t *stamps, int clock, const unsigned long long *__restrict__ claim,
+                                  int32_t *stamps, const BatchCtl *__restrict__ bctl,
+                                  const unsigned long long *__restrict__ claim,
                                   const int64_t *__restrict__ victim, const uint8_t *__restrict__ features,
                                   uint8_t *rows, int row_bytes, unsigned long long *stats)
 {
+    const int clock = bctl->clock;
     const int n = nc[LEGION_INTRABATCH_CON * 3 + nc[LEGION_INTRABATCH_CON * 3 - 1]];  // all nodes of the batch
     const int lane = threadIdx.x & 31;
     const int n_warps = (gridDim.x * blockDim.x) >> 5;
@@ -522,12 +528,12 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
         lp.stamps = c->stamps;
         lp.sets = c->sets;
         lp.ways = c->ways;
-        lp.clock = c->clock;
+        lp.bctl = p->bctl[pipe];
         lp.rows = (const uint8_t *)c->rows;
         lp.host = (const uint8_t *)c->host_table;
         lp.n_nodes = c->n_nodes;
         lp.dst = (uint8_t *)p->features[pipe];
-        lp.cache_index = p->cache_index;
+        lp.cache_index = p->cache_index[pipe];
         lp.stats = c->stats;
         lp.row_bytes = row_bytes;
         lp.miss_rows = p->miss_rows[pipe];
@@ -556,7 +562,7 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
     gp.host = c ? (const uint8_t *)c->host_table : nullptr;
     gp.n_nodes = c ? c->n_nodes : 1;
     gp.dst = (uint8_t *)p->features[pipe];
-    gp.cache_index = reinterpret_cast<int32_t *>(p->cache_index);
+    gp.cache_index = reinterpret_cast<int32_t *>(p->cache_index[pipe]);
     gp.stats = c ? c->stats : nullptr;
     gp.row_bytes = row_bytes;
     gp.slot_bytes = c ? c->slot_bytes : row_bytes;
@@ -631,16 +637,15 @@ int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c)
     int grid_t = (int)(g_thread > cap ? cap : g_thread);
     int grid_w = (int)(g_warp > cap ? cap : g_warp);
     unsigned long long *claim = reinterpret_cast<unsigned long long *>(c->claim);
-    lru_claim_kernel<<<grid_t, 256, 0, s>>>(p->ids[pipe], p->cache_index, p->node_counter[pipe], c->keys, c->stamps, c->sets,
-                                            c->ways, c->clock, claim, p->lru_victim);
+    lru_claim_kernel<<<grid_t, 256, 0, s>>>(p->ids[pipe], p->cache_index[pipe], p->node_counter[pipe], c->keys, c->stamps,
+                                            c->sets, c->ways, p->bctl[pipe], claim, p->lru_victim[pipe]);
     LG_LAUNCH_CHECK();
-    lru_commit_kernel<<<grid_w, 256, 0, s>>>(p->ids[pipe], p->node_counter[pipe], c->keys, c->stamps, c->clock, claim,
-                                             p->lru_victim, (const uint8_t *)p->features[pipe],
+    lru_commit_kernel<<<grid_w, 256, 0, s>>>(p->ids[pipe], p->node_counter[pipe], c->keys, c->stamps, p->bctl[pipe], claim,
+                                             p->lru_victim[pipe], (const uint8_t *)p->features[pipe],
                                              (uint8_t *)c->rows, c->row_bytes, c->stats);
     LG_LAUNCH_CHECK();
-    lru_claim_reset_kernel<<<grid_t, 256, 0, s>>>(p->lru_victim, p->node_counter[pipe], claim);
+    lru_claim_reset_kernel<<<grid_t, 256, 0, s>>>(p->lru_victim[pipe], p->node_counter[pipe], claim);
     LG_LAUNCH_CHECK();
-    c->clock += 1;
     return LEGION_OK;
 }
 

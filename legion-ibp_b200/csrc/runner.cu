@@ -7,12 +7,46 @@
 // the three resources the path is bound by: sampling (latency of random topology reads) on one,
 // lookup + gather of cached rows (HBM / NVLink bandwidth) on a second one behind an event per
 // segment, and the fetch of missed rows from pinned host memory (host link) on a third.  The
-// gather of hop h overlaps the sampling of hop h+1, and the host-link traffic of batch k overlaps
-// everything of batch k+1.  Scratch shared between pipes is touched by one stream only, so
-// in-stream order keeps it consistent.
+// gather of hop h overlaps the sampling of hop h+1.
+//
+// A batch is ~25 small launches, so issuing it from the host costs more than running it.  Every
+// size lives on the device and the per-batch parameters are written by the first kernel, so the
+// whole three-stream sequence of one pipe is captured once into a CUDA graph; a batch is then one
+// parameter update of that first node plus one graph launch.  The two pipes own separate scratch
+// and are launched on two streams, so consecutive batches overlap freely (the host-link traffic of
+// batch k runs under the sampling of batch k+1); an LRU cache, whose state changes every batch,
+// keeps them in order by using one launch stream.
 #include "common.cuh"
 
+#include <string.h>
+#include <time.h>
+
 #include <vector>
+
+namespace {
+
+struct EvPair {
+    cudaEvent_t a, b;
+};
+
+struct PipeGraph {
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+    cudaGraphNode_t ctl_node;
+    cudaKernelNodeParams ctl_params;
+    // argument storage of the first kernel (kept alive for cudaGraphExecKernelNodeSetParams)
+    uint4 *a_slots;
+    int64_t a_pairs;
+    int32_t *a_ctl, *a_nc, *a_ec;
+    legion::BatchCtl *a_bctl;
+    legion::BatchCtl a_value;
+    void *args[7];
+    bool valid;
+    bool launched;  // since the last sync
+    EvPair hit[LEGION_MAX_HOPS + 1], miss[LEGION_MAX_HOPS + 1];
+};
+
+}  // namespace
 
 struct LegionRunner {
     int32_t dev_id;
@@ -22,22 +56,30 @@ struct LegionRunner {
     LegionPool *pool;
     LegionIpcEnv *env;
     cudaStream_t s_sample, s_gather, s_miss;
+    cudaStream_t s_launch[LEGION_INTERBATCH_CON];
     cudaEvent_t seg_ready[LEGION_MAX_HOPS + 1];
     cudaEvent_t hit_done[LEGION_MAX_HOPS + 1];
+    cudaEvent_t join_ev, cross_ev;
     cudaEvent_t pipe_done[LEGION_INTERBATCH_CON];
     bool pipe_busy[LEGION_INTERBATCH_CON];
-    int current_pipe;
+    int current_pipe, last_pipe;
+    bool use_graph, time_kernels;
+    PipeGraph pg[LEGION_INTERBATCH_CON];
     // timing of the batches enqueued since the last sync
     cudaEvent_t t_begin, t_end;
     bool open_window;
     int window_batches;
     std::vector<cudaEvent_t> ev_free;
-    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> gather_ev, miss_ev;
+    std::vector<EvPair> gather_ev, miss_ev;
     float last_batch_ms, last_gather_ms, last_miss_ms;
-    int last_pipe;
-    int last_batches;
+    int last_batches, last_timed;
     long long served;
     double served_us;
+    // host-buffer batches submitted and not yet collected (oldest first)
+    int host_fifo[LEGION_INTERBATCH_CON];
+    int32_t host_seeds[LEGION_INTERBATCH_CON];
+    int host_pending;
+    cudaStream_t s_copy;
 };
 
 using namespace legion;
@@ -73,13 +115,17 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     r->pool = pool;
     r->env = env;
     r->current_pipe = 0;
+    r->last_pipe = -1;
+    r->use_graph = true;
+    r->time_kernels = false;
     r->open_window = false;
     r->window_batches = 0;
     r->last_batch_ms = r->last_gather_ms = r->last_miss_ms = 0.0f;
-    r->last_pipe = -1;
-    r->last_batches = 0;
+    r->last_batches = r->last_timed = 0;
     r->served = 0;
     r->served_us = 0.0;
+    r->host_pending = 0;
+    LG_CUDA(cudaStreamCreateWithFlags(&r->s_copy, cudaStreamNonBlocking));
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_sample, cudaStreamNonBlocking));
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_gather, cudaStreamNonBlocking));
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_miss, cudaStreamNonBlocking));
@@ -87,9 +133,19 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
         LG_CUDA(cudaEventCreateWithFlags(&r->seg_ready[i], cudaEventDisableTiming));
         LG_CUDA(cudaEventCreateWithFlags(&r->hit_done[i], cudaEventDisableTiming));
     }
+    LG_CUDA(cudaEventCreateWithFlags(&r->join_ev, cudaEventDisableTiming));
+    LG_CUDA(cudaEventCreateWithFlags(&r->cross_ev, cudaEventDisableTiming));
     for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+        LG_CUDA(cudaStreamCreateWithFlags(&r->s_launch[i], cudaStreamNonBlocking));
         LG_CUDA(cudaEventCreateWithFlags(&r->pipe_done[i], cudaEventDisableTiming));
         r->pipe_busy[i] = false;
+        memset(&r->pg[i], 0, sizeof(PipeGraph));
+        for (int s = 0; s <= LEGION_MAX_HOPS; ++s) {
+            LG_CUDA(cudaEventCreate(&r->pg[i].hit[s].a));
+            LG_CUDA(cudaEventCreate(&r->pg[i].hit[s].b));
+            LG_CUDA(cudaEventCreate(&r->pg[i].miss[s].a));
+            LG_CUDA(cudaEventCreate(&r->pg[i].miss[s].b));
+        }
     }
     LG_CUDA(cudaEventCreate(&r->t_begin));
     LG_CUDA(cudaEventCreate(&r->t_end));
@@ -97,34 +153,217 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     return LEGION_OK;
 }
 
+static void drop_graphs(LegionRunner *r)
+{
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+        if (r->pg[i].valid) {
+            cudaGraphExecDestroy(r->pg[i].exec);
+            cudaGraphDestroy(r->pg[i].graph);
+            r->pg[i].valid = false;
+        }
+    }
+}
+
+// use_graph: replay each batch as a CUDA graph (default) or issue it launch by launch.
+// time_kernels: bracket the gather launches with CUDA events on their streams.
+extern "C" int legion_runner_set_options(LegionRunner *r, int32_t use_graph, int32_t time_kernels)
+{
+    LG_ARG(r != nullptr, "runner is NULL");
+    LG_CUDA(cudaSetDevice(r->dev_id));
+    LG_CUDA(cudaDeviceSynchronize());
+    if ((use_graph != 0) != r->use_graph || (time_kernels != 0) != r->time_kernels) drop_graphs(r);
+    r->use_graph = use_graph != 0;
+    r->time_kernels = time_kernels != 0;
+    return LEGION_OK;
+}
+
+// Marks a point on `s`: an external event-record node while capturing, a plain record otherwise.
+static cudaError_t mark(cudaEvent_t e, cudaStream_t s, bool capturing)
+{
+    return capturing ? cudaEventRecordWithFlags(e, s, cudaEventRecordExternal) : cudaEventRecord(e, s);
+}
+
 // One segment: cached rows on the gather stream, missed rows on the miss stream behind it.
-static int timed_gather(LegionRunner *r, int op_id, int seg)
+static int gather_segment(LegionRunner *r, int op_id, int seg, bool capturing)
 {
     LegionPool *p = r->pool;
     LegionCache *c = r->cache;
     if (c != nullptr) LG_ARG(c->row_bytes == p->row_bytes_out, "cache and pool disagree on the row size");
-    const bool record = r->gather_ev.size() < 8192;
-    cudaEvent_t a = record ? take_event(r) : nullptr, b = record ? take_event(r) : nullptr;
-    if (a) cudaEventRecord(a, r->s_gather);
+    const bool has_miss = c != nullptr && c->host_table != nullptr;
+    EvPair h = { nullptr, nullptr }, m = { nullptr, nullptr };
+    if (r->time_kernels) {
+        if (capturing) {
+            h = r->pg[p->pipe].hit[seg];
+            m = r->pg[p->pipe].miss[seg];
+        } else if (r->gather_ev.size() < 8192) {
+            h.a = take_event(r); h.b = take_event(r);
+            if (has_miss) { m.a = take_event(r); m.b = take_event(r); }
+        }
+    }
+    if (h.a) LG_CUDA(mark(h.a, r->s_gather, capturing));
     int rc = launch_gather_hits(r->s_gather, p, c, op_id);
-    if (b) cudaEventRecord(b, r->s_gather);
-    if (a && b) r->gather_ev.push_back(std::make_pair(a, b));
     if (rc != LEGION_OK) return rc;
+    if (h.b) LG_CUDA(mark(h.b, r->s_gather, capturing));
+    if (h.a && h.b && !capturing) r->gather_ev.push_back(h);
     LG_CUDA(cudaEventRecord(r->hit_done[seg], r->s_gather));
     LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->hit_done[seg], 0));
-    if (c != nullptr && c->host_table != nullptr) {
-        cudaEvent_t m0 = record ? take_event(r) : nullptr, m1 = record ? take_event(r) : nullptr;
-        if (m0) cudaEventRecord(m0, r->s_miss);
+    if (has_miss) {
+        if (m.a) LG_CUDA(mark(m.a, r->s_miss, capturing));
         rc = launch_gather_misses(r->s_miss, p, c, op_id);
-        if (m1) cudaEventRecord(m1, r->s_miss);
-        if (m0 && m1) r->miss_ev.push_back(std::make_pair(m0, m1));
+        if (rc != LEGION_OK) return rc;
+        if (m.b) LG_CUDA(mark(m.b, r->s_miss, capturing));
+        if (m.a && m.b && !capturing) r->miss_ev.push_back(m);
     }
-    return rc;
+    return LEGION_OK;
+}
+
+// The whole batch on the three streams; origin s_sample, last work on s_miss.
+static int issue_batch(LegionRunner *r, const BatchCtl &v, bool capturing)
+{
+    LegionPool *p = r->pool;
+    int rc = launch_batch_generate(r->s_sample, p, v);
+    if (rc != LEGION_OK) return rc;
+    LG_CUDA(cudaEventRecord(r->seg_ready[0], r->s_sample));
+    LG_CUDA(cudaStreamWaitEvent(r->s_gather, r->seg_ready[0], 0));
+    rc = gather_segment(r, 1, 0, capturing);
+    if (rc != LEGION_OK) return rc;
+    for (int h = 0; h < p->hop_num; ++h) {
+        const int op = LEGION_INTRABATCH_CON * (h + 1);
+        rc = launch_sample_hop(r->s_sample, p, r->graph, p->fanout[h], h, op);
+        if (rc != LEGION_OK) return rc;
+        LG_CUDA(cudaEventRecord(r->seg_ready[h + 1], r->s_sample));
+        LG_CUDA(cudaStreamWaitEvent(r->s_gather, r->seg_ready[h + 1], 0));
+        rc = gather_segment(r, op + 1, h + 1, capturing);
+        if (rc != LEGION_OK) return rc;
+    }
+    return launch_lru_insert(r->s_miss, p, r->cache);  // IOComplete; every gather precedes it on s_miss
+}
+
+static int capture_pipe(LegionRunner *r, int pipe, const BatchCtl &v)
+{
+    PipeGraph &g = r->pg[pipe];
+    LG_CUDA(cudaStreamBeginCapture(r->s_sample, cudaStreamCaptureModeThreadLocal));
+    int rc = issue_batch(r, v, true);
+    cudaError_t e = cudaSuccess;
+    if (rc == LEGION_OK) {
+        e = cudaEventRecord(r->join_ev, r->s_miss);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(r->s_sample, r->join_ev, 0);
+    }
+    cudaGraph_t graph = nullptr;
+    cudaError_t e2 = cudaStreamEndCapture(r->s_sample, &graph);
+    if (rc != LEGION_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        return rc;
+    }
+    if (e != cudaSuccess || e2 != cudaSuccess) {
+        set_error("graph capture failed: %s", cudaGetErrorString(e != cudaSuccess ? e : e2));
+        if (graph) cudaGraphDestroy(graph);
+        return LEGION_E_CUDA;
+    }
+    // the node that carries the per-batch parameters: the first kernel of the batch
+    size_t n_nodes = 0;
+    LG_CUDA(cudaGraphGetNodes(graph, nullptr, &n_nodes));
+    std::vector<cudaGraphNode_t> nodes(n_nodes);
+    LG_CUDA(cudaGraphGetNodes(graph, nodes.data(), &n_nodes));
+    bool found = false;
+    for (size_t i = 0; i < n_nodes && !found; ++i) {
+        cudaGraphNodeType t;
+        LG_CUDA(cudaGraphNodeGetType(nodes[i], &t));
+        if (t != cudaGraphNodeTypeKernel) continue;
+        cudaKernelNodeParams kp;
+        LG_CUDA(cudaGraphKernelNodeGetParams(nodes[i], &kp));
+        if (kp.func == map_clear_kernel_address()) {
+            g.ctl_node = nodes[i];
+            g.ctl_params = kp;
+            g.a_slots = *(uint4 **)kp.kernelParams[0];
+            g.a_pairs = *(int64_t *)kp.kernelParams[1];
+            g.a_ctl = *(int32_t **)kp.kernelParams[2];
+            g.a_nc = *(int32_t **)kp.kernelParams[3];
+            g.a_ec = *(int32_t **)kp.kernelParams[4];
+            g.a_bctl = *(BatchCtl **)kp.kernelParams[5];
+            g.a_value = v;
+            found = true;
+        }
+    }
+    if (!found) {
+        set_error("graph capture: parameter node not found");
+        cudaGraphDestroy(graph);
+        return LEGION_E_STATE;
+    }
+    g.args[0] = &g.a_slots; g.args[1] = &g.a_pairs; g.args[2] = &g.a_ctl; g.args[3] = &g.a_nc;
+    g.args[4] = &g.a_ec; g.args[5] = &g.a_bctl; g.args[6] = &g.a_value;
+    g.ctl_params.kernelParams = g.args;
+    g.ctl_params.extra = nullptr;
+    LG_CUDA(cudaGraphInstantiate(&g.exec, graph, 0));
+    g.graph = graph;
+    g.valid = true;
+    return LEGION_OK;
+}
+
+// Enqueues one batch described by `v` on the current pipe.  host_seeds > 0: the seeds and labels
+// wait in the pipe's pinned staging area and are copied in first, and both counter arrays are
+// copied back to it behind the batch.
+static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
+{
+    LegionPool *p = r->pool;
+    LegionCache *c = r->cache;
+    const int pipe = r->current_pipe;
+    int rc;
+    const bool lru = c != nullptr && c->kind == 1;
+    // two launch streams let consecutive batches overlap; an LRU cache needs them in order
+    cudaStream_t launch = r->use_graph ? r->s_launch[lru ? 0 : pipe] : r->s_sample;
+    cudaStream_t tail = r->use_graph ? launch : r->s_miss;
+    if (!r->open_window) {
+        LG_CUDA(cudaEventRecord(r->t_begin, launch));
+        r->open_window = true;
+        r->window_batches = 0;
+    }
+    if (!r->use_graph) {
+        // the buffers of this pipe are rewritten: the gather that last read them must be over;
+        // an LRU cache also has to see the previous batch's insertions before the next lookup
+        if (r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(r->s_sample, r->pipe_done[pipe], 0));
+        if (lru && r->last_pipe >= 0 && r->pipe_busy[r->last_pipe])
+            LG_CUDA(cudaStreamWaitEvent(r->s_sample, r->pipe_done[r->last_pipe], 0));
+    }
+    if (host_seeds > 0) {
+        int32_t *hs = p->h_stage[pipe];
+        LG_CUDA(cudaMemcpyAsync(p->seed_stage[pipe], hs, sizeof(int32_t) * host_seeds, cudaMemcpyHostToDevice, launch));
+        LG_CUDA(cudaMemcpyAsync(p->label_stage[pipe], hs + p->batch_size, sizeof(int32_t) * host_seeds,
+                                cudaMemcpyHostToDevice, launch));
+    }
+    if (r->use_graph) {
+        PipeGraph &g = r->pg[pipe];
+        if (!g.valid) {
+            rc = capture_pipe(r, pipe, v);
+            if (rc != LEGION_OK) return rc;
+        }
+        g.a_value = v;
+        LG_CUDA(cudaGraphExecKernelNodeSetParams(g.exec, g.ctl_node, &g.ctl_params));
+        LG_CUDA(cudaGraphLaunch(g.exec, launch));
+        g.launched = true;
+    } else {
+        rc = issue_batch(r, v, false);
+        if (rc != LEGION_OK) return rc;
+    }
+    if (host_seeds > 0) {
+        int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
+        LG_CUDA(cudaMemcpyAsync(hc, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, tail));
+        LG_CUDA(cudaMemcpyAsync(hc + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, tail));
+    }
+    LG_CUDA(cudaEventRecord(r->pipe_done[pipe], tail));
+    if (lru) c->clock += 1;
+    r->pipe_busy[pipe] = true;
+    r->last_pipe = pipe;
+    r->window_batches += 1;
+    r->current_pipe = (pipe + 1) % p->pipes;  // engine/server.cu:398-399
+    return LEGION_OK;
 }
 
 extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, int32_t mode, int32_t local_batch_id)
 {
     LG_ARG(r != nullptr, "runner is NULL");
+    LG_ARG(mode >= 0 && mode <= 2, "invalid mode");
+    LG_ARG(r->host_pending == 0, "host-buffer batches are waiting to be collected");
     LG_CUDA(cudaSetDevice(r->dev_id));
     LegionPool *p = r->pool;
     const int pipe = r->current_pipe;
@@ -135,39 +374,78 @@ extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, i
         bs = legion_ipc_current_batchsize(r->env, r->dev_id, mode);
         LG_ARG(bs > 0 && bs <= p->batch_size, "batch size of this mode is above the pool's");
     }
-    if (!r->open_window) {
-        LG_CUDA(cudaEventRecord(r->t_begin, r->s_sample));
-        r->open_window = true;
-        r->window_batches = 0;
+    const int32_t total_cap = r->feature->count[mode];
+    LG_ARG(r->feature->ids[mode] != nullptr && total_cap > 0, "no seed list for this mode");
+    LG_ARG(local_batch_id >= 0, "negative batch number");
+    const int64_t first = (int64_t)bs * local_batch_id;
+    int64_t size = ((int64_t)bs * (local_batch_id + 1) >= total_cap) ? (total_cap - first) : bs;  // operator_impl.cu:162
+    if (size < 0) size = 0;
+    return enqueue_ctl(r, make_batch_ctl(p, r->cache, r->feature->ids[mode], r->feature->labels[mode], total_cap, first,
+                                         (int32_t)size), 0);
+}
+
+// Host-buffer interface with batches in flight.  submit copies the seeds in and starts the batch;
+// collect waits for the oldest submitted batch and copies its block structure (and, optionally, its
+// gathered rows) out.  Up to `pipes` batches may be submitted before the first collect, so the copies
+// of one batch overlap the sampling and gathering of the next.
+extern "C" int legion_runner_submit_host(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                                         int32_t global_batch_id)
+{
+    LG_ARG(r != nullptr && seeds != nullptr && labels != nullptr, "NULL pointer");
+    LegionPool *p = r->pool;
+    LG_ARG(n_seeds > 0 && n_seeds <= p->batch_size, "n_seeds above the pool's batch size");
+    if (r->host_pending >= p->pipes) {
+        set_error("legion_runner_submit_host: %d batches are in flight, collect one first", r->host_pending);
+        return LEGION_E_STATE;
     }
-    // the buffers of this pipe are rewritten: the gather that last read them must be over
-    if (r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(r->s_sample, r->pipe_done[pipe], 0));
-    rc = legion_batch_generate(r->s_sample, r->feature, r->cache, p, bs, local_batch_id, r->dev_id, r->dev_id, mode, 0,
-                               p->hop_num, 0);
+    LG_CUDA(cudaSetDevice(r->dev_id));
+    const int pipe = r->current_pipe;
+    int rc = legion_pool_set_batch(p, 0, LEGION_TRAINMODE, pipe, (uint32_t)global_batch_id);
     if (rc != LEGION_OK) return rc;
-    LG_CUDA(cudaEventRecord(r->seg_ready[0], r->s_sample));
-    LG_CUDA(cudaStreamWaitEvent(r->s_gather, r->seg_ready[0], 0));
-    // an LRU cache changes at the end of every batch: its next lookup has to see the insertions
-    if (r->cache != nullptr && r->cache->kind == 1 && r->last_pipe >= 0 && r->pipe_busy[r->last_pipe])
-        LG_CUDA(cudaStreamWaitEvent(r->s_gather, r->pipe_done[r->last_pipe], 0));
-    rc = timed_gather(r, 1, 0);
+    memcpy(p->h_stage[pipe], seeds, sizeof(int32_t) * n_seeds);
+    memcpy(p->h_stage[pipe] + p->batch_size, labels, sizeof(int32_t) * n_seeds);
+    rc = enqueue_ctl(r, make_batch_ctl(p, r->cache, p->seed_stage[pipe], p->label_stage[pipe], n_seeds, 0, n_seeds), n_seeds);
     if (rc != LEGION_OK) return rc;
-    for (int h = 0; h < p->hop_num; ++h) {
-        const int op = LEGION_INTRABATCH_CON * (h + 1);
-        rc = legion_random_sample(r->s_sample, r->graph, r->cache, p, p->fanout[h], r->dev_id, op, 0, 0);
-        if (rc != LEGION_OK) return rc;
-        LG_CUDA(cudaEventRecord(r->seg_ready[h + 1], r->s_sample));
-        LG_CUDA(cudaStreamWaitEvent(r->s_gather, r->seg_ready[h + 1], 0));
-        rc = timed_gather(r, op + 1, h + 1);
-        if (rc != LEGION_OK) return rc;
+    r->host_fifo[r->host_pending] = pipe;
+    r->host_seeds[r->host_pending] = n_seeds;
+    r->host_pending += 1;
+    return LEGION_OK;
+}
+
+extern "C" int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
+                                          int32_t *agg_dst_out, int32_t node_counter_out[16],
+                                          int32_t edge_counter_out[16], void *features_out)
+{
+    LG_ARG(r != nullptr && node_counter_out != nullptr && edge_counter_out != nullptr, "NULL pointer");
+    if (r->host_pending == 0) {
+        set_error("legion_runner_collect_host: nothing was submitted");
+        return LEGION_E_STATE;
     }
-    rc = legion_io_complete(r->s_miss, r->cache, p, r->dev_id, mode);
-    if (rc != LEGION_OK) return rc;
-    LG_CUDA(cudaEventRecord(r->pipe_done[pipe], r->s_miss));
-    r->pipe_busy[pipe] = true;
-    r->last_pipe = pipe;
-    r->window_batches += 1;
-    r->current_pipe = (pipe + 1) % p->pipes;  // engine/server.cu:398-399
+    LG_CUDA(cudaSetDevice(r->dev_id));
+    LegionPool *p = r->pool;
+    const int pipe = r->host_fifo[0];
+    const int32_t n_seeds = r->host_seeds[0];
+    for (int i = 1; i < r->host_pending; ++i) {
+        r->host_fifo[i - 1] = r->host_fifo[i];
+        r->host_seeds[i - 1] = r->host_seeds[i];
+    }
+    r->host_pending -= 1;
+    LG_CUDA(cudaEventSynchronize(r->pipe_done[pipe]));
+    const int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
+    memcpy(node_counter_out, hc, 64);
+    memcpy(edge_counter_out, hc + 16, 64);
+    const int hops = hc[LEGION_INTRABATCH_CON * 3 - 1];
+    const int64_t n_nodes = hc[LEGION_INTRABATCH_CON * 3 + hops];
+    const int64_t n_edges = (int64_t)hc[16] + hc[17];
+    cudaStream_t s = r->s_copy;
+    if (ids_out) LG_CUDA(cudaMemcpyAsync(ids_out, p->ids[pipe], 4 * n_nodes, cudaMemcpyDeviceToHost, s));
+    if (labels_out) LG_CUDA(cudaMemcpyAsync(labels_out, p->labels[pipe], 4 * (int64_t)n_seeds, cudaMemcpyDeviceToHost, s));
+    if (agg_src_out) LG_CUDA(cudaMemcpyAsync(agg_src_out, p->agg_src[pipe], 4 * n_edges, cudaMemcpyDeviceToHost, s));
+    if (agg_dst_out) LG_CUDA(cudaMemcpyAsync(agg_dst_out, p->agg_dst[pipe], 4 * n_edges, cudaMemcpyDeviceToHost, s));
+    if (features_out)
+        LG_CUDA(cudaMemcpyAsync(features_out, p->features[pipe], n_nodes * (int64_t)p->row_bytes_out,
+                                cudaMemcpyDeviceToHost, s));
+    LG_CUDA(cudaStreamSynchronize(s));
     return LEGION_OK;
 }
 
@@ -175,45 +453,75 @@ extern "C" int legion_runner_sync(LegionRunner *r)
 {
     LG_ARG(r != nullptr, "runner is NULL");
     LG_CUDA(cudaSetDevice(r->dev_id));
-    if (r->open_window) LG_CUDA(cudaEventRecord(r->t_end, r->s_miss));  // the miss stream ends every batch
+    if (r->open_window) {
+        if (r->use_graph) {
+            // t_end after both launch streams
+            LG_CUDA(cudaEventRecord(r->cross_ev, r->s_launch[1]));
+            LG_CUDA(cudaStreamWaitEvent(r->s_launch[0], r->cross_ev, 0));
+            LG_CUDA(cudaEventRecord(r->t_end, r->s_launch[0]));
+        } else {
+            LG_CUDA(cudaEventRecord(r->t_end, r->s_miss));  // the miss stream ends every batch
+        }
+    }
     LG_CUDA(cudaStreamSynchronize(r->s_sample));
     LG_CUDA(cudaStreamSynchronize(r->s_gather));
     LG_CUDA(cudaStreamSynchronize(r->s_miss));
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) LG_CUDA(cudaStreamSynchronize(r->s_launch[i]));
     if (r->open_window) {
         float ms = 0.0f, g = 0.0f, m = 0.0f;
+        int timed = 0;
         LG_CUDA(cudaEventElapsedTime(&ms, r->t_begin, r->t_end));
         for (auto &pr : r->gather_ev) {
             float t = 0.0f;
-            if (cudaEventElapsedTime(&t, pr.first, pr.second) == cudaSuccess) g += t;
-            r->ev_free.push_back(pr.first);
-            r->ev_free.push_back(pr.second);
+            if (cudaEventElapsedTime(&t, pr.a, pr.b) == cudaSuccess) g += t;
+            r->ev_free.push_back(pr.a);
+            r->ev_free.push_back(pr.b);
         }
         for (auto &pr : r->miss_ev) {
             float t = 0.0f;
-            if (cudaEventElapsedTime(&t, pr.first, pr.second) == cudaSuccess) m += t;
-            r->ev_free.push_back(pr.first);
-            r->ev_free.push_back(pr.second);
+            if (cudaEventElapsedTime(&t, pr.a, pr.b) == cudaSuccess) m += t;
+            r->ev_free.push_back(pr.a);
+            r->ev_free.push_back(pr.b);
         }
+        if (!r->use_graph && r->time_kernels) timed = r->window_batches;
         r->gather_ev.clear();
         r->miss_ev.clear();
+        if (r->use_graph && r->time_kernels) {
+            // the events of a pipe's graph hold the times of its last launch
+            const bool has_miss = r->cache != nullptr && r->cache->host_table != nullptr;
+            for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+                if (!r->pg[i].launched) continue;
+                for (int s = 0; s <= r->pool->hop_num; ++s) {
+                    float t = 0.0f;
+                    if (cudaEventElapsedTime(&t, r->pg[i].hit[s].a, r->pg[i].hit[s].b) == cudaSuccess) g += t;
+                    if (has_miss && cudaEventElapsedTime(&t, r->pg[i].miss[s].a, r->pg[i].miss[s].b) == cudaSuccess) m += t;
+                }
+                timed += 1;
+            }
+        }
         r->last_batch_ms = ms;
         r->last_gather_ms = g;
         r->last_miss_ms = m;
         r->last_batches = r->window_batches;
+        r->last_timed = timed;
         r->open_window = false;
     }
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) r->pipe_busy[i] = false;
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+        r->pipe_busy[i] = false;
+        r->pg[i].launched = false;
+    }
     return LEGION_OK;
 }
 
 extern "C" int legion_runner_timing(LegionRunner *r, float *batch_ms, float *gather_ms, float *miss_ms,
-                                    int32_t *n_batches)
+                                    int32_t *n_batches, int32_t *n_timed)
 {
     LG_ARG(r != nullptr, "runner is NULL");
     if (batch_ms) *batch_ms = r->last_batch_ms;
     if (gather_ms) *gather_ms = r->last_gather_ms;
     if (miss_ms) *miss_ms = r->last_miss_ms;
     if (n_batches) *n_batches = r->last_batches;
+    if (n_timed) *n_timed = r->last_timed;
     return LEGION_OK;
 }
 
@@ -282,19 +590,28 @@ extern "C" int legion_runner_destroy(LegionRunner *r)
 {
     if (r == nullptr) return LEGION_OK;
     cudaSetDevice(r->dev_id);
-    cudaStreamSynchronize(r->s_sample);
-    cudaStreamSynchronize(r->s_gather);
-    cudaStreamSynchronize(r->s_miss);
-    for (auto &pr : r->gather_ev) { cudaEventDestroy(pr.first); cudaEventDestroy(pr.second); }
-    for (auto &pr : r->miss_ev) { cudaEventDestroy(pr.first); cudaEventDestroy(pr.second); }
+    cudaDeviceSynchronize();
+    drop_graphs(r);
+    for (auto &pr : r->gather_ev) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
+    for (auto &pr : r->miss_ev) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
     for (auto e : r->ev_free) cudaEventDestroy(e);
     for (int i = 0; i <= LEGION_MAX_HOPS; ++i) { cudaEventDestroy(r->seg_ready[i]); cudaEventDestroy(r->hit_done[i]); }
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) cudaEventDestroy(r->pipe_done[i]);
+    cudaEventDestroy(r->join_ev);
+    cudaEventDestroy(r->cross_ev);
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+        cudaEventDestroy(r->pipe_done[i]);
+        cudaStreamDestroy(r->s_launch[i]);
+        for (int s = 0; s <= LEGION_MAX_HOPS; ++s) {
+            cudaEventDestroy(r->pg[i].hit[s].a); cudaEventDestroy(r->pg[i].hit[s].b);
+            cudaEventDestroy(r->pg[i].miss[s].a); cudaEventDestroy(r->pg[i].miss[s].b);
+        }
+    }
     cudaEventDestroy(r->t_begin);
     cudaEventDestroy(r->t_end);
     cudaStreamDestroy(r->s_sample);
     cudaStreamDestroy(r->s_gather);
     cudaStreamDestroy(r->s_miss);
+    cudaStreamDestroy(r->s_copy);
     delete r;
     return LEGION_OK;
 }

@@ -191,8 +191,12 @@ __device__ __forceinline__ void counter_update(int32_t *nc, int32_t *ec, int op_
 
 // ---- batch start -----------------------------------------------------------------------------
 
-__global__ void map_clear_kernel(uint4 *slots2, int64_t n_pairs, int32_t *ctl, int32_t *nc, int32_t *ec)
+// First kernel of every batch: empties the id map, zeroes the counters and stores the batch's
+// parameters, the only values of the batch that are passed by value.
+__global__ void map_clear_kernel(uint4 *slots2, int64_t n_pairs, int32_t *ctl, int32_t *nc, int32_t *ec,
+                                 BatchCtl *bctl, BatchCtl value)
 {
+    if (blockIdx.x == 0 && threadIdx.x == 32) *bctl = value;
     const uint4 empty = make_uint4((uint32_t)kEmptyKey, (uint32_t)kEmptyVal, (uint32_t)kEmptyKey,
                                    (uint32_t)kEmptyVal);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_pairs;
@@ -205,11 +209,13 @@ __global__ void map_clear_kernel(uint4 *slots2, int64_t n_pairs, int32_t *ctl, i
     }
 }
 
-__global__ void batch_generate_kernel(const int32_t *__restrict__ all_ids, const int32_t *__restrict__ all_labels,
-                                      int32_t total_cap, int64_t first, int32_t size, int32_t hop_num,
-                                      int32_t *ids, int32_t *labels, MapSlot *map, uint32_t mask, int32_t *ctl,
-                                      int32_t *nc, int32_t *ec)
+__global__ void batch_generate_kernel(const BatchCtl *__restrict__ b, int32_t *ids, int32_t *labels, MapSlot *map,
+                                      uint32_t mask, int32_t *ctl, int32_t *nc, int32_t *ec)
 {
+    const int32_t *__restrict__ all_ids = b->all_ids;
+    const int32_t *__restrict__ all_labels = b->all_labels;
+    const int32_t total_cap = b->total_cap, size = b->size, hop_num = b->hop_num;
+    const int64_t first = b->first;
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < size) {
         int64_t pos = first + idx;
@@ -284,11 +290,13 @@ hop_count_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict__
 
 __global__ void __launch_bounds__(256)
 hop_sample_kernel(const int32_t *__restrict__ indices, const NodeRec *__restrict__ rec,
-                  const int32_t *__restrict__ tile_off, int32_t fanout, uint32_t hop, uint32_t batch_id,
-                  uint32_t k0, uint32_t k1, int max_rounds, int32_t *src_global, int32_t *agg_dst,
+                  const int32_t *__restrict__ tile_off, int32_t fanout, uint32_t hop,
+                  const BatchCtl *__restrict__ b, int32_t *src_global, int32_t *agg_dst,
                   int32_t *eslot, MapSlot *map, uint32_t mask, int32_t *ctl)
 {
     if (ctl[CTL_ERROR] != DERR_NONE) return;
+    const uint32_t batch_id = b->global_batch, k0 = b->k0, k1 = b->k1;
+    const int max_rounds = b->max_rounds;
     const int n = ctl[CTL_N_NODES];
     const int e_base = ctl[CTL_E_TOTAL];
     const int lane = threadIdx.x & 31;
@@ -438,17 +446,37 @@ static inline int grid_for(int64_t items, int per_cta, int cap)
     return (int)g;
 }
 
-int launch_batch_generate(cudaStream_t s, LegionPool *p, const int32_t *all_ids, const int32_t *all_labels,
-                          int32_t total_cap, int64_t first, int32_t size, int32_t hop_num)
+const void *map_clear_kernel_address() { return (const void *)map_clear_kernel; }
+
+BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t *all_ids, const int32_t *all_labels,
+                        int32_t total_cap, int64_t first, int32_t size)
+{
+    BatchCtl v;
+    v.all_ids = all_ids;
+    v.all_labels = all_labels;
+    v.first = first;
+    v.total_cap = total_cap;
+    v.size = size;
+    v.hop_num = p->hop_num;
+    v.global_batch = p->global_batch;
+    v.k0 = (uint32_t)p->rng_seed;
+    v.k1 = (uint32_t)(p->rng_seed >> 32);
+    v.max_rounds = p->max_rounds;
+    v.clock = (c != nullptr && c->kind == 1) ? c->clock : 0;
+    return v;
+}
+
+int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &v)
 {
     const int pipe = p->pipe;
     int64_t n_pairs = ((int64_t)p->map_mask + 1) / 2;
     map_clear_kernel<<<grid_for(n_pairs, 256 * 4, p->sm_count * 8), 256, 0, s>>>(
-        reinterpret_cast<uint4 *>(p->map), n_pairs, p->ctl, p->node_counter[pipe], p->edge_counter[pipe]);
+        reinterpret_cast<uint4 *>(p->map[pipe]), n_pairs, p->ctl[pipe], p->node_counter[pipe], p->edge_counter[pipe],
+        p->bctl[pipe], v);
     LG_LAUNCH_CHECK();
-    batch_generate_kernel<<<grid_for(size, 256, 1 << 20), 256, 0, s>>>(
-        all_ids, all_labels, total_cap, first, size, hop_num, p->ids[pipe], p->labels[pipe], p->map,
-        p->map_mask, p->ctl, p->node_counter[pipe], p->edge_counter[pipe]);
+    batch_generate_kernel<<<grid_for(p->batch_size, 256, 1 << 20), 256, 0, s>>>(
+        p->bctl[pipe], p->ids[pipe], p->labels[pipe], p->map[pipe], p->map_mask, p->ctl[pipe], p->node_counter[pipe],
+        p->edge_counter[pipe]);
     LG_LAUNCH_CHECK();
     return LEGION_OK;
 }
@@ -462,25 +490,24 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
     int64_t inputs = p->batch_size;
     for (int h = 0; h < hop; ++h) inputs += inputs * p->fanout[h];
     int64_t edges = inputs * fanout;
+    int32_t *ctl = p->ctl[pipe];
     hop_count_kernel<<<grid_for(inputs, kTile, cap), kScanThreads, 0, s>>>(
-        g->indptr, p->ids[pipe], fanout, p->node_rec, p->tile_sum, p->tile_off, p->ctl, p->max_edges);
+        g->indptr, p->ids[pipe], fanout, p->node_rec[pipe], p->tile_sum[pipe], p->tile_off[pipe], ctl, p->max_edges);
     LG_LAUNCH_CHECK();
     hop_sample_kernel<<<grid_for(inputs, 8, cap), 256, 0, s>>>(
-        g->indices, p->node_rec, p->tile_off, fanout, (uint32_t)hop, p->global_batch, (uint32_t)p->rng_seed,
-        (uint32_t)(p->rng_seed >> 32), p->max_rounds, p->src_global, p->agg_dst[pipe], p->eslot, p->map,
-        p->map_mask, p->ctl);
+        g->indices, p->node_rec[pipe], p->tile_off[pipe], fanout, (uint32_t)hop, p->bctl[pipe], p->src_global[pipe],
+        p->agg_dst[pipe], p->eslot[pipe], p->map[pipe], p->map_mask, ctl);
     LG_LAUNCH_CHECK();
-    int32_t *tile_sum2 = p->tile_sum + p->max_inputs / kTile + 2;
-    int32_t *tile_off2 = p->tile_off + p->max_inputs / kTile + 2;
-    hop_flag_kernel<<<grid_for(edges, kTile, cap), kScanThreads, 0, s>>>(p->eslot, p->map, p->erank, tile_sum2,
-                                                                         tile_off2, p->ctl, p->max_nodes);
+    int32_t *tile_sum2 = p->tile_sum[pipe] + p->max_inputs / kTile + 2;
+    int32_t *tile_off2 = p->tile_off[pipe] + p->max_inputs / kTile + 2;
+    hop_flag_kernel<<<grid_for(edges, kTile, cap), kScanThreads, 0, s>>>(p->eslot[pipe], p->map[pipe], p->erank[pipe],
+                                                                         tile_sum2, tile_off2, ctl, p->max_nodes);
     LG_LAUNCH_CHECK();
-    hop_assign_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->erank, tile_off2, p->eslot, p->src_global,
-                                                                   p->ids[pipe], p->map, p->ctl);
+    hop_assign_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->erank[pipe], tile_off2, p->eslot[pipe],
+                                                                   p->src_global[pipe], p->ids[pipe], p->map[pipe], ctl);
     LG_LAUNCH_CHECK();
-    hop_relabel_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->eslot, p->map, p->agg_src[pipe], p->ctl,
-                                                                    p->node_counter[pipe], p->edge_counter[pipe],
-                                                                    op_id);
+    hop_relabel_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->eslot[pipe], p->map[pipe], p->agg_src[pipe], ctl,
+                                                                    p->node_counter[pipe], p->edge_counter[pipe], op_id);
     LG_LAUNCH_CHECK();
     return LEGION_OK;
 }

@@ -207,7 +207,7 @@ def test_lru_cache_sequence(oracle_mod, ways, sets, feat_len):
         cnt, feat, _ = rig.gather(it, pipe=it % 2)
         assert cnt == bsz
         ci = ref.lookup(ids, clock)
-        got_ci = rig.pool.read(L.BUF_CACHE_INDEX, 0, cnt, np.int64)
+        got_ci = rig.pool.read(L.BUF_CACHE_INDEX, it % 2, cnt, np.int64)
         np.testing.assert_array_equal(got_ci, ci)
         valid = ids >= 0
         got = feat.view(np.float32).reshape(cnt, feat_len)

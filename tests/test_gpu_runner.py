@@ -57,9 +57,11 @@ def _check_pipe(oracle_mod, w, pipe, it, global_batch):
     np.testing.assert_array_equal(feat, w["table"][ref["ids"]])
 
 
-def test_runner_two_batches_in_flight(oracle_mod):
+@pytest.mark.parametrize("use_graph", [True, False])
+def test_runner_two_batches_in_flight(oracle_mod, use_graph):
     w = _world(oracle_mod)
     r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], None)
+    r.set_options(use_graph=use_graph, time_kernels=True)
     # pairs of batches are enqueued back to back, then both pipes are checked
     for it in range(0, 6, 2):
         r.enqueue(it, L.TRAINMODE, it)
@@ -68,7 +70,7 @@ def test_runner_two_batches_in_flight(oracle_mod):
         _check_pipe(oracle_mod, w, 0, it, it)
         _check_pipe(oracle_mod, w, 1, it + 1, it + 1)
         t = r.timing()
-        assert t["batches"] == 2 and t["batch_ms"] > 0 and t["gather_ms"] > 0
+        assert t["batches"] == 2 and t["timed"] == 2 and t["batch_ms"] > 0 and t["gather_ms"] > 0 and t["miss_ms"] > 0
     # many batches without a sync in between: only the last two survive in the pipes
     for it in range(6):
         r.enqueue(10 + it, L.TRAINMODE, it)
@@ -78,7 +80,55 @@ def test_runner_two_batches_in_flight(oracle_mod):
     assert w["pool"].device_error() == 0
     r.RunOnce(20, L.TRAINMODE, 2)
     _check_pipe(oracle_mod, w, 0, 2, 20)
+    # switching the launch mode in the middle of a run keeps the results
+    r.set_options(use_graph=not use_graph, time_kernels=False)
+    r.enqueue(31, L.TRAINMODE, 3)
+    r.enqueue(32, L.TRAINMODE, 4)
+    r.sync()
+    _check_pipe(oracle_mod, w, 1, 3, 31)
+    _check_pipe(oracle_mod, w, 0, 4, 32)
+    assert r.timing()["timed"] == 0
     r.Finalize()
+
+
+def test_runner_with_lru_cache_keeps_batches_in_order(oracle_mod):
+    """Graph replay with an LRU cache: hit / miss sets of consecutive batches follow the host replay,
+    which inserts the rows of batch k before looking up batch k+1."""
+    import torch
+    w = _world(oracle_mod, n=3000, pairs=40000, feat_len=128, batch=64, fanout=(10, 5), seed=8)
+    sets, ways = 256, 8
+    cache = L.UnifiedCache(0, w["n"], 128 * 4, 0, lru=(sets, ways))
+    cache.set_host_table(w["h_table"])
+    ref = oracle_mod.LruCache(sets, ways)
+    for use_graph in (True, False):
+        r = L.Runner(0, w["g"], w["f"], cache, w["pool"], None)
+        r.set_options(use_graph=use_graph)
+        base = 0 if use_graph else 4
+        for it in range(4):
+            r.enqueue(base + it, L.TRAINMODE, (base + it) % 6)
+        r.sync()
+        # replay all four, compare the two that are still in the pipes and the final cache state
+        for it in range(4):
+            b = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], w["batch"], (base + it) % 6,
+                                     w["fanout"], base + it, 99)
+            clock = base + it + 1
+            ci = ref.lookup(b["ids"], clock)
+            ref.insert(b["ids"], ci, clock)
+            if it >= 2:
+                pipe = (base + it) % 2
+                got_ci = w["pool"].read(L.BUF_CACHE_INDEX, pipe, len(b["ids"]), np.int64)
+                np.testing.assert_array_equal(got_ci, ci)
+                feat = w["pool"].read(L.BUF_FEATURES, pipe, len(b["ids"]) * 128, np.float32).reshape(-1, 128)
+                np.testing.assert_array_equal(feat, w["table"][b["ids"]])
+        k, s, _ = cache.lru_state()
+        keys = np.empty(sets * ways, np.int32); stamps = np.empty(sets * ways, np.int32)
+        for dst, src in ((keys, k), (stamps, s)):
+            L._check(L.lib().legion_copy(dst.ctypes.data_as(L.C.c_void_p), L.C.c_void_p(src), L.C.c_int64(dst.nbytes),
+                                         L.C.c_int32(2)))
+        np.testing.assert_array_equal(keys, ref.keys)
+        np.testing.assert_array_equal(stamps, ref.stamps)
+        r.Finalize()
+    cache.close()
 
 
 def test_run_batch_host_buffers(oracle_mod):
@@ -104,6 +154,48 @@ def test_run_batch_host_buffers(oracle_mod):
         np.testing.assert_array_equal(dst[:n_edges], ref["agg_dst"])
         np.testing.assert_array_equal(lab[:len(seeds)], ref["labels"])
         np.testing.assert_array_equal(feat[:n_nodes], w["table"][ref["ids"]])
+
+
+@pytest.mark.parametrize("use_graph", [True, False])
+def test_submit_collect_host_pipelined(oracle_mod, use_graph):
+    """Host-buffer batches with two in flight: results arrive in submission order and match the replay."""
+    w = _world(oracle_mod, seed=4)
+    pool = w["pool"]
+    r = L.Runner(0, w["g"], w["f"], w["cache"], pool, None)
+    r.set_options(use_graph=use_graph)
+    ids = np.empty(pool.max_nodes, np.int32); lab = np.empty(w["batch"], np.int32)
+    src = np.empty(pool.max_edges, np.int32); dst = np.empty(pool.max_edges, np.int32)
+    nc = np.zeros(16, np.int32); ec = np.zeros(16, np.int32)
+    feat = np.empty((pool.max_nodes, w["table"].shape[1]), np.float32)
+    b = w["batch"]
+
+    def submit(it):
+        r.submit_host(w["train"][it * b:(it + 1) * b], w["labels"][it * b:(it + 1) * b], 70 + it)
+
+    def collect_and_check(it, with_features):
+        n_nodes, n_edges = r.collect_host(ids, lab, src, dst, nc, ec, feat if with_features else None)
+        ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], b, it, w["fanout"], 70 + it, 99)
+        assert n_nodes == len(ref["ids"]) and n_edges == len(ref["agg_src"])
+        np.testing.assert_array_equal(nc, ref["node_counter"])
+        np.testing.assert_array_equal(ec, ref["edge_counter"])
+        np.testing.assert_array_equal(ids[:n_nodes], ref["ids"])
+        np.testing.assert_array_equal(src[:n_edges], ref["agg_src"])
+        np.testing.assert_array_equal(dst[:n_edges], ref["agg_dst"])
+        np.testing.assert_array_equal(lab[:b], ref["labels"])
+        if with_features:
+            np.testing.assert_array_equal(feat[:n_nodes], w["table"][ref["ids"]])
+
+    submit(0)
+    for it in range(1, 6):
+        submit(it)
+        collect_and_check(it - 1, with_features=(it % 2 == 0))
+    with pytest.raises(L.LegionError, match="in flight"):
+        submit(6); submit(7)
+    collect_and_check(5, True)
+    collect_and_check(6, True)
+    with pytest.raises(L.LegionError, match="nothing was submitted"):
+        r.collect_host(ids, lab, src, dst, nc, ec, None)
+    r.Finalize()
 
 
 CONSUMER = r'''

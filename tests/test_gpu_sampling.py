@@ -49,7 +49,7 @@ def _fetch(pool, pipe=0):
                 labels=pool.read(L.BUF_LABELS, pipe, int(nc[9]), np.int32),
                 agg_src=pool.read(L.BUF_AGG_SRC, pipe, n_edges, np.int32),
                 agg_dst=pool.read(L.BUF_AGG_DST, pipe, n_edges, np.int32),
-                src_global=pool.read(L.BUF_SRC_GLOBAL, 0, n_edges, np.int32))
+                src_global=pool.read(L.BUF_SRC_GLOBAL, pipe, n_edges, np.int32))
 
 
 def _compare(got, ref):
