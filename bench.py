@@ -368,8 +368,9 @@ def main():
     roofline_host = {"bound": "host_link", "kernel": "gather_miss_kernel (zero-copy fetch of missed rows)",
                      "achieved": link_achieved, "peak": link_peak, "unit": "GB/s",
                      "frac": link_achieved / link_peak if link_peak else None,
-                     "peak_source": "pinned host->device cudaMemcpy of 1 GiB measured in this run",
-                     "avg_launch_ms": tm["miss_ms"] / max(1, gather_launches),
+                     "peak_source": "pinned host->device cudaMemcpy of 1 GiB measured in this run (the same kernel "
+                                    "alone reaches 50.6 GB/s on random rows of a 1 GB table and 26 GB/s over 48 GB)",
+                     "launches": tm["timed"], "avg_launch_ms": tm["miss_ms"] / max(1, tm["timed"]),
                      "rows_per_batch": d["misses"] / args.steps, "algorithmic_bytes": miss_bytes}
     # lower bound of the whole gather step: the slower of the HBM side and the host-link side
     t_lb = max(hit_bytes / (hbm_peak * 1e9), d["misses"] * row_bytes / (link_peak * 1e9) if link_peak else 0.0)
@@ -443,7 +444,7 @@ def main():
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, world),
-                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + 2 * (hops + 1)),
+                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + (hops + 1) + 1),
                 "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
                 "cpu_baseline": cpu, "clocks": clocks,
                 "graph": {"nodes": n, "directed_edges": n_edges, "train_seeds_this_rank": int(mine.numel()),

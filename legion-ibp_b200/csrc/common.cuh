@@ -155,8 +155,8 @@ struct LegionPool {
     int32_t *tile_sum[LEGION_INTERBATCH_CON], *tile_off[LEGION_INTERBATCH_CON];
     int32_t *eslot[LEGION_INTERBATCH_CON], *erank[LEGION_INTERBATCH_CON];
     int64_t *lru_victim[LEGION_INTERBATCH_CON];       // per node: way chosen for insertion, or -1
-    int32_t *miss_rows[LEGION_INTERBATCH_CON];        // rows to fetch from the host table, by segment
-    int32_t *miss_count[LEGION_INTERBATCH_CON];       // [0..3] entries per segment, [4] ticket
+    int32_t *miss_rows[LEGION_INTERBATCH_CON];        // rows to fetch from the host table
+    int32_t *miss_count[LEGION_INTERBATCH_CON];       // [0] entries, [4] ticket
     int32_t *ctl[LEGION_INTERBATCH_CON];
     legion::BatchCtl *bctl[LEGION_INTERBATCH_CON];
     int32_t *seed_stage[LEGION_INTERBATCH_CON], *label_stage[LEGION_INTERBATCH_CON];  // device staging for host-provided seeds
@@ -179,6 +179,6 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
                       int32_t op_id);
 int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
 int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
-int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
+int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c);
 int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c);
 }  // namespace legion

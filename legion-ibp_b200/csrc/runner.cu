@@ -6,8 +6,9 @@
 // read counters back to the host in between.  Here nothing is read back, and three streams carry
 // the three resources the path is bound by: sampling (latency of random topology reads) on one,
 // lookup + gather of cached rows (HBM / NVLink bandwidth) on a second one behind an event per
-// segment, and the fetch of missed rows from pinned host memory (host link) on a third.  The
-// gather of hop h overlaps the sampling of hop h+1.
+// segment, and the fetch of missed rows from pinned host memory (host link) on a third, as one
+// launch per batch behind the last gather so that the link sees one long burst instead of three
+// short ones.  The gather of hop h overlaps the sampling of hop h+1.
 //
 // A batch is ~25 small launches, so issuing it from the host costs more than running it.  Every
 // size lives on the device and the per-batch parameters are written by the first kernel, so the
@@ -43,7 +44,7 @@ struct PipeGraph {
     void *args[7];
     bool valid;
     bool launched;  // since the last sync
-    EvPair hit[LEGION_MAX_HOPS + 1], miss[LEGION_MAX_HOPS + 1];
+    EvPair hit[LEGION_MAX_HOPS + 1], miss;
 };
 
 }  // namespace
@@ -143,9 +144,9 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
         for (int s = 0; s <= LEGION_MAX_HOPS; ++s) {
             LG_CUDA(cudaEventCreate(&r->pg[i].hit[s].a));
             LG_CUDA(cudaEventCreate(&r->pg[i].hit[s].b));
-            LG_CUDA(cudaEventCreate(&r->pg[i].miss[s].a));
-            LG_CUDA(cudaEventCreate(&r->pg[i].miss[s].b));
         }
+        LG_CUDA(cudaEventCreate(&r->pg[i].miss.a));
+        LG_CUDA(cudaEventCreate(&r->pg[i].miss.b));
     }
     LG_CUDA(cudaEventCreate(&r->t_begin));
     LG_CUDA(cudaEventCreate(&r->t_end));
@@ -183,21 +184,19 @@ static cudaError_t mark(cudaEvent_t e, cudaStream_t s, bool capturing)
     return capturing ? cudaEventRecordWithFlags(e, s, cudaEventRecordExternal) : cudaEventRecord(e, s);
 }
 
-// One segment: cached rows on the gather stream, missed rows on the miss stream behind it.
+// One segment: lookup and cached rows on the gather stream; missed rows are only listed here.
 static int gather_segment(LegionRunner *r, int op_id, int seg, bool capturing)
 {
     LegionPool *p = r->pool;
     LegionCache *c = r->cache;
     if (c != nullptr) LG_ARG(c->row_bytes == p->row_bytes_out, "cache and pool disagree on the row size");
-    const bool has_miss = c != nullptr && c->host_table != nullptr;
-    EvPair h = { nullptr, nullptr }, m = { nullptr, nullptr };
+    EvPair h = { nullptr, nullptr };
     if (r->time_kernels) {
         if (capturing) {
             h = r->pg[p->pipe].hit[seg];
-            m = r->pg[p->pipe].miss[seg];
         } else if (r->gather_ev.size() < 8192) {
-            h.a = take_event(r); h.b = take_event(r);
-            if (has_miss) { m.a = take_event(r); m.b = take_event(r); }
+            h.a = take_event(r);
+            h.b = take_event(r);
         }
     }
     if (h.a) LG_CUDA(mark(h.a, r->s_gather, capturing));
@@ -205,15 +204,6 @@ static int gather_segment(LegionRunner *r, int op_id, int seg, bool capturing)
     if (rc != LEGION_OK) return rc;
     if (h.b) LG_CUDA(mark(h.b, r->s_gather, capturing));
     if (h.a && h.b && !capturing) r->gather_ev.push_back(h);
-    LG_CUDA(cudaEventRecord(r->hit_done[seg], r->s_gather));
-    LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->hit_done[seg], 0));
-    if (has_miss) {
-        if (m.a) LG_CUDA(mark(m.a, r->s_miss, capturing));
-        rc = launch_gather_misses(r->s_miss, p, c, op_id);
-        if (rc != LEGION_OK) return rc;
-        if (m.b) LG_CUDA(mark(m.b, r->s_miss, capturing));
-        if (m.a && m.b && !capturing) r->miss_ev.push_back(m);
-    }
     return LEGION_OK;
 }
 
@@ -221,6 +211,7 @@ static int gather_segment(LegionRunner *r, int op_id, int seg, bool capturing)
 static int issue_batch(LegionRunner *r, const BatchCtl &v, bool capturing)
 {
     LegionPool *p = r->pool;
+    LegionCache *c = r->cache;
     int rc = launch_batch_generate(r->s_sample, p, v);
     if (rc != LEGION_OK) return rc;
     LG_CUDA(cudaEventRecord(r->seg_ready[0], r->s_sample));
@@ -236,7 +227,26 @@ static int issue_batch(LegionRunner *r, const BatchCtl &v, bool capturing)
         rc = gather_segment(r, op + 1, h + 1, capturing);
         if (rc != LEGION_OK) return rc;
     }
-    return launch_lru_insert(r->s_miss, p, r->cache);  // IOComplete; every gather precedes it on s_miss
+    // every row that missed is on the list now
+    LG_CUDA(cudaEventRecord(r->hit_done[0], r->s_gather));
+    LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->hit_done[0], 0));
+    if (c != nullptr && c->host_table != nullptr) {
+        EvPair m = { nullptr, nullptr };
+        if (r->time_kernels) {
+            if (capturing) {
+                m = r->pg[p->pipe].miss;
+            } else if (r->miss_ev.size() < 8192) {
+                m.a = take_event(r);
+                m.b = take_event(r);
+            }
+        }
+        if (m.a) LG_CUDA(mark(m.a, r->s_miss, capturing));
+        rc = launch_gather_misses(r->s_miss, p, c);
+        if (rc != LEGION_OK) return rc;
+        if (m.b) LG_CUDA(mark(m.b, r->s_miss, capturing));
+        if (m.a && m.b && !capturing) r->miss_ev.push_back(m);
+    }
+    return launch_lru_insert(r->s_miss, p, c);  // IOComplete
 }
 
 static int capture_pipe(LegionRunner *r, int pipe, const BatchCtl &v)
@@ -491,11 +501,10 @@ extern "C" int legion_runner_sync(LegionRunner *r)
             const bool has_miss = r->cache != nullptr && r->cache->host_table != nullptr;
             for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
                 if (!r->pg[i].launched) continue;
-                for (int s = 0; s <= r->pool->hop_num; ++s) {
-                    float t = 0.0f;
+                float t = 0.0f;
+                for (int s = 0; s <= r->pool->hop_num; ++s)
                     if (cudaEventElapsedTime(&t, r->pg[i].hit[s].a, r->pg[i].hit[s].b) == cudaSuccess) g += t;
-                    if (has_miss && cudaEventElapsedTime(&t, r->pg[i].miss[s].a, r->pg[i].miss[s].b) == cudaSuccess) m += t;
-                }
+                if (has_miss && cudaEventElapsedTime(&t, r->pg[i].miss.a, r->pg[i].miss.b) == cudaSuccess) m += t;
                 timed += 1;
             }
         }
@@ -603,8 +612,8 @@ extern "C" int legion_runner_destroy(LegionRunner *r)
         cudaStreamDestroy(r->s_launch[i]);
         for (int s = 0; s <= LEGION_MAX_HOPS; ++s) {
             cudaEventDestroy(r->pg[i].hit[s].a); cudaEventDestroy(r->pg[i].hit[s].b);
-            cudaEventDestroy(r->pg[i].miss[s].a); cudaEventDestroy(r->pg[i].miss[s].b);
         }
+        cudaEventDestroy(r->pg[i].miss.a); cudaEventDestroy(r->pg[i].miss.b);
     }
     cudaEventDestroy(r->t_begin);
     cudaEventDestroy(r->t_end);

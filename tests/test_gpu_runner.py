@@ -189,10 +189,11 @@ def test_submit_collect_host_pipelined(oracle_mod, use_graph):
     for it in range(1, 6):
         submit(it)
         collect_and_check(it - 1, with_features=(it % 2 == 0))
+    submit(0)                       # two in flight now (5 and 0)
     with pytest.raises(L.LegionError, match="in flight"):
-        submit(6); submit(7)
+        submit(1)
     collect_and_check(5, True)
-    collect_and_check(6, True)
+    collect_and_check(0, True)
     with pytest.raises(L.LegionError, match="nothing was submitted"):
         r.collect_host(ids, lab, src, dst, nc, ec, None)
     r.Finalize()
