@@ -217,10 +217,14 @@ def main():
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--cpu-sample-batches", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cache-frac", type=float, default=None, help="override the cached fraction of the table")
+    ap.add_argument("--pipes", type=int, default=2, help="batches in flight (the hand-off protocol uses 2)")
     ap.add_argument("--profile-only", action="store_true",
                     help="set-up, warm-up and the timed steps only (for runs under a profiler); prints no bench line")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.cache_frac is not None:
+        cfg["cache_frac"] = args.cache_frac
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
@@ -270,7 +274,7 @@ def main():
     del order
     if world > 1:
         exchange_partitions(L, cache, rank, world, dist)
-    pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, 2)
+    pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, args.pipes)
     pool.set_rng(0x5EED + rank, 64)
     runner = L.Runner(dev, g, fs, cache, pool, None)
     n_iters = (int(mine.numel()) - 1) // cfg["batch"]

@@ -249,8 +249,9 @@ int legion_runner_set_options(LegionRunner *r, int32_t use_graph, int32_t time_k
 /* Device time of the batches enqueued between the last two legion_runner_sync calls, measured
  * with CUDA events (ms).  With time_kernels: gather_ms is the sum over the launches that gather
  * cached rows (HBM / peer memory), miss_ms the sum over the launches that fetch missed rows from
- * pinned host memory, over n_timed batches (all batches of the window when launching one by one;
- * the last batch of each pipe when replaying graphs, whose events are overwritten per launch). */
+ * pinned host memory (every batch of the window); gather_ms covers n_timed batches: all batches of
+ * the window when launching one by one, the last batch of each pipe when replaying graphs, whose
+ * events are overwritten per launch. */
 int legion_runner_timing(LegionRunner *r, float *batch_ms, float *gather_ms, float *miss_ms, int32_t *n_batches,
                          int32_t *n_timed);
 /* The serving loop of GPUServer (engine/server.cu:39-44,124-143) for `count` batches starting at

@@ -12,11 +12,14 @@
 //
 // A batch is ~25 small launches, so issuing it from the host costs more than running it.  Every
 // size lives on the device and the per-batch parameters are written by the first kernel, so the
-// whole three-stream sequence of one pipe is captured once into a CUDA graph; a batch is then one
-// parameter update of that first node plus one graph launch.  The two pipes own separate scratch
-// and are launched on two streams, so consecutive batches overlap freely (the host-link traffic of
-// batch k runs under the sampling of batch k+1); an LRU cache, whose state changes every batch,
-// keeps them in order by using one launch stream.
+// sampling + gather sequence of one pipe (two streams) is captured once into a CUDA graph; a batch
+// is then one parameter update of that first node, one graph launch and the host-link fetch.  The
+// two pipes own separate scratch and are launched on two streams, so consecutive batches overlap.
+// The host-link fetches of all batches run in order on one stream of their own, outside the
+// graphs: if they shared the link, two batches would enter and leave their host-link phase
+// together and the link would idle while both sample; first-in first-out staggers them, so the
+// fetch of batch k runs under the sampling and gathering of batch k+1.  An LRU cache, whose state
+// changes every batch, keeps whole batches in order.
 #include "common.cuh"
 
 #include <string.h>
@@ -44,7 +47,7 @@ struct PipeGraph {
     void *args[7];
     bool valid;
     bool launched;  // since the last sync
-    EvPair hit[LEGION_MAX_HOPS + 1], miss;
+    EvPair hit[LEGION_MAX_HOPS + 1];
 };
 
 }  // namespace
@@ -145,8 +148,6 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
             LG_CUDA(cudaEventCreate(&r->pg[i].hit[s].a));
             LG_CUDA(cudaEventCreate(&r->pg[i].hit[s].b));
         }
-        LG_CUDA(cudaEventCreate(&r->pg[i].miss.a));
-        LG_CUDA(cudaEventCreate(&r->pg[i].miss.b));
     }
     LG_CUDA(cudaEventCreate(&r->t_begin));
     LG_CUDA(cudaEventCreate(&r->t_end));
@@ -207,11 +208,11 @@ static int gather_segment(LegionRunner *r, int op_id, int seg, bool capturing)
     return LEGION_OK;
 }
 
-// The whole batch on the three streams; origin s_sample, last work on s_miss.
-static int issue_batch(LegionRunner *r, const BatchCtl &v, bool capturing)
+// Sampling and the gather of cached rows, on s_sample and s_gather; origin s_sample, last work on
+// s_gather.  This is the part that is captured into the pipe's graph.
+static int issue_front(LegionRunner *r, const BatchCtl &v, bool capturing)
 {
     LegionPool *p = r->pool;
-    LegionCache *c = r->cache;
     int rc = launch_batch_generate(r->s_sample, p, v);
     if (rc != LEGION_OK) return rc;
     LG_CUDA(cudaEventRecord(r->seg_ready[0], r->s_sample));
@@ -227,24 +228,26 @@ static int issue_batch(LegionRunner *r, const BatchCtl &v, bool capturing)
         rc = gather_segment(r, op + 1, h + 1, capturing);
         if (rc != LEGION_OK) return rc;
     }
-    // every row that missed is on the list now
-    LG_CUDA(cudaEventRecord(r->hit_done[0], r->s_gather));
-    LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->hit_done[0], 0));
+    return LEGION_OK;
+}
+
+// The rows that missed (all on the list once the front part is over) and the end-of-batch cache
+// maintenance, on s_miss, which every batch shares.
+static int issue_back(LegionRunner *r)
+{
+    LegionPool *p = r->pool;
+    LegionCache *c = r->cache;
     if (c != nullptr && c->host_table != nullptr) {
         EvPair m = { nullptr, nullptr };
-        if (r->time_kernels) {
-            if (capturing) {
-                m = r->pg[p->pipe].miss;
-            } else if (r->miss_ev.size() < 8192) {
-                m.a = take_event(r);
-                m.b = take_event(r);
-            }
+        if (r->time_kernels && r->miss_ev.size() < 8192) {
+            m.a = take_event(r);
+            m.b = take_event(r);
         }
-        if (m.a) LG_CUDA(mark(m.a, r->s_miss, capturing));
-        rc = launch_gather_misses(r->s_miss, p, c);
+        if (m.a) LG_CUDA(cudaEventRecord(m.a, r->s_miss));
+        int rc = launch_gather_misses(r->s_miss, p, c);
         if (rc != LEGION_OK) return rc;
-        if (m.b) LG_CUDA(mark(m.b, r->s_miss, capturing));
-        if (m.a && m.b && !capturing) r->miss_ev.push_back(m);
+        if (m.b) LG_CUDA(cudaEventRecord(m.b, r->s_miss));
+        if (m.a && m.b) r->miss_ev.push_back(m);
     }
     return launch_lru_insert(r->s_miss, p, c);  // IOComplete
 }
@@ -253,10 +256,10 @@ static int capture_pipe(LegionRunner *r, int pipe, const BatchCtl &v)
 {
     PipeGraph &g = r->pg[pipe];
     LG_CUDA(cudaStreamBeginCapture(r->s_sample, cudaStreamCaptureModeThreadLocal));
-    int rc = issue_batch(r, v, true);
+    int rc = issue_front(r, v, true);
     cudaError_t e = cudaSuccess;
     if (rc == LEGION_OK) {
-        e = cudaEventRecord(r->join_ev, r->s_miss);
+        e = cudaEventRecord(r->join_ev, r->s_gather);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(r->s_sample, r->join_ev, 0);
     }
     cudaGraph_t graph = nullptr;
@@ -320,26 +323,22 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
     const int pipe = r->current_pipe;
     int rc;
     const bool lru = c != nullptr && c->kind == 1;
-    // two launch streams let consecutive batches overlap; an LRU cache needs them in order
-    cudaStream_t launch = r->use_graph ? r->s_launch[lru ? 0 : pipe] : r->s_sample;
-    cudaStream_t tail = r->use_graph ? launch : r->s_miss;
+    cudaStream_t front = r->use_graph ? r->s_launch[pipe] : r->s_sample;
     if (!r->open_window) {
-        LG_CUDA(cudaEventRecord(r->t_begin, launch));
+        LG_CUDA(cudaEventRecord(r->t_begin, front));
         r->open_window = true;
         r->window_batches = 0;
     }
-    if (!r->use_graph) {
-        // the buffers of this pipe are rewritten: the gather that last read them must be over;
-        // an LRU cache also has to see the previous batch's insertions before the next lookup
-        if (r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(r->s_sample, r->pipe_done[pipe], 0));
-        if (lru && r->last_pipe >= 0 && r->pipe_busy[r->last_pipe])
-            LG_CUDA(cudaStreamWaitEvent(r->s_sample, r->pipe_done[r->last_pipe], 0));
-    }
+    // the buffers of this pipe are rewritten: the fetch that last wrote them must be over;
+    // an LRU cache also has to see the previous batch's insertions before the next lookup
+    if (r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
+    if (lru && r->last_pipe >= 0 && r->last_pipe != pipe && r->pipe_busy[r->last_pipe])
+        LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[r->last_pipe], 0));
     if (host_seeds > 0) {
         int32_t *hs = p->h_stage[pipe];
-        LG_CUDA(cudaMemcpyAsync(p->seed_stage[pipe], hs, sizeof(int32_t) * host_seeds, cudaMemcpyHostToDevice, launch));
+        LG_CUDA(cudaMemcpyAsync(p->seed_stage[pipe], hs, sizeof(int32_t) * host_seeds, cudaMemcpyHostToDevice, front));
         LG_CUDA(cudaMemcpyAsync(p->label_stage[pipe], hs + p->batch_size, sizeof(int32_t) * host_seeds,
-                                cudaMemcpyHostToDevice, launch));
+                                cudaMemcpyHostToDevice, front));
     }
     if (r->use_graph) {
         PipeGraph &g = r->pg[pipe];
@@ -349,18 +348,23 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
         }
         g.a_value = v;
         LG_CUDA(cudaGraphExecKernelNodeSetParams(g.exec, g.ctl_node, &g.ctl_params));
-        LG_CUDA(cudaGraphLaunch(g.exec, launch));
+        LG_CUDA(cudaGraphLaunch(g.exec, front));
         g.launched = true;
+        LG_CUDA(cudaEventRecord(r->hit_done[pipe], front));
     } else {
-        rc = issue_batch(r, v, false);
+        rc = issue_front(r, v, false);
         if (rc != LEGION_OK) return rc;
+        LG_CUDA(cudaEventRecord(r->hit_done[pipe], r->s_gather));
     }
+    LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->hit_done[pipe], 0));
+    rc = issue_back(r);
+    if (rc != LEGION_OK) return rc;
     if (host_seeds > 0) {
         int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
-        LG_CUDA(cudaMemcpyAsync(hc, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, tail));
-        LG_CUDA(cudaMemcpyAsync(hc + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, tail));
+        LG_CUDA(cudaMemcpyAsync(hc, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_miss));
+        LG_CUDA(cudaMemcpyAsync(hc + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_miss));
     }
-    LG_CUDA(cudaEventRecord(r->pipe_done[pipe], tail));
+    LG_CUDA(cudaEventRecord(r->pipe_done[pipe], r->s_miss));
     if (lru) c->clock += 1;
     r->pipe_busy[pipe] = true;
     r->last_pipe = pipe;
@@ -463,16 +467,7 @@ extern "C" int legion_runner_sync(LegionRunner *r)
 {
     LG_ARG(r != nullptr, "runner is NULL");
     LG_CUDA(cudaSetDevice(r->dev_id));
-    if (r->open_window) {
-        if (r->use_graph) {
-            // t_end after both launch streams
-            LG_CUDA(cudaEventRecord(r->cross_ev, r->s_launch[1]));
-            LG_CUDA(cudaStreamWaitEvent(r->s_launch[0], r->cross_ev, 0));
-            LG_CUDA(cudaEventRecord(r->t_end, r->s_launch[0]));
-        } else {
-            LG_CUDA(cudaEventRecord(r->t_end, r->s_miss));  // the miss stream ends every batch
-        }
-    }
+    if (r->open_window) LG_CUDA(cudaEventRecord(r->t_end, r->s_miss));  // the miss stream ends every batch
     LG_CUDA(cudaStreamSynchronize(r->s_sample));
     LG_CUDA(cudaStreamSynchronize(r->s_gather));
     LG_CUDA(cudaStreamSynchronize(r->s_miss));
@@ -497,14 +492,12 @@ extern "C" int legion_runner_sync(LegionRunner *r)
         r->gather_ev.clear();
         r->miss_ev.clear();
         if (r->use_graph && r->time_kernels) {
-            // the events of a pipe's graph hold the times of its last launch
-            const bool has_miss = r->cache != nullptr && r->cache->host_table != nullptr;
+            // the events inside a pipe's graph hold the times of its last launch
             for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
                 if (!r->pg[i].launched) continue;
                 float t = 0.0f;
                 for (int s = 0; s <= r->pool->hop_num; ++s)
                     if (cudaEventElapsedTime(&t, r->pg[i].hit[s].a, r->pg[i].hit[s].b) == cudaSuccess) g += t;
-                if (has_miss && cudaEventElapsedTime(&t, r->pg[i].miss.a, r->pg[i].miss.b) == cudaSuccess) m += t;
                 timed += 1;
             }
         }
@@ -613,7 +606,6 @@ extern "C" int legion_runner_destroy(LegionRunner *r)
         for (int s = 0; s <= LEGION_MAX_HOPS; ++s) {
             cudaEventDestroy(r->pg[i].hit[s].a); cudaEventDestroy(r->pg[i].hit[s].b);
         }
-        cudaEventDestroy(r->pg[i].miss.a); cudaEventDestroy(r->pg[i].miss.b);
     }
     cudaEventDestroy(r->t_begin);
     cudaEventDestroy(r->t_end);
