@@ -166,6 +166,36 @@ int legion_io_submit(void *stream, LegionFeatures *feature, LegionPool *pool, in
  * position_map; here the LRU insertion phase runs). */
 int legion_io_complete(void *stream, LegionCache *cache, LegionPool *pool, int32_t dev_id, int32_t mode);
 
+/* Lookup + gather of one id list without any allocation.  No counterpart in the reference (there
+ * FeatureCacheLookup always works on a MemoryPool that was allocated beforehand).
+ *
+ * For callers that must not allocate device memory at the moment they call in: a trainer-side
+ * process whose framework allocator already owns the GPU's memory, or a serving loop that cannot
+ * take the device-wide synchronisation, the fragmentation or the failure of a cudaMalloc in the
+ * middle of a step.  The caller passes inputs and output only; the scratch the gather needs (hit /
+ * miss index per row, the list of missed rows, its counters) lives in a fixed array inside the
+ * library image, so every GPU that loads the library holds about 2 MB for it until the process
+ * exits.  This call, and everything it calls, performs no cudaMalloc / cudaFree.
+ *
+ *   ids_dev      n_rows int32 node ids on the device (ids < 0 leave their output row untouched)
+ *   lut_dev      one int32 per node: gpu*capacity + row for a cached node, LEGION_CACHEMISS_FLAG
+ *                otherwise (legion_cache_lut); NULL = nothing is cached
+ *   partitions   host array of kg device pointers, the clique's cache partitions (uncompressed rows)
+ *   host_table   pinned host table that serves the misses, or NULL (missed rows stay untouched)
+ *   out_dev      n_rows * row_bytes bytes on the device, rows in the order of ids_dev
+ *
+ * Limits and rules: n_rows <= LEGION_NOALLOC_MAX_ROWS (LEGION_E_LIMIT with a message otherwise;
+ * split the list or use a LegionPool); rows are multiples of 4 bytes.  The first call on a device
+ * looks up the device address of the built-in array; make that first call before starting any
+ * stream capture.  All calls share the one array: calls whose kernels overlap on the same GPU
+ * (different streams, different threads) race on it, so keep them on one stream or order them with
+ * events.  The array keeps the previous call's contents; the call resets what has to start from zero. */
+#define LEGION_NOALLOC_MAX_ROWS (1 << 18)
+int legion_gather_rows_noalloc(void *stream, int32_t dev_id, const int32_t *ids_dev, int64_t n_rows,
+                               const int32_t *lut_dev, int32_t capacity, int32_t kg, int32_t ki,
+                               const void *const *partitions, const void *host_table, int64_t n_nodes,
+                               int32_t row_bytes, void *out_dev);
+
 /* ---- whole batch --------------------------------------------------------------------- */
 
 /* The op list of GPURunner::RunOnce (engine/server.cu:342-351) for one batch on one stream set.

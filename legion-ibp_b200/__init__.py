@@ -273,6 +273,21 @@ def run_batch_host(graph, feature, cache, pool, dev_id, seeds, labels, ids_out, 
     return int(nc_out[INTRABATCH_CON * 3 + hops]), int(ec_out[0] + ec_out[1])
 
 
+NOALLOC_MAX_ROWS = 1 << 18
+
+
+def gather_rows_noalloc(stream, dev_id, ids_dev, lut_ptr, capacity, kg, ki, partition_ptrs, host_table, n_nodes,
+                        row_bytes, out_dev):
+    """Lookup + gather of one id list through the entry point that allocates nothing (its scratch is a
+    fixed array inside the library).  For callers that must not allocate device memory when they call in;
+    at most NOALLOC_MAX_ROWS ids per call, calls on one GPU must not overlap."""
+    parts = (C.c_void_p * max(1, len(partition_ptrs)))(*partition_ptrs)
+    _check(lib().legion_gather_rows_noalloc(_stream(stream), C.c_int32(dev_id), _ptr(ids_dev),
+                                            C.c_int64(ids_dev.numel()), C.c_void_p(lut_ptr), C.c_int32(capacity),
+                                            C.c_int32(kg), C.c_int32(ki), parts, _ptr(host_table), C.c_int64(n_nodes),
+                                            C.c_int32(row_bytes), _ptr(out_dev)))
+
+
 class IPCEnv:
     """Shared segment + semaphores of the server <-> trainer hand-off (engine/ipc_service.h:6-35)."""
 

@@ -645,3 +645,137 @@ int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c)
 }
 
 }  // namespace legion
+
+// ---- gather without any allocation ---------------------------------------------------------------------
+// legion_gather_rows_noalloc: the lookup + gather of one list of node ids (cached rows from the
+// clique's partitions, the others from the pinned host table) for callers that must not allocate
+// device memory when they call into this library: a trainer-side process whose framework allocator
+// already owns the GPU's memory, or a serving loop that cannot afford the device-wide
+// synchronisation, the fragmentation or the failure of a cudaMalloc in the middle of a step.  The
+// entry points above take their scratch (cache_index, the miss list and its counters, the segment
+// words the kernels read) from a LegionPool, which allocates; this one keeps the same scratch in a
+// fixed array inside the library image.  Every GPU that loads the library holds that array
+// (256 B + 8 B per row of LEGION_NOALLOC_MAX_ROWS, about 2 MB) until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[256 + 8 * (size_t)LEGION_NOALLOC_MAX_ROWS];
+
+namespace legion {
+
+// byte offsets inside the array
+constexpr size_t kNaCounter = 0;     // 16 int32: the node_counter words the gather kernels read
+constexpr size_t kNaMissCount = 64;  // 8 int32: [0] entries of the miss list, [4] ticket
+constexpr size_t kNaMissRows = 256;  // int32[LEGION_NOALLOC_MAX_ROWS]
+constexpr size_t kNaCacheIndex = 256 + 4 * (size_t)LEGION_NOALLOC_MAX_ROWS;  // int32[LEGION_NOALLOC_MAX_ROWS]
+
+// The array is shared by every call and keeps what the last call left: the words that must start
+// from a known value are rewritten here at the start of each call.
+__global__ void noalloc_setup_kernel(int32_t *nc, int32_t *miss_count, int32_t n_rows)
+{
+    const int t = threadIdx.x;
+    if (t < 16) nc[t] = 0;
+    if (t < 8) miss_count[t] = 0;
+    __syncthreads();
+    if (t == 0) {
+        nc[LEGION_INTRABATCH_CON * 3 - 1] = 0;   // no hops: one segment
+        nc[LEGION_INTRABATCH_CON * 3] = n_rows;  // rows [0, n_rows)
+    }
+}
+
+}  // namespace legion
+
+// In host code the name g_noalloc_scratch is only a stand-in for the device array: its device
+// address is asked for once per device, with that device current, and kept here.
+static void *g_noalloc_ptr[64] = { nullptr };
+static cudaError_t noalloc_scratch_of(int dev_id, unsigned char **out)
+{
+    if (g_noalloc_ptr[dev_id] == nullptr) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        g_noalloc_ptr[dev_id] = p;
+    }
+    *out = (unsigned char *)g_noalloc_ptr[dev_id];
+    return cudaSuccess;
+}
+
+extern "C" int legion_gather_rows_noalloc(void *stream, int32_t dev_id, const int32_t *ids_dev, int64_t n_rows,
+                                          const int32_t *lut_dev, int32_t capacity, int32_t kg, int32_t ki,
+                                          const void *const *partitions, const void *host_table, int64_t n_nodes,
+                                          int32_t row_bytes, void *out_dev)
+{
+    using namespace legion;
+    LG_ARG(dev_id >= 0 && dev_id < 64, "dev_id out of range");
+    LG_ARG(n_rows >= 0 && (n_rows == 0 || (ids_dev != nullptr && out_dev != nullptr)), "NULL pointer");
+    if (n_rows > LEGION_NOALLOC_MAX_ROWS) {
+        set_error("legion_gather_rows_noalloc: %lld rows are above the built-in scratch of %d rows; split the list or "
+                  "use legion_feature_cache_lookup with a LegionPool",
+                  (long long)n_rows, LEGION_NOALLOC_MAX_ROWS);
+        return LEGION_E_LIMIT;
+    }
+    LG_ARG(row_bytes > 0 && row_bytes % 4 == 0, "row_bytes must be a positive multiple of 4");
+    LG_ARG(kg >= 1 && kg <= LEGION_MAX_DEVICE && ki >= 0 && ki < kg, "bad clique size or member index");
+    LG_ARG(lut_dev == nullptr || (capacity > 0 && partitions != nullptr), "a lookup table needs partitions");
+    LG_ARG(n_nodes > 0, "n_nodes must be positive");
+    LG_CUDA(cudaSetDevice(dev_id));
+    unsigned char *scratch = nullptr;
+    LG_CUDA(noalloc_scratch_of(dev_id, &scratch));
+    if (n_rows == 0) return LEGION_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    int32_t *nc = reinterpret_cast<int32_t *>(scratch + kNaCounter);
+    int32_t *miss_count = reinterpret_cast<int32_t *>(scratch + kNaMissCount);
+    noalloc_setup_kernel<<<1, 32, 0, s>>>(nc, miss_count, (int32_t)n_rows);
+    LG_LAUNCH_CHECK();
+
+    GatherParams gp;
+    gp.ids = ids_dev;
+    gp.nc = nc;
+    gp.op_id = 1;
+    gp.lut = lut_dev;
+    gp.capacity = capacity > 0 ? capacity : 1;
+    gp.kg = kg;
+    gp.ki = ki;
+    for (int k = 0; k < LEGION_MAX_DEVICE; ++k)
+        gp.part[k] = (lut_dev != nullptr && k < kg) ? (const uint8_t *)partitions[k] : nullptr;
+    gp.host = (const uint8_t *)host_table;
+    gp.n_nodes = n_nodes;
+    gp.dst = (uint8_t *)out_dev;
+    gp.cache_index = reinterpret_cast<int32_t *>(scratch + kNaCacheIndex);
+    gp.stats = nullptr;
+    gp.row_bytes = row_bytes;
+    gp.slot_bytes = row_bytes;
+    gp.feature_len = row_bytes / 4;
+    gp.miss_rows = reinterpret_cast<int32_t *>(scratch + kNaMissRows);
+    gp.miss_count = miss_count;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_id);
+    if (sms <= 0) sms = 148;
+    int64_t g64 = ((n_rows + 31) / 32 + 7) / 8;
+    int grid = (int)(g64 < 1 ? 1 : (g64 > (int64_t)sms * 8 ? (int64_t)sms * 8 : g64));
+    if (row_bytes % 16 == 0 && row_bytes <= 2048) {
+        int vpl = (row_bytes / 16 + 31) / 32;
+        switch (vpl) {
+        case 1: launch_vec<1, 4>(grid, s, gp); break;
+        case 2: launch_vec<2, 2>(grid, s, gp); break;
+        case 3: launch_vec<3, 2>(grid, s, gp); break;
+        default: launch_vec<4, 2>(grid, s, gp); break;
+        }
+    } else {
+        gather_word_kernel<<<grid, 256, 0, s>>>(gp);
+    }
+    LG_LAUNCH_CHECK();
+    if (host_table != nullptr) {
+        MissParams mp;
+        mp.ids = ids_dev;
+        mp.miss_rows = gp.miss_rows;
+        mp.miss_count = miss_count;
+        mp.ticket = miss_count + 4;
+        mp.host = (const uint8_t *)host_table;
+        mp.n_nodes = n_nodes;
+        mp.dst = (uint8_t *)out_dev;
+        mp.row_bytes = row_bytes;
+        int64_t m64 = (n_rows + 31) / 32;
+        int mgrid = (int)(m64 < 1 ? 1 : (m64 > (int64_t)sms * 2 ? (int64_t)sms * 2 : m64));
+        gather_miss_kernel<4><<<mgrid, 256, 0, s>>>(mp);
+        LG_LAUNCH_CHECK();
+    }
+    return LEGION_OK;
+}
