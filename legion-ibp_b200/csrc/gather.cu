@@ -606,9 +606,10 @@ int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c)
     mp.n_nodes = c->n_nodes;
     mp.dst = (uint8_t *)p->features[pipe];
     mp.row_bytes = p->row_bytes_out;
-    // 4 rows per warp and pass; at most two CTAs per SM so that HBM-bound kernels keep their share
+    // 4 rows per warp and pass; one CTA per SM keeps ~2.4 MB of reads in flight, far more than the
+    // host link needs, and leaves the SMs to the HBM-bound kernels of the next batch
     int64_t g64 = (p->max_nodes + 31) / 32;
-    int cap = p->sm_count * 2;
+    int cap = p->sm_count;
     int grid = (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
     gather_miss_kernel<4><<<grid, 256, 0, s>>>(mp);
     LG_LAUNCH_CHECK();

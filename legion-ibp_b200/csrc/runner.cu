@@ -132,7 +132,13 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_copy, cudaStreamNonBlocking));
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_sample, cudaStreamNonBlocking));
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_gather, cudaStreamNonBlocking));
-    LG_CUDA(cudaStreamCreateWithFlags(&r->s_miss, cudaStreamNonBlocking));
+    {
+        // The host-link fetch needs few SM resources but a long time: at the highest priority its
+        // CTAs take the next free slots instead of queueing behind the wide kernels of the other batch.
+        int lo = 0, hi = 0;
+        LG_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        LG_CUDA(cudaStreamCreateWithPriority(&r->s_miss, cudaStreamNonBlocking, hi));
+    }
     for (int i = 0; i <= LEGION_MAX_HOPS; ++i) {
         LG_CUDA(cudaEventCreateWithFlags(&r->seg_ready[i], cudaEventDisableTiming));
         LG_CUDA(cudaEventCreateWithFlags(&r->hit_done[i], cudaEventDisableTiming));
