@@ -58,6 +58,10 @@ int legion_abi_version(void);
  * 2 device->host, 3 device->device. */
 int legion_copy(void *dst, const void *src, int64_t bytes, int32_t kind);
 
+/* EnableP2PAccess (storage/storage_management.cu:9-27) for one ordered pair of devices of this
+ * process; needed when the clique's partitions are allocated by threads of one process. */
+int legion_enable_peer_access(int32_t dev_id, int32_t peer_id);
+
 /* ---- storage --------------------------------------------------------------------- */
 
 /* NewCompleteGraphStorage + Build (storage/graph_storage.cu:12-74).  indptr/indices must be

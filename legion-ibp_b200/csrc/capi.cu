@@ -424,3 +424,24 @@ extern "C" int legion_copy(void *dst, const void *src, int64_t bytes, int32_t ki
     LG_CUDA(cudaMemcpy(dst, src, (size_t)bytes, (cudaMemcpyKind)kind));
     return LEGION_OK;
 }
+
+// EnableP2PAccess (storage/storage_management.cu:9-27) for one pair: lets kernels of `dev_id` read
+// memory of `peer_id` allocated in this process.  Already-enabled is not an error.
+extern "C" int legion_enable_peer_access(int32_t dev_id, int32_t peer_id)
+{
+    LG_ARG(dev_id >= 0 && peer_id >= 0 && dev_id != peer_id, "need two different devices");
+    int can = 0;
+    LG_CUDA(cudaDeviceCanAccessPeer(&can, dev_id, peer_id));
+    if (!can) {
+        set_error("legion_enable_peer_access: device %d cannot access device %d", dev_id, peer_id);
+        return LEGION_E_STATE;
+    }
+    LG_CUDA(cudaSetDevice(dev_id));
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer_id, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();
+        return LEGION_OK;
+    }
+    LG_CUDA(e);
+    return LEGION_OK;
+}
