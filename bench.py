@@ -272,8 +272,10 @@ def main():
     cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank)
     cache.fill_static(order, table)
     del order
+    share = None
     if world > 1:
-        exchange_partitions(L, cache, rank, world, dist)
+        from legion_ibp_b200 import server
+        share = server.exchange_partitions(cache, rank, world, dist)
     pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, args.pipes)
     pool.set_rng(0x5EED + rank, 64)
     runner = L.Runner(dev, g, fs, cache, pool, None)
@@ -452,35 +454,12 @@ def main():
                 "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
                 "cpu_baseline": cpu, "clocks": clocks,
                 "graph": {"nodes": n, "directed_edges": n_edges, "train_seeds_this_rank": int(mine.numel()),
-                          "cache_rows_per_gpu": cap}, "setup_s": setup_s}
+                          "cache_rows_per_gpu": cap, "peer_mapping": share}, "setup_s": setup_s}
         print(json.dumps(line), flush=True)
     runner.Finalize()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
-
-
-def exchange_partitions(L, cache, rank, world, dist):
-    """Every rank publishes its cache partition as a CUDA IPC handle and maps the others'
-    (the pointer table d_float_feature_cache_ptr_ of the reference, cache/cache.cu:601-622, across
-    processes instead of threads).  Peers are then read by plain loads over NVLink."""
-    import ctypes as C
-    import torch
-    ptr, nbytes = cache.partition()
-    handle = (C.c_char * 64)()
-    rc = L.lib().legion_ipc_get_handle(C.c_void_p(ptr), handle)
-    assert rc == 0, L.lib().legion_last_error()
-    mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device="cuda")
-    allh = [torch.empty_like(mine) for _ in range(world)]
-    dist.all_gather(allh, mine)
-    for k in range(world):
-        if k == rank:
-            continue
-        raw = bytes(allh[k].cpu().tolist())
-        p = C.c_void_p()
-        rc = L.lib().legion_ipc_open_handle(raw, C.byref(p))
-        assert rc == 0, L.lib().legion_last_error()
-        cache.set_peer(k, p.value)
 
 
 if __name__ == "__main__":

@@ -105,6 +105,14 @@ int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n
 int legion_cache_partition(LegionCache *c, void **ptr, int64_t *bytes);
 int legion_cache_set_peer(LegionCache *c, int32_t k, const void *partition_ptr);
 int legion_cache_lut(LegionCache *c, int32_t **lut_dev);
+/* The same pointer table across processes (one process per GPU).  With kg > 1 the partition is
+ * allocated as shareable memory: export it as a POSIX file descriptor (pass it to the peers over a
+ * unix socket with SCM_RIGHTS, then close it), and map member k's partition from the descriptor
+ * its process sent.  Peers are then read by plain loads over NVLink.  LEGION_E_STATE when the
+ * partition is ordinary cudaMalloc memory; legion_ipc_get_handle / legion_ipc_open_handle +
+ * legion_cache_set_peer remain as the fallback. */
+int legion_cache_export_partition(LegionCache *c, int32_t *fd_out, int64_t *bytes_out);
+int legion_cache_import_peer(LegionCache *c, int32_t k, int32_t fd, int64_t bytes);
 /* Table that serves the misses (cpu_float_features_, cache/cache.cu:771-776); set by
  * legion_cache_fill_static, or here for a cache that is filled some other way. */
 int legion_cache_set_host_table(LegionCache *c, const void *host_table);

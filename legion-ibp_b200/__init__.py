@@ -148,6 +148,15 @@ class UnifiedCache:
         _check(lib().legion_cache_partition(self.h, C.byref(p), C.byref(b)))
         return p.value or 0, b.value
 
+    def export_partition(self):
+        """(fd, bytes) of this GPU's partition as shareable memory; the caller closes the fd."""
+        fd, b = C.c_int32(-1), C.c_int64()
+        _check(lib().legion_cache_export_partition(self.h, C.byref(fd), C.byref(b)))
+        return fd.value, b.value
+
+    def import_peer(self, k, fd, nbytes):
+        _check(lib().legion_cache_import_peer(self.h, C.c_int32(k), C.c_int32(fd), C.c_int64(nbytes)))
+
     def set_peer(self, k, ptr):
         _check(lib().legion_cache_set_peer(self.h, C.c_int32(k), C.c_void_p(ptr)))
 

@@ -142,11 +142,19 @@ extern "C" int legion_cache_create(LegionCache **out, int32_t dev_id, int64_t n_
     c->capacity = capacity;
     c->slot_bytes = codec == LEGION_CODEC_RAW ? row_bytes : (row_bytes / 4 + 4 + 15) / 16 * 16;
     cudaError_t e = cudaMalloc(&c->lut, sizeof(int32_t) * n_nodes);
-    if (e == cudaSuccess && capacity > 0) e = cudaMalloc(&c->part[ki], (int64_t)capacity * c->slot_bytes);
+    if (e == cudaSuccess && capacity > 0) {
+        // a partition that peers will read is allocated as shareable memory so that other processes
+        // can map it; when that is not available it falls back to cudaMalloc (+ legacy IPC handles)
+        if (kg > 1 && vmm_alloc(dev_id, (int64_t)capacity * c->slot_bytes, &c->own_block) == LEGION_OK)
+            c->part[ki] = c->own_block.ptr;
+        else
+            e = cudaMalloc(&c->part[ki], (int64_t)capacity * c->slot_bytes);
+    }
     if (e == cudaSuccess) e = cudaMalloc(&c->stats, sizeof(unsigned long long) * 4);
     if (e != cudaSuccess) {
         set_error("legion_cache_create: cudaMalloc failed: %s", cudaGetErrorString(e));
-        cudaFree(c->lut); cudaFree(c->part[ki]); cudaFree(c->stats);
+        cudaFree(c->lut); cudaFree(c->stats);
+        if (c->own_block.ptr) vmm_free(&c->own_block); else cudaFree(c->part[ki]);
         delete c;
         return LEGION_E_NOMEM;
     }
@@ -339,8 +347,11 @@ extern "C" int legion_cache_destroy(LegionCache *c)
     if (c == nullptr) return LEGION_OK;
     cudaSetDevice(c->dev_id);
     if (c->kind == 0) {
+        cudaDeviceSynchronize();
         cudaFree(c->lut);
-        cudaFree(c->part[c->ki]);
+        if (c->own_block.ptr) vmm_free(&c->own_block); else cudaFree(c->part[c->ki]);
+        for (int k = 0; k < LEGION_MAX_DEVICE; ++k)
+            if (c->peer_block[k].ptr) vmm_free(&c->peer_block[k]);
     } else {
         cudaFree(c->keys); cudaFree(c->stamps); cudaFree(c->claim); cudaFree(c->rows);
     }

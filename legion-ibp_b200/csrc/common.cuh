@@ -90,6 +90,19 @@ struct BatchCtl {
 
 }  // namespace legion
 
+namespace legion {
+struct VmmBlock {  // one mapping made through the virtual memory management API
+    void *ptr;
+    int64_t size;
+    unsigned long long handle;
+    int32_t imported;
+};
+int vmm_alloc(int dev, int64_t bytes, VmmBlock *out);
+int vmm_export_fd(const VmmBlock *b, int *fd_out);
+int vmm_import_fd(int dev, int fd, int64_t size, VmmBlock *out);
+void vmm_free(VmmBlock *b);
+}  // namespace legion
+
 // ---- handle structs (opaque in the C ABI) ------------------------------------------------------
 struct LegionGraph {
     int32_t dev_id;
@@ -119,6 +132,8 @@ struct LegionCache {
     int32_t kg, ki, capacity;
     int32_t *lut;                      // n_nodes entries, global index or CACHEMISS
     void *part[LEGION_MAX_DEVICE];     // part[ki] is owned
+    legion::VmmBlock own_block;        // set when part[ki] is shareable memory (clique of more than one GPU)
+    legion::VmmBlock peer_block[LEGION_MAX_DEVICE];  // partitions mapped from other processes
     // lru
     int64_t sets;
     int32_t ways;

@@ -5,8 +5,9 @@ The reference runs one host thread per GPU inside one process (engine/server.cu:
 raw pointers between the threads; here every GPU has its own process, so the two things the threads
 shared travel through ``torch.distributed`` once at start-up:
   * the per-GPU seed counts that the step arithmetic needs (IPCEnv::Coordinate), and
-  * the CUDA IPC handles of the cache partitions, from which each rank builds the pointer table that
-    its gather kernel reads peers through (plain loads over NVLink; no collective on the data path).
+  * the cache partitions, exported as file descriptors of shareable device memory and mapped by
+    every peer, from which each rank builds the pointer table that its gather kernel reads peers
+    through (plain loads over NVLink; no collective on the data path).
 """
 import ctypes as C
 
@@ -50,9 +51,45 @@ def all_gather_bytes(blob, dist, device="cpu"):
     return [bytes(o.cpu().tolist()) for o in out]
 
 
-def exchange_partitions(cache, rank, world, dist, device="cuda"):
-    """Publishes this rank's cache partition and maps the peers' (the pointer table
-    d_float_feature_cache_ptr_ of cache/cache.cu:601-622, across processes)."""
+def exchange_partitions(cache, rank, world, dist, device="cuda", tag=None):
+    """Builds the clique's pointer table (d_float_feature_cache_ptr_ of cache/cache.cu:601-622) across
+    processes: every rank exports its partition as a file descriptor, hands it to every peer over a
+    unix socket (SCM_RIGHTS) and maps the descriptors it receives.  Peers are then read by plain loads
+    over NVLink.  Falls back to legacy CUDA IPC handles when the partition is not shareable memory."""
+    import os
+    import socket
+    import struct
+    try:
+        fd, nbytes = cache.export_partition()
+    except LegionError:
+        return _exchange_partitions_ipc(cache, rank, world, dist, device)
+    tag = tag or "%s_%d" % (os.environ.get("MASTER_PORT", "0"), os.getuid())
+    name = "\0legion_b200_%s_%d"
+    srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    srv.bind(name % (tag, rank))
+    srv.listen(world)
+    dist.barrier()
+    for k in range(world):
+        if k == rank:
+            continue
+        s = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        s.connect(name % (tag, k))
+        socket.send_fds(s, [struct.pack("iq", rank, nbytes)], [fd])
+        s.close()
+    for _ in range(world - 1):
+        conn, _addr = srv.accept()
+        msg, fds, _flags, _a = socket.recv_fds(conn, 64, 1)
+        peer, peer_bytes = struct.unpack("iq", msg[:struct.calcsize("iq")])
+        cache.import_peer(peer, fds[0], peer_bytes)
+        os.close(fds[0])
+        conn.close()
+    os.close(fd)
+    srv.close()
+    dist.barrier()
+    return "vmm"
+
+
+def _exchange_partitions_ipc(cache, rank, world, dist, device="cuda"):
     ptr, _ = cache.partition()
     handle = (C.c_char * 64)()
     if ptr:
@@ -68,7 +105,7 @@ def exchange_partitions(cache, rank, world, dist, device="cuda"):
         if rc != 0:
             raise LegionError(lib().legion_last_error().decode())
         cache.set_peer(k, p.value)
-    return blobs
+    return "ipc"
 
 
 class Server:

@@ -139,6 +139,46 @@ def test_clique_striped_cache_on_one_device(oracle_mod, kg):
         r.close()
 
 
+def test_partitions_shared_through_file_descriptors(oracle_mod):
+    """The cross-process path on one GPU: a member's partition is exported as a file descriptor and
+    mapped a second time through it, as a peer process would; rows read through that mapping are the
+    rows of the partition."""
+    import os
+    rng = np.random.default_rng(3)
+    indptr, _ = small_graph(8000, 100000, 6)
+    n = len(indptr) - 1
+    table = rng.standard_normal((n, 128)).astype(np.float32)
+    ids_list = rng.integers(0, n, 6000).astype(np.int32)
+    kg, cap = 2, n // 4
+    order = oracle_mod.degree_order(indptr)
+    rigs = [Rig(table, ids_list, 6000, capacity=cap, kg=kg, ki=ki, order=order) for ki in range(kg)]
+    fds = []
+    for a in range(kg):
+        fd, nbytes = rigs[1 - a].cache.export_partition()
+        assert fd >= 0 and nbytes >= cap * 512 and nbytes % (2 << 20) == 0
+        rigs[a].cache.import_peer(1 - a, fd, nbytes)
+        fds.append(fd)
+    for fd in fds:
+        os.close(fd)
+    lut = oracle_mod.static_cache_lut(order, cap, kg)
+    parts = [oracle_mod.static_cache_fill(order, cap, kg, ki, table) for ki in range(kg)]
+    ci = oracle_mod.find_feat(ids_list, lut)
+    ref = oracle_mod.gather(ids_list, ci, cap, parts, table)
+    for ki in range(kg):
+        cnt, feat, _ = rigs[ki].gather(0)
+        np.testing.assert_array_equal(feat.view(np.float32), ref)
+        st = rigs[ki].cache.stats()
+        assert st["peer_hits"] == int(((ci >= 0) & (ci // cap != ki)).sum()) and st["peer_hits"] > 0
+    with pytest.raises(L.LegionError):
+        rigs[0].cache.import_peer(0, 0, 1 << 21)  # own index
+    single = Rig(table, ids_list, 6000, capacity=cap, kg=1, ki=0, order=order)
+    with pytest.raises(L.LegionError, match="not allocated as shareable"):
+        single.cache.export_partition()
+    single.close()
+    for r in rigs:
+        r.close()
+
+
 @pytest.mark.parametrize("codec", [L.CODEC_INT8, L.CODEC_E4M3])
 @pytest.mark.parametrize("feat_len", [100, 128])
 def test_compressed_cache(oracle_mod, codec, feat_len):
