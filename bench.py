@@ -332,6 +332,14 @@ def main():
         for k in tm:
             tm[k] += t1[k]
     stats1 = cache.stats()
+    # the same events with batches in flight: how busy the host-link stream is in steady state
+    for _ in range(args.steps):
+        runner.enqueue(step, L.TRAINMODE, step % n_iters)
+        step += 1
+    runner.sync()
+    tp = runner.timing()
+    pipeline = {"window_ms_per_batch": tp["batch_ms"] / args.steps, "miss_ms_per_batch": tp["miss_ms"] / args.steps,
+                "miss_stream_busy_frac": tp["miss_ms"] / tp["batch_ms"] if tp["batch_ms"] > 0 else None}
     runner.set_options(use_graph=True, time_kernels=False)
     if args.profile_only:
         if rank == 0:
@@ -452,6 +460,7 @@ def main():
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, world),
                 "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + (hops + 1) + 1),
                 "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
+                "pipeline": pipeline,
                 "cpu_baseline": cpu, "clocks": clocks,
                 "graph": {"nodes": n, "directed_edges": n_edges, "train_seeds_this_rank": int(mine.numel()),
                           "cache_rows_per_gpu": cap, "peer_mapping": share}, "setup_s": setup_s}
