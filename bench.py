@@ -355,7 +355,7 @@ def main():
     d = {k: stats1[k] - stats0[k] for k in stats0}
     hits = d["local_hits"] + d["peer_hits"]
     rows = hits + d["misses"]
-    gather_launches = tm["timed"] * (len(cfg["fanout"]) + 1)
+    gather_launches = tm["timed"]  # one lookup + gather launch per batch
     timed_frac = tm["timed"] / float(args.steps)
     hit_bytes = hits * (2 * row_bytes + 8) + d["misses"] * 12
     miss_bytes = d["misses"] * (2 * row_bytes + 8)
@@ -458,7 +458,7 @@ def main():
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, world),
-                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + (hops + 1) + 1),
+                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + 1 + 1),
                 "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
                 "pipeline": pipeline,
                 "cpu_baseline": cpu, "clocks": clocks,

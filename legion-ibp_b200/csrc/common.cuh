@@ -41,6 +41,8 @@ constexpr int kScanThreads = 256;  // kTile / 4 items per thread
 // this hop carries kNewBase + (index of the first edge that reached it) until it gets its
 // local id.  Local ids stay below kNewBase.
 constexpr int32_t kNewBase = 0x40000000;
+// op id of the runner's single lookup + gather over every node of a batch
+constexpr int32_t kOpGatherAll = -1;
 constexpr int32_t kEmptyKey = -1;
 constexpr int32_t kEmptyVal = 0x7FFFFFFF;
 

@@ -52,6 +52,19 @@ __device__ __forceinline__ const uint8_t *shfl_ptr(const uint8_t *p, int src)
 // snapshot that counter_update writes for a lookup op (operator_impl.cu:85-87).
 __device__ __forceinline__ void segment_of(int32_t *nc, int op_id, int &off, int &n)
 {
+    if (op_id == kOpGatherAll) {
+        // every node of the batch in one launch (the runner's choice: one long gather instead of one
+        // short one per hop); the snapshot words get the values the last per-hop lookup would leave
+        const int hops = nc[LEGION_INTRABATCH_CON * 3 - 1];
+        off = 0;
+        n = nc[LEGION_INTRABATCH_CON * 3 + hops];
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            const int last = hops > 0 ? nc[LEGION_INTRABATCH_CON * 3 + hops - 1] : 0;
+            nc[2] = last;
+            nc[3] = n - last;
+        }
+        return;
+    }
     const int h = op_id / LEGION_INTRABATCH_CON;
     off = h > 0 ? nc[LEGION_INTRABATCH_CON * 3 + h - 1] : 0;
     n = nc[LEGION_INTRABATCH_CON * 3 + h] - off;
@@ -496,11 +509,12 @@ static void launch_lru(int grid, cudaStream_t s, const LruParams &lp)
 
 static int segment_grid(const LegionPool *p, int32_t op_id, int64_t *rows_out)
 {
-    // worst-case rows of this segment: the seeds, or the new nodes of hop (op_id / 3)
+    // worst-case rows of this segment: the seeds, or the new nodes of hop (op_id / 3), or all nodes
     int hop = op_id / LEGION_INTRABATCH_CON;  // 0 = seeds
     int64_t rows = p->batch_size;
     int64_t nodes = p->batch_size;
     for (int h = 0; h < hop; ++h) { rows = nodes * p->fanout[h]; nodes += rows; }
+    if (op_id == kOpGatherAll) rows = p->max_nodes;
     if (rows_out) *rows_out = rows;
     int64_t chunks = (rows + 31) / 32;
     int64_t g64 = (chunks + 7) / 8;
