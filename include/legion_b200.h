@@ -57,6 +57,9 @@ int legion_abi_version(void);
  * reference's alloc/copy helpers, engine/server_imp.cuh:1-51).  kind: 1 host->device,
  * 2 device->host, 3 device->device. */
 int legion_copy(void *dst, const void *src, int64_t bytes, int32_t kind);
+/* Launch-shape knobs for measurements (the reference hard-codes its grids, e.g. cache/cache.cu:746-752).
+ * "miss_ctas": CTAs of the host-link fetch kernel, 0 = one per SM. */
+int legion_set_tunable(const char *name, int32_t value);
 
 /* EnableP2PAccess (storage/storage_management.cu:9-27) for one ordered pair of devices of this
  * process; needed when the clique's partitions are allocated by threads of one process. */

@@ -14,6 +14,7 @@
 #include "common.cuh"
 
 #include <cuda_fp8.h>
+#include <string.h>
 
 namespace legion {
 
@@ -605,6 +606,8 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
     return LEGION_OK;
 }
 
+int g_miss_ctas = 0;  // 0 = one CTA per SM; see legion_set_tunable
+
 // The rows the hit kernels listed so far, fetched from the pinned host table; empties the list.
 // No-op without a host table.
 int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c)
@@ -623,7 +626,7 @@ int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c)
     // 4 rows per warp and pass; one CTA per SM keeps ~2.4 MB of reads in flight, far more than the
     // host link needs, and leaves the SMs to the HBM-bound kernels of the next batch
     int64_t g64 = (p->max_nodes + 31) / 32;
-    int cap = p->sm_count;
+    int cap = g_miss_ctas > 0 ? g_miss_ctas : p->sm_count;
     int grid = (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
     gather_miss_kernel<4><<<grid, 256, 0, s>>>(mp);
     LG_LAUNCH_CHECK();
@@ -793,4 +796,18 @@ extern "C" int legion_gather_rows_noalloc(void *stream, int32_t dev_id, const in
         LG_LAUNCH_CHECK();
     }
     return LEGION_OK;
+}
+
+// Launch-shape knobs for measurements.  "miss_ctas": CTAs of the host-link fetch (0 = one per SM).
+extern "C" int legion_set_tunable(const char *name, int32_t value)
+{
+    using namespace legion;
+    LG_ARG(name != nullptr, "name is NULL");
+    if (strcmp(name, "miss_ctas") == 0) {
+        LG_ARG(value >= 0 && value <= 4096, "miss_ctas out of range");
+        g_miss_ctas = value;
+        return LEGION_OK;
+    }
+    set_error("legion_set_tunable: unknown name %s", name);
+    return LEGION_E_ARG;
 }
