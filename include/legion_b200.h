@@ -85,6 +85,36 @@ int legion_features_set_split(LegionFeatures *f, int32_t mode, const int32_t *id
                               const int32_t *labels_dev, int32_t count);
 int legion_features_destroy(LegionFeatures *f);
 
+/* ---- Legion-format datasets (storage/storage_management.cu:33-279) -------------------- */
+
+/* The single line of ./meta_config in in-memory mode, written by legion_server.py:45-46 and parsed by
+ * StorageManagement::ReadMetaFIle (storage/storage_management.cu:33-68). */
+typedef struct LegionMetaConfig {
+    char dataset_path[512];
+    char feature_path[512];   /* same as dataset_path when the line has no 11th field */
+    int32_t raw_batch_size;
+    int64_t node_num, edge_num;
+    int32_t float_feature_len;
+    int32_t training_set_num, validation_set_num, testing_set_num;
+    int64_t cache_memory;     /* bytes per GPU */
+    int32_t epoch;
+} LegionMetaConfig;
+typedef struct LegionDataset LegionDataset;
+int legion_meta_config_read(const char *file, LegionMetaConfig *out);
+int legion_meta_config_write(const char *file, const LegionMetaConfig *m);
+/* LoadGraph + LoadFeature (storage/storage_management.cu:106-279, storage_management_impl.cuh:48-196):
+ * reads edge_src (int64 offsets), edge_dst (int32), features (fp32), labels, trainingset /
+ * validationset / testingset and the optional partition file.  pin != 0 puts topology and features
+ * in mapped pinned host memory (needs a GPU), pin == 0 in plain host memory. */
+int legion_dataset_load(LegionDataset **out, const LegionMetaConfig *meta, int32_t pin, int32_t load_features);
+int legion_dataset_arrays(LegionDataset *d, const int64_t **indptr, const int32_t **indices, const float **features,
+                          const int32_t **labels);
+/* Seeds of one GPU (storage/storage_management.cu:214-250): partition file for the training set when
+ * present, else id % partition_count.  ids_out == NULL returns the count only. */
+int legion_dataset_split(LegionDataset *d, int32_t mode, int32_t partition_count, int32_t part_id, int32_t *ids_out,
+                         int32_t *labels_out, int32_t *count_out);
+int legion_dataset_destroy(LegionDataset *d);
+
 /* ---- cache ----------------------------------------------------------------------- */
 
 /* UnifiedCache::Initialize + the allocation half of FillUp (cache/cache.cu:559-600).

@@ -65,6 +65,10 @@ def _ptr(t):
     return C.c_void_p(t.ctypes.data)
 
 
+def _numel(t):
+    return int(t.numel()) if hasattr(t, "numel") else int(t.size)
+
+
 def _stream(s):
     if s is None:
         return C.c_void_p(0)
@@ -78,8 +82,8 @@ class GraphStorage:
 
     def __init__(self, dev_id, indptr, indices):
         self._keep = (indptr, indices)
-        self.n_nodes = int(indptr.numel()) - 1
-        self.n_edges = int(indices.numel())
+        self.n_nodes = _numel(indptr) - 1
+        self.n_edges = _numel(indices)
         self.h = C.c_void_p()
         _check(lib().legion_graph_create(C.byref(self.h), C.c_int32(dev_id), C.c_int64(self.n_nodes),
                                          C.c_int64(self.n_edges), _ptr(indptr), _ptr(indices)))
@@ -103,7 +107,7 @@ class FeatureStorage:
     def set_split(self, mode, ids_dev, labels_dev):
         self._keep += [ids_dev, labels_dev]
         _check(lib().legion_features_set_split(self.h, C.c_int32(mode), _ptr(ids_dev), _ptr(labels_dev),
-                                               C.c_int32(ids_dev.numel())))
+                                               C.c_int32(_numel(ids_dev))))
 
     def close(self):
         if self.h:
@@ -404,4 +408,65 @@ class Runner:
     def Finalize(self):
         if self.h:
             lib().legion_runner_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class MetaConfig(C.Structure):
+    """The line of ./meta_config (legion_server.py:45-46, storage/storage_management.cu:33-68)."""
+    _fields_ = [("dataset_path", C.c_char * 512), ("feature_path", C.c_char * 512), ("raw_batch_size", C.c_int32),
+                ("node_num", C.c_int64), ("edge_num", C.c_int64), ("float_feature_len", C.c_int32),
+                ("training_set_num", C.c_int32), ("validation_set_num", C.c_int32), ("testing_set_num", C.c_int32),
+                ("cache_memory", C.c_int64), ("epoch", C.c_int32)]
+
+    @staticmethod
+    def read(path="./meta_config"):
+        m = MetaConfig()
+        _check(lib().legion_meta_config_read(path.encode(), C.byref(m)))
+        return m
+
+    def write(self, path="./meta_config"):
+        _check(lib().legion_meta_config_write(path.encode(), C.byref(self)))
+
+
+class Dataset:
+    """A Legion-format dataset in host memory (StorageManagement::LoadGraph / LoadFeature,
+    storage/storage_management.cu:106-279).  Arrays are numpy views of the loader's memory."""
+
+    def __init__(self, meta, pin=True, load_features=True):
+        import numpy as np
+        self.meta = meta
+        self.h = C.c_void_p()
+        _check(lib().legion_dataset_load(C.byref(self.h), C.byref(meta), C.c_int32(int(pin)),
+                                         C.c_int32(int(load_features))))
+        ip, ix, ft, lb = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+        _check(lib().legion_dataset_arrays(self.h, C.byref(ip), C.byref(ix), C.byref(ft), C.byref(lb)))
+        n, e, f = meta.node_num, meta.edge_num, meta.float_feature_len
+
+        def view(ptr, count, ctype, dtype):
+            if not ptr.value or count == 0:
+                return np.empty(0, dtype)
+            return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(ctype)), shape=(count,)).view(dtype)
+
+        self.indptr = view(ip, n + 1, C.c_int64, np.int64)
+        self.indices = view(ix, e, C.c_int32, np.int32)
+        self.features = view(ft, n * f, C.c_float, np.float32).reshape(-1, f) if load_features else None
+        self.labels = view(lb, n, C.c_int32, np.int32)
+        self.features_ptr = ft.value
+
+    def split(self, mode, partition_count, part_id):
+        """(ids, labels) of one GPU: partition file or id % partition_count (storage_management.cu:214-250)."""
+        import numpy as np
+        cnt = C.c_int32()
+        _check(lib().legion_dataset_split(self.h, C.c_int32(mode), C.c_int32(partition_count), C.c_int32(part_id),
+                                          None, None, C.byref(cnt)))
+        ids = np.empty(cnt.value, np.int32)
+        lab = np.empty(cnt.value, np.int32)
+        _check(lib().legion_dataset_split(self.h, C.c_int32(mode), C.c_int32(partition_count), C.c_int32(part_id),
+                                          _ptr(ids), _ptr(lab), C.byref(cnt)))
+        return ids, lab
+
+    def close(self):
+        if self.h:
+            self.indptr = self.indices = self.features = self.labels = None
+            lib().legion_dataset_destroy(self.h)
             self.h = C.c_void_p()

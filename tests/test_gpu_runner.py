@@ -314,3 +314,42 @@ def test_ipc_handoff_to_trainer_process(oracle_mod, tmp_path):
     r.Finalize()
     env.Finalize()
     assert not os.path.exists("/dev/shm/" + shm)
+
+
+def test_dataset_files_to_batches_with_topology_in_host_memory(oracle_mod, tmp_path):
+    """From Legion-format files to served batches: the loader puts CSR and features in mapped pinned
+    host memory, the sampler reads the topology in place (zero-copy, as the reference does for
+    uncached adjacency lists), and the result equals the host replay."""
+    import torch
+    from test_dataset_cpu import meta_for, write_dataset
+    ref = write_dataset(tmp_path / "ds", n=4000, f=32, seed=3)
+    meta = meta_for(tmp_path / "ds", ref, f=32)
+    ds = L.Dataset(meta, pin=True)
+    n = meta.node_num
+    g = L.GraphStorage(0, ds.indptr, ds.indices)           # host pointers, read through UVA
+    f = L.FeatureStorage(0, n, 32 * 4, ds.features)
+    ids, lab = ds.split(L.TRAINMODE, 1, 0)
+    d_ids, d_lab = torch.from_numpy(ids).cuda(), torch.from_numpy(lab).cuda()
+    f.set_split(L.TRAINMODE, d_ids, d_lab)
+    d_ip = torch.from_numpy(np.ascontiguousarray(ds.indptr)).cuda()
+    order = torch.empty(n, dtype=torch.int32, device="cuda")
+    L.UnifiedCache.degree_order(0, d_ip, order)
+    cache = L.UnifiedCache(0, n, 32 * 4, n // 10)
+    cache.fill_static(order, ds.features)
+    pool = L.MemoryPool(0, 48, [25, 10], 32 * 4, 2)
+    pool.set_rng(5, 64)
+    r = L.Runner(0, g, f, cache, pool, None)
+    w = dict(pool=pool, indptr=ref["indptr"], indices=ref["indices"], train=ids, labels=lab, batch=48, fanout=[25, 10],
+             table=ref["feats"])
+    for it in range(0, 4, 2):
+        r.enqueue(it, L.TRAINMODE, it)
+        r.enqueue(it + 1, L.TRAINMODE, it + 1)
+        r.sync()
+        for pipe in (0, 1):
+            b = oracle_mod.run_batch(w["indptr"], w["indices"], ids, lab, 48, it + pipe, [25, 10], it + pipe, 5)
+            np.testing.assert_array_equal(pool.read(L.BUF_IDS, pipe, len(b["ids"]), np.int32), b["ids"])
+            np.testing.assert_array_equal(pool.read(L.BUF_AGG_SRC, pipe, len(b["agg_src"]), np.int32), b["agg_src"])
+            np.testing.assert_array_equal(pool.read(L.BUF_NODE_COUNTER, pipe, 16, np.int32), b["node_counter"])
+            feat = pool.read(L.BUF_FEATURES, pipe, len(b["ids"]) * 32, np.float32).reshape(-1, 32)
+            np.testing.assert_array_equal(feat, ref["feats"][b["ids"]])
+    r.Finalize(); pool.close(); cache.close(); f.close(); g.close(); ds.close()
