@@ -129,6 +129,11 @@ int legion_cache_create(LegionCache **out, int32_t dev_id, int64_t n_nodes, int3
  * the key.  order_dev: n_nodes int32 in device memory. */
 int legion_cache_degree_order(int32_t dev_id, const int64_t *indptr, int64_t n_nodes,
                               int32_t *order_dev, void *stream);
+/* The reference's own ranking: nodes by descending presampled hotness (CandidateSelection,
+ * cache/cache.cu:354-447), ties by ascending id.  counts_dev: one uint32 per node, filled by
+ * legion_runner_presample (HotnessMeasure, cache/cache_impl.cuh:190-198). */
+int legion_cache_hotness_order(int32_t dev_id, const uint32_t *counts_dev, int64_t n_nodes, int32_t *order_dev,
+                               void *stream);
 /* InitPair + Insert + FeatFillUp (cache/cache_impl.cuh:104-109,183-188; cache/cache.cu:74-141):
  * rank t of `order` lives on GPU t % kg at row t / kg.  Builds the whole lookup table and copies
  * (and encodes) this GPU's rows from host_table. */
@@ -292,6 +297,35 @@ int legion_ipc_open_handle(const void *handle_bytes, void **dev_ptr);
 int legion_ipc_get_handle(const void *dev_ptr, void *handle_bytes_out);
 int legion_ipc_close_handle(void *dev_ptr);
 
+/* ---- trainer side of the hand-off (training_backend/ipc_service.cpp:30-100) ---------------- */
+
+/* One batch as the trainer sees it (cuda_get_next, training_backend/ipc_cuda_kernel.cu:177-243, and
+ * get_block_size, ipc_service.cpp:61-79).  Pointers are device pointers into the server's buffers,
+ * valid until legion_client_synchronize.  Hop entries are ordered last hop first. */
+typedef struct LegionBatchView {
+    int32_t hop_num;
+    int32_t n_ids;      /* rows of ids and of features */
+    int32_t n_labels;   /* seeds */
+    const int32_t *ids;
+    const void *features;
+    const int32_t *labels;
+    const int32_t *agg_src[LEGION_MAX_HOPS];
+    const int32_t *agg_dst[LEGION_MAX_HOPS];
+    int32_t n_edges[LEGION_MAX_HOPS];
+    int32_t block_src[LEGION_MAX_HOPS];  /* num_src of the DGL block */
+    int32_t block_dst[LEGION_MAX_HOPS];  /* num_dst of the DGL block */
+    int32_t node_counter[16];
+    int32_t edge_counter[16];
+} LegionBatchView;
+typedef struct LegionClient LegionClient;
+/* initialize (GPUIPCEnv::Initialize, ipc_cuda_kernel.cu:37-95): maps the segment, opens the 7 buffers
+ * of both pipes of device slot dev_id, opens the semaphores and marks both slots free. */
+int legion_client_open(LegionClient **out, int32_t dev_id, const char *shm_name);
+int legion_client_steps(LegionClient *c, int32_t steps[3]);                                   /* get_steps */
+int legion_client_get_next(LegionClient *c, int32_t timeout_ms, LegionBatchView *out);       /* get_next */
+int legion_client_synchronize(LegionClient *c);                                              /* synchronize */
+int legion_client_close(LegionClient *c);                                                    /* finalize */
+
 /* ---- runner (engine/server.h:23-34, engine/server.cu:176-416) ---------------------------- */
 
 /* GPURunner::Initialize: binds storage, cache, pool and (optionally) an IPC environment. */
@@ -317,6 +351,10 @@ int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int32_t *label
                                int32_t *agg_dst_out, int32_t node_counter_out[16], int32_t edge_counter_out[16],
                                void *features_out);
 int legion_runner_current_pipe(LegionRunner *r);
+/* The presampling epoch (GPUServer::PreSc / GPURunner::RunPreSc, engine/server.cu:94-122,313-328): samples
+ * training batches [first_batch, first_batch+count) without lookup or gather and counts every node they
+ * touch in counts_dev (uint32 per node, zeroed by the caller). */
+int legion_runner_presample(LegionRunner *r, int32_t first_batch, int32_t count, uint32_t *counts_dev);
 /* use_graph (default 1): replay every batch as one CUDA graph per pipe instead of ~25 launches and
  * ~20 event calls from the host.  time_kernels (default 0): bracket the gather launches with CUDA
  * events on the streams they run on.  Call between batches; waits for the device. */

@@ -138,6 +138,11 @@ class UnifiedCache:
         _check(lib().legion_cache_degree_order(C.c_int32(dev_id), _ptr(indptr), C.c_int64(indptr.numel() - 1),
                                                _ptr(order_out), _stream(stream)))
 
+    @staticmethod
+    def hotness_order(dev_id, counts_dev, order_out, stream=None):
+        _check(lib().legion_cache_hotness_order(C.c_int32(dev_id), _ptr(counts_dev), C.c_int64(_numel(counts_dev)),
+                                                _ptr(order_out), _stream(stream)))
+
     def fill_static(self, order_dev, host_table, stream=None):
         self._keep += [host_table]
         _check(lib().legion_cache_fill_static(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()),
@@ -394,6 +399,10 @@ class Runner:
         _check(lib().legion_runner_serve(self.h, C.c_int32(first_global_batch), C.c_int32(count),
                                          C.c_int32(timeout_ms)))
 
+    def presample(self, first_batch, count, counts_dev):
+        """RunPreSc: sample only, count node accesses into counts_dev (uint32 per node)."""
+        _check(lib().legion_runner_presample(self.h, C.c_int32(first_batch), C.c_int32(count), _ptr(counts_dev)))
+
     def current_pipe(self):
         return lib().legion_runner_current_pipe(self.h)
 
@@ -469,4 +478,49 @@ class Dataset:
         if self.h:
             self.indptr = self.indices = self.features = self.labels = None
             lib().legion_dataset_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class BatchView(C.Structure):
+    _fields_ = [("hop_num", C.c_int32), ("n_ids", C.c_int32), ("n_labels", C.c_int32), ("ids", C.c_void_p),
+                ("features", C.c_void_p), ("labels", C.c_void_p), ("agg_src", C.c_void_p * 3),
+                ("agg_dst", C.c_void_p * 3), ("n_edges", C.c_int32 * 3), ("block_src", C.c_int32 * 3),
+                ("block_dst", C.c_int32 * 3), ("node_counter", C.c_int32 * 16), ("edge_counter", C.c_int32 * 16)]
+
+
+class ipc_service:
+    """Trainer side of the hand-off with the function names of the trainers' torch extension
+    (training_backend/ipc_service.cpp:93-100): initialize, get_next, get_block_size, get_steps,
+    synchronize, finalize.  get_next returns device pointers and counts instead of torch tensors."""
+
+    def __init__(self, dev_id, shm_name=None):
+        self.h = C.c_void_p()
+        self.view = BatchView()
+        name = shm_name.encode() if shm_name else None
+        _check(lib().legion_client_open(C.byref(self.h), C.c_int32(dev_id), name))
+
+    initialize = __init__
+
+    def get_steps(self):
+        a = (C.c_int32 * 3)()
+        _check(lib().legion_client_steps(self.h, a))
+        return list(a)
+
+    def get_next(self, timeout_ms=-1):
+        _check(lib().legion_client_get_next(self.h, C.c_int32(timeout_ms), C.byref(self.view)))
+        return self.view
+
+    def get_block_size(self):
+        v = self.view
+        out = []
+        for j in range(v.hop_num):
+            out += [v.block_src[j], v.block_dst[j]]
+        return out
+
+    def synchronize(self):
+        _check(lib().legion_client_synchronize(self.h))
+
+    def finalize(self):
+        if self.h:
+            lib().legion_client_close(self.h)
             self.h = C.c_void_p()

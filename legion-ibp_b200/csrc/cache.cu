@@ -35,6 +35,22 @@ __global__ void degree_keys_kernel(const int64_t *__restrict__ indptr, int64_t n
     }
 }
 
+__global__ void iota_kernel(int32_t *id, int64_t n)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        id[i] = (int32_t)i;
+}
+
+// HotnessMeasure (cache/cache_impl.cuh:190-198): one count per node of the batch
+__global__ void hotness_kernel(const int32_t *__restrict__ ids, const int32_t *__restrict__ nc, uint32_t *counts)
+{
+    const int n = nc[LEGION_INTRABATCH_CON * 3 + nc[LEGION_INTRABATCH_CON * 3 - 1]];
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        int32_t v = ids[i];
+        if (v >= 0) atomicAdd(&counts[v], 1u);
+    }
+}
+
 // rank t -> GPU t % kg, row t / kg (InitPair, cache_impl.cuh:104-109)
 __global__ void static_place_kernel(const int32_t *__restrict__ order, int64_t n_cached, int32_t capacity, int32_t kg,
                                     int32_t *lut)
@@ -115,6 +131,15 @@ static int sm_count_of(int dev)
     return n > 0 ? n : 148;
 }
 
+int launch_hotness(cudaStream_t s, LegionPool *p, uint32_t *counts)
+{
+    int64_t g = (p->max_nodes + 255) / 256;
+    int cap = p->sm_count * 8;
+    hotness_kernel<<<(int)(g > cap ? cap : g), 256, 0, s>>>(p->ids[p->pipe], p->node_counter[p->pipe], counts);
+    LG_LAUNCH_CHECK();
+    return LEGION_OK;
+}
+
 }  // namespace legion
 
 using namespace legion;
@@ -167,39 +192,74 @@ extern "C" int legion_cache_create(LegionCache **out, int32_t dev_id, int64_t n_
     return LEGION_OK;
 }
 
+// ids 0..n-1 sorted by descending 32-bit key, ties by ascending id (LSD radix sort is stable)
+static int order_by_key_desc(int32_t dev_id, uint32_t *keys_in, int64_t n_nodes, int32_t *order_dev, cudaStream_t s,
+                             const int64_t *indptr_for_degree)
+{
+    uint32_t *deg_out = nullptr;
+    int32_t *id_in = nullptr;
+    void *tmp = nullptr;
+    size_t tmp_bytes = 0;
+    int rc = LEGION_OK;
+    cudaError_t e = cudaMalloc(&deg_out, sizeof(uint32_t) * n_nodes);
+    if (e == cudaSuccess) e = cudaMalloc(&id_in, sizeof(int32_t) * n_nodes);
+    if (e == cudaSuccess)
+        e = cub::DeviceRadixSort::SortPairsDescending(nullptr, tmp_bytes, keys_in, deg_out, id_in, order_dev,
+                                                      (int)n_nodes, 0, 32, s);
+    if (e == cudaSuccess) e = cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1);
+    if (e == cudaSuccess) {
+        if (indptr_for_degree != nullptr)
+            degree_keys_kernel<<<grid_stride(n_nodes, sm_count_of(dev_id)), 256, 0, s>>>(indptr_for_degree, n_nodes, keys_in, id_in);
+        else
+            iota_kernel<<<grid_stride(n_nodes, sm_count_of(dev_id)), 256, 0, s>>>(id_in, n_nodes);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess)
+        e = cub::DeviceRadixSort::SortPairsDescending(tmp, tmp_bytes, keys_in, deg_out, id_in, order_dev, (int)n_nodes,
+                                                      0, 32, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        set_error("node ranking failed: %s", cudaGetErrorString(e));
+        rc = LEGION_E_CUDA;
+    }
+    cudaFree(deg_out); cudaFree(id_in); cudaFree(tmp);
+    return rc;
+}
+
 extern "C" int legion_cache_degree_order(int32_t dev_id, const int64_t *indptr, int64_t n_nodes,
                                          int32_t *order_dev, void *stream)
 {
     LG_ARG(indptr != nullptr && order_dev != nullptr, "NULL pointer");
     LG_ARG(n_nodes > 0 && n_nodes < (1ll << 31), "n_nodes must fit int32");
     LG_CUDA(cudaSetDevice(dev_id));
-    cudaStream_t s = (cudaStream_t)stream;
-    uint32_t *deg_in = nullptr, *deg_out = nullptr;
-    int32_t *id_in = nullptr;
-    void *tmp = nullptr;
-    size_t tmp_bytes = 0;
-    int rc = LEGION_OK;
-    cudaError_t e = cudaMalloc(&deg_in, sizeof(uint32_t) * n_nodes);
-    if (e == cudaSuccess) e = cudaMalloc(&deg_out, sizeof(uint32_t) * n_nodes);
-    if (e == cudaSuccess) e = cudaMalloc(&id_in, sizeof(int32_t) * n_nodes);
-    if (e == cudaSuccess)
-        e = cub::DeviceRadixSort::SortPairsDescending(nullptr, tmp_bytes, deg_in, deg_out, id_in, order_dev,
-                                                      (int)n_nodes, 0, 32, s);
-    if (e == cudaSuccess) e = cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1);
-    if (e == cudaSuccess) {
-        degree_keys_kernel<<<grid_stride(n_nodes, sm_count_of(dev_id)), 256, 0, s>>>(indptr, n_nodes, deg_in, id_in);
-        e = cudaGetLastError();
+    uint32_t *keys = nullptr;
+    if (cudaMalloc(&keys, sizeof(uint32_t) * n_nodes) != cudaSuccess) {
+        set_error("legion_cache_degree_order: out of memory");
+        return LEGION_E_NOMEM;
     }
-    // LSD radix sort is stable: equal degrees keep ascending id order
-    if (e == cudaSuccess)
-        e = cub::DeviceRadixSort::SortPairsDescending(tmp, tmp_bytes, deg_in, deg_out, id_in, order_dev,
-                                                      (int)n_nodes, 0, 32, s);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-    if (e != cudaSuccess) {
-        set_error("legion_cache_degree_order: %s", cudaGetErrorString(e));
-        rc = LEGION_E_CUDA;
+    int rc = order_by_key_desc(dev_id, keys, n_nodes, order_dev, (cudaStream_t)stream, indptr);
+    cudaFree(keys);
+    return rc;
+}
+
+// CandidateSelection (cache/cache.cu:354-447): nodes ranked by how often the presampling epoch
+// touched them, most often first (thrust::sort_by_key with greater<>, cache.cu:419); ties, which the
+// reference leaves to the sort, go by ascending id.  counts_dev: one uint32 per node, as filled by
+// legion_runner_presample.
+extern "C" int legion_cache_hotness_order(int32_t dev_id, const uint32_t *counts_dev, int64_t n_nodes,
+                                          int32_t *order_dev, void *stream)
+{
+    LG_ARG(counts_dev != nullptr && order_dev != nullptr, "NULL pointer");
+    LG_ARG(n_nodes > 0 && n_nodes < (1ll << 31), "n_nodes must fit int32");
+    LG_CUDA(cudaSetDevice(dev_id));
+    uint32_t *keys = nullptr;
+    if (cudaMalloc(&keys, sizeof(uint32_t) * n_nodes) != cudaSuccess) {
+        set_error("legion_cache_hotness_order: out of memory");
+        return LEGION_E_NOMEM;
     }
-    cudaFree(deg_in); cudaFree(deg_out); cudaFree(id_in); cudaFree(tmp);
+    cudaError_t e = cudaMemcpyAsync(keys, counts_dev, sizeof(uint32_t) * n_nodes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+    int rc = e == cudaSuccess ? order_by_key_desc(dev_id, keys, n_nodes, order_dev, (cudaStream_t)stream, nullptr) : LEGION_E_CUDA;
+    cudaFree(keys);
     return rc;
 }
 

@@ -198,4 +198,5 @@ int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
 int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
 int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c);
 int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c);
+int launch_hotness(cudaStream_t s, LegionPool *p, uint32_t *counts);
 }  // namespace legion

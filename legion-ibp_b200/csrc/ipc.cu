@@ -300,3 +300,173 @@ extern "C" int legion_ipc_get_handle(const void *dev_ptr, void *handle_bytes_out
     memcpy(handle_bytes_out, &h, sizeof(h));
     return LEGION_OK;
 }
+
+// ---- trainer side -----------------------------------------------------------------------------------------
+// What the trainers' torch extension does (training_backend/ipc_cuda_kernel.cu:37-106,177-243 and
+// ipc_service.cpp:44-92: initialize / get_next / get_block_size / get_steps / synchronize / finalize),
+// without torch: the batch comes back as device pointers and counts.  Unlike the extension it does
+// not copy the feature rows into a fresh tensor (ipc_cuda_kernel.cu:205-211): the rows stay where the
+// server wrote them until legion_client_synchronize releases the pipe.
+struct LegionClient {
+    int32_t dev_id;
+    std::string shm_name, sem_prefix;
+    int shm_fd;
+    volatile legion::ShmLayout *shm;
+    void *buf[LEGION_INTERBATCH_CON][LEGION_MEMORY_USAGE];
+    sem_t *semr[LEGION_INTERBATCH_CON], *semw[LEGION_INTERBATCH_CON];
+    int current_pipe;
+    int32_t *h_counters;  // pinned, 32 ints
+};
+
+extern "C" int legion_client_close(LegionClient *c)
+{
+    if (c == nullptr) return LEGION_OK;
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+        for (int k = 0; k < LEGION_MEMORY_USAGE; ++k)
+            if (c->buf[i][k]) cudaIpcCloseMemHandle(c->buf[i][k]);  // ipc_cuda_kernel.cu:141-150
+        if (c->semr[i]) sem_close(c->semr[i]);
+        if (c->semw[i]) sem_close(c->semw[i]);
+    }
+    if (c->h_counters) cudaFreeHost(c->h_counters);
+    if (c->shm) munmap((void *)c->shm, sizeof(ShmLayout));
+    if (c->shm_fd >= 0) close(c->shm_fd);
+    delete c;
+    return LEGION_OK;
+}
+
+// GPUIPCEnv::Initialize (ipc_cuda_kernel.cu:37-95) for the current device's slot `dev_id`.
+extern "C" int legion_client_open(LegionClient **out, int32_t dev_id, const char *shm_name)
+{
+    LG_ARG(out != nullptr && dev_id >= 0 && dev_id < LEGION_MAX_DEVICE, "bad argument");
+    LG_CUDA(cudaSetDevice(dev_id));
+    LegionClient *c = new LegionClient();
+    c->dev_id = dev_id;
+    bool is_default = (shm_name == nullptr || shm_name[0] == 0 || strcmp(shm_name, kDefaultShm) == 0);
+    c->shm_name = is_default ? kDefaultShm : shm_name;
+    c->sem_prefix = is_default ? "" : (c->shm_name + "_");
+    c->shm = nullptr;
+    c->current_pipe = 0;
+    c->h_counters = nullptr;
+    memset(c->buf, 0, sizeof(c->buf));
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) c->semr[i] = c->semw[i] = nullptr;
+    c->shm_fd = shm_open(c->shm_name.c_str(), O_RDWR | O_CREAT, 0777);  // sharedMemoryCreate, as the trainer calls it
+    if (c->shm_fd < 0 || ftruncate(c->shm_fd, sizeof(ShmLayout)) != 0) {
+        set_error("legion_client_open: shared segment %s: %s", c->shm_name.c_str(), strerror(errno));
+        legion_client_close(c);
+        return LEGION_E_SYS;
+    }
+    void *addr = mmap(nullptr, sizeof(ShmLayout), PROT_READ | PROT_WRITE, MAP_SHARED, c->shm_fd, 0);
+    if (addr == MAP_FAILED) {
+        set_error("legion_client_open: mmap: %s", strerror(errno));
+        legion_client_close(c);
+        return LEGION_E_SYS;
+    }
+    c->shm = (volatile ShmLayout *)addr;
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+        for (int k = 0; k < LEGION_MEMORY_USAGE; ++k) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, (const void *)&c->shm->memHandle[dev_id][i][k], sizeof(h));
+            cudaError_t e = cudaIpcOpenMemHandle(&c->buf[i][k], h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                set_error("legion_client_open: handle %d of pipe %d: %s (is the server ready?)", k, i, cudaGetErrorString(e));
+                c->buf[i][k] = nullptr;
+                legion_client_close(c);
+                return LEGION_E_CUDA;
+            }
+        }
+    }
+    if (cudaMallocHost(reinterpret_cast<void **>(&c->h_counters), 128) != cudaSuccess) {
+        set_error("legion_client_open: pinned allocation failed");
+        legion_client_close(c);
+        return LEGION_E_NOMEM;
+    }
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+        std::string r = c->sem_prefix + "sem_r_" + std::to_string(dev_id) + "_" + std::to_string(i);
+        std::string w = c->sem_prefix + "sem_w_" + std::to_string(dev_id) + "_" + std::to_string(i);
+        c->semr[i] = sem_open(r.c_str(), O_CREAT | O_RDWR, 0666, 0);
+        c->semw[i] = sem_open(w.c_str(), O_CREAT | O_RDWR, 0666, 0);
+        if (c->semr[i] == SEM_FAILED || c->semw[i] == SEM_FAILED) {
+            if (c->semr[i] == SEM_FAILED) c->semr[i] = nullptr;
+            if (c->semw[i] == SEM_FAILED) c->semw[i] = nullptr;
+            set_error("legion_client_open: sem_open: %s", strerror(errno));
+            legion_client_close(c);
+            return LEGION_E_SYS;
+        }
+        sem_post(c->semr[i]);  // both slots start free, ipc_cuda_kernel.cu:90
+    }
+    *out = c;
+    return LEGION_OK;
+}
+
+extern "C" int legion_client_steps(LegionClient *c, int32_t steps[3])
+{
+    LG_ARG(c != nullptr && steps != nullptr, "NULL pointer");
+    for (int i = 0; i < 3; ++i) steps[i] = c->shm->steps[i];  // get_steps, ipc_service.cpp:81-87
+    return LEGION_OK;
+}
+
+// get_next + get_block_size (ipc_service.cpp:44-79, ipc_cuda_kernel.cu:177-243)
+extern "C" int legion_client_get_next(LegionClient *c, int32_t timeout_ms, LegionBatchView *out)
+{
+    LG_ARG(c != nullptr && out != nullptr, "NULL pointer");
+    sem_t *s = c->semw[c->current_pipe];
+    if (timeout_ms < 0) {
+        while (sem_wait(s) != 0)
+            if (errno != EINTR) { set_error("sem_wait: %s", strerror(errno)); return LEGION_E_SYS; }
+    } else {
+        struct timespec ts;
+        clock_gettime(CLOCK_REALTIME, &ts);
+        ts.tv_sec += timeout_ms / 1000;
+        ts.tv_nsec += (long)(timeout_ms % 1000) * 1000000L;
+        if (ts.tv_nsec >= 1000000000L) { ts.tv_sec += 1; ts.tv_nsec -= 1000000000L; }
+        while (sem_timedwait(s, &ts) != 0) {
+            if (errno == EINTR) continue;
+            if (errno == ETIMEDOUT) {
+                set_error("legion_client_get_next: no batch within %d ms", timeout_ms);
+                return LEGION_E_TIMEOUT;
+            }
+            set_error("sem_timedwait: %s", strerror(errno));
+            return LEGION_E_SYS;
+        }
+    }
+    LG_CUDA(cudaSetDevice(c->dev_id));
+    void **b = c->buf[c->current_pipe];
+    LG_CUDA(cudaMemcpyAsync(c->h_counters, b[5], 64, cudaMemcpyDeviceToHost, 0));
+    LG_CUDA(cudaMemcpyAsync(c->h_counters + 16, b[6], 64, cudaMemcpyDeviceToHost, 0));
+    LG_CUDA(cudaStreamSynchronize(0));
+    memset(out, 0, sizeof(*out));
+    memcpy(out->node_counter, c->h_counters, 64);
+    memcpy(out->edge_counter, c->h_counters + 16, 64);
+    const int32_t *nc = out->node_counter, *ec = out->edge_counter;
+    const int hops = nc[LEGION_INTRABATCH_CON * 3 - 1];
+    if (hops < 0 || hops > LEGION_MAX_HOPS) {
+        set_error("legion_client_get_next: counter block holds %d hops", hops);
+        return LEGION_E_STATE;
+    }
+    out->hop_num = hops;
+    out->n_ids = nc[LEGION_INTRABATCH_CON * 3 + hops];
+    out->n_labels = nc[LEGION_INTRABATCH_CON * 3];
+    out->ids = (const int32_t *)b[0];
+    out->features = b[1];
+    out->labels = (const int32_t *)b[2];
+    for (int i = hops, j = 0; i > 0; --i, ++j) {  // last hop first, like the trainer unpacks it
+        out->agg_src[j] = (const int32_t *)b[3] + ec[LEGION_INTRABATCH_CON * 4 + i];
+        out->agg_dst[j] = (const int32_t *)b[4] + ec[LEGION_INTRABATCH_CON * 4 + i];
+        out->n_edges[j] = ec[LEGION_INTRABATCH_CON * 3 + i];
+        out->block_src[j] = nc[LEGION_INTRABATCH_CON * 3 + i];
+        out->block_dst[j] = nc[LEGION_INTRABATCH_CON * 3 + i - 1];
+    }
+    return LEGION_OK;
+}
+
+// synchronize (ipc_service.cpp:89-91, ipc_cuda_kernel.cu:102-106): release the slot, move to the next
+extern "C" int legion_client_synchronize(LegionClient *c)
+{
+    LG_ARG(c != nullptr, "client is NULL");
+    if (sem_post(c->semr[c->current_pipe]) != 0) {
+        set_error("sem_post: %s", strerror(errno));
+        return LEGION_E_SYS;
+    }
+    c->current_pipe = (c->current_pipe + 1) % LEGION_INTERBATCH_CON;
+    return LEGION_OK;
+}

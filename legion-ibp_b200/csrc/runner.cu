@@ -588,6 +588,37 @@ extern "C" int legion_runner_serve(LegionRunner *r, int32_t first_global_batch, 
     return legion_runner_sync(r);
 }
 
+// The presampling epoch (GPUServer::PreSc -> GPURunner::RunPreSc, engine/server.cu:94-122,313-328): batches
+// [first, first+count) of the training list are sampled (no lookup, no gather) and every node they touch
+// is counted in counts_dev (one uint32 per node, the caller zeroes it), the input of
+// legion_cache_hotness_order.
+extern "C" int legion_runner_presample(LegionRunner *r, int32_t first_batch, int32_t count, uint32_t *counts_dev)
+{
+    LG_ARG(r != nullptr && counts_dev != nullptr && count >= 0 && first_batch >= 0, "bad argument");
+    LG_ARG(r->host_pending == 0, "host-buffer batches are waiting to be collected");
+    int rc = legion_runner_sync(r);
+    if (rc != LEGION_OK) return rc;
+    LegionPool *p = r->pool;
+    const int32_t total_cap = r->feature->count[LEGION_TRAINMODE];
+    LG_ARG(r->feature->ids[LEGION_TRAINMODE] != nullptr && total_cap > 0, "no training seed list");
+    for (int32_t b = first_batch; b < first_batch + count; ++b) {
+        rc = legion_pool_set_batch(p, b, LEGION_TRAINMODE, 0, (uint32_t)b);
+        if (rc != LEGION_OK) return rc;
+        const int64_t first = (int64_t)p->batch_size * b;
+        int64_t size = ((int64_t)p->batch_size * (b + 1) >= total_cap) ? (total_cap - first) : p->batch_size;
+        if (size <= 0) break;
+        rc = launch_batch_generate(r->s_sample, p, make_batch_ctl(p, r->cache, r->feature->ids[LEGION_TRAINMODE],
+                                                                   r->feature->labels[LEGION_TRAINMODE], total_cap, first,
+                                                                   (int32_t)size));
+        for (int h = 0; h < p->hop_num && rc == LEGION_OK; ++h)
+            rc = launch_sample_hop(r->s_sample, p, r->graph, p->fanout[h], h, LEGION_INTRABATCH_CON * (h + 1));
+        if (rc == LEGION_OK) rc = launch_hotness(r->s_sample, p, counts_dev);
+        if (rc != LEGION_OK) return rc;
+    }
+    LG_CUDA(cudaStreamSynchronize(r->s_sample));
+    return LEGION_OK;
+}
+
 extern "C" int legion_runner_destroy(LegionRunner *r)
 {
     if (r == nullptr) return LEGION_OK;

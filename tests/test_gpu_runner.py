@@ -353,3 +353,101 @@ def test_dataset_files_to_batches_with_topology_in_host_memory(oracle_mod, tmp_p
             feat = pool.read(L.BUF_FEATURES, pipe, len(b["ids"]) * 32, np.float32).reshape(-1, 32)
             np.testing.assert_array_equal(feat, ref["feats"][b["ids"]])
     r.Finalize(); pool.close(); cache.close(); f.close(); g.close(); ds.close()
+
+
+def test_presampling_hotness_and_ranking(oracle_mod):
+    """RunPreSc + CandidateSelection: access counts of a presampling epoch and the ranking made from
+    them equal the host replay (counts by bincount over the replayed batches, order by (-count, id))."""
+    import torch
+    w = _world(oracle_mod, n=6000, pairs=80000, batch=64, fanout=(25, 10), seed=12)
+    r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], None)
+    counts = torch.zeros(w["n"], dtype=torch.int32, device="cuda")
+    n_batches = (len(w["train"]) - 1) // w["batch"]      # train_step of the reference
+    r.presample(0, n_batches, counts)
+    want = np.zeros(w["n"], np.int64)
+    for it in range(n_batches):
+        b = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], w["batch"], it, w["fanout"], it, 99)
+        want += np.bincount(b["ids"], minlength=w["n"])
+    np.testing.assert_array_equal(counts.cpu().numpy(), want)
+    order = torch.empty(w["n"], dtype=torch.int32, device="cuda")
+    L.UnifiedCache.hotness_order(0, counts, order)
+    np.testing.assert_array_equal(order.cpu().numpy(), np.lexsort((np.arange(w["n"]), -want)).astype(np.int32))
+    # a cache filled in that order serves the same rows
+    cache = L.UnifiedCache(0, w["n"], 128 * 4, w["n"] // 10)
+    cache.fill_static(order, w["h_table"])
+    r2 = L.Runner(0, w["g"], w["f"], cache, w["pool"], None)
+    r2.enqueue(3, L.TRAINMODE, 3)
+    r2.sync()
+    b = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], w["batch"], 3, w["fanout"], 3, 99)
+    feat = w["pool"].read(L.BUF_FEATURES, 0, len(b["ids"]) * 128, np.float32).reshape(-1, 128)
+    np.testing.assert_array_equal(feat, w["table"][b["ids"]])
+    hot_hits = cache.stats()["local_hits"]
+    assert hot_hits > 0
+    r.Finalize(); r2.Finalize(); cache.close()
+
+
+CLIENT = r'''
+import sys, os, numpy as np, ctypes as C
+sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+import conftest
+import legion_ibp_b200 as L
+shm_name, n_batches, feat_len, out_path = sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
+svc = L.ipc_service(0, shm_name)
+def d2h(ptr, count, dtype):
+    out = np.empty(count, dtype)
+    if out.nbytes:
+        L._check(L.lib().legion_copy(C.c_void_p(out.ctypes.data), C.c_void_p(ptr), C.c_int64(out.nbytes), C.c_int32(2)))
+    return out
+res = {"steps": np.array(svc.get_steps(), np.int32)}
+for b in range(n_batches):
+    v = svc.get_next(timeout_ms=120000)
+    res["ids%d" % b] = d2h(v.ids, v.n_ids, np.int32)
+    res["feat%d" % b] = d2h(v.features, v.n_ids * feat_len, np.float32)
+    res["labels%d" % b] = d2h(v.labels, v.n_labels, np.int32)
+    res["blocks%d" % b] = np.array(svc.get_block_size(), np.int32)
+    for j in range(v.hop_num):
+        res["src%d_%d" % (b, j)] = d2h(v.agg_src[j], v.n_edges[j], np.int32)
+        res["dst%d_%d" % (b, j)] = d2h(v.agg_dst[j], v.n_edges[j], np.int32)
+    svc.synchronize()
+svc.finalize()
+np.savez(out_path, **res)
+'''
+
+
+def test_client_api_consumes_batches(oracle_mod, tmp_path):
+    """The trainer-side C-ABI client (initialize / get_next / get_block_size / get_steps / synchronize /
+    finalize) in a second process, fed by legion_runner_serve."""
+    w = _world(oracle_mod, seed=6)
+    shm = "legion_b200_cli_%d" % os.getpid()
+    env = L.IPCEnv(1, shm)
+    env.Coordinate([len(w["train"])], [1], [1], w["batch"], 1)
+    env.publish_pool(w["pool"], 0)
+    script = tmp_path / "client.py"
+    script.write_text(CLIENT)
+    out = tmp_path / "client.npz"
+    n_batches = 4
+    proc = subprocess.Popen([sys.executable, str(script), ROOT, shm, str(n_batches), str(w["table"].shape[1]), str(out)],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], env)
+    try:
+        r.serve(0, n_batches, timeout_ms=120000)
+        stdout, _ = proc.communicate(timeout=120)
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    assert proc.returncode == 0, stdout.decode()[-2000:]
+    got = np.load(out)
+    np.testing.assert_array_equal(got["steps"], env.steps())
+    for b in range(n_batches):
+        ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], w["batch"], b, w["fanout"], b, 99)
+        nc, ec = ref["node_counter"], ref["edge_counter"]
+        np.testing.assert_array_equal(got["ids%d" % b], ref["ids"])
+        np.testing.assert_array_equal(got["labels%d" % b], ref["labels"])
+        np.testing.assert_array_equal(got["feat%d" % b].reshape(len(ref["ids"]), -1), w["table"][ref["ids"]])
+        assert list(got["blocks%d" % b]) == [nc[11], nc[10], nc[10], nc[9]]   # get_block_size, last hop first
+        for j, hop in enumerate((2, 1)):
+            lo, cnt = int(ec[12 + hop]), int(ec[9 + hop])
+            np.testing.assert_array_equal(got["src%d_%d" % (b, j)], ref["agg_src"][lo:lo + cnt])
+            np.testing.assert_array_equal(got["dst%d_%d" % (b, j)], ref["agg_dst"][lo:lo + cnt])
+    r.Finalize()
+    env.Finalize()
