@@ -351,13 +351,13 @@ def main():
     # Algorithmic bytes per gathered row: the row read from its source + the row written + 4 B id +
     # 4 B lookup-table entry.  Rows served from GPU memory are moved by the hit kernel (HBM bound);
     # rows that miss the cache are moved by the miss kernel over the host link, for which the hit
-    # kernel still reads id + table entry and writes a 4-byte list entry.
+    # kernel still reads id + table entry and writes an 8-byte list entry.
     d = {k: stats1[k] - stats0[k] for k in stats0}
     hits = d["local_hits"] + d["peer_hits"]
     rows = hits + d["misses"]
     gather_launches = tm["timed"]  # one lookup + gather launch per batch
     timed_frac = tm["timed"] / float(args.steps)
-    hit_bytes = hits * (2 * row_bytes + 8) + d["misses"] * 12
+    hit_bytes = hits * (2 * row_bytes + 8) + d["misses"] * 16
     miss_bytes = d["misses"] * (2 * row_bytes + 8)
     gather_s = tm["gather_ms"] * 1e-3
     miss_s = tm["miss_ms"] * 1e-3
@@ -375,8 +375,8 @@ def main():
                 "avg_launch_ms": tm["gather_ms"] / max(1, gather_launches),
                 "rows_per_batch": rows / args.steps,
                 "source_split": {k: d[k] / max(1, rows) for k in ("local_hits", "peer_hits", "misses")},
-                "measured": "CUDA events around each launch on its stream, graph replay, %d batches run one at a "
-                            "time right after the timed region" % tm["timed"]}
+                "measured": "CUDA events around each launch on its stream, %d batches run one at a time right "
+                            "after the timed region" % tm["timed"]}
     link_peak = host_link_peak(table)
     link_achieved = d["misses"] * row_bytes / miss_s / 1e9 if miss_s > 0 else 0.0
     roofline_host = {"bound": "host_link", "kernel": "gather_miss_kernel (zero-copy fetch of missed rows)",

@@ -224,7 +224,7 @@ int legion_io_complete(void *stream, LegionCache *cache, LegionPool *pool, int32
  * take the device-wide synchronisation, the fragmentation or the failure of a cudaMalloc in the
  * middle of a step.  The caller passes inputs and output only; the scratch the gather needs (hit /
  * miss index per row, the list of missed rows, its counters) lives in a fixed array inside the
- * library image, so every GPU that loads the library holds about 2 MB for it until the process
+ * library image, so every GPU that loads the library holds about 3 MB for it until the process
  * exits.  This call, and everything it calls, performs no cudaMalloc / cudaFree.
  *
  *   ids_dev      n_rows int32 node ids on the device (ids < 0 leave their output row untouched)

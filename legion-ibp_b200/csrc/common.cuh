@@ -172,7 +172,7 @@ struct LegionPool {
     int32_t *tile_sum[LEGION_INTERBATCH_CON], *tile_off[LEGION_INTERBATCH_CON];
     int32_t *eslot[LEGION_INTERBATCH_CON], *erank[LEGION_INTERBATCH_CON];
     int64_t *lru_victim[LEGION_INTERBATCH_CON];       // per node: way chosen for insertion, or -1
-    int32_t *miss_rows[LEGION_INTERBATCH_CON];        // rows to fetch from the host table
+    int2 *miss_rows[LEGION_INTERBATCH_CON];           // (row, node id) to fetch from the host table
     int32_t *miss_count[LEGION_INTERBATCH_CON];       // [0] entries, [4] ticket
     int32_t *ctl[LEGION_INTERBATCH_CON];
     legion::BatchCtl *bctl[LEGION_INTERBATCH_CON];

@@ -35,7 +35,7 @@ struct GatherParams {
     int32_t row_bytes;   // bytes of one output row
     int32_t slot_bytes;  // bytes of one cached row
     int32_t feature_len; // elements per row (quantised codecs)
-    int32_t *miss_rows;  // rows (positions in ids) whose source is the host table
+    int2 *miss_rows;     // (position in ids, node id) of rows whose source is the host table
     int32_t *miss_count; // [0] number of entries
 };
 
@@ -97,8 +97,9 @@ __device__ __forceinline__ const uint8_t *resolve(const GatherParams &p, int32_t
 
 // Rows served by the host table are not copied by the hit kernels: the warp appends them to the
 // batch's miss list (one atomicAdd per warp, ranks by ballot) and clears their source pointer.
-// The list holds positions in `ids`; the miss kernel empties it.
-__device__ __forceinline__ void defer_misses(int32_t *miss_rows, int32_t *miss_count, int row, int where,
+// The list holds (position in `ids`, node id), so the miss kernel needs nothing else of the batch
+// and may still run while the next batch on the same pipe is being sampled; it empties the list.
+__device__ __forceinline__ void defer_misses(int2 *miss_rows, int32_t *miss_count, int row, int32_t id, int where,
                                              const uint8_t *&src, int lane)
 {
     unsigned m = __ballot_sync(kFull, where == 2);
@@ -107,7 +108,7 @@ __device__ __forceinline__ void defer_misses(int32_t *miss_rows, int32_t *miss_c
     if (lane == 0) base = atomicAdd(&miss_count[0], __popc(m));
     base = __shfl_sync(kFull, base, 0);
     if (where == 2) {
-        miss_rows[base + __popc(m & ((1u << lane) - 1u))] = row;
+        miss_rows[base + __popc(m & ((1u << lane) - 1u))] = make_int2(row, id);
         src = nullptr;
     }
 }
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
         const uint8_t *src = resolve(p, id, gidx, where);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
-        defer_misses(p.miss_rows, p.miss_count, off + r, where, src, lane);
+        defer_misses(p.miss_rows, p.miss_count, off + r, id, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         uint8_t *dst_base = p.dst + (int64_t)(off + c * 32) * p.row_bytes;
         for (int j0 = 0; j0 < rows_here; j0 += R) {
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(256) gather_word_kernel(GatherParams p)
         const uint8_t *src = resolve(p, id, gidx, where);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
-        defer_misses(p.miss_rows, p.miss_count, off + r, where, src, lane);
+        defer_misses(p.miss_rows, p.miss_count, off + r, id, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         uint32_t *dst_base = reinterpret_cast<uint32_t *>(p.dst + (int64_t)(off + c * 32) * p.row_bytes);
         for (int j = 0; j < rows_here; ++j) {
@@ -230,7 +231,7 @@ __global__ void __launch_bounds__(256) gather_quant_kernel(GatherParams p)
         const uint8_t *src = resolve(p, id, gidx, where);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
-        defer_misses(p.miss_rows, p.miss_count, off + r, where, src, lane);
+        defer_misses(p.miss_rows, p.miss_count, off + r, id, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         float *dst_base = reinterpret_cast<float *>(p.dst + (int64_t)(off + c * 32) * p.row_bytes);
         for (int j = 0; j < rows_here; ++j) {
@@ -261,8 +262,7 @@ __global__ void __launch_bounds__(256) gather_quant_kernel(GatherParams p)
 // list.  Measured alone on random 512-byte rows: 50.6 GB/s over a 1 GB table (0.91 of a pinned
 // cudaMemcpy), 26 GB/s over 48 GB, where address translation of the scattered pages limits the link.
 struct MissParams {
-    const int32_t *ids;
-    const int32_t *miss_rows;
+    const int2 *miss_rows;
     int32_t *miss_count;
     int32_t *ticket;
     const uint8_t *host;
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(256) gather_miss_kernel(MissParams p)
     const int n = p.miss_count[0];
     const int lane = threadIdx.x & 31;
     const int n_warps = (gridDim.x * blockDim.x) >> 5;
-    const int32_t *list = p.miss_rows;
+    const int2 *list = p.miss_rows;
     if ((p.row_bytes & 15) == 0) {
         const int row_vec = p.row_bytes >> 4;
         for (int m0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * R; m0 < n; m0 += n_warps * R) {
@@ -289,10 +289,9 @@ __global__ void __launch_bounds__(256) gather_miss_kernel(MissParams p)
                 sp[jj] = nullptr;
                 dp[jj] = nullptr;
                 if (m0 + jj < n) {
-                    int row = __ldg(&list[m0 + jj]);
-                    int32_t id = __ldg(&p.ids[row]);
-                    sp[jj] = p.host + ((int64_t)id % p.n_nodes) * (int64_t)p.row_bytes;
-                    dp[jj] = p.dst + (int64_t)row * p.row_bytes;
+                    const int2 e = __ldg(&list[m0 + jj]);
+                    sp[jj] = p.host + ((int64_t)e.y % p.n_nodes) * (int64_t)p.row_bytes;
+                    dp[jj] = p.dst + (int64_t)e.x * p.row_bytes;
                 }
             }
             for (int q0 = 0; q0 < row_vec; q0 += 32) {
@@ -309,10 +308,9 @@ __global__ void __launch_bounds__(256) gather_miss_kernel(MissParams p)
     } else {
         const int row_words = p.row_bytes >> 2;
         for (int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; m < n; m += n_warps) {
-            int row = __ldg(&list[m]);
-            int32_t id = __ldg(&p.ids[row]);
-            const uint32_t *sp = reinterpret_cast<const uint32_t *>(p.host + ((int64_t)id % p.n_nodes) * (int64_t)p.row_bytes);
-            uint32_t *dp = reinterpret_cast<uint32_t *>(p.dst + (int64_t)row * p.row_bytes);
+            const int2 e = __ldg(&list[m]);
+            const uint32_t *sp = reinterpret_cast<const uint32_t *>(p.host + ((int64_t)e.y % p.n_nodes) * (int64_t)p.row_bytes);
+            uint32_t *dp = reinterpret_cast<uint32_t *>(p.dst + (int64_t)e.x * p.row_bytes);
             for (int w = lane; w < row_words; w += 32) __stcs(&dp[w], sp[w]);
         }
     }
@@ -345,7 +343,7 @@ struct LruParams {
     int64_t *cache_index;
     unsigned long long *stats;
     int32_t row_bytes;
-    int32_t *miss_rows;
+    int2 *miss_rows;
     int32_t *miss_count;
 };
 
@@ -390,7 +388,7 @@ __global__ void __launch_bounds__(256) gather_lru_kernel(LruParams p)
             else if (p.host != nullptr) { where = 2; src = p.host + ((int64_t)my_id % p.n_nodes) * (int64_t)p.row_bytes; }
         }
         add_stats(p.stats, where, lane);
-        defer_misses(p.miss_rows, p.miss_count, off + r, where, src, lane);
+        defer_misses(p.miss_rows, p.miss_count, off + r, my_id, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         uint8_t *dst_base = p.dst + (int64_t)(off + c * 32) * p.row_bytes;
         for (int j0 = 0; j0 < rows_here; j0 += R) {
@@ -615,7 +613,6 @@ int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c)
     if (c == nullptr || c->host_table == nullptr) return LEGION_OK;
     const int pipe = p->pipe;
     MissParams mp;
-    mp.ids = p->ids[pipe];
     mp.miss_rows = p->miss_rows[pipe];
     mp.miss_count = p->miss_count[pipe];
     mp.ticket = p->miss_count[pipe] + 4;
@@ -673,16 +670,16 @@ int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c)
 // entry points above take their scratch (cache_index, the miss list and its counters, the segment
 // words the kernels read) from a LegionPool, which allocates; this one keeps the same scratch in a
 // fixed array inside the library image.  Every GPU that loads the library holds that array
-// (256 B + 8 B per row of LEGION_NOALLOC_MAX_ROWS, about 2 MB) until the process exits.
-static __device__ __align__(256) unsigned char g_noalloc_scratch[256 + 8 * (size_t)LEGION_NOALLOC_MAX_ROWS];
+// (256 B + 12 B per row of LEGION_NOALLOC_MAX_ROWS, about 3 MB) until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[256 + 12 * (size_t)LEGION_NOALLOC_MAX_ROWS];
 
 namespace legion {
 
 // byte offsets inside the array
 constexpr size_t kNaCounter = 0;     // 16 int32: the node_counter words the gather kernels read
 constexpr size_t kNaMissCount = 64;  // 8 int32: [0] entries of the miss list, [4] ticket
-constexpr size_t kNaMissRows = 256;  // int32[LEGION_NOALLOC_MAX_ROWS]
-constexpr size_t kNaCacheIndex = 256 + 4 * (size_t)LEGION_NOALLOC_MAX_ROWS;  // int32[LEGION_NOALLOC_MAX_ROWS]
+constexpr size_t kNaMissRows = 256;  // int2[LEGION_NOALLOC_MAX_ROWS]
+constexpr size_t kNaCacheIndex = 256 + 8 * (size_t)LEGION_NOALLOC_MAX_ROWS;  // int32[LEGION_NOALLOC_MAX_ROWS]
 
 // The array is shared by every call and keeps what the last call left: the words that must start
 // from a known value are rewritten here at the start of each call.
@@ -761,7 +758,7 @@ extern "C" int legion_gather_rows_noalloc(void *stream, int32_t dev_id, const in
     gp.row_bytes = row_bytes;
     gp.slot_bytes = row_bytes;
     gp.feature_len = row_bytes / 4;
-    gp.miss_rows = reinterpret_cast<int32_t *>(scratch + kNaMissRows);
+    gp.miss_rows = reinterpret_cast<int2 *>(scratch + kNaMissRows);
     gp.miss_count = miss_count;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_id);
@@ -782,7 +779,6 @@ extern "C" int legion_gather_rows_noalloc(void *stream, int32_t dev_id, const in
     LG_LAUNCH_CHECK();
     if (host_table != nullptr) {
         MissParams mp;
-        mp.ids = ids_dev;
         mp.miss_rows = gp.miss_rows;
         mp.miss_count = miss_count;
         mp.ticket = miss_count + 4;

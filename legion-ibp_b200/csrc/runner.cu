@@ -10,16 +10,19 @@
 // launch per batch behind the last gather so that the link sees one long burst instead of three
 // short ones.  The gather of hop h overlaps the sampling of hop h+1.
 //
-// A batch is ~25 small launches, so issuing it from the host costs more than running it.  Every
+// A batch is ~15 small launches, so issuing it from the host costs more than running it.  Every
 // size lives on the device and the per-batch parameters are written by the first kernel, so the
-// sampling + gather sequence of one pipe (two streams) is captured once into a CUDA graph; a batch
-// is then one parameter update of that first node, one graph launch and the host-link fetch.  The
-// two pipes own separate scratch and are launched on two streams, so consecutive batches overlap.
-// The host-link fetches of all batches run in order on one stream of their own, outside the
-// graphs: if they shared the link, two batches would enter and leave their host-link phase
-// together and the link would idle while both sample; first-in first-out staggers them, so the
-// fetch of batch k runs under the sampling and gathering of batch k+1.  An LRU cache, whose state
-// changes every batch, keeps whole batches in order.
+// sampling sequence of one pipe is captured once into a CUDA graph; a batch is then one parameter
+// update of that first node, one graph launch, the gather launch and the host-link fetch.  The two
+// pipes own separate scratch and are launched on two streams, so consecutive batches overlap.
+//
+// What may overlap with what is decided by who touches the pipe's buffers.  The host-link fetch
+// reads nothing of the batch but its miss list (which carries node ids) and writes feature rows, so
+// the SAMPLING of batch k+2 (same pipe) starts while the fetch of batch k is still running; only the
+// gather of batch k+2, which writes the same feature buffer and miss list, waits for it.  The
+// fetches of all batches run in order on one stream of their own at the highest priority: when they
+// shared the link, two batches entered and left their host-link phase together and the link idled
+// while both sampled.  An LRU cache, whose state changes every batch, keeps whole batches in order.
 #include "common.cuh"
 
 #include <string.h>
@@ -185,54 +188,39 @@ extern "C" int legion_runner_set_options(LegionRunner *r, int32_t use_graph, int
     return LEGION_OK;
 }
 
-// Marks a point on `s`: an external event-record node while capturing, a plain record otherwise.
-static cudaError_t mark(cudaEvent_t e, cudaStream_t s, bool capturing)
-{
-    return capturing ? cudaEventRecordWithFlags(e, s, cudaEventRecordExternal) : cudaEventRecord(e, s);
-}
-
-// One segment: lookup and cached rows on the gather stream; missed rows are only listed here.
-static int gather_segment(LegionRunner *r, int op_id, int seg, bool capturing)
+// Lookup + gather of cached rows over every node of the batch (one launch; the operator entry
+// points still gather hop by hop like the reference: one launch over ~2x10^5 rows runs near HBM
+// speed, three launches of 8 k / 60 k / 140 k rows mostly pay start-up and tail).  Missed rows are
+// only listed here.
+static int issue_gather(LegionRunner *r, cudaStream_t s)
 {
     LegionPool *p = r->pool;
     LegionCache *c = r->cache;
     if (c != nullptr) LG_ARG(c->row_bytes == p->row_bytes_out, "cache and pool disagree on the row size");
     EvPair h = { nullptr, nullptr };
-    if (r->time_kernels) {
-        if (capturing) {
-            h = r->pg[p->pipe].hit[seg];
-        } else if (r->gather_ev.size() < 8192) {
-            h.a = take_event(r);
-            h.b = take_event(r);
-        }
+    if (r->time_kernels && r->gather_ev.size() < 8192) {
+        h.a = take_event(r);
+        h.b = take_event(r);
     }
-    if (h.a) LG_CUDA(mark(h.a, r->s_gather, capturing));
-    int rc = launch_gather_hits(r->s_gather, p, c, op_id);
+    if (h.a) LG_CUDA(cudaEventRecord(h.a, s));
+    int rc = launch_gather_hits(s, p, c, kOpGatherAll);
     if (rc != LEGION_OK) return rc;
-    if (h.b) LG_CUDA(mark(h.b, r->s_gather, capturing));
-    if (h.a && h.b && !capturing) r->gather_ev.push_back(h);
+    if (h.b) LG_CUDA(cudaEventRecord(h.b, s));
+    if (h.a && h.b) r->gather_ev.push_back(h);
     return LEGION_OK;
 }
 
-// Sampling, then one lookup + gather of cached rows over every node of the batch; origin s_sample,
-// last work on s_gather.  This is the part that is captured into the pipe's graph.  (The operator
-// entry points still gather hop by hop like the reference; one launch over ~2x10^5 rows runs near
-// HBM speed, three launches of 8 k / 60 k / 140 k rows mostly pay start-up and tail.)
-static int issue_front(LegionRunner *r, const BatchCtl &v, bool capturing)
+// Seed batch and all hops, on one stream: the part that is captured into the pipe's graph.
+static int issue_sampling(LegionRunner *r, const BatchCtl &v, cudaStream_t s)
 {
     LegionPool *p = r->pool;
-    int rc = launch_batch_generate(r->s_sample, p, v);
-    if (rc != LEGION_OK) return rc;
-    for (int h = 0; h < p->hop_num; ++h) {
-        rc = launch_sample_hop(r->s_sample, p, r->graph, p->fanout[h], h, LEGION_INTRABATCH_CON * (h + 1));
-        if (rc != LEGION_OK) return rc;
-    }
-    LG_CUDA(cudaEventRecord(r->seg_ready[0], r->s_sample));
-    LG_CUDA(cudaStreamWaitEvent(r->s_gather, r->seg_ready[0], 0));
-    return gather_segment(r, kOpGatherAll, 0, capturing);
+    int rc = launch_batch_generate(s, p, v);
+    for (int h = 0; h < p->hop_num && rc == LEGION_OK; ++h)
+        rc = launch_sample_hop(s, p, r->graph, p->fanout[h], h, LEGION_INTRABATCH_CON * (h + 1));
+    return rc;
 }
 
-// The rows that missed (all on the list once the front part is over) and the end-of-batch cache
+// The rows that missed (all on the list once the gather is over) and the end-of-batch cache
 // maintenance, on s_miss, which every batch shares.
 static int issue_back(LegionRunner *r)
 {
@@ -257,12 +245,8 @@ static int capture_pipe(LegionRunner *r, int pipe, const BatchCtl &v)
 {
     PipeGraph &g = r->pg[pipe];
     LG_CUDA(cudaStreamBeginCapture(r->s_sample, cudaStreamCaptureModeThreadLocal));
-    int rc = issue_front(r, v, true);
+    int rc = issue_sampling(r, v, r->s_sample);
     cudaError_t e = cudaSuccess;
-    if (rc == LEGION_OK) {
-        e = cudaEventRecord(r->join_ev, r->s_gather);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(r->s_sample, r->join_ev, 0);
-    }
     cudaGraph_t graph = nullptr;
     cudaError_t e2 = cudaStreamEndCapture(r->s_sample, &graph);
     if (rc != LEGION_OK) {
@@ -330,9 +314,11 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
         r->open_window = true;
         r->window_batches = 0;
     }
-    // the buffers of this pipe are rewritten: the fetch that last wrote them must be over;
-    // an LRU cache also has to see the previous batch's insertions before the next lookup
-    if (r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
+    // An LRU cache has to see the previous batch's insertions before anything of this batch runs.
+    // Otherwise sampling only rewrites buffers that the last fetch on this pipe does not touch, so it
+    // starts at once; the wait for that fetch comes before the gather, below.
+    const bool early_sampling = !lru && host_seeds == 0;
+    if (!early_sampling && r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
     if (lru && r->last_pipe >= 0 && r->last_pipe != pipe && r->pipe_busy[r->last_pipe])
         LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[r->last_pipe], 0));
     if (host_seeds > 0) {
@@ -351,12 +337,14 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
         LG_CUDA(cudaGraphExecKernelNodeSetParams(g.exec, g.ctl_node, &g.ctl_params));
         LG_CUDA(cudaGraphLaunch(g.exec, front));
         g.launched = true;
-        LG_CUDA(cudaEventRecord(r->hit_done[pipe], front));
     } else {
-        rc = issue_front(r, v, false);
+        rc = issue_sampling(r, v, front);
         if (rc != LEGION_OK) return rc;
-        LG_CUDA(cudaEventRecord(r->hit_done[pipe], r->s_gather));
     }
+    if (early_sampling && r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
+    rc = issue_gather(r, front);
+    if (rc != LEGION_OK) return rc;
+    LG_CUDA(cudaEventRecord(r->hit_done[pipe], front));
     LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->hit_done[pipe], 0));
     rc = issue_back(r);
     if (rc != LEGION_OK) return rc;
@@ -489,18 +477,9 @@ extern "C" int legion_runner_sync(LegionRunner *r)
             r->ev_free.push_back(pr.a);
             r->ev_free.push_back(pr.b);
         }
-        if (!r->use_graph && r->time_kernels) timed = r->window_batches;
+        if (r->time_kernels) timed = (int)r->gather_ev.size();
         r->gather_ev.clear();
         r->miss_ev.clear();
-        if (r->use_graph && r->time_kernels) {
-            // the events inside a pipe's graph hold the times of its last launch
-            for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
-                if (!r->pg[i].launched) continue;
-                float t = 0.0f;
-                if (cudaEventElapsedTime(&t, r->pg[i].hit[0].a, r->pg[i].hit[0].b) == cudaSuccess) g += t;
-                timed += 1;
-            }
-        }
         r->last_batch_ms = ms;
         r->last_gather_ms = g;
         r->last_miss_ms = m;
