@@ -187,3 +187,45 @@ def test_rejects_bad_arguments():
     with pytest.raises(L.LegionError):
         L.MemoryPool(0, 10, [40], 16)
     pool.close(); f.close(); g.close()
+
+
+def test_isolated_nodes_hubs_and_empty_topology(oracle_mod):
+    """Edge cases of the topology: a graph without edges (every hop is empty), a star (one hub whose
+    degree is far above the fanout, leaves of degree 1) plus isolated seeds, and ids at both ends of
+    the id range."""
+    # no edges at all
+    n = 100
+    indptr = np.zeros(n + 1, np.int64)
+    indices = np.zeros(1, np.int32)
+    train = np.arange(n, dtype=np.int32)[::-1].copy()
+    labels = np.arange(n, dtype=np.int32)
+    g, f, pool = _setup(indptr, indices, train, labels, 40, [25, 10])
+    pool.set_rng(1, 64)
+    for it in range(3):
+        _run_ops(g, f, pool, 40, it, [25, 10], global_batch=it, pipe=it % 2)
+        got = _fetch(pool, it % 2)
+        ref = oracle_mod.run_batch(indptr, indices, train, labels, 40, it, [25, 10], it, 1)
+        _compare(got, ref)
+        assert got["edge_counter"][10] == 0 and got["edge_counter"][11] == 0 and len(got["ids"]) == min(40, 100 - 40 * it)
+    pool.close(); f.close(); g.close()
+    # star: node 0 is the hub of 5000 leaves; nodes 5001..5999 are isolated
+    n = 6000
+    deg = np.zeros(n, np.int64)
+    deg[0] = 5000
+    deg[1:5001] = 1
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = np.concatenate([np.arange(1, 5001), np.zeros(5000)]).astype(np.int32)
+    train = np.array([0, 5999, 1, 5000, 5500, 2500, 5001], np.int32)
+    labels = np.arange(len(train), dtype=np.int32)
+    for fanout in ([25, 10], [32, 32, 32], [1, 1]):
+        g, f, pool = _setup(indptr, indices, train, labels, 7, fanout)
+        pool.set_rng(9, 64)
+        for gb in range(3):
+            _run_ops(g, f, pool, 7, 0, fanout, global_batch=gb)
+            got = _fetch(pool)
+            ref = oracle_mod.run_batch(indptr, indices, train, labels, 7, 0, fanout, gb, 9)
+            _compare(got, ref)
+            e1 = int(got["edge_counter"][10])
+            assert e1 == min(fanout[0], 5000) + 3        # the hub's picks + one edge for each of the three leaves
+            assert pool.device_error() == 0
+        pool.close(); f.close(); g.close()
