@@ -367,6 +367,10 @@ int legion_runner_set_options(LegionRunner *r, int32_t use_graph, int32_t time_k
  * events are overwritten per launch. */
 int legion_runner_timing(LegionRunner *r, float *batch_ms, float *gather_ms, float *miss_ms, int32_t *n_batches,
                          int32_t *n_timed);
+/* Stage times of the last window that ran with time_kernels (the per-op times of the reference's
+ * MONITOR build, engine/server.cu:346-395): six floats per batch = begin / end of sampling, of the
+ * gather and of the host-link fetch, in ms since the window's start.  Returns the batch count. */
+int legion_runner_trace(LegionRunner *r, float *out, int32_t max_batches);
 /* The serving loop of GPUServer (engine/server.cu:39-44,124-143) for `count` batches starting at
  * first_global_batch, with mode and local batch number taken from the IPC environment. */
 int legion_runner_serve(LegionRunner *r, int32_t first_global_batch, int32_t count, int32_t timeout_ms);

@@ -411,6 +411,14 @@ class Runner:
         _check(lib().legion_runner_timing(self.h, C.byref(a), C.byref(b), C.byref(m), C.byref(n), C.byref(t)))
         return dict(batch_ms=a.value, gather_ms=b.value, miss_ms=m.value, batches=n.value, timed=t.value)
 
+    def trace(self, max_batches=4096):
+        """[[samp_begin, samp_end, gather_begin, gather_end, miss_begin, miss_end], ...] of the last timed window (ms)."""
+        buf = (C.c_float * (6 * max_batches))()
+        n = lib().legion_runner_trace(self.h, buf, C.c_int32(max_batches))
+        if n < 0:
+            raise LegionError("legion_runner_trace failed")
+        return [list(buf[6 * i:6 * i + 6]) for i in range(n)]
+
     def set_options(self, use_graph=True, time_kernels=False):
         _check(lib().legion_runner_set_options(self.h, C.c_int32(int(use_graph)), C.c_int32(int(time_kernels))))
 

@@ -77,7 +77,8 @@ struct LegionRunner {
     bool open_window;
     int window_batches;
     std::vector<cudaEvent_t> ev_free;
-    std::vector<EvPair> gather_ev, miss_ev;
+    std::vector<EvPair> gather_ev, miss_ev, sample_ev;
+    std::vector<float> trace;  // per batch of the last timed window: begin/end of sampling, gather, fetch (ms)
     float last_batch_ms, last_gather_ms, last_miss_ms;
     int last_batches, last_timed;
     long long served;
@@ -327,6 +328,11 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
         LG_CUDA(cudaMemcpyAsync(p->label_stage[pipe], hs + p->batch_size, sizeof(int32_t) * host_seeds,
                                 cudaMemcpyHostToDevice, front));
     }
+    EvPair se = { nullptr, nullptr };
+    if (r->time_kernels && r->sample_ev.size() < 8192) {
+        se.a = take_event(r);
+        se.b = take_event(r);
+    }
     if (r->use_graph) {
         PipeGraph &g = r->pg[pipe];
         if (!g.valid) {
@@ -335,12 +341,16 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
         }
         g.a_value = v;
         LG_CUDA(cudaGraphExecKernelNodeSetParams(g.exec, g.ctl_node, &g.ctl_params));
+        if (se.a) LG_CUDA(cudaEventRecord(se.a, front));
         LG_CUDA(cudaGraphLaunch(g.exec, front));
         g.launched = true;
     } else {
+        if (se.a) LG_CUDA(cudaEventRecord(se.a, front));
         rc = issue_sampling(r, v, front);
         if (rc != LEGION_OK) return rc;
     }
+    if (se.b) LG_CUDA(cudaEventRecord(se.b, front));
+    if (se.a && se.b) r->sample_ev.push_back(se);
     if (early_sampling && r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
     rc = issue_gather(r, front);
     if (rc != LEGION_OK) return rc;
@@ -478,6 +488,27 @@ extern "C" int legion_runner_sync(LegionRunner *r)
             r->ev_free.push_back(pr.b);
         }
         if (r->time_kernels) timed = (int)r->gather_ev.size();
+        r->trace.clear();
+        if (r->time_kernels && r->sample_ev.size() == r->gather_ev.size() &&
+            (r->miss_ev.empty() || r->miss_ev.size() == r->gather_ev.size())) {
+            for (size_t i = 0; i < r->gather_ev.size(); ++i) {
+                float v6[6] = { 0, 0, 0, 0, 0, 0 };
+                cudaEventElapsedTime(&v6[0], r->t_begin, r->sample_ev[i].a);
+                cudaEventElapsedTime(&v6[1], r->t_begin, r->sample_ev[i].b);
+                cudaEventElapsedTime(&v6[2], r->t_begin, r->gather_ev[i].a);
+                cudaEventElapsedTime(&v6[3], r->t_begin, r->gather_ev[i].b);
+                if (!r->miss_ev.empty()) {
+                    cudaEventElapsedTime(&v6[4], r->t_begin, r->miss_ev[i].a);
+                    cudaEventElapsedTime(&v6[5], r->t_begin, r->miss_ev[i].b);
+                }
+                r->trace.insert(r->trace.end(), v6, v6 + 6);
+            }
+        }
+        for (auto &pr : r->sample_ev) {
+            r->ev_free.push_back(pr.a);
+            r->ev_free.push_back(pr.b);
+        }
+        r->sample_ev.clear();
         r->gather_ev.clear();
         r->miss_ev.clear();
         r->last_batch_ms = ms;
@@ -504,6 +535,18 @@ extern "C" int legion_runner_timing(LegionRunner *r, float *batch_ms, float *gat
     if (n_batches) *n_batches = r->last_batches;
     if (n_timed) *n_timed = r->last_timed;
     return LEGION_OK;
+}
+
+// Stage times of the last window that ran with time_kernels: six floats per batch, the begin and
+// end of its sampling, of its gather and of its host-link fetch, in ms since the window's start.
+// Returns the number of batches written (at most max_batches).
+extern "C" int legion_runner_trace(LegionRunner *r, float *out, int32_t max_batches)
+{
+    if (r == nullptr || out == nullptr || max_batches < 0) return LEGION_E_ARG;
+    int n = (int)(r->trace.size() / 6);
+    if (n > max_batches) n = max_batches;
+    memcpy(out, r->trace.data(), sizeof(float) * 6 * (size_t)n);
+    return n;
 }
 
 extern "C" int legion_runner_current_pipe(LegionRunner *r) { return r ? r->current_pipe : LEGION_E_ARG; }
@@ -606,6 +649,7 @@ extern "C" int legion_runner_destroy(LegionRunner *r)
     drop_graphs(r);
     for (auto &pr : r->gather_ev) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
     for (auto &pr : r->miss_ev) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
+    for (auto &pr : r->sample_ev) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
     for (auto e : r->ev_free) cudaEventDestroy(e);
     for (int i = 0; i <= LEGION_MAX_HOPS; ++i) { cudaEventDestroy(r->seg_ready[i]); cudaEventDestroy(r->hit_done[i]); }
     cudaEventDestroy(r->join_ev);
