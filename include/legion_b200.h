@@ -151,6 +151,10 @@ int legion_cache_lut(LegionCache *c, int32_t **lut_dev);
  * legion_cache_set_peer remain as the fallback. */
 int legion_cache_export_partition(LegionCache *c, int32_t *fd_out, int64_t *bytes_out);
 int legion_cache_import_peer(LegionCache *c, int32_t k, int32_t fd, int64_t bytes);
+/* One process with a thread per GPU, as the reference runs (engine/server.cu:127-135): give device
+ * `dev` read access to this cache's partition, whose pointer the other thread then hands to
+ * legion_cache_set_peer. */
+int legion_cache_allow_device(LegionCache *c, int32_t dev);
 /* Table that serves the misses (cpu_float_features_, cache/cache.cu:771-776); set by
  * legion_cache_fill_static, or here for a cache that is filled some other way. */
 int legion_cache_set_host_table(LegionCache *c, const void *host_table);

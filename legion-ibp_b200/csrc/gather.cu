@@ -261,6 +261,9 @@ __global__ void __launch_bounds__(256) gather_quant_kernel(GatherParams p)
 // reads in flight while the HBM-bound kernels of the next batch carry on.  The last CTA empties the
 // list.  Measured alone on random 512-byte rows: 50.6 GB/s over a 1 GB table (0.91 of a pinned
 // cudaMemcpy), 26 GB/s over 48 GB, where address translation of the scattered pages limits the link.
+constexpr int kMissCtas = 16;      // CTAs of the host-link fetch (see launch_gather_misses)
+constexpr int kMissThreads = 1024;
+
 struct MissParams {
     const int2 *miss_rows;
     int32_t *miss_count;
@@ -272,7 +275,7 @@ struct MissParams {
 };
 
 template <int R>
-__global__ void __launch_bounds__(256) gather_miss_kernel(MissParams p)
+__global__ void __launch_bounds__(1024) gather_miss_kernel(MissParams p)
 {
     __shared__ int s_last;
     const int n = p.miss_count[0];
@@ -604,7 +607,8 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
     return LEGION_OK;
 }
 
-int g_miss_ctas = 0;  // 0 = one CTA per SM; see legion_set_tunable
+int g_miss_ctas = 0;     // 0 = default; see legion_set_tunable
+int g_miss_threads = 0;  // 0 = default
 
 // The rows the hit kernels listed so far, fetched from the pinned host table; empties the list.
 // No-op without a host table.
@@ -623,9 +627,10 @@ int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c)
     // 4 rows per warp and pass; one CTA per SM keeps ~2.4 MB of reads in flight, far more than the
     // host link needs, and leaves the SMs to the HBM-bound kernels of the next batch
     int64_t g64 = (p->max_nodes + 31) / 32;
-    int cap = g_miss_ctas > 0 ? g_miss_ctas : p->sm_count;
+    int cap = g_miss_ctas > 0 ? g_miss_ctas : kMissCtas;
+    int threads = g_miss_threads > 0 ? g_miss_threads : kMissThreads;
     int grid = (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
-    gather_miss_kernel<4><<<grid, 256, 0, s>>>(mp);
+    gather_miss_kernel<4><<<grid, threads, 0, s>>>(mp);
     LG_LAUNCH_CHECK();
     return LEGION_OK;
 }
@@ -802,6 +807,11 @@ extern "C" int legion_set_tunable(const char *name, int32_t value)
     if (strcmp(name, "miss_ctas") == 0) {
         LG_ARG(value >= 0 && value <= 4096, "miss_ctas out of range");
         g_miss_ctas = value;
+        return LEGION_OK;
+    }
+    if (strcmp(name, "miss_threads") == 0) {
+        LG_ARG(value == 0 || (value >= 32 && value <= 1024 && value % 32 == 0), "miss_threads must be a multiple of 32 up to 1024");
+        g_miss_threads = value;
         return LEGION_OK;
     }
     set_error("legion_set_tunable: unknown name %s", name);

@@ -1,0 +1,230 @@
+// sampling_server: the server binary of the reference (sampling_server/src/main.cu:5-17 ->
+// GPUServer::Initialize / PreSc / Run / Finalize, engine/server.cu:46-170) on top of the C ABI.
+//
+//   sampling_server <ngpu> <cache_agg_mode> <dyn_flags> [fanout ...]
+//
+// reads ./meta_config (written by legion_server.py:45-46), loads the Legion-format dataset, runs one
+// host thread per GPU, builds the caches (presampled hotness order like the reference; set
+// LEGION_ORDER=degree for the degree order), publishes the hand-off buffers, prints
+// "System is ready for serving" (engine/server.cu:121; scripts/wait_file.sh waits for that line) and
+// serves every batch of the schedule to the trainers.  cache_agg_mode is accepted and ignored: an
+// NVSwitch box is one clique.  dyn_flags: bit 3 (DYN_COMP, comp_cache/cache_helper.cuh:34-45) selects
+// int8-compressed cache rows, bit 0 (DYN_ENABLE) the per-GPU LRU cache, 0 the static cache.  The
+// fanout defaults to the reference's hard-coded {25, 10} (main.cu:9-11).
+#include <pthread.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <thread>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "../../include/legion_b200.h"
+
+#define CHECK(call)                                                              \
+    do {                                                                         \
+        int rc_ = (call);                                                        \
+        if (rc_ != LEGION_OK) {                                                  \
+            fprintf(stderr, "%s:%d: %s\n", __FILE__, __LINE__, legion_last_error()); \
+            exit(EXIT_FAILURE);                                                  \
+        }                                                                        \
+    } while (0)
+#define CUCHECK(call)                                                            \
+    do {                                                                         \
+        cudaError_t e_ = (call);                                                 \
+        if (e_ != cudaSuccess) {                                                 \
+            fprintf(stderr, "%s:%d: %s\n", __FILE__, __LINE__, cudaGetErrorString(e_)); \
+            exit(EXIT_FAILURE);                                                  \
+        }                                                                        \
+    } while (0)
+
+struct Rank {
+    int dev;
+    LegionGraph *graph = nullptr;
+    LegionFeatures *feature = nullptr;
+    LegionCache *cache = nullptr;
+    LegionPool *pool = nullptr;
+    LegionRunner *runner = nullptr;
+    int64_t *d_indptr = nullptr;
+    int32_t *d_indices = nullptr;
+    int32_t *d_ids[3] = { nullptr, nullptr, nullptr }, *d_labels[3] = { nullptr, nullptr, nullptr };
+    int32_t count[3] = { 0, 0, 0 };
+};
+
+static pthread_barrier_t g_barrier;
+
+int main(int argc, char **argv)
+{
+    if (argc < 4) {
+        fprintf(stderr, "usage: %s <ngpu> <cache_agg_mode> <dyn_flags> [fanout ...]\n", argv[0]);
+        return 1;
+    }
+    const int ngpu = atoi(argv[1]);
+    const int dyn_flags = atoi(argv[3]);
+    std::vector<int32_t> fanout;
+    for (int i = 4; i < argc; ++i) fanout.push_back(atoi(argv[i]));
+    if (fanout.empty()) fanout = { 25, 10 };
+    const char *order_env = getenv("LEGION_ORDER");
+    const bool degree_order = order_env != nullptr && strcmp(order_env, "degree") == 0;
+    const char *shm_env = getenv("LEGION_SHM_NAME");  // tests only; the trainers expect the default
+    const char *seed_env = getenv("LEGION_SEED");
+    const uint64_t seed = seed_env ? strtoull(seed_env, nullptr, 0) : 0;
+    const int timeout_ms = getenv("LEGION_TIMEOUT_MS") ? atoi(getenv("LEGION_TIMEOUT_MS")) : -1;
+    if (ngpu < 1 || ngpu > LEGION_MAX_DEVICE) {
+        fprintf(stderr, "ngpu must be 1..%d\n", LEGION_MAX_DEVICE);
+        return 1;
+    }
+
+    LegionMetaConfig meta;
+    CHECK(legion_meta_config_read("./meta_config", &meta));
+    printf("Dataset path:       %s\nRaw Batchsize:      %d\nGraph nodes num:    %lld\nGraph edges num:    %lld\n"
+           "Feature dim:        %d\nTraining set num:   %d\nValidation set num: %d\nTesting set num:    %d\n"
+           "Cache memory:       %lld\nTrain epoch:        %d\n",
+           meta.dataset_path, meta.raw_batch_size, (long long)meta.node_num, (long long)meta.edge_num,
+           meta.float_feature_len, meta.training_set_num, meta.validation_set_num, meta.testing_set_num,
+           (long long)meta.cache_memory, meta.epoch);
+    CUCHECK(cudaSetDevice(0));
+    LegionDataset *ds = nullptr;
+    CHECK(legion_dataset_load(&ds, &meta, 1, 1));
+    const int64_t *indptr;
+    const int32_t *indices, *labels;
+    const float *features;
+    CHECK(legion_dataset_arrays(ds, &indptr, &indices, &features, &labels));
+    const int64_t n = meta.node_num, e = meta.edge_num;
+    const int32_t row_bytes = meta.float_feature_len * 4;
+
+    // IPCEnv + Coordinate (storage_management.cu:303-305, ipc_service.cu:60-128)
+    std::vector<Rank> ranks(ngpu);
+    std::vector<int32_t> ntrain(ngpu), nvalid(ngpu), ntest(ngpu);
+    for (int g = 0; g < ngpu; ++g) {
+        ranks[g].dev = g;
+        for (int m = 0; m < 3; ++m) CHECK(legion_dataset_split(ds, m, ngpu, g, nullptr, nullptr, &ranks[g].count[m]));
+        ntrain[g] = ranks[g].count[0];
+        nvalid[g] = ranks[g].count[1] > 0 ? ranks[g].count[1] : 1;
+        ntest[g] = ranks[g].count[2] > 0 ? ranks[g].count[2] : 1;
+    }
+    LegionIpcEnv *env = nullptr;
+    CHECK(legion_ipc_create(&env, ngpu, shm_env));
+    CHECK(legion_ipc_coordinate(env, ntrain.data(), nvalid.data(), ntest.data(), ngpu, meta.raw_batch_size, meta.epoch));
+    int32_t steps[3];
+    CHECK(legion_ipc_steps(env, steps));
+    printf("Train Steps: %d\nValid Steps: %d\nTest Steps: %d\n", steps[0], steps[1], steps[2]);
+    int32_t max_bs = meta.raw_batch_size;
+    for (int g = 0; g < ngpu; ++g)
+        for (int m = 1; m < 3; ++m) {
+            int b = legion_ipc_current_batchsize(env, g, m);
+            if (b > max_bs) max_bs = b;
+        }
+    int64_t cap64 = meta.cache_memory / row_bytes;  // rows per GPU
+    if (cap64 > n) cap64 = n;
+    if (cap64 * ngpu >= n) cap64 = (n + ngpu - 1) / ngpu;
+    const int32_t capacity = (int32_t)cap64;
+    const int max_step = legion_ipc_max_step(env);
+    pthread_barrier_init(&g_barrier, nullptr, ngpu);
+
+    auto worker = [&](int g) {
+        Rank &r = ranks[g];
+        CUCHECK(cudaSetDevice(g));
+        // topology in HBM when it fits next to the cache, else read in place from pinned host memory
+        size_t free_b = 0, total_b = 0;
+        CUCHECK(cudaMemGetInfo(&free_b, &total_b));
+        const size_t topo = 8 * (size_t)(n + 1) + 4 * (size_t)e;
+        const int64_t *ip = indptr;
+        const int32_t *ix = indices;
+        if (topo + (size_t)capacity * row_bytes + ((size_t)8 << 30) < free_b) {
+            CUCHECK(cudaMalloc(&r.d_indptr, 8 * (size_t)(n + 1)));
+            CUCHECK(cudaMalloc(&r.d_indices, 4 * (size_t)(e > 0 ? e : 1)));
+            CUCHECK(cudaMemcpy(r.d_indptr, indptr, 8 * (size_t)(n + 1), cudaMemcpyHostToDevice));
+            CUCHECK(cudaMemcpy(r.d_indices, indices, 4 * (size_t)e, cudaMemcpyHostToDevice));
+            ip = r.d_indptr;
+            ix = r.d_indices;
+        }
+        CHECK(legion_graph_create(&r.graph, g, n, e, ip, ix));
+        CHECK(legion_features_create(&r.feature, g, n, row_bytes, features));
+        for (int m = 0; m < 3; ++m) {
+            if (r.count[m] <= 0) continue;
+            std::vector<int32_t> ids(r.count[m]), lab(r.count[m]);
+            int32_t cnt = 0;
+            CHECK(legion_dataset_split(ds, m, ngpu, g, ids.data(), lab.data(), &cnt));
+            CUCHECK(cudaMalloc(&r.d_ids[m], 4 * (size_t)cnt));
+            CUCHECK(cudaMalloc(&r.d_labels[m], 4 * (size_t)cnt));
+            CUCHECK(cudaMemcpy(r.d_ids[m], ids.data(), 4 * (size_t)cnt, cudaMemcpyHostToDevice));
+            CUCHECK(cudaMemcpy(r.d_labels[m], lab.data(), 4 * (size_t)cnt, cudaMemcpyHostToDevice));
+            CHECK(legion_features_set_split(r.feature, m, r.d_ids[m], r.d_labels[m], cnt));
+        }
+        CHECK(legion_pool_create(&r.pool, g, max_bs, (int32_t)fanout.size(), fanout.data(), row_bytes, LEGION_INTERBATCH_CON));
+        CHECK(legion_pool_set_rng(r.pool, seed + (uint64_t)g, 64));
+
+        // PreSc (engine/server.cu:94-122): rank the nodes, fill the cache
+        int32_t *order = nullptr;
+        CUCHECK(cudaMalloc(&order, 4 * (size_t)n));
+        if (degree_order) {
+            const int64_t *ip_dev = r.d_indptr;
+            int64_t *tmp_ip = nullptr;
+            if (ip_dev == nullptr) {
+                CUCHECK(cudaMalloc(&tmp_ip, 8 * (size_t)(n + 1)));
+                CUCHECK(cudaMemcpy(tmp_ip, indptr, 8 * (size_t)(n + 1), cudaMemcpyHostToDevice));
+                ip_dev = tmp_ip;
+            }
+            CHECK(legion_cache_degree_order(g, ip_dev, n, order, nullptr));
+            if (tmp_ip) cudaFree(tmp_ip);
+        } else {
+            uint32_t *counts = nullptr;
+            CUCHECK(cudaMalloc(&counts, 4 * (size_t)n));
+            CUCHECK(cudaMemset(counts, 0, 4 * (size_t)n));
+            LegionRunner *pre = nullptr;
+            CHECK(legion_runner_create(&pre, g, r.graph, r.feature, nullptr, r.pool, nullptr));
+            CHECK(legion_runner_presample(pre, 0, steps[0], counts));
+            CHECK(legion_runner_destroy(pre));
+            CHECK(legion_cache_hotness_order(g, counts, n, order, nullptr));
+            cudaFree(counts);
+        }
+        if (dyn_flags & 1) {
+            int64_t sets = capacity / 8 > 0 ? capacity / 8 : 1;  // 8 ways, cache/cache.cu:628-629
+            CHECK(legion_cache_create_lru(&r.cache, g, n, row_bytes, sets, 8));
+            CHECK(legion_cache_set_host_table(r.cache, features));
+        } else {
+            int codec = (dyn_flags & 8) ? LEGION_CODEC_INT8 : LEGION_CODEC_RAW;
+            CHECK(legion_cache_create(&r.cache, g, n, row_bytes, ngpu, g, capacity, codec));
+            CHECK(legion_cache_fill_static(r.cache, order, n, features, nullptr));
+        }
+        cudaFree(order);
+        pthread_barrier_wait(&g_barrier);
+        if (!(dyn_flags & 1) && ngpu > 1) {
+            for (int k = 0; k < ngpu; ++k) {
+                if (k == g) continue;
+                CHECK(legion_cache_allow_device(ranks[k].cache, g));
+                void *ptr = nullptr;
+                int64_t bytes = 0;
+                CHECK(legion_cache_partition(ranks[k].cache, &ptr, &bytes));
+                CHECK(legion_cache_set_peer(r.cache, k, ptr));
+            }
+        }
+        CHECK(legion_ipc_publish_pool(env, r.pool, g));
+        CHECK(legion_runner_create(&r.runner, g, r.graph, r.feature, r.cache, r.pool, env));
+        pthread_barrier_wait(&g_barrier);
+        if (g == 0) {
+            printf("System is ready for serving\n");
+            fflush(stdout);
+        }
+        CHECK(legion_runner_serve(r.runner, 0, max_step, timeout_ms));  // GPUServer::Run, engine/server.cu:124-143
+        pthread_barrier_wait(&g_barrier);
+        CHECK(legion_runner_destroy(r.runner));
+        CHECK(legion_cache_destroy(r.cache));
+        CHECK(legion_pool_destroy(r.pool));
+        CHECK(legion_features_destroy(r.feature));
+        CHECK(legion_graph_destroy(r.graph));
+        for (int m = 0; m < 3; ++m) { cudaFree(r.d_ids[m]); cudaFree(r.d_labels[m]); }
+        cudaFree(r.d_indptr);
+        cudaFree(r.d_indices);
+    };
+    std::vector<std::thread> threads;
+    for (int g = 0; g < ngpu; ++g) threads.emplace_back(worker, g);
+    for (auto &t : threads) t.join();
+    CHECK(legion_ipc_destroy(env));
+    CHECK(legion_dataset_destroy(ds));
+    printf("System finalized\n");
+    return 0;
+}

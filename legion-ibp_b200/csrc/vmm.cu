@@ -207,3 +207,20 @@ extern "C" int legion_cache_import_peer(LegionCache *c, int32_t k, int32_t fd, i
     c->part[k] = c->peer_block[k].ptr;
     return LEGION_OK;
 }
+
+// One process, one thread per GPU (the reference's layout, engine/server.cu:127-135): lets device
+// `dev` read this cache's partition in place; the other thread then passes legion_cache_partition's
+// pointer to legion_cache_set_peer.  Ordinary cudaMalloc partitions use legion_enable_peer_access.
+extern "C" int legion_cache_allow_device(LegionCache *c, int32_t dev)
+{
+    LG_ARG(c != nullptr && c->kind == 0 && dev >= 0, "not a static cache");
+    if (c->own_block.ptr == nullptr || dev == c->dev_id) return LEGION_OK;
+    Driver *d = driver();
+    CUmemAccessDesc acc;
+    memset(&acc, 0, sizeof(acc));
+    acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    acc.location.id = dev;
+    acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READ;
+    LG_DRV(d->SetAccess((CUdeviceptr)c->own_block.ptr, (size_t)c->own_block.size, &acc, 1), "cuMemSetAccess");
+    return LEGION_OK;
+}

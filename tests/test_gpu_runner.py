@@ -451,3 +451,62 @@ def test_client_api_consumes_batches(oracle_mod, tmp_path):
             np.testing.assert_array_equal(got["dst%d_%d" % (b, j)], ref["agg_dst"][lo:lo + cnt])
     r.Finalize()
     env.Finalize()
+
+
+def test_sampling_server_binary_end_to_end(oracle_mod, tmp_path):
+    """The server binary as the reference is started (`sampling_server <ngpu> <cache_agg_mode> <dyn_flags>`
+    in a directory holding ./meta_config): it loads Legion-format files, prints the ready line that
+    scripts/wait_file.sh waits for, and serves the whole schedule (train, validation, test batches of all
+    epochs) to a trainer, which here is this process using the client API."""
+    import select
+    import time
+    from test_dataset_cpu import meta_for, write_dataset
+    ref = write_dataset(tmp_path / "ds", n=3000, f=16, seed=5)
+    meta = meta_for(tmp_path / "ds", ref, f=16)
+    meta.raw_batch_size = 24
+    meta.epoch = 2
+    meta.cache_memory = 16 * 4 * 600          # room for 600 rows
+    meta.write(str(tmp_path / "meta_config"))
+    shm = "legion_b200_srv_%d" % os.getpid()
+    env = dict(os.environ, LEGION_SHM_NAME=shm, LEGION_ORDER="degree", LEGION_SEED="7", LEGION_TIMEOUT_MS="120000")
+    binary = os.path.join(ROOT, "legion-ibp_b200", "sampling_server")
+    assert os.path.exists(binary), "build the library first (make -C legion-ibp_b200/csrc)"
+    proc = subprocess.Popen([binary, "1", "0", "0"], cwd=str(tmp_path), env=env, stdout=subprocess.PIPE,
+                            stderr=subprocess.STDOUT)
+    try:
+        seen, deadline = b"", time.time() + 120
+        while b"System is ready for serving" not in seen:
+            assert time.time() < deadline and proc.poll() is None, seen.decode()[-2000:]
+            if select.select([proc.stdout], [], [], 1.0)[0]:
+                seen += os.read(proc.stdout.fileno(), 4096)
+        svc = L.ipc_service(0, shm)
+        train, valid, test = ref["train"], ref["valid"], ref["test"]
+        steps, vbs, tbs = oracle_mod.coordinate([len(train)], [len(valid)], [len(test)], 24)
+        assert svc.get_steps() == list(steps)
+        total = (steps[0] + steps[1]) * 2 + steps[2]
+        lists = {0: (train, 24), 1: (valid, int(vbs[0])), 2: (test, int(tbs[0]))}
+        for b in range(total):
+            v = svc.get_next(timeout_ms=120000)
+            mode, local = oracle_mod.mode_of_batch(b, steps[0], steps[1], steps[2], 2)
+            ids_all, bs = lists[mode]
+            want = oracle_mod.run_batch(ref["indptr"], ref["indices"], ids_all, ref["labels"][ids_all], bs, local, [25, 10], b, 7)
+            got_ids = np.empty(v.n_ids, np.int32)
+            L._check(L.lib().legion_copy(got_ids.ctypes.data_as(L.C.c_void_p), L.C.c_void_p(v.ids), L.C.c_int64(got_ids.nbytes), 2))
+            np.testing.assert_array_equal(got_ids, want["ids"], err_msg="batch %d mode %d" % (b, mode))
+            np.testing.assert_array_equal(np.array(v.node_counter[:]), want["node_counter"])
+            np.testing.assert_array_equal(np.array(v.edge_counter[:]), want["edge_counter"])
+            feat = np.empty((v.n_ids, 16), np.float32)
+            L._check(L.lib().legion_copy(feat.ctypes.data_as(L.C.c_void_p), L.C.c_void_p(v.features), L.C.c_int64(feat.nbytes), 2))
+            np.testing.assert_array_equal(feat, ref["feats"][want["ids"]])
+            lab = np.empty(v.n_labels, np.int32)
+            L._check(L.lib().legion_copy(lab.ctypes.data_as(L.C.c_void_p), L.C.c_void_p(v.labels), L.C.c_int64(lab.nbytes), 2))
+            np.testing.assert_array_equal(lab, want["labels"])
+            svc.synchronize()
+        svc.finalize()
+        out, _ = proc.communicate(timeout=60)
+        assert proc.returncode == 0, (seen + out).decode()[-2000:]
+        assert b"System finalized" in out
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    assert not os.path.exists("/dev/shm/" + shm)
