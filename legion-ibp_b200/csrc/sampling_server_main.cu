@@ -210,6 +210,9 @@ int main(int argc, char **argv)
             fflush(stdout);
         }
         CHECK(legion_runner_serve(r.runner, 0, max_step, timeout_ms));  // GPUServer::Run, engine/server.cu:124-143
+        // GPURunner::Finalize (engine/server.cu:402-407): the trainer must have released every slot
+        // before the buffers go away
+        for (int p = 0; p < LEGION_INTERBATCH_CON; ++p) CHECK(legion_ipc_wait(env, g, p, timeout_ms));
         pthread_barrier_wait(&g_barrier);
         CHECK(legion_runner_destroy(r.runner));
         CHECK(legion_cache_destroy(r.cache));
