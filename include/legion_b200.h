@@ -139,6 +139,15 @@ int legion_cache_hotness_order(int32_t dev_id, const uint32_t *counts_dev, int64
  * (and encodes) this GPU's rows from host_table. */
 int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n_order,
                              const void *host_table, void *stream);
+/* Same for a host table that is NOT laid out in node-id order: row_of_id_dev[id] (device, one int32
+ * per node) is the row of the table that holds node id.  The reference keeps the table in id order
+ * (cpu_float_features[id * F], cache/cache_impl.cuh:283-286); on this platform random zero-copy
+ * reads are limited by address translation of widely scattered host pages (50 GB/s inside 1 GB,
+ * 26 GB/s across 48 GB), so a loader may pack the rows it expects to miss most (seed nodes, then
+ * nodes by falling degree) next to each other.  The lookup table then remembers the row of every
+ * uncached node. */
+int legion_cache_fill_static_rows(LegionCache *c, const int32_t *order_dev, int64_t n_order, const void *host_table,
+                                  const int32_t *row_of_id_dev, void *stream);
 /* Pointer tables of the clique (d_float_feature_cache_ptr_, cache/cache.cu:601-622). */
 int legion_cache_partition(LegionCache *c, void **ptr, int64_t *bytes);
 int legion_cache_set_peer(LegionCache *c, int32_t k, const void *partition_ptr);

@@ -143,10 +143,12 @@ class UnifiedCache:
         _check(lib().legion_cache_hotness_order(C.c_int32(dev_id), _ptr(counts_dev), C.c_int64(_numel(counts_dev)),
                                                 _ptr(order_out), _stream(stream)))
 
-    def fill_static(self, order_dev, host_table, stream=None):
+    def fill_static(self, order_dev, host_table, stream=None, row_of_id=None):
+        """row_of_id (device int32 per node): row of host_table that holds each node, for tables that are
+        not in id order."""
         self._keep += [host_table]
-        _check(lib().legion_cache_fill_static(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()),
-                                              _ptr(host_table), _stream(stream)))
+        _check(lib().legion_cache_fill_static_rows(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()),
+                                                   _ptr(host_table), _ptr(row_of_id), _stream(stream)))
 
     def set_host_table(self, host_table):
         self._keep += [host_table]

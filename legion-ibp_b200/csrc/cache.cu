@@ -35,6 +35,13 @@ __global__ void degree_keys_kernel(const int64_t *__restrict__ indptr, int64_t n
     }
 }
 
+// nodes that are not cached: remember where their row sits in a host table that is not in id order
+__global__ void encode_host_rows_kernel(int32_t *lut, const int32_t *__restrict__ row_of, int64_t n)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        if (lut[i] < 0) lut[i] = -(row_of[i] + 3);
+}
+
 __global__ void iota_kernel(int32_t *id, int64_t n)
 {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
@@ -71,14 +78,16 @@ __device__ __forceinline__ float warp_max(float v)
 template <int CODEC>
 __global__ void __launch_bounds__(256)
 static_fill_kernel(const int32_t *__restrict__ order, int64_t n_order, int32_t capacity, int32_t kg, int32_t ki,
-                   const uint8_t *__restrict__ host, int32_t row_bytes, uint8_t *part, int32_t slot_bytes)
+                   const uint8_t *__restrict__ host, const int32_t *__restrict__ row_of, int32_t row_bytes, uint8_t *part,
+                   int32_t slot_bytes)
 {
     const int lane = threadIdx.x & 31;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t s = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < capacity; s += n_warps) {
         int64_t t = s * kg + ki;
         if (t >= n_order) break;
-        const uint8_t *src = host + (int64_t)order[t] * row_bytes;
+        const int32_t node = order[t];
+        const uint8_t *src = host + (int64_t)(row_of != nullptr ? row_of[node] : node) * row_bytes;
         uint8_t *dst = part + s * (int64_t)slot_bytes;
         if (CODEC == LEGION_CODEC_RAW) {
             if ((row_bytes & 15) == 0) {
@@ -263,8 +272,8 @@ extern "C" int legion_cache_hotness_order(int32_t dev_id, const uint32_t *counts
     return rc;
 }
 
-extern "C" int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n_order,
-                                        const void *host_table, void *stream)
+extern "C" int legion_cache_fill_static_rows(LegionCache *c, const int32_t *order_dev, int64_t n_order,
+                                             const void *host_table, const int32_t *row_of_id_dev, void *stream)
 {
     LG_ARG(c != nullptr && c->kind == 0, "not a static cache");
     LG_ARG(order_dev != nullptr && n_order >= 0 && n_order <= c->n_nodes, "bad order");
@@ -287,17 +296,27 @@ extern "C" int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev
         const uint8_t *host = (const uint8_t *)host_table;
         if (c->codec == LEGION_CODEC_RAW)
             static_fill_kernel<LEGION_CODEC_RAW><<<grid, 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->ki,
-                                                                     host, c->row_bytes, part, c->slot_bytes);
+                                                                     host, row_of_id_dev, c->row_bytes, part, c->slot_bytes);
         else if (c->codec == LEGION_CODEC_INT8)
             static_fill_kernel<LEGION_CODEC_INT8><<<grid, 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->ki,
-                                                                      host, c->row_bytes, part, c->slot_bytes);
+                                                                      host, row_of_id_dev, c->row_bytes, part, c->slot_bytes);
         else
             static_fill_kernel<LEGION_CODEC_E4M3><<<grid, 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->ki,
-                                                                      host, c->row_bytes, part, c->slot_bytes);
+                                                                      host, row_of_id_dev, c->row_bytes, part, c->slot_bytes);
+        LG_LAUNCH_CHECK();
+    }
+    if (row_of_id_dev != nullptr) {
+        encode_host_rows_kernel<<<grid_stride(c->n_nodes, sms), 256, 0, s>>>(c->lut, row_of_id_dev, c->n_nodes);
         LG_LAUNCH_CHECK();
     }
     LG_CUDA(cudaStreamSynchronize(s));
     return LEGION_OK;
+}
+
+extern "C" int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n_order,
+                                        const void *host_table, void *stream)
+{
+    return legion_cache_fill_static_rows(c, order_dev, n_order, host_table, nullptr, stream);
 }
 
 extern "C" int legion_cache_set_host_table(LegionCache *c, const void *host_table)

@@ -35,7 +35,7 @@ struct GatherParams {
     int32_t row_bytes;   // bytes of one output row
     int32_t slot_bytes;  // bytes of one cached row
     int32_t feature_len; // elements per row (quantised codecs)
-    int2 *miss_rows;     // (position in ids, node id) of rows whose source is the host table
+    int2 *miss_rows;     // (position in ids, host table row) of rows whose source is the host table
     int32_t *miss_count; // [0] number of entries
 };
 
@@ -76,10 +76,16 @@ __device__ __forceinline__ void segment_of(int32_t *nc, int op_id, int &off, int
 }
 
 // Looks one id up and resolves it to a source row.  `where`: 0 local, 1 peer, 2 host, 3 none.
-__device__ __forceinline__ const uint8_t *resolve(const GatherParams &p, int32_t id, int32_t &gidx, int &where)
+// A table entry >= 0 is the global cache index; LEGION_CACHEMISS_FLAG (-2) means "row `id` of the
+// host table"; an entry <= -3 means "row -(entry + 3) of the host table", for host tables that are
+// not laid out in id order (legion_cache_fill_static_rows).  `host_row` is the row to fetch on a miss;
+// gidx leaves as the reference's FindFeat would write it.
+__device__ __forceinline__ const uint8_t *resolve(const GatherParams &p, int32_t id, int32_t &gidx, int &where,
+                                                  int32_t &host_row)
 {
     gidx = LEGION_CACHEMISS_FLAG;
     where = 3;
+    host_row = id;
     if (id < 0) return nullptr;
     if (p.lut != nullptr) gidx = __ldg(&p.lut[id]);
     if (gidx >= 0) {
@@ -88,16 +94,18 @@ __device__ __forceinline__ const uint8_t *resolve(const GatherParams &p, int32_t
         where = (d == p.ki) ? 0 : 1;
         return p.part[d] + (int64_t)row * p.slot_bytes;
     }
+    if (gidx <= -3) host_row = -(gidx + 3);
+    gidx = LEGION_CACHEMISS_FLAG;
     if (p.host != nullptr) {
         where = 2;
-        return p.host + ((int64_t)id % p.n_nodes) * (int64_t)p.row_bytes;
+        return p.host + ((int64_t)host_row % p.n_nodes) * (int64_t)p.row_bytes;
     }
     return nullptr;
 }
 
 // Rows served by the host table are not copied by the hit kernels: the warp appends them to the
 // batch's miss list (one atomicAdd per warp, ranks by ballot) and clears their source pointer.
-// The list holds (position in `ids`, node id), so the miss kernel needs nothing else of the batch
+// The list holds (position in `ids`, row of the host table), so the miss kernel needs nothing else of the batch
 // and may still run while the next batch on the same pipe is being sampled; it empties the list.
 __device__ __forceinline__ void defer_misses(int2 *miss_rows, int32_t *miss_count, int row, int32_t id, int where,
                                              const uint8_t *&src, int lane)
@@ -138,12 +146,12 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
     for (int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; c * 32 < n; c += n_warps) {
         const int r = c * 32 + lane;
         int32_t id = (r < n) ? __ldg(&p.ids[off + r]) : -1;
-        int32_t gidx;
+        int32_t gidx, host_row;
         int where;
-        const uint8_t *src = resolve(p, id, gidx, where);
+        const uint8_t *src = resolve(p, id, gidx, where, host_row);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
-        defer_misses(p.miss_rows, p.miss_count, off + r, id, where, src, lane);
+        defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         uint8_t *dst_base = p.dst + (int64_t)(off + c * 32) * p.row_bytes;
         for (int j0 = 0; j0 < rows_here; j0 += R) {
@@ -188,12 +196,12 @@ __global__ void __launch_bounds__(256) gather_word_kernel(GatherParams p)
     for (int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; c * 32 < n; c += n_warps) {
         const int r = c * 32 + lane;
         int32_t id = (r < n) ? __ldg(&p.ids[off + r]) : -1;
-        int32_t gidx;
+        int32_t gidx, host_row;
         int where;
-        const uint8_t *src = resolve(p, id, gidx, where);
+        const uint8_t *src = resolve(p, id, gidx, where, host_row);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
-        defer_misses(p.miss_rows, p.miss_count, off + r, id, where, src, lane);
+        defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         uint32_t *dst_base = reinterpret_cast<uint32_t *>(p.dst + (int64_t)(off + c * 32) * p.row_bytes);
         for (int j = 0; j < rows_here; ++j) {
@@ -226,12 +234,12 @@ __global__ void __launch_bounds__(256) gather_quant_kernel(GatherParams p)
     for (int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; c * 32 < n; c += n_warps) {
         const int r = c * 32 + lane;
         int32_t id = (r < n) ? __ldg(&p.ids[off + r]) : -1;
-        int32_t gidx;
+        int32_t gidx, host_row;
         int where;
-        const uint8_t *src = resolve(p, id, gidx, where);
+        const uint8_t *src = resolve(p, id, gidx, where, host_row);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
-        defer_misses(p.miss_rows, p.miss_count, off + r, id, where, src, lane);
+        defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         float *dst_base = reinterpret_cast<float *>(p.dst + (int64_t)(off + c * 32) * p.row_bytes);
         for (int j = 0; j < rows_here; ++j) {

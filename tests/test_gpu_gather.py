@@ -22,7 +22,7 @@ class Rig:
     """One GPU's storage objects around a host table, with the id list as the seed list (0 hops)."""
 
     def __init__(self, table, ids_list, batch, lru=None, capacity=0, kg=1, ki=0, codec=L.CODEC_RAW, order=None,
-                 out_row_bytes=None):
+                 out_row_bytes=None, row_of=None):
         import torch
         self.table = table
         self.n = table.shape[0]
@@ -40,7 +40,8 @@ class Rig:
             self.cache = L.UnifiedCache(0, self.n, self.row_bytes, capacity, kg, ki, codec)
             if order is not None:
                 self.order = torch.from_numpy(order.astype(np.int32)).cuda()
-                self.cache.fill_static(self.order, self.h_table)
+                self.row_of = torch.from_numpy(row_of.astype(np.int32)).cuda() if row_of is not None else None
+                self.cache.fill_static(self.order, self.h_table, row_of_id=self.row_of)
         self.batch = batch
 
     def gather(self, it, pipe=0):
@@ -93,6 +94,47 @@ def test_static_cache_gather(oracle_mod, feat_len, dtype, cached_frac):
         assert nc[2] == 0 and nc[3] == cnt
     st = rig.cache.stats()
     assert st["local_hits"] + st["misses"] == 5000 and st["peer_hits"] == 0
+    rig.close()
+
+
+@pytest.mark.parametrize("feat_len,codec", [(128, L.CODEC_RAW), (100, L.CODEC_RAW), (128, L.CODEC_INT8)])
+def test_host_table_in_another_row_order(oracle_mod, feat_len, codec):
+    """A host table whose rows are permuted (row_of[id] = row holding node id): cache fill, hit / miss
+    index and gathered rows are those of the id-ordered table."""
+    rng = np.random.default_rng(feat_len)
+    indptr, _ = small_graph(5000, 60000, 4)
+    n = len(indptr) - 1
+    table = rng.standard_normal((n, feat_len)).astype(np.float32)
+    perm = rng.permutation(n)                    # row r of the stored table holds node perm[r]
+    stored = np.ascontiguousarray(table[perm])
+    row_of = np.empty(n, np.int64)
+    row_of[perm] = np.arange(n)
+    ids_list = rng.integers(0, n, 7000).astype(np.int32)
+    ids_list[11] = -1
+    cap = n // 5
+    order = oracle_mod.degree_order(indptr)
+    rig = Rig(stored, ids_list, 7000, capacity=cap, order=order, codec=codec, row_of=row_of)
+    lut = oracle_mod.static_cache_lut(order, cap, 1)
+    ci = oracle_mod.find_feat(ids_list, lut)
+    cnt, feat, _ = rig.gather(0)
+    got = feat.view(np.float32).reshape(cnt, feat_len)
+    np.testing.assert_array_equal(rig.pool.read(L.BUF_CACHE_INDEX, 0, cnt, np.int32), ci)   # misses still read -2
+    if codec == L.CODEC_RAW:
+        part = oracle_mod.static_cache_fill(order, cap, 1, 0, table)
+        ref = oracle_mod.gather(ids_list, ci, cap, [part], table)
+    else:
+        part = oracle_mod.quant_rows(table[order[:cap]], codec)
+        ref = oracle_mod.gather_quant(ids_list, ci, cap, [part], table, codec)
+    valid = ids_list >= 0
+    np.testing.assert_array_equal(got[valid].view(np.uint32), ref[valid].view(np.uint32))
+    # the allocation-free entry point reads the same table
+    import torch
+    if codec == L.CODEC_RAW:
+        out = torch.zeros((cnt, feat_len), dtype=torch.float32, device="cuda")
+        L.gather_rows_noalloc(None, 0, rig.ids, rig.cache.lut_ptr(), cap, 1, 0, [rig.cache.partition()[0]], rig.h_table, n,
+                              feat_len * 4, out)
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(out.cpu().numpy()[valid], table[ids_list[valid]])
     rig.close()
 
 
