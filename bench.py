@@ -142,6 +142,24 @@ def host_link_peak(table):
     return 3 * n * 4 / (a.elapsed_time(b) * 1e-3) / 1e9
 
 
+def host_rows_seeds_first(order, seeds, n_cached):
+    """row_of[id] for a host table that holds, in this order: the uncached seed nodes, the other
+    uncached nodes by falling degree, and last the nodes whose rows live in the GPU caches (read once,
+    at fill time).  The synthetic table is random, so it can be taken to be in this order already."""
+    import torch
+    n = order.numel()
+    rank_of = torch.empty(n, dtype=torch.int64, device=order.device)
+    rank_of[order.long()] = torch.arange(n, dtype=torch.int64, device=order.device)
+    cls = torch.ones(n, dtype=torch.int64, device=order.device)
+    cls[seeds.long()] = 0
+    cls[order[:min(n, n_cached)].long()] = 2
+    perm = torch.argsort(cls * n + rank_of)
+    del cls, rank_of
+    row_of = torch.empty(n, dtype=torch.int32, device=order.device)
+    row_of[perm] = torch.arange(n, dtype=torch.int32, device=order.device)
+    return row_of
+
+
 def bounds(batch, fanout):
     nodes, edges = batch, 0
     for k in fanout:
@@ -208,6 +226,7 @@ def workload_config(cfg, n_gpus):
             "l2": "inputs larger than L2 (topology, cache partition and host table are each GBs)"}
 
 
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -219,6 +238,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cache-frac", type=float, default=None, help="override the cached fraction of the table")
     ap.add_argument("--pipes", type=int, default=2, help="batches in flight (the hand-off protocol uses 2)")
+    ap.add_argument("--host-layout", default="seeds_first", choices=["id", "seeds_first"],
+                    help="row order of the pinned host table: node-id order, or uncached seed nodes first and the "
+                         "other uncached nodes by falling degree (shorter spans for the zero-copy misses)")
     ap.add_argument("--profile-only", action="store_true",
                     help="set-up, warm-up and the timed steps only (for runs under a profiler); prints no bench line")
     args = ap.parse_args()
@@ -270,7 +292,10 @@ def main():
     if cap * world >= n:
         cap = (n + world - 1) // world
     cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank)
-    cache.fill_static(order, table)
+    row_of = None
+    if args.host_layout == "seeds_first":
+        row_of = host_rows_seeds_first(order, train, cap * world)
+    cache.fill_static(order, table, row_of_id=row_of)
     del order
     share = None
     if world > 1:
@@ -301,6 +326,20 @@ def main():
         runner.enqueue(step, L.TRAINMODE, step % n_iters)
         step += 1
     runner.sync()
+    # full-size spot check: gathered rows of the last warm-up batch are bit copies of their host rows
+    last_pipe = (step - 1) % args.pipes
+    nc_chk = pool.read(L.BUF_NODE_COUNTER, last_pipe, 16, np.int32)
+    n_chk = int(nc_chk[9 + int(nc_chk[8])])
+    ids_chk = torch.from_numpy(pool.read(L.BUF_IDS, last_pipe, n_chk, np.int32))
+    pick = torch.randint(0, n_chk, (min(2000, n_chk),))
+    fptr, _ = pool.buffer(L.BUF_FEATURES, last_pipe)
+    rows_chk = np.empty((n_chk, f), np.float32)
+    import ctypes
+    L._check(L.lib().legion_copy(ctypes.c_void_p(rows_chk.ctypes.data), ctypes.c_void_p(fptr), ctypes.c_int64(rows_chk.nbytes),
+                                 ctypes.c_int32(2)))
+    src_rows = ids_chk[pick].long() if row_of is None else row_of.cpu()[ids_chk[pick].long()].long()
+    assert np.array_equal(rows_chk[pick.numpy()], table[src_rows].numpy()), "gathered rows differ from the host table"
+    del rows_chk
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -457,7 +496,8 @@ def main():
         line = {"metric": "sampled+gathered mini-batches/sec", "value": value, "unit": "batches/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, world),
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": dict(workload_config(cfg, world), host_table_layout=args.host_layout),
                 "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + 1 + 1),
                 "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
                 "pipeline": pipeline,
