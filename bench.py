@@ -33,6 +33,18 @@ CONFIGS = {
     # c2 scaled down to a few GB (inputs still larger than L2) for profiler captures
     "mid": dict(name="mid RMAT (profiler capture)", n_nodes=8000000, n_pairs=64000000, feat_len=128, classes=172,
                 train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2),
+    # compressed-cache variant of c2 (configs[3]): the same byte budget holds int8 rows + fp32 scale
+    "c4": dict(name="paper100M-shaped RMAT, int8 cache", n_nodes=111059956, n_pairs=900000000, feat_len=128,
+               classes=172, train_frac=0.011, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="int8"),
+    "mid-int8": dict(name="mid RMAT, int8 cache", n_nodes=8000000, n_pairs=64000000, feat_len=128, classes=172,
+                     train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="int8"),
+    "mid-e4m3": dict(name="mid RMAT, fp8 e4m3 cache", n_nodes=8000000, n_pairs=64000000, feat_len=128, classes=172,
+                     train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="e4m3"),
+    # dynamic-LRU stress (configs[4]) scaled 1:25 so that the host table (10 GB) fits any box: Zipf(1.1)
+    # seeds, three hops, set-associative LRU cache of 10% of the table
+    "c5s": dict(name="LRU stress RMAT (configs[4] scaled 1:25)", n_nodes=20000000, n_pairs=80000000, feat_len=128,
+                classes=172, train_frac=0.0, batch=4096, fanout=[15, 10, 5], cache_frac=0.1, lru_ways=8,
+                zipf=1.1, zipf_batches=160),
     # reduced copy of c2 for checking the harness itself on small machines (never the default)
     "tiny": dict(name="tiny RMAT (harness check)", n_nodes=200000, n_pairs=2000000, feat_len=128, classes=172,
                  train_frac=0.2, batch=2000, fanout=[25, 10], cache_frac=0.2),
@@ -160,6 +172,27 @@ def host_rows_seeds_first(order, seeds, n_cached):
     return row_of
 
 
+def zipf_batches(n_nodes, batch, n_batches, s, world=1, rank=0):
+    """Seed sequence of one rank for the LRU stress workload: Zipf(s) draws over node id, those with
+    id % world == rank, made distinct inside every window of `batch` seeds (a mini-batch holds a node once)."""
+    import torch
+    from legion_ibp_b200 import synth
+    draws = synth.zipf_seeds(n_nodes, 4 * batch * n_batches * world, s=s, seed=0, device="cuda")
+    draws = draws[(draws % world) == rank]
+    assert draws.numel() >= 3 * batch * n_batches
+    draws = draws[:3 * batch * n_batches].view(n_batches, 3 * batch)
+    out = []
+    for i in range(n_batches):
+        row = draws[i].long()
+        first = torch.full((n_nodes,), 1 << 40, dtype=torch.int64, device=row.device)
+        first.scatter_reduce_(0, row, torch.arange(row.numel(), device=row.device), reduce="amin")
+        keep = first[row] == torch.arange(row.numel(), device=row.device)
+        uniq = row[keep][:batch]
+        assert uniq.numel() == batch, "not enough distinct Zipf draws for a batch"
+        out.append(uniq.to(torch.int32))
+    return torch.cat(out)
+
+
 def bounds(batch, fanout):
     nodes, edges = batch, 0
     for k in fanout:
@@ -217,10 +250,16 @@ def run_reference(args, cfg):
 
 
 def workload_config(cfg, n_gpus):
-    return {"workload": "%s: %d nodes, fp32 dim %d, batch %d, fanout %s, static degree-ordered cache %d%% of the "
-                        "table per GPU, misses by zero-copy from pinned host memory" %
-                        (cfg["name"], cfg["n_nodes"], cfg["feat_len"], cfg["batch"], cfg["fanout"],
-                         int(cfg["cache_frac"] * 100)),
+    if cfg.get("lru_ways"):
+        kind = "%d-way set-associative LRU cache of %d%% of the table per GPU, Zipf(%.1f) seeds" % (
+            cfg["lru_ways"], int(cfg["cache_frac"] * 100), cfg.get("zipf", 0.0))
+    elif cfg.get("codec", "raw") != "raw":
+        kind = "static degree-ordered %s cache (codes + fp32 row scale) in %d%% of the table's bytes per GPU" % (
+            cfg["codec"], int(cfg["cache_frac"] * 100))
+    else:
+        kind = "static degree-ordered cache %d%% of the table per GPU" % int(cfg["cache_frac"] * 100)
+    return {"workload": "%s: %d nodes, fp32 dim %d, batch %d, fanout %s, %s, misses by zero-copy from pinned host "
+                        "memory" % (cfg["name"], cfg["n_nodes"], cfg["feat_len"], cfg["batch"], cfg["fanout"], kind),
             "batch_per_gpu": cfg["batch"], "fanout": cfg["fanout"], "feat_len": cfg["feat_len"],
             "parallelism": "dp%d, cache striped over %d GPU(s)" % (n_gpus, n_gpus),
             "l2": "inputs larger than L2 (topology, cache partition and host table are each GBs)"}
@@ -241,6 +280,8 @@ def main():
     ap.add_argument("--host-layout", default="seeds_first", choices=["id", "seeds_first"],
                     help="row order of the pinned host table: node-id order, or uncached seed nodes first and the "
                          "other uncached nodes by falling degree (shorter spans for the zero-copy misses)")
+    ap.add_argument("--tunable", action="append", default=[], metavar="NAME=VALUE",
+                    help="launch-shape knob passed to legion_set_tunable (measurement sweeps)")
     ap.add_argument("--profile-only", action="store_true",
                     help="set-up, warm-up and the timed steps only (for runs under a profiler); prints no bench line")
     args = ap.parse_args()
@@ -257,6 +298,9 @@ def main():
     import torch
     L = load_pkg()
     L.lib()  # fails loudly when the CUDA library is missing
+    for kv in args.tunable:
+        name, _, val = kv.partition("=")
+        L._check(L.lib().legion_set_tunable(name.encode(), int(val)))
     from legion_ibp_b200 import synth
     assert torch.cuda.is_available(), "bench.py needs a GPU (use --impl reference for the CPU arm)"
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -277,7 +321,9 @@ def main():
     n, f = cfg["n_nodes"], cfg["feat_len"]
     row_bytes = f * 4
     n_edges = int(indices.numel())
-    labels, train, _, _ = synth.labels_and_split(n, cfg["classes"], cfg["train_frac"], device="cuda")
+    labels, train, _, _ = synth.labels_and_split(n, cfg["classes"], max(cfg["train_frac"], 1e-6), device="cuda")
+    if cfg.get("zipf"):
+        train = zipf_batches(n, cfg["batch"], cfg["zipf_batches"], cfg["zipf"], world, rank)
     mine = train[(train % world) == rank].contiguous()  # id % ngpu split, storage_management.cu:214-250
     mine_labels = labels[mine.long()].contiguous()
     table = host_table(cfg, "legion_b200_bench_features", rank, world)
@@ -288,17 +334,28 @@ def main():
     fs.set_split(L.TRAINMODE, mine, mine_labels)
     order = torch.empty(n, dtype=torch.int32, device="cuda")
     L.UnifiedCache.degree_order(dev, indptr, order)
-    cap = min(n, int(n * cfg["cache_frac"]))
+    codec_name = cfg.get("codec", "raw")
+    codec = {"raw": L.CODEC_RAW, "int8": L.CODEC_INT8, "e4m3": L.CODEC_E4M3}[codec_name]
+    slot_bytes = row_bytes if codec == L.CODEC_RAW else (f + 4 + 15) // 16 * 16
+    cap = min(n, int(n * cfg["cache_frac"] * row_bytes / slot_bytes))
     if cap * world >= n:
         cap = (n + world - 1) // world
-    cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank)
     row_of = None
-    if args.host_layout == "seeds_first":
-        row_of = host_rows_seeds_first(order, train, cap * world)
-    cache.fill_static(order, table, row_of_id=row_of)
+    lru_ways = cfg.get("lru_ways", 0)
+    if lru_ways:
+        # every GPU keeps its own LRU cache (no clique: the contents change every batch)
+        cap = cap // lru_ways * lru_ways
+        cache = L.UnifiedCache(dev, n, row_bytes, 0, lru=(cap // lru_ways, lru_ways))
+        cache.set_host_table(table)
+        args.host_layout = "id"
+    else:
+        cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank, codec=codec)
+        if args.host_layout == "seeds_first":
+            row_of = host_rows_seeds_first(order, train, cap * world)
+        cache.fill_static(order, table, row_of_id=row_of)
     del order
     share = None
-    if world > 1:
+    if world > 1 and not lru_ways:
         from legion_ibp_b200 import server
         share = server.exchange_partitions(cache, rank, world, dist)
     pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, args.pipes)
@@ -338,7 +395,15 @@ def main():
     L._check(L.lib().legion_copy(ctypes.c_void_p(rows_chk.ctypes.data), ctypes.c_void_p(fptr), ctypes.c_int64(rows_chk.nbytes),
                                  ctypes.c_int32(2)))
     src_rows = ids_chk[pick].long() if row_of is None else row_of.cpu()[ids_chk[pick].long()].long()
-    assert np.array_equal(rows_chk[pick.numpy()], table[src_rows].numpy()), "gathered rows differ from the host table"
+    want_rows = table[src_rows].numpy()
+    if codec == L.CODEC_RAW:
+        assert np.array_equal(rows_chk[pick.numpy()], want_rows), "gathered rows differ from the host table"
+    else:
+        # rows served by the compressed cache: |x - x^| <= absmax / 254 for int8 (half a code step);
+        # half an e4m3 step (2^-4 relative) of the scaled value for fp8
+        amax = np.abs(want_rows).max(axis=1, keepdims=True)
+        tol = amax / 254.0 * 1.001 if codec == L.CODEC_INT8 else np.maximum(np.abs(want_rows) / 16.0, amax / 448.0 / 1024.0) * 1.001
+        assert np.all(np.abs(rows_chk[pick.numpy()] - want_rows) <= tol), "dequantised rows out of tolerance"
     del rows_chk
     barrier()
     sampler = ClockSampler(local_rank)
@@ -396,7 +461,10 @@ def main():
     rows = hits + d["misses"]
     gather_launches = tm["timed"]  # one lookup + gather launch per batch
     timed_frac = tm["timed"] / float(args.steps)
-    hit_bytes = hits * (2 * row_bytes + 8) + d["misses"] * 16
+    # a hit reads its cache slot (the raw row; codes + scale; for the LRU cache also the keys of its set
+    # and one stamp) and writes the fp32 row
+    hit_read = slot_bytes + (4 * lru_ways + 4 if lru_ways else 0)
+    hit_bytes = hits * (hit_read + row_bytes + 8) + d["misses"] * 16
     miss_bytes = d["misses"] * (2 * row_bytes + 8)
     gather_s = tm["gather_ms"] * 1e-3
     miss_s = tm["miss_ms"] * 1e-3
@@ -407,7 +475,10 @@ def main():
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = hit_bytes / gather_s / 1e9 if gather_s > 0 else 0.0
-    roofline = {"bound": "hbm", "kernel": "gather_vec_kernel (cache lookup + gather of rows held in GPU memory)",
+    kname = ("gather_lru_kernel (set probe + gather of rows held in the LRU cache)" if lru_ways else
+             "gather_quant_kernel<%s> (cache lookup + gather with in-kernel dequantisation)" % codec_name
+             if codec != L.CODEC_RAW else "gather_vec_kernel (cache lookup + gather of rows held in GPU memory)")
+    roofline = {"bound": "hbm", "kernel": kname,
                 "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "peak_source": "of measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "of fallback 6650 GB/s",
                 "traffic": None, "launches": gather_launches,
@@ -498,12 +569,12 @@ def main():
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": dict(workload_config(cfg, world), host_table_layout=args.host_layout),
-                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + 1 + 1),
+                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + 1 + 1 + (3 if lru_ways else 0)),
                 "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
                 "pipeline": pipeline,
                 "cpu_baseline": cpu, "clocks": clocks,
                 "graph": {"nodes": n, "directed_edges": n_edges, "train_seeds_this_rank": int(mine.numel()),
-                          "cache_rows_per_gpu": cap, "peer_mapping": share}, "setup_s": setup_s}
+                          "cache_rows_per_gpu": cap, "peer_mapping": share}, "setup_s": setup_s, "tunables": args.tunable or None}
         print(json.dumps(line), flush=True)
     runner.Finalize()
     if dist is not None:

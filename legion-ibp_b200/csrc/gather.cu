@@ -133,8 +133,38 @@ __device__ __forceinline__ void add_stats(unsigned long long *stats, int where, 
     }
 }
 
+// The two halves of resolve(), for callers that fetch the table entry of the next chunk early.
+__device__ __forceinline__ int32_t lookup_raw(const GatherParams &p, int32_t id)
+{
+    return (id >= 0 && p.lut != nullptr) ? __ldg(&p.lut[id]) : LEGION_CACHEMISS_FLAG;
+}
+__device__ __forceinline__ const uint8_t *decode_raw(const GatherParams &p, int32_t id, int32_t raw, int32_t &gidx,
+                                                     int &where, int32_t &host_row)
+{
+    gidx = LEGION_CACHEMISS_FLAG;
+    where = 3;
+    host_row = id;
+    if (id < 0) return nullptr;
+    if (raw >= 0) {
+        gidx = raw;
+        int d = raw / p.capacity;
+        int row = raw - d * p.capacity;
+        where = (d == p.ki) ? 0 : 1;
+        return p.part[d] + (int64_t)row * p.slot_bytes;
+    }
+    if (raw <= -3) host_row = -(raw + 3);
+    if (p.host != nullptr) {
+        where = 2;
+        return p.host + ((int64_t)host_row % p.n_nodes) * (int64_t)p.row_bytes;
+    }
+    return nullptr;
+}
+
 // Rows whose size is a multiple of 16 bytes.  VPL = 16-byte vectors per lane per row,
-// R = rows copied together.
+// R = rows copied together (R * VPL * 512 bytes in flight per warp).  A warp looks 32 ids up, one per
+// lane, then copies their rows R at a time; while the first rows of a chunk are in flight it already
+// fetches the id and the table entry of its next chunk, so that only the first lookup of a warp is
+// exposed.
 template <int VPL, int R>
 __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
 {
@@ -143,17 +173,22 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
     const int lane = threadIdx.x & 31;
     const int n_warps = (gridDim.x * blockDim.x) >> 5;
     const int row_vec = p.row_bytes >> 4;
-    for (int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; c * 32 < n; c += n_warps) {
+    int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (c * 32 >= n) return;
+    int32_t id = (c * 32 + lane < n) ? __ldg(&p.ids[off + c * 32 + lane]) : -1;
+    int32_t raw = lookup_raw(p, id);
+    for (; c * 32 < n; c += n_warps) {
         const int r = c * 32 + lane;
-        int32_t id = (r < n) ? __ldg(&p.ids[off + r]) : -1;
         int32_t gidx, host_row;
         int where;
-        const uint8_t *src = resolve(p, id, gidx, where, host_row);
+        const uint8_t *src = decode_raw(p, id, raw, gidx, where, host_row);
         if (r < n) p.cache_index[off + r] = gidx;
         add_stats(p.stats, where, lane);
         defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         uint8_t *dst_base = p.dst + (int64_t)(off + c * 32) * p.row_bytes;
+        const int rn = (c + n_warps) * 32 + lane;
+        id = (rn < n) ? __ldg(&p.ids[off + rn]) : -1;
         for (int j0 = 0; j0 < rows_here; j0 += R) {
             uint4 v[R][VPL];
             const uint8_t *sp[R];
@@ -171,6 +206,7 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
                         v[jj][q] = *reinterpret_cast<const uint4 *>(sp[jj] + idx * 16);
                 }
             }
+            if (j0 == 0) raw = lookup_raw(p, id);
 #pragma unroll
             for (int jj = 0; jj < R; ++jj) {
 #pragma unroll
@@ -517,6 +553,9 @@ static void launch_lru(int grid, cudaStream_t s, const LruParams &lp)
     gather_lru_kernel<VPL, R><<<grid, 256, 0, s>>>(lp);
 }
 
+int g_gather_cps = 0;  // CTAs per SM of the hit gathers (0 = default); see legion_set_tunable
+int g_gather_rows = 0; // rows in flight per warp for 512-byte-class rows (0 = default)
+
 static int segment_grid(const LegionPool *p, int32_t op_id, int64_t *rows_out)
 {
     // worst-case rows of this segment: the seeds, or the new nodes of hop (op_id / 3), or all nodes
@@ -528,7 +567,7 @@ static int segment_grid(const LegionPool *p, int32_t op_id, int64_t *rows_out)
     if (rows_out) *rows_out = rows;
     int64_t chunks = (rows + 31) / 32;
     int64_t g64 = (chunks + 7) / 8;
-    int cap = p->sm_count * 8;
+    int cap = p->sm_count * (g_gather_cps > 0 ? g_gather_cps : 8);
     return (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
 }
 
@@ -602,7 +641,12 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
     if (row_bytes % 16 == 0 && row_bytes <= 2048) {
         int vpl = (row_bytes / 16 + 31) / 32;
         switch (vpl) {
-        case 1: launch_vec<1, 4>(grid, s, gp); break;
+        case 1:
+            if (g_gather_rows == 8) launch_vec<1, 8>(grid, s, gp);
+            else if (g_gather_rows == 16) launch_vec<1, 16>(grid, s, gp);
+            else if (g_gather_rows == 2) launch_vec<1, 2>(grid, s, gp);
+            else launch_vec<1, 4>(grid, s, gp);
+            break;
         case 2: launch_vec<2, 2>(grid, s, gp); break;
         case 3: launch_vec<3, 2>(grid, s, gp); break;
         default: launch_vec<4, 2>(grid, s, gp); break;
@@ -821,6 +865,16 @@ extern "C" int legion_set_tunable(const char *name, int32_t value)
     if (strcmp(name, "miss_threads") == 0) {
         LG_ARG(value == 0 || (value >= 32 && value <= 1024 && value % 32 == 0), "miss_threads must be a multiple of 32 up to 1024");
         g_miss_threads = value;
+        return LEGION_OK;
+    }
+    if (strcmp(name, "gather_ctas_per_sm") == 0) {
+        LG_ARG(value >= 0 && value <= 16, "gather_ctas_per_sm out of range");
+        g_gather_cps = value;
+        return LEGION_OK;
+    }
+    if (strcmp(name, "gather_rows_in_flight") == 0) {
+        LG_ARG(value == 0 || value == 2 || value == 4 || value == 8 || value == 16, "gather_rows_in_flight must be 0, 2, 4, 8 or 16");
+        g_gather_rows = value;
         return LEGION_OK;
     }
     set_error("legion_set_tunable: unknown name %s", name);

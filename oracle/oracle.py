@@ -259,7 +259,13 @@ def mode_of_batch(global_batch, train_step, valid_step, test_step, epochs):
 
 
 def num_threads():
-    return int(lib().orc_num_threads())
+    """Host cores this process may use.  Launchers such as torchrun export OMP_NUM_THREADS=1 to their
+    workers, so the OpenMP default is not the answer; cpu_pipeline sets the count it is given."""
+    import os
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or int(lib().orc_num_threads()))
 
 
 def cpu_pipeline(indptr, indices, all_ids, all_labels, batch_size, first_iter, n_batches, fanout, seed,
