@@ -280,6 +280,9 @@ def main():
     ap.add_argument("--host-layout", default="seeds_first", choices=["id", "seeds_first"],
                     help="row order of the pinned host table: node-id order, or uncached seed nodes first and the "
                          "other uncached nodes by falling degree (shorter spans for the zero-copy misses)")
+    ap.add_argument("--no-replicas", action="store_true",
+                    help="N > 1: stripe the whole per-GPU budget over the clique (the reference's placement) instead "
+                         "of planning private copies of the hottest peer rows")
     ap.add_argument("--tunable", action="append", default=[], metavar="NAME=VALUE",
                     help="launch-shape knob passed to legion_set_tunable (measurement sweeps)")
     ap.add_argument("--profile-only", action="store_true",
@@ -337,7 +340,8 @@ def main():
     codec_name = cfg.get("codec", "raw")
     codec = {"raw": L.CODEC_RAW, "int8": L.CODEC_INT8, "e4m3": L.CODEC_E4M3}[codec_name]
     slot_bytes = row_bytes if codec == L.CODEC_RAW else (f + 4 + 15) // 16 * 16
-    cap = min(n, int(n * cfg["cache_frac"] * row_bytes / slot_bytes))
+    budget = cap = min(n, int(n * cfg["cache_frac"] * row_bytes / slot_bytes))
+    replica_rows = 0
     if cap * world >= n:
         cap = (n + world - 1) // world
     row_of = None
@@ -349,10 +353,15 @@ def main():
         cache.set_host_table(table)
         args.host_layout = "id"
     else:
+        if world > 1 and not args.no_replicas:
+            from legion_ibp_b200 import server
+            cap, replica_rows = server.plan_clique_cache(server.degree_mass(indptr, order), n, budget, world)
         cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank, codec=codec)
         if args.host_layout == "seeds_first":
             row_of = host_rows_seeds_first(order, train, cap * world)
         cache.fill_static(order, table, row_of_id=row_of)
+        if replica_rows > 0:
+            cache.add_replicas(order, replica_rows, row_of_id=row_of)
     del order
     share = None
     if world > 1 and not lru_ways:
@@ -574,7 +583,8 @@ def main():
                 "pipeline": pipeline,
                 "cpu_baseline": cpu, "clocks": clocks,
                 "graph": {"nodes": n, "directed_edges": n_edges, "train_seeds_this_rank": int(mine.numel()),
-                          "cache_rows_per_gpu": cap, "peer_mapping": share}, "setup_s": setup_s, "tunables": args.tunable or None}
+                          "cache_rows_per_gpu": cap, "replica_rows_per_gpu": replica_rows,
+                          "peer_mapping": share}, "setup_s": setup_s, "tunables": args.tunable or None}
         print(json.dumps(line), flush=True)
     runner.Finalize()
     if dist is not None:

@@ -148,6 +148,16 @@ int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n
  * uncached node. */
 int legion_cache_fill_static_rows(LegionCache *c, const int32_t *order_dev, int64_t n_order, const void *host_table,
                                   const int32_t *row_of_id_dev, void *stream);
+/* Private copies of the hottest rows that the striping gave to OTHER clique members, so that this
+ * GPU serves them from its own memory instead of over NVLink.  The reference stripes only
+ * (cache/cache_impl.cuh:104-109): when the clique's budget exceeds the table (8 GPUs x 20%), its
+ * spare memory stays empty and 7 of 8 hits cross NVLink.  Call after legion_cache_fill_static[_rows]
+ * with the same order (and row_of_id_dev, or NULL): replica row s holds the s-th rank t with
+ * t % kg != ki.  n_rows <= capacity; ranks that the striping did not place are not replicated.  The
+ * lookup table names a replica as member `kg` of the clique; peers never see it.  Gathered rows do not
+ * change, only where they are read from.  A refill drops the replicas. */
+int legion_cache_add_replicas(LegionCache *c, const int32_t *order_dev, int64_t n_order, int64_t n_rows,
+                              const int32_t *row_of_id_dev, void *stream);
 /* Pointer tables of the clique (d_float_feature_cache_ptr_, cache/cache.cu:601-622). */
 int legion_cache_partition(LegionCache *c, void **ptr, int64_t *bytes);
 int legion_cache_set_peer(LegionCache *c, int32_t k, const void *partition_ptr);

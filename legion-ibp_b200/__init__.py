@@ -150,6 +150,11 @@ class UnifiedCache:
         _check(lib().legion_cache_fill_static_rows(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()),
                                                    _ptr(host_table), _ptr(row_of_id), _stream(stream)))
 
+    def add_replicas(self, order_dev, n_rows, stream=None, row_of_id=None):
+        """Private copies of the n_rows hottest rows that the striping placed on peers."""
+        _check(lib().legion_cache_add_replicas(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()), C.c_int64(n_rows),
+                                               _ptr(row_of_id), _stream(stream)))
+
     def set_host_table(self, host_table):
         self._keep += [host_table]
         _check(lib().legion_cache_set_host_table(self.h, _ptr(host_table)))

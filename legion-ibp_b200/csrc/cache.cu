@@ -73,9 +73,28 @@ __device__ __forceinline__ float warp_max(float v)
     return v;
 }
 
-// One warp per cached row: row s of GPU ki <- host row order[s*kg + ki] (FeatFillUp, cache_impl.cuh:183-188).
+// Rank held by row s of a GPU's private replica region: the ranks that the striping gives to the
+// other kg-1 members, in rank order (s = 0 is the hottest row this GPU does not hold itself).
+__host__ __device__ __forceinline__ int64_t replica_rank(int64_t s, int32_t kg, int32_t ki)
+{
+    const int64_t round = s / (kg - 1);
+    const int32_t j = (int32_t)(s - round * (kg - 1));
+    return round * kg + j + (j >= ki ? 1 : 0);
+}
+
+__global__ void replica_place_kernel(const int32_t *__restrict__ order, int64_t n_ranked, int64_t n_rows, int32_t capacity,
+                                     int32_t kg, int32_t ki, int32_t *lut)
+{
+    for (int64_t s = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; s < n_rows; s += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = replica_rank(s, kg, ki);
+        if (t < n_ranked) lut[order[t]] = (int32_t)((int64_t)kg * capacity + s);
+    }
+}
+
+// One warp per cached row: row s of GPU ki <- host row order[s*kg + ki] (FeatFillUp, cache_impl.cuh:183-188);
+// with REPLICA, row s of the replica region <- host row order[replica_rank(s)].
 // CODEC 0 copies bytes; 1 / 2 store feature_len codes + one fp32 scale, zero padded to slot_bytes.
-template <int CODEC>
+template <int CODEC, bool REPLICA = false>
 __global__ void __launch_bounds__(256)
 static_fill_kernel(const int32_t *__restrict__ order, int64_t n_order, int32_t capacity, int32_t kg, int32_t ki,
                    const uint8_t *__restrict__ host, const int32_t *__restrict__ row_of, int32_t row_bytes, uint8_t *part,
@@ -84,7 +103,7 @@ static_fill_kernel(const int32_t *__restrict__ order, int64_t n_order, int32_t c
     const int lane = threadIdx.x & 31;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t s = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < capacity; s += n_warps) {
-        int64_t t = s * kg + ki;
+        int64_t t = REPLICA ? replica_rank(s, kg, ki) : s * kg + ki;
         if (t >= n_order) break;
         const int32_t node = order[t];
         const uint8_t *src = host + (int64_t)(row_of != nullptr ? row_of[node] : node) * row_bytes;
@@ -283,6 +302,12 @@ extern "C" int legion_cache_fill_static_rows(LegionCache *c, const int32_t *orde
     int sms = sm_count_of(c->dev_id);
     int64_t n_cached = (int64_t)c->capacity * c->kg;
     if (n_cached > n_order) n_cached = n_order;
+    if (c->part[c->kg] != nullptr) {  // a refill drops the replicas of the previous ranking
+        LG_CUDA(cudaStreamSynchronize(s));
+        cudaFree(c->part[c->kg]);
+        c->part[c->kg] = nullptr;
+        c->replica_rows = 0;
+    }
     fill_i32_kernel<<<grid_stride(c->n_nodes, sms), 256, 0, s>>>(c->lut, c->n_nodes, LEGION_CACHEMISS_FLAG);
     LG_LAUNCH_CHECK();
     if (n_cached > 0) {
@@ -310,6 +335,58 @@ extern "C" int legion_cache_fill_static_rows(LegionCache *c, const int32_t *orde
         LG_LAUNCH_CHECK();
     }
     LG_CUDA(cudaStreamSynchronize(s));
+    return LEGION_OK;
+}
+
+extern "C" int legion_cache_add_replicas(LegionCache *c, const int32_t *order_dev, int64_t n_order, int64_t n_rows,
+                                         const int32_t *row_of_id_dev, void *stream)
+{
+    LG_ARG(c != nullptr && c->kind == 0, "not a static cache");
+    LG_ARG(c->kg > 1, "a clique of one GPU has nothing to replicate");
+    LG_ARG(c->host_table != nullptr, "fill the cache first (legion_cache_fill_static)");
+    LG_ARG(c->part[c->kg] == nullptr, "the cache already holds replicas; refill it first");
+    LG_ARG(order_dev != nullptr && n_order >= 0 && n_order <= c->n_nodes, "bad order");
+    LG_ARG(n_rows >= 0 && n_rows <= c->capacity, "replica rows must not exceed the capacity of a partition");
+    LG_ARG(((int64_t)c->kg + 1) * c->capacity < (1ll << 31), "capacity * (kg + 1) must fit int32");
+    LG_CUDA(cudaSetDevice(c->dev_id));
+    cudaStream_t s = (cudaStream_t)stream;
+    // only ranks that the striping placed can be replicated
+    int64_t n_ranked = (int64_t)c->capacity * c->kg;
+    if (n_ranked > n_order) n_ranked = n_order;
+    while (n_rows > 0 && replica_rank(n_rows - 1, c->kg, c->ki) >= n_ranked) --n_rows;
+    if (n_rows == 0) return LEGION_OK;
+    void *rep = nullptr;
+    if (cudaMalloc(&rep, n_rows * (int64_t)c->slot_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("legion_cache_add_replicas: out of device memory for %lld rows", (long long)n_rows);
+        return LEGION_E_NOMEM;
+    }
+    int sms = sm_count_of(c->dev_id);
+    int64_t g = (n_rows + 7) / 8;
+    int grid = (int)(g > (int64_t)sms * 16 ? (int64_t)sms * 16 : (g < 1 ? 1 : g));
+    const uint8_t *host = (const uint8_t *)c->host_table;
+    if (c->codec == LEGION_CODEC_RAW)
+        static_fill_kernel<LEGION_CODEC_RAW, true><<<grid, 256, 0, s>>>(order_dev, n_ranked, (int32_t)n_rows, c->kg, c->ki, host,
+                                                                         row_of_id_dev, c->row_bytes, (uint8_t *)rep, c->slot_bytes);
+    else if (c->codec == LEGION_CODEC_INT8)
+        static_fill_kernel<LEGION_CODEC_INT8, true><<<grid, 256, 0, s>>>(order_dev, n_ranked, (int32_t)n_rows, c->kg, c->ki, host,
+                                                                          row_of_id_dev, c->row_bytes, (uint8_t *)rep, c->slot_bytes);
+    else
+        static_fill_kernel<LEGION_CODEC_E4M3, true><<<grid, 256, 0, s>>>(order_dev, n_ranked, (int32_t)n_rows, c->kg, c->ki, host,
+                                                                          row_of_id_dev, c->row_bytes, (uint8_t *)rep, c->slot_bytes);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) {
+        replica_place_kernel<<<grid_stride(n_rows, sms), 256, 0, s>>>(order_dev, n_ranked, n_rows, c->capacity, c->kg, c->ki, c->lut);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        set_error("legion_cache_add_replicas: %s", cudaGetErrorString(e));
+        cudaFree(rep);
+        return LEGION_E_CUDA;
+    }
+    c->part[c->kg] = rep;
+    c->replica_rows = (int32_t)n_rows;
     return LEGION_OK;
 }
 
@@ -345,6 +422,7 @@ extern "C" int legion_cache_set_peer(LegionCache *c, int32_t k, const void *part
 extern "C" int legion_cache_lut(LegionCache *c, int32_t **lut_dev)
 {
     LG_ARG(c != nullptr && c->kind == 0 && lut_dev != nullptr, "not a static cache");
+    LG_ARG(c->part[c->kg] == nullptr, "the lookup table of a cache with replicas is only usable through the cache handle");
     *lut_dev = c->lut;
     return LEGION_OK;
 }
@@ -429,6 +507,7 @@ extern "C" int legion_cache_destroy(LegionCache *c)
         cudaDeviceSynchronize();
         cudaFree(c->lut);
         if (c->own_block.ptr) vmm_free(&c->own_block); else cudaFree(c->part[c->ki]);
+        cudaFree(c->part[c->kg]);
         for (int k = 0; k < LEGION_MAX_DEVICE; ++k)
             if (c->peer_block[k].ptr) vmm_free(&c->peer_block[k]);
     } else {

@@ -133,7 +133,8 @@ struct LegionCache {
     // static
     int32_t kg, ki, capacity;
     int32_t *lut;                      // n_nodes entries, global index or CACHEMISS
-    void *part[LEGION_MAX_DEVICE];     // part[ki] is owned
+    void *part[LEGION_MAX_DEVICE + 1]; // part[ki] is owned; part[kg] = private copies of hot rows that peers hold
+    int32_t replica_rows;              // rows of part[kg] (legion_cache_add_replicas)
     legion::VmmBlock own_block;        // set when part[ki] is shareable memory (clique of more than one GPU)
     legion::VmmBlock peer_block[LEGION_MAX_DEVICE];  // partitions mapped from other processes
     // lru

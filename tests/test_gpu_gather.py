@@ -181,6 +181,70 @@ def test_clique_striped_cache_on_one_device(oracle_mod, kg):
         r.close()
 
 
+@pytest.mark.parametrize("kg,codec", [(2, L.CODEC_RAW), (4, L.CODEC_RAW), (8, L.CODEC_RAW), (4, L.CODEC_INT8)])
+def test_clique_with_private_replicas(oracle_mod, kg, codec):
+    """Hot rows that the striping gave to peers, copied into a member's own memory: gathered rows are
+    unchanged, the replicated nodes turn from peer hits into local hits, and the cache index names
+    them as member `kg`."""
+    rng = np.random.default_rng(40 + kg)
+    indptr, _ = small_graph(6000, 80000, 5)
+    n = len(indptr) - 1
+    table = rng.standard_normal((n, 128)).astype(np.float32)
+    ids_list = rng.integers(0, n, 3000).astype(np.int32)
+    cap = n // (kg * 2)
+    n_rep = cap // 3
+    order = oracle_mod.degree_order(indptr)
+    rigs = [Rig(table, ids_list, 3000, capacity=cap, kg=kg, ki=ki, order=order, codec=codec) for ki in range(kg)]
+    for a in range(kg):
+        for b in range(kg):
+            if a != b:
+                rigs[a].cache.set_peer(b, rigs[b].cache.partition()[0])
+    lut = oracle_mod.static_cache_lut(order, cap, kg)
+    ci = oracle_mod.find_feat(ids_list, lut)
+    if codec == L.CODEC_RAW:
+        parts = [oracle_mod.static_cache_fill(order, cap, kg, ki, table) for ki in range(kg)]
+        ref = oracle_mod.gather(ids_list, ci, cap, parts, table)
+    else:
+        parts = [oracle_mod.quant_rows(table[order[ki:cap * kg:kg]], codec) for ki in range(kg)]
+        ref = oracle_mod.gather_quant(ids_list, ci, cap, parts, table, codec)
+    rank_of = np.full(n, -1, np.int64)
+    rank_of[order] = np.arange(n)
+    for ki in (0, kg - 1):
+        cnt, before, _ = rigs[ki].gather(0)
+        np.testing.assert_array_equal(before.view(np.uint32), ref.view(np.uint32))
+        st0 = rigs[ki].cache.stats()
+        rigs[ki].cache.add_replicas(rigs[ki].order, n_rep)
+        with pytest.raises(L.LegionError, match="already holds replicas"):
+            rigs[ki].cache.add_replicas(rigs[ki].order, n_rep)
+        with pytest.raises(L.LegionError, match="replicas"):
+            rigs[ki].cache.lut_ptr()
+        # the s-th rank that is not this member's own, in rank order
+        foreign = np.array([t for t in range(cap * kg) if t % kg != ki][:n_rep])
+        slot_of_rank = {int(t): s for s, t in enumerate(foreign)}
+        cnt, after, _ = rigs[ki].gather(0)
+        np.testing.assert_array_equal(after, before)
+        got_ci = rigs[ki].pool.read(L.BUF_CACHE_INDEX, 0, cnt, np.int32)
+        want_ci = ci.copy()
+        for i, v in enumerate(ids_list):
+            s = slot_of_rank.get(int(rank_of[v]))
+            if s is not None:
+                want_ci[i] = kg * cap + s
+        np.testing.assert_array_equal(got_ci, want_ci)
+        st1 = rigs[ki].cache.stats()
+        moved = int(sum(1 for v in ids_list if int(rank_of[v]) in slot_of_rank))
+        owner = ci[ci >= 0] // cap
+        assert moved > 0
+        assert st1["local_hits"] - st0["local_hits"] == int((owner == ki).sum()) + moved
+        assert st1["peer_hits"] - st0["peer_hits"] == int((owner != ki).sum()) - moved
+        assert st1["misses"] - st0["misses"] == int((ci < 0).sum())
+    single = Rig(table, ids_list, 3000, capacity=cap, kg=1, ki=0, order=order)
+    with pytest.raises(L.LegionError, match="nothing to replicate"):
+        single.cache.add_replicas(single.order, 10)
+    single.close()
+    for r in rigs:
+        r.close()
+
+
 def test_partitions_shared_through_file_descriptors(oracle_mod):
     """The cross-process path on one GPU: a member's partition is exported as a file descriptor and
     mapped a second time through it, as a peer process would; rows read through that mapping are the

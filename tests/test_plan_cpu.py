@@ -1,0 +1,55 @@
+"""Host-side cache plan of a clique: stripe rows vs private copies of hot peer rows."""
+import numpy as np
+import torch
+
+from legion_ibp_b200 import server
+
+
+def _mass_from_weights(w):
+    cum = np.cumsum(np.sort(np.asarray(w, np.float64))[::-1])
+    return lambda x: 0.0 if x <= 0 else float(cum[min(int(x), len(cum)) - 1] / cum[-1])
+
+
+def test_single_gpu_has_no_replicas():
+    assert server.plan_clique_cache(lambda x: 0.5, 1000, 200, 1) == (200, 0)
+    assert server.plan_clique_cache(lambda x: 0.5, 1000, 5000, 1) == (1000, 0)
+
+
+def test_spare_budget_becomes_replicas():
+    n = 80000
+    mass = _mass_from_weights(1.0 / np.arange(1, n + 1))
+    stripe, rep = server.plan_clique_cache(mass, n, n // 5, 8)
+    assert stripe == n // 8 and rep == n // 5 - n // 8        # 8 x 20%: 12.5% stripe + 7.5% copies
+    stripe, rep = server.plan_clique_cache(mass, n, n, 4)
+    assert stripe == n // 4 and rep == stripe                  # never more copies than a partition holds
+
+
+def test_uniform_accesses_are_only_striped():
+    n = 100000
+    stripe, rep = server.plan_clique_cache(lambda x: x / n, n, n // 10, 4)
+    assert (stripe, rep) == (n // 10, 0)                       # copies would only shrink the coverage
+
+
+def test_skewed_accesses_get_replicas_and_plan_is_no_worse_than_striping():
+    n = 200000
+    w = 1.0 / np.arange(1, n + 1) ** 1.2
+    mass = _mass_from_weights(w)
+    for world in (2, 4):
+        budget = n // 10
+        stripe, rep = server.plan_clique_cache(mass, n, budget, world)
+        assert 0 < rep <= stripe and stripe + rep <= budget
+
+        def cost(s, r):
+            c_l, c_p, c_h = server.ROW_COST
+            cov = min(n, s * world)
+            top = min(cov, r * world // (world - 1))
+            return (c_h * (1 - mass(cov)) + c_p * (mass(cov) - mass(top)) * (world - 1) / world +
+                    c_l * (mass(top) + (mass(cov) - mass(top)) / world))
+        assert cost(stripe, rep) <= cost(budget, 0)
+
+
+def test_degree_mass():
+    indptr = torch.tensor([0, 5, 5, 6, 10], dtype=torch.int64)   # degrees 5 0 1 4
+    order = torch.tensor([0, 3, 2, 1], dtype=torch.int32)
+    mass = server.degree_mass(indptr, order)
+    assert mass(0) == 0.0 and mass(1) == 0.5 and mass(2) == 0.9 and mass(4) == 1.0 and mass(99) == 1.0
