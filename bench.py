@@ -51,6 +51,11 @@ CONFIGS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of gather_vec_kernel per row served from GPU memory, from the
+# profiler capture of the "mid" config summarised in profiles/gather_kernels_mid_config.md
+NCU_DRAM_BYTES_PER_HIT_ROW = 799
+
+
 def load_pkg():
     import __graft_entry__ as ge
     return ge._package()
@@ -484,18 +489,35 @@ def main():
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = hit_bytes / gather_s / 1e9 if gather_s > 0 else 0.0
+    # DRAM bytes per launch: the full-size workload is too large for a multi-pass profiler capture, so the
+    # figure of the captured "mid" case (profiles/gather_kernels_mid_config.md: dram read + write bytes per
+    # row served from GPU memory) is scaled by the rows one launch serves here; raw 512-byte rows only
+    traffic = traffic_source = None
+    if codec == L.CODEC_RAW and not lru_ways and row_bytes == 512 and world == 1:
+        traffic = NCU_DRAM_BYTES_PER_HIT_ROW * hits / max(1, gather_launches)
+        traffic_source = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of the mid config (%d B per row served "
+                          "from GPU memory; part of the written rows is still in L2 when the kernel ends), scaled "
+                          "by the rows per launch" % NCU_DRAM_BYTES_PER_HIT_ROW)
     kname = ("gather_lru_kernel (set probe + gather of rows held in the LRU cache)" if lru_ways else
              "gather_quant_kernel<%s> (cache lookup + gather with in-kernel dequantisation)" % codec_name
              if codec != L.CODEC_RAW else "gather_vec_kernel (cache lookup + gather of rows held in GPU memory)")
     roofline = {"bound": "hbm", "kernel": kname,
                 "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "peak_source": "of measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "of fallback 6650 GB/s",
-                "traffic": None, "launches": gather_launches,
+                "traffic": traffic, "traffic_source": traffic_source, "launches": gather_launches,
                 "avg_launch_ms": tm["gather_ms"] / max(1, gather_launches),
                 "rows_per_batch": rows / args.steps,
                 "source_split": {k: d[k] / max(1, rows) for k in ("local_hits", "peer_hits", "misses")},
                 "measured": "CUDA events around each launch on its stream, %d batches run one at a time right "
                             "after the timed region" % tm["timed"]}
+    roofline_nvlink = None
+    if d["peer_hits"] > 0:
+        # rows read from peer partitions cross NVLink inside the same kernel; 770 GB/s per direction is the
+        # peer copy measured on this pool (900 nominal)
+        nv = d["peer_hits"] * slot_bytes / gather_s / 1e9 if gather_s > 0 else 0.0
+        roofline_nvlink = {"bound": "nvlink", "kernel": kname, "achieved": nv, "peak": 770.0, "unit": "GB/s",
+                           "frac": nv / 770.0, "peak_source": "peer copy measured on this pool, per direction",
+                           "peer_rows_per_batch": d["peer_hits"] / args.steps}
     link_peak = host_link_peak(table)
     link_achieved = d["misses"] * row_bytes / miss_s / 1e9 if miss_s > 0 else 0.0
     roofline_host = {"bound": "host_link", "kernel": "gather_miss_kernel (zero-copy fetch of missed rows)",
@@ -505,8 +527,9 @@ def main():
                                     "alone reaches 50.6 GB/s on random rows of a 1 GB table and 26 GB/s over 48 GB)",
                      "launches": tm["timed"], "avg_launch_ms": tm["miss_ms"] / max(1, tm["timed"]),
                      "rows_per_batch": d["misses"] / args.steps, "algorithmic_bytes": miss_bytes}
-    # lower bound of the whole gather step: the slower of the HBM side and the host-link side
-    t_lb = max(hit_bytes / (hbm_peak * 1e9), d["misses"] * row_bytes / (link_peak * 1e9) if link_peak else 0.0)
+    # lower bound of the whole gather step: the slowest of the HBM side, the NVLink side and the host-link side
+    t_lb = max(hit_bytes / (hbm_peak * 1e9), d["peer_hits"] * slot_bytes / 770e9,
+               d["misses"] * row_bytes / (link_peak * 1e9) if link_peak else 0.0)
     roofline_path = {"lower_bound_ms_per_batch": t_lb / args.steps * 1e3,
                      "gather_ms_per_batch": (tm["gather_ms"] + tm["miss_ms"]) / max(1, tm["timed"]),
                      "batch_ms": ms_total / args.steps}
@@ -579,7 +602,7 @@ def main():
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": dict(workload_config(cfg, world), host_table_layout=args.host_layout),
                 "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + 1 + 1 + (3 if lru_ways else 0)),
-                "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
+                "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path, "roofline_nvlink": roofline_nvlink,
                 "pipeline": pipeline,
                 "cpu_baseline": cpu, "clocks": clocks,
                 "graph": {"nodes": n, "directed_edges": n_edges, "train_seeds_this_rank": int(mine.numel()),
