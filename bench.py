@@ -601,7 +601,7 @@ def main():
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": dict(workload_config(cfg, world), host_table_layout=args.host_layout),
-                "e2e": e2e, "gpu_launches": args.steps * (2 + 5 * hops + 1 + 1 + (3 if lru_ways else 0)),
+                "e2e": e2e, "gpu_launches": args.steps * (1 + 4 * hops + 1 + 1 + (3 if lru_ways else 0)),
                 "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path, "roofline_nvlink": roofline_nvlink,
                 "pipeline": pipeline,
                 "cpu_baseline": cpu, "clocks": clocks,

@@ -189,12 +189,12 @@ struct LegionPool {
 
 namespace legion {
 // kernel launchers (defined in sample.cu / gather.cu / cache.cu)
-int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &ctl);
+int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &ctl, bool defer_seeds = false);
 BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t *all_ids, const int32_t *all_labels,
                         int32_t total_cap, int64_t first, int32_t size);
 const void *map_clear_kernel_address();
 int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32_t fanout, int32_t hop,
-                      int32_t op_id);
+                      int32_t op_id, bool seeds_pending = false);
 int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
 int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
 int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c);

@@ -278,6 +278,40 @@ __global__ void __launch_bounds__(256) gather_quant_kernel(GatherParams p)
         defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
         const int rows_here = min(32, n - c * 32);
         float *dst_base = reinterpret_cast<float *>(p.dst + (int64_t)(off + c * 32) * p.row_bytes);
+        if (f <= 128) {
+            // up to 128 codes per row: one 4-byte word per lane and row, 8 rows in flight per warp
+            constexpr int R = 8;
+            const bool mine = lane < (f >> 2);
+            for (int j0 = 0; j0 < rows_here; j0 += R) {
+                const uint8_t *sp[R];
+                uint32_t packed[R];
+                float scale[R];
+#pragma unroll
+                for (int jj = 0; jj < R; ++jj) {
+                    sp[jj] = shfl_ptr(src, (j0 + jj) & 31);
+                    if (j0 + jj >= rows_here) sp[jj] = nullptr;
+                }
+#pragma unroll
+                for (int jj = 0; jj < R; ++jj) {
+                    if (sp[jj] != nullptr && mine) {
+                        packed[jj] = *reinterpret_cast<const uint32_t *>(sp[jj] + lane * 4);
+                        scale[jj] = *reinterpret_cast<const float *>(sp[jj] + f);
+                    }
+                }
+#pragma unroll
+                for (int jj = 0; jj < R; ++jj) {
+                    if (sp[jj] != nullptr && mine) {
+                        float4 o;
+                        o.x = __fmul_rn(decode_code<CODEC>((uint8_t)(packed[jj])), scale[jj]);
+                        o.y = __fmul_rn(decode_code<CODEC>((uint8_t)(packed[jj] >> 8)), scale[jj]);
+                        o.z = __fmul_rn(decode_code<CODEC>((uint8_t)(packed[jj] >> 16)), scale[jj]);
+                        o.w = __fmul_rn(decode_code<CODEC>((uint8_t)(packed[jj] >> 24)), scale[jj]);
+                        __stcs(reinterpret_cast<float4 *>(dst_base + (int64_t)(j0 + jj) * f) + lane, o);
+                    }
+                }
+            }
+            continue;
+        }
         for (int j = 0; j < rows_here; ++j) {
             const uint8_t *sp = shfl_ptr(src, j);
             if (sp == nullptr) continue;  // invalid id, or a miss left to the miss kernel (raw fp32 row)

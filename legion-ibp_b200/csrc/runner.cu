@@ -215,9 +215,11 @@ static int issue_gather(LegionRunner *r, cudaStream_t s)
 static int issue_sampling(LegionRunner *r, const BatchCtl &v, cudaStream_t s)
 {
     LegionPool *p = r->pool;
-    int rc = launch_batch_generate(s, p, v);
+    // with at least one hop, the first hop's counting kernel also takes the seed slice
+    const bool defer = p->hop_num > 0;
+    int rc = launch_batch_generate(s, p, v, defer);
     for (int h = 0; h < p->hop_num && rc == LEGION_OK; ++h)
-        rc = launch_sample_hop(s, p, r->graph, p->fanout[h], h, LEGION_INTRABATCH_CON * (h + 1));
+        rc = launch_sample_hop(s, p, r->graph, p->fanout[h], h, LEGION_INTRABATCH_CON * (h + 1), defer && h == 0);
     return rc;
 }
 

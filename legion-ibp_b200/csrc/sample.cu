@@ -1,14 +1,15 @@
 // Seed batch generation, neighbour sampling, per-hop dedup and relabel.
 //
-// One hop is five launches on one stream, with every size kept on the device:
+// One hop is four launches on one stream, with every size kept on the device:
 //   hop_count   : per input node degree, CSR start and its edge offset inside a 1024-node tile;
-//                 the last CTA to finish turns the tile sums into tile offsets (no host sync)
+//                 the last CTA to finish turns the tile sums into tile offsets (no host sync);
+//                 over the seeds it can also take the seed slice itself (batch_generate's work)
 //   hop_sample  : one warp per input node draws the neighbours (Philox4x32-10 counter RNG),
 //                 writes the edges at their final positions and enters every neighbour into the
 //                 batch-local id map with atomicMin(first edge index)
 //   hop_flag    : marks the edge that reached a new node first, ranks the marks per tile
-//   hop_assign  : gives new nodes their local ids in order of first appearance
-//   hop_relabel : writes local source ids; the last CTA advances the counters
+//   hop_finish  : gives new nodes their local ids in order of first appearance and writes the
+//                 local source id of every edge; the last CTA advances the counters
 // The edge order (input after input, slot after slot) and the node order (first appearance in
 // that edge order) do not depend on scheduling, so a host replay reproduces them bit for bit.
 //
@@ -238,18 +239,49 @@ __global__ void batch_generate_kernel(const BatchCtl *__restrict__ b, int32_t *i
 
 // ---- one hop -----------------------------------------------------------------------------------
 
+// FIRST: the hop over the seeds also does the work of batch_generate_kernel (seed slice, labels, seeds
+// into the id map, counter words of op 0), which saves one launch per batch.
+template <bool FIRST>
 __global__ void __launch_bounds__(kScanThreads)
-hop_count_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict__ ids, int32_t fanout,
-                 NodeRec *rec, int32_t *tile_sum, int32_t *tile_off, int32_t *ctl, int64_t max_edges)
+hop_count_kernel(const int64_t *__restrict__ indptr, int32_t *ids, int32_t fanout,
+                 NodeRec *rec, int32_t *tile_sum, int32_t *tile_off, int32_t *ctl, int64_t max_edges,
+                 const BatchCtl *__restrict__ b, int32_t *labels, MapSlot *map, uint32_t mask, int32_t *nc, int32_t *ec)
 {
     __shared__ int smem[kScanThreads / 32];
     __shared__ int s_flag;
-    const int n = ctl[CTL_N_NODES];
+    const int n = FIRST ? b->size : ctl[CTL_N_NODES];
     const int n_tiles = (n + kTile - 1) / kTile;
+    if (FIRST && blockIdx.x == 0 && threadIdx.x == 0) {
+        counter_update(nc, ec, 0, n, b->hop_num);
+        ctl[CTL_N_NODES] = n;
+        ctl[CTL_E_TOTAL] = 0;
+    }
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const int base = tile * kTile + threadIdx.x * 4;
-        int4 v4 = *reinterpret_cast<const int4 *>(ids + base);  // ids is padded to a whole tile
-        int32_t v[4] = { v4.x, v4.y, v4.z, v4.w };
+        int32_t v[4];
+        if (FIRST) {
+            const int32_t total_cap = b->total_cap;
+            const int64_t first = b->first;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[j] = -1;
+                const int idx = base + j;
+                if (idx < n) {
+                    const int64_t pos = first + idx;
+                    int32_t lab = -1;
+                    if (pos < total_cap) {  // operator_impl.cu:41-43
+                        v[j] = b->all_ids[pos % total_cap];
+                        lab = b->all_labels[pos % total_cap];
+                    }
+                    ids[idx] = v[j];
+                    labels[idx] = lab;
+                    if (v[j] >= 0 && pos < total_cap) map_insert_min(map, mask, v[j], idx, ctl);
+                }
+            }
+        } else {
+            int4 v4 = *reinterpret_cast<const int4 *>(ids + base);  // ids is padded to a whole tile
+            v[0] = v4.x; v[1] = v4.y; v[2] = v4.z; v[3] = v4.w;
+        }
         int64_t start[4];
         int32_t deg[4], cnt[4];
 #pragma unroll
@@ -283,7 +315,8 @@ hop_count_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict__
     if (last_cta_scan(&ctl[CTL_TICKET_A], tile_sum, tile_off, n_tiles, smem, &s_flag, &grand)) {
         if (threadIdx.x == 0) {
             ctl[CTL_E_HOP] = grand;
-            if ((int64_t)ctl[CTL_E_TOTAL] + grand > max_edges) atomicCAS(&ctl[CTL_ERROR], DERR_NONE, DERR_EDGE_OVERFLOW);
+            const int e_total = FIRST ? 0 : ctl[CTL_E_TOTAL];
+            if ((int64_t)e_total + grand > max_edges) atomicCAS(&ctl[CTL_ERROR], DERR_NONE, DERR_EDGE_OVERFLOW);
         }
     }
 }
@@ -385,34 +418,40 @@ hop_flag_kernel(const int32_t *__restrict__ eslot, const MapSlot *map, int32_t *
     }
 }
 
-__global__ void hop_assign_kernel(const int32_t *__restrict__ erank, const int32_t *__restrict__ tile_off,
+// New nodes get their local ids (order of first appearance: rank of the flagged edge) and every edge of
+// the hop is relabelled, in one pass.  The local id of a node whose first edge is fe is
+// n0 + tile_off[fe / tile] + erank[fe], which every edge can compute for itself once the flags are
+// scanned; the map entry is rewritten to that id by the first edge, and an edge that reads the entry
+// after the rewrite finds the same number.  The last CTA advances the counters.
+__global__ void hop_finish_kernel(const int32_t *__restrict__ erank, const int32_t *__restrict__ tile_off,
                                   const int32_t *__restrict__ eslot, const int32_t *__restrict__ src_global,
-                                  int32_t *ids, MapSlot *map, const int32_t *ctl)
-{
-    if (ctl[CTL_ERROR] != DERR_NONE) return;
-    const int n_edges = ctl[CTL_E_HOP];
-    const int n0 = ctl[CTL_N_NODES];
-    const int e_base = ctl[CTL_E_TOTAL];
-    for (int eh = blockIdx.x * blockDim.x + threadIdx.x; eh < n_edges; eh += gridDim.x * blockDim.x) {
-        int r = erank[eh];
-        if (r >= 0) {
-            int nid = n0 + tile_off[eh >> 10] + r;
-            ids[nid] = src_global[e_base + eh];
-            map[eslot[eh]].val = nid;
-        }
-    }
-}
-
-__global__ void hop_relabel_kernel(const int32_t *__restrict__ eslot, const MapSlot *map, int32_t *agg_src,
-                                   int32_t *ctl, int32_t *nc, int32_t *ec, int op_id)
+                                  int32_t *ids, MapSlot *map, int32_t *agg_src, int32_t *ctl, int32_t *nc, int32_t *ec,
+                                  int op_id)
 {
     __shared__ int s_flag;
     const int n_edges = ctl[CTL_E_HOP];
+    const int n0 = ctl[CTL_N_NODES];
     const int e_base = ctl[CTL_E_TOTAL];
+    const int c_hop = ctl[CTL_C_HOP];
     const bool ok = ctl[CTL_ERROR] == DERR_NONE;
     if (ok) {
-        for (int eh = blockIdx.x * blockDim.x + threadIdx.x; eh < n_edges; eh += gridDim.x * blockDim.x)
-            agg_src[e_base + eh] = __ldcg(&map[eslot[eh]].val);
+        for (int eh = blockIdx.x * blockDim.x + threadIdx.x; eh < n_edges; eh += gridDim.x * blockDim.x) {
+            const int slot = eslot[eh];
+            const int r = erank[eh];
+            int local;
+            if (r >= 0) {
+                local = n0 + tile_off[eh >> 10] + r;
+                ids[local] = src_global[e_base + eh];
+                map[slot].val = local;
+            } else {
+                local = __ldcg(&map[slot].val);
+                if (local >= kNewBase) {
+                    const int fe = local - kNewBase;
+                    local = n0 + tile_off[fe >> 10] + erank[fe];
+                }
+            }
+            agg_src[e_base + eh] = local;
+        }
     }
     __threadfence();
     __syncthreads();
@@ -423,12 +462,12 @@ __global__ void hop_relabel_kernel(const int32_t *__restrict__ eslot, const MapS
     __syncthreads();
     if (s_flag && threadIdx.x == 0) {
         // every other CTA has read ctl by now
-        int c = ok ? ctl[CTL_C_HOP] : 0;
+        int c = ok ? c_hop : 0;
         int e = ok ? n_edges : 0;
         nc[LEGION_INTRABATCH_CON * 2] += c;  // operator_impl.cu:281
         ec[2] += e;                          // operator_impl.cu:282
         counter_update(nc, ec, op_id, 0, 0);
-        ctl[CTL_N_NODES] = ctl[CTL_N_NODES] + c;
+        ctl[CTL_N_NODES] = n0 + c;
         ctl[CTL_E_TOTAL] = e_base + e;
         ctl[CTL_E_HOP] = 0;
         ctl[CTL_C_HOP] = 0;
@@ -466,7 +505,9 @@ BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t
     return v;
 }
 
-int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &v)
+// defer_seeds: only the first kernel (map, counters, batch parameters) is issued; the seed slice is then
+// taken by the first hop (launch_sample_hop with seeds_pending), one launch fewer per batch.
+int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &v, bool defer_seeds)
 {
     const int pipe = p->pipe;
     int64_t n_pairs = ((int64_t)p->map_mask + 1) / 2;
@@ -474,6 +515,7 @@ int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &v)
         reinterpret_cast<uint4 *>(p->map[pipe]), n_pairs, p->ctl[pipe], p->node_counter[pipe], p->edge_counter[pipe],
         p->bctl[pipe], v);
     LG_LAUNCH_CHECK();
+    if (defer_seeds) return LEGION_OK;
     batch_generate_kernel<<<grid_for(p->batch_size, 256, 1 << 20), 256, 0, s>>>(
         p->bctl[pipe], p->ids[pipe], p->labels[pipe], p->map[pipe], p->map_mask, p->ctl[pipe], p->node_counter[pipe],
         p->edge_counter[pipe]);
@@ -482,7 +524,7 @@ int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &v)
 }
 
 int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32_t fanout, int32_t hop,
-                      int32_t op_id)
+                      int32_t op_id, bool seeds_pending)
 {
     const int pipe = p->pipe;
     const int cap = p->sm_count * 8;
@@ -491,8 +533,16 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
     for (int h = 0; h < hop; ++h) inputs += inputs * p->fanout[h];
     int64_t edges = inputs * fanout;
     int32_t *ctl = p->ctl[pipe];
-    hop_count_kernel<<<grid_for(inputs, kTile, cap), kScanThreads, 0, s>>>(
-        g->indptr, p->ids[pipe], fanout, p->node_rec[pipe], p->tile_sum[pipe], p->tile_off[pipe], ctl, p->max_edges);
+    if (seeds_pending) {
+        LG_ARG(hop == 0, "only the first hop can take the seed slice");
+        hop_count_kernel<true><<<grid_for(inputs, kTile, cap), kScanThreads, 0, s>>>(
+            g->indptr, p->ids[pipe], fanout, p->node_rec[pipe], p->tile_sum[pipe], p->tile_off[pipe], ctl, p->max_edges,
+            p->bctl[pipe], p->labels[pipe], p->map[pipe], p->map_mask, p->node_counter[pipe], p->edge_counter[pipe]);
+    } else {
+        hop_count_kernel<false><<<grid_for(inputs, kTile, cap), kScanThreads, 0, s>>>(
+            g->indptr, p->ids[pipe], fanout, p->node_rec[pipe], p->tile_sum[pipe], p->tile_off[pipe], ctl, p->max_edges,
+            p->bctl[pipe], p->labels[pipe], p->map[pipe], p->map_mask, p->node_counter[pipe], p->edge_counter[pipe]);
+    }
     LG_LAUNCH_CHECK();
     hop_sample_kernel<<<grid_for(inputs, 8, cap), 256, 0, s>>>(
         g->indices, p->node_rec[pipe], p->tile_off[pipe], fanout, (uint32_t)hop, p->bctl[pipe], p->src_global[pipe],
@@ -503,11 +553,10 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
     hop_flag_kernel<<<grid_for(edges, kTile, cap), kScanThreads, 0, s>>>(p->eslot[pipe], p->map[pipe], p->erank[pipe],
                                                                          tile_sum2, tile_off2, ctl, p->max_nodes);
     LG_LAUNCH_CHECK();
-    hop_assign_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->erank[pipe], tile_off2, p->eslot[pipe],
-                                                                   p->src_global[pipe], p->ids[pipe], p->map[pipe], ctl);
-    LG_LAUNCH_CHECK();
-    hop_relabel_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->eslot[pipe], p->map[pipe], p->agg_src[pipe], ctl,
-                                                                    p->node_counter[pipe], p->edge_counter[pipe], op_id);
+    hop_finish_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->erank[pipe], tile_off2, p->eslot[pipe],
+                                                                   p->src_global[pipe], p->ids[pipe], p->map[pipe],
+                                                                   p->agg_src[pipe], ctl, p->node_counter[pipe],
+                                                                   p->edge_counter[pipe], op_id);
     LG_LAUNCH_CHECK();
     return LEGION_OK;
 }
