@@ -40,6 +40,13 @@ CONFIGS = {
                      train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="int8"),
     "mid-e4m3": dict(name="mid RMAT, fp8 e4m3 cache", n_nodes=8000000, n_pairs=64000000, feat_len=128, classes=172,
                      train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="e4m3"),
+    # compressed rows in the host table too: a miss moves 144 instead of 512 bytes over the host link
+    "c4h": dict(name="paper100M-shaped RMAT, int8 cache and int8 host table", n_nodes=111059956, n_pairs=900000000,
+                feat_len=128, classes=172, train_frac=0.011, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="int8",
+                host_codec=True),
+    "mid-int8-host": dict(name="mid RMAT, int8 cache and int8 host table", n_nodes=8000000, n_pairs=64000000,
+                          feat_len=128, classes=172, train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2,
+                          codec="int8", host_codec=True),
     # dynamic-LRU stress (configs[4]) scaled 1:25 so that the host table (10 GB) fits any box: Zipf(1.1)
     # seeds, three hops, set-associative LRU cache of 10% of the table
     "c5s": dict(name="LRU stress RMAT (configs[4] scaled 1:25)", n_nodes=20000000, n_pairs=80000000, feat_len=128,
@@ -116,29 +123,48 @@ def make_graph(cfg, device, seed=0):
     return synth.rmat_csr(cfg["n_nodes"], cfg["n_pairs"], seed=seed, device=device)
 
 
-def host_table(cfg, shared_name=None, rank=0, world=1, pinned=True):
-    """[N, F] fp32 table in host memory, filled by rank 0; pinned / registered for zero-copy reads."""
+def host_buffer(n_bytes, shared_name, rank, world, dev=0, fill=None):
+    """uint8 buffer in host memory that every rank's GPU can read: pinned (one rank) or one POSIX shared
+    segment that rank 0 creates and populates (`fill(buffer)`, else zeros) and every rank page-locks."""
     import torch
-    from legion_ibp_b200 import synth
-    n, f = cfg["n_nodes"], cfg["feat_len"]
     if world == 1:
-        t = torch.empty((n, f), dtype=torch.float32, pin_memory=pinned)
-        synth.features_into(t, seed=0)
+        t = torch.empty(n_bytes, dtype=torch.uint8, pin_memory=True)
+        if fill is not None:
+            fill(t)
         return t
     import torch.distributed as dist
+    L = load_pkg()
     path = "/dev/shm/" + shared_name
     if rank == 0:
-        t = torch.from_file(path, shared=True, size=n * f, dtype=torch.float32).view(n, f)
-        synth.features_into(t, seed=0)
+        t = torch.from_file(path, shared=True, size=n_bytes, dtype=torch.uint8)
+        if fill is not None:
+            fill(t)
+        else:
+            t.zero_()
     dist.barrier()
     if rank != 0:
-        t = torch.from_file(path, shared=True, size=n * f, dtype=torch.float32).view(n, f)
-    err = torch.cuda.cudart().cudaHostRegister(t.data_ptr(), t.numel() * 4, 0)
-    assert int(err) == 0, "cudaHostRegister failed: %s" % err
+        t = torch.from_file(path, shared=True, size=n_bytes, dtype=torch.uint8)
+    try:
+        L.host_register(dev, t)
+    except L.LegionError as e:
+        # the driver would not page-lock the shared segment: every rank keeps a pinned copy of its own
+        print("rank %d: %s; falling back to a private pinned copy" % (rank, e), file=sys.stderr, flush=True)
+        own = torch.empty(n_bytes, dtype=torch.uint8, pin_memory=True)
+        own.copy_(t)
+        t = own
     dist.barrier()
     if rank == 0:
         os.unlink(path)  # the mappings stay valid
     return t
+
+
+def host_table(cfg, shared_name=None, rank=0, world=1, dev=0):
+    """[N, F] fp32 table in host memory, filled by rank 0; pinned / registered for zero-copy reads."""
+    import torch
+    from legion_ibp_b200 import synth
+    n, f = cfg["n_nodes"], cfg["feat_len"]
+    fill = lambda b: synth.features_into(b.view(torch.float32).view(n, f), seed=0)
+    return host_buffer(n * f * 4, shared_name, rank, world, dev, fill).view(torch.float32).view(n, f)
 
 
 def host_link_peak(table):
@@ -261,6 +287,8 @@ def workload_config(cfg, n_gpus):
     elif cfg.get("codec", "raw") != "raw":
         kind = "static degree-ordered %s cache (codes + fp32 row scale) in %d%% of the table's bytes per GPU" % (
             cfg["codec"], int(cfg["cache_frac"] * 100))
+        if cfg.get("host_codec"):
+            kind += ", host table held as the same compressed rows"
     else:
         kind = "static degree-ordered cache %d%% of the table per GPU" % int(cfg["cache_frac"] * 100)
     return {"workload": "%s: %d nodes, fp32 dim %d, batch %d, fanout %s, %s, misses by zero-copy from pinned host "
@@ -334,7 +362,7 @@ def main():
         train = zipf_batches(n, cfg["batch"], cfg["zipf_batches"], cfg["zipf"], world, rank)
     mine = train[(train % world) == rank].contiguous()  # id % ngpu split, storage_management.cu:214-250
     mine_labels = labels[mine.long()].contiguous()
-    table = host_table(cfg, "legion_b200_bench_features", rank, world)
+    table = host_table(cfg, "legion_b200_bench_features", rank, world, dev)
 
     # ---- storage, cache, pool, runner ------------------------------------------------------------
     g = L.GraphStorage(dev, indptr, indices)
@@ -350,6 +378,12 @@ def main():
     if cap * world >= n:
         cap = (n + world - 1) // world
     row_of = None
+    stored = None  # compressed copy of the host table (configs with host_codec)
+
+    def barrier0():
+        if dist is not None:
+            dist.barrier()
+
     lru_ways = cfg.get("lru_ways", 0)
     if lru_ways:
         # every GPU keeps its own LRU cache (no clique: the contents change every batch)
@@ -358,13 +392,20 @@ def main():
         cache.set_host_table(table)
         args.host_layout = "id"
     else:
+        if cfg.get("host_codec"):
+            stored = host_buffer(n * slot_bytes, "legion_b200_bench_codes", rank, world, dev).view(n, slot_bytes)
+            if rank == 0:
+                L.quantize_table(dev, codec, table, n, f, stored)
+            barrier0()
         if world > 1 and not args.no_replicas:
             from legion_ibp_b200 import server
             cap, replica_rows = server.plan_clique_cache(server.degree_mass(indptr, order), n, budget, world)
         cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank, codec=codec)
         if args.host_layout == "seeds_first":
             row_of = host_rows_seeds_first(order, train, cap * world)
-        cache.fill_static(order, table, row_of_id=row_of)
+        if stored is not None:
+            cache.set_host_codec(codec)
+        cache.fill_static(order, table if stored is None else stored, row_of_id=row_of)
         if replica_rows > 0:
             cache.add_replicas(order, replica_rows, row_of_id=row_of)
     del order
@@ -479,7 +520,8 @@ def main():
     # and one stamp) and writes the fp32 row
     hit_read = slot_bytes + (4 * lru_ways + 4 if lru_ways else 0)
     hit_bytes = hits * (hit_read + row_bytes + 8) + d["misses"] * 16
-    miss_bytes = d["misses"] * (2 * row_bytes + 8)
+    host_row_bytes = slot_bytes if stored is not None else row_bytes   # bytes a miss moves over the host link
+    miss_bytes = d["misses"] * (host_row_bytes + row_bytes + 8)
     gather_s = tm["gather_ms"] * 1e-3
     miss_s = tm["miss_ms"] * 1e-3
     peaks = {}
@@ -519,7 +561,7 @@ def main():
                            "frac": nv / 770.0, "peak_source": "peer copy measured on this pool, per direction",
                            "peer_rows_per_batch": d["peer_hits"] / args.steps}
     link_peak = host_link_peak(table)
-    link_achieved = d["misses"] * row_bytes / miss_s / 1e9 if miss_s > 0 else 0.0
+    link_achieved = d["misses"] * host_row_bytes / miss_s / 1e9 if miss_s > 0 else 0.0
     roofline_host = {"bound": "host_link", "kernel": "gather_miss_kernel (zero-copy fetch of missed rows)",
                      "achieved": link_achieved, "peak": link_peak, "unit": "GB/s",
                      "frac": link_achieved / link_peak if link_peak else None,
@@ -529,7 +571,7 @@ def main():
                      "rows_per_batch": d["misses"] / args.steps, "algorithmic_bytes": miss_bytes}
     # lower bound of the whole gather step: the slowest of the HBM side, the NVLink side and the host-link side
     t_lb = max(hit_bytes / (hbm_peak * 1e9), d["peer_hits"] * slot_bytes / 770e9,
-               d["misses"] * row_bytes / (link_peak * 1e9) if link_peak else 0.0)
+               d["misses"] * host_row_bytes / (link_peak * 1e9) if link_peak else 0.0)
     roofline_path = {"lower_bound_ms_per_batch": t_lb / args.steps * 1e3,
                      "gather_ms_per_batch": (tm["gather_ms"] + tm["miss_ms"]) / max(1, tm["timed"]),
                      "batch_ms": ms_total / args.steps}

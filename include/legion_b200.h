@@ -57,6 +57,11 @@ int legion_abi_version(void);
  * reference's alloc/copy helpers, engine/server_imp.cuh:1-51).  kind: 1 host->device,
  * 2 device->host, 3 device->device. */
 int legion_copy(void *dst, const void *src, int64_t bytes, int32_t kind);
+/* Page-locks a range of host memory that CUDA did not allocate (a shared segment or mapped file that
+ * several server processes share) so that this process's kernels can read it by zero-copy loads.  The
+ * reference has one process and allocates its host tables with cudaHostAlloc
+ * (storage/storage_management.cu:114-115,171). */
+int legion_host_register(int32_t dev_id, void *ptr, int64_t bytes);
 /* Launch-shape knobs for measurements (the reference hard-codes its grids, e.g. cache/cache.cu:746-752).
  * "miss_ctas": CTAs of the host-link fetch kernel, 0 = one per SM. */
 int legion_set_tunable(const char *name, int32_t value);
@@ -148,6 +153,17 @@ int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n
  * uncached node. */
 int legion_cache_fill_static_rows(LegionCache *c, const int32_t *order_dev, int64_t n_order, const void *host_table,
                                   const int32_t *row_of_id_dev, void *stream);
+/* Host table stored compressed ("IBP(M)" of the reference: compress_cpu_transfer_kernel,
+ * comp_cache/static_cache.cu:656-772, with the int8 / e4m3 per-row codec in place of the absent
+ * bit-packing): every row of the host table is feature_len one-byte codes + one fp32 scale, padded to
+ * 16 bytes, exactly a cache slot.  A miss then moves that many bytes over the host link and is decoded
+ * in the fetch kernel; cache fill copies slots.  Hits and misses decode to the same values.  Call on a
+ * cache of the same codec before legion_cache_fill_static[_rows]. */
+int legion_cache_set_host_codec(LegionCache *c, int32_t codec);
+/* Encodes n_rows fp32 rows (device-accessible: device or pinned host memory) into compressed rows of
+ * (feature_len + 4) bytes rounded up to 16, with the quantiser the caches use. */
+int legion_quantize_table(int32_t dev_id, int32_t codec, const void *rows, int64_t n_rows, int32_t feature_len,
+                          void *out_rows, void *stream);
 /* Private copies of the hottest rows that the striping gave to OTHER clique members, so that this
  * GPU serves them from its own memory instead of over NVLink.  The reference stripes only
  * (cache/cache_impl.cuh:104-109): when the clique's budget exceeds the table (8 GPUs x 20%), its

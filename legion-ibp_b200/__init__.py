@@ -150,6 +150,10 @@ class UnifiedCache:
         _check(lib().legion_cache_fill_static_rows(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()),
                                                    _ptr(host_table), _ptr(row_of_id), _stream(stream)))
 
+    def set_host_codec(self, codec):
+        """The host table holds compressed rows (codes + fp32 scale) of this cache's codec."""
+        _check(lib().legion_cache_set_host_codec(self.h, C.c_int32(codec)))
+
     def add_replicas(self, order_dev, n_rows, stream=None, row_of_id=None):
         """Private copies of the n_rows hottest rows that the striping placed on peers."""
         _check(lib().legion_cache_add_replicas(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()), C.c_int64(n_rows),
@@ -200,6 +204,17 @@ class UnifiedCache:
         if self.h:
             lib().legion_cache_destroy(self.h)
             self.h = C.c_void_p()
+
+
+def host_register(dev_id, tensor):
+    """Page-locks a host tensor that CUDA did not allocate (shared segment, mapped file) for zero-copy reads."""
+    _check(lib().legion_host_register(C.c_int32(dev_id), _ptr(tensor), C.c_int64(tensor.numel() * tensor.element_size())))
+
+
+def quantize_table(dev_id, codec, rows, n_rows, feature_len, out_rows, stream=None):
+    """fp32 rows -> compressed rows [(feature_len + 4) rounded up to 16 bytes] with the caches' quantiser."""
+    _check(lib().legion_quantize_table(C.c_int32(dev_id), C.c_int32(codec), _ptr(rows), C.c_int64(n_rows),
+                                       C.c_int32(feature_len), _ptr(out_rows), _stream(stream)))
 
 
 class MemoryPool:

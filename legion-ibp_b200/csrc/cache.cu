@@ -105,7 +105,7 @@ static_fill_kernel(const int32_t *__restrict__ order, int64_t n_order, int32_t c
     for (int64_t s = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < capacity; s += n_warps) {
         int64_t t = REPLICA ? replica_rank(s, kg, ki) : s * kg + ki;
         if (t >= n_order) break;
-        const int32_t node = order[t];
+        const int32_t node = order != nullptr ? order[t] : (int32_t)t;  // no order: row t of the table
         const uint8_t *src = host + (int64_t)(row_of != nullptr ? row_of[node] : node) * row_bytes;
         uint8_t *dst = part + s * (int64_t)slot_bytes;
         if (CODEC == LEGION_CODEC_RAW) {
@@ -319,7 +319,10 @@ extern "C" int legion_cache_fill_static_rows(LegionCache *c, const int32_t *orde
         int grid = (int)(g > (int64_t)sms * 16 ? (int64_t)sms * 16 : (g < 1 ? 1 : g));
         uint8_t *part = (uint8_t *)c->part[c->ki];
         const uint8_t *host = (const uint8_t *)host_table;
-        if (c->codec == LEGION_CODEC_RAW)
+        if (c->host_codec != LEGION_CODEC_RAW)  // rows of the host table are cache slots already: copy them
+            static_fill_kernel<LEGION_CODEC_RAW><<<grid, 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->ki,
+                                                                     host, row_of_id_dev, c->slot_bytes, part, c->slot_bytes);
+        else if (c->codec == LEGION_CODEC_RAW)
             static_fill_kernel<LEGION_CODEC_RAW><<<grid, 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->ki,
                                                                      host, row_of_id_dev, c->row_bytes, part, c->slot_bytes);
         else if (c->codec == LEGION_CODEC_INT8)
@@ -365,7 +368,10 @@ extern "C" int legion_cache_add_replicas(LegionCache *c, const int32_t *order_de
     int64_t g = (n_rows + 7) / 8;
     int grid = (int)(g > (int64_t)sms * 16 ? (int64_t)sms * 16 : (g < 1 ? 1 : g));
     const uint8_t *host = (const uint8_t *)c->host_table;
-    if (c->codec == LEGION_CODEC_RAW)
+    if (c->host_codec != LEGION_CODEC_RAW)
+        static_fill_kernel<LEGION_CODEC_RAW, true><<<grid, 256, 0, s>>>(order_dev, n_ranked, (int32_t)n_rows, c->kg, c->ki, host,
+                                                                         row_of_id_dev, c->slot_bytes, (uint8_t *)rep, c->slot_bytes);
+    else if (c->codec == LEGION_CODEC_RAW)
         static_fill_kernel<LEGION_CODEC_RAW, true><<<grid, 256, 0, s>>>(order_dev, n_ranked, (int32_t)n_rows, c->kg, c->ki, host,
                                                                          row_of_id_dev, c->row_bytes, (uint8_t *)rep, c->slot_bytes);
     else if (c->codec == LEGION_CODEC_INT8)
@@ -394,6 +400,38 @@ extern "C" int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev
                                         const void *host_table, void *stream)
 {
     return legion_cache_fill_static_rows(c, order_dev, n_order, host_table, nullptr, stream);
+}
+
+extern "C" int legion_cache_set_host_codec(LegionCache *c, int32_t codec)
+{
+    LG_ARG(c != nullptr && c->kind == 0, "not a static cache");
+    LG_ARG(codec == LEGION_CODEC_RAW || codec == c->codec, "a compressed host table needs a cache of the same codec");
+    c->host_codec = codec;
+    return LEGION_OK;
+}
+
+extern "C" int legion_quantize_table(int32_t dev_id, int32_t codec, const void *rows, int64_t n_rows, int32_t feature_len,
+                                     void *out_rows, void *stream)
+{
+    LG_ARG(codec == LEGION_CODEC_INT8 || codec == LEGION_CODEC_E4M3, "codec must be INT8 or E4M3");
+    LG_ARG(rows != nullptr && out_rows != nullptr && n_rows >= 0 && n_rows < (1ll << 31), "bad rows");
+    LG_ARG(feature_len > 0 && feature_len % 4 == 0, "compressed rows need feature_len % 4 == 0");
+    if (n_rows == 0) return LEGION_OK;
+    LG_CUDA(cudaSetDevice(dev_id));
+    cudaStream_t s = (cudaStream_t)stream;
+    const int sms = sm_count_of(dev_id);
+    const int32_t slot = (feature_len + 4 + 15) / 16 * 16;
+    int64_t g = (n_rows + 7) / 8;
+    int grid = (int)(g > (int64_t)sms * 16 ? (int64_t)sms * 16 : g);
+    if (codec == LEGION_CODEC_INT8)
+        static_fill_kernel<LEGION_CODEC_INT8><<<grid, 256, 0, s>>>(nullptr, n_rows, (int32_t)n_rows, 1, 0, (const uint8_t *)rows,
+                                                                  nullptr, feature_len * 4, (uint8_t *)out_rows, slot);
+    else
+        static_fill_kernel<LEGION_CODEC_E4M3><<<grid, 256, 0, s>>>(nullptr, n_rows, (int32_t)n_rows, 1, 0, (const uint8_t *)rows,
+                                                                  nullptr, feature_len * 4, (uint8_t *)out_rows, slot);
+    LG_LAUNCH_CHECK();
+    LG_CUDA(cudaStreamSynchronize(s));
+    return LEGION_OK;
 }
 
 extern "C" int legion_cache_set_host_table(LegionCache *c, const void *host_table)

@@ -425,6 +425,38 @@ extern "C" int legion_copy(void *dst, const void *src, int64_t bytes, int32_t ki
     return LEGION_OK;
 }
 
+// Page-locks host memory that this process did not allocate through CUDA (a POSIX shared segment or a
+// mapped file that several server processes share) so that kernels of this process can read it by
+// zero-copy loads; the reference allocates its host tables with cudaHostAlloc inside its one process
+// (storage/storage_management.cu:114-115,171).  If the driver refuses the range as a whole it is
+// registered in 1 GiB pieces.  Already-registered memory is not an error.
+extern "C" int legion_host_register(int32_t dev_id, void *ptr, int64_t bytes)
+{
+    LG_ARG(ptr != nullptr && bytes > 0, "bad range");
+    LG_CUDA(cudaSetDevice(dev_id));
+    cudaError_t e = cudaHostRegister(ptr, (size_t)bytes, cudaHostRegisterDefault);
+    if (e == cudaSuccess || e == cudaErrorHostMemoryAlreadyRegistered) {
+        cudaGetLastError();
+        return LEGION_OK;
+    }
+    const cudaError_t whole = e;
+    cudaGetLastError();
+    const int64_t piece = 1ll << 30;
+    int64_t done = 0;
+    for (; done < bytes; done += piece) {
+        int64_t len = bytes - done < piece ? bytes - done : piece;
+        e = cudaHostRegister((char *)ptr + done, (size_t)len, cudaHostRegisterDefault);
+        if (e != cudaSuccess && e != cudaErrorHostMemoryAlreadyRegistered) break;
+    }
+    cudaGetLastError();
+    if (done >= bytes) return LEGION_OK;
+    for (int64_t u = 0; u < done; u += piece) cudaHostUnregister((char *)ptr + u);
+    cudaGetLastError();
+    set_error("legion_host_register: %lld bytes: %s (%d); in 1 GiB pieces: %s (%d) after %lld bytes", (long long)bytes,
+              cudaGetErrorName(whole), (int)whole, cudaGetErrorName(e), (int)e, (long long)done);
+    return LEGION_E_CUDA;
+}
+
 // EnableP2PAccess (storage/storage_management.cu:9-27) for one pair: lets kernels of `dev_id` read
 // memory of `peer_id` allocated in this process.  Already-enabled is not an error.
 extern "C" int legion_enable_peer_access(int32_t dev_id, int32_t peer_id)

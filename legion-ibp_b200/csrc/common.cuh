@@ -145,6 +145,7 @@ struct LegionCache {
     void *rows;
     int32_t clock;
     const void *host_table;
+    int32_t host_codec;         // codec of the host table's rows (RAW unless legion_cache_set_host_codec)
     unsigned long long *stats;  // 4 counters on the device
 };
 

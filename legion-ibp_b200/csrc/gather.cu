@@ -350,7 +350,74 @@ struct MissParams {
     int64_t n_nodes;
     uint8_t *dst;
     int32_t row_bytes;
+    int32_t host_row_bytes;  // bytes of one row of the host table (compressed host tables: codes + scale, padded)
 };
+
+// The list is complete and consumed: the last CTA to finish empties it for the next batch.
+__device__ __forceinline__ void miss_list_done(const MissParams &p, int *s_last)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = atomicAdd(p.ticket, 1);
+        *s_last = (t == (int)gridDim.x - 1);
+    }
+    __syncthreads();
+    if (*s_last && threadIdx.x == 0) {
+        p.miss_count[0] = 0;
+        *p.ticket = 0;
+    }
+}
+
+// Host table stored as compressed rows (feature_len one-byte codes + fp32 scale): the fetch moves
+// host_row_bytes per row over the host link instead of 4 * feature_len and decodes into the fp32 output row.
+template <int CODEC, int R>
+__global__ void __launch_bounds__(1024) gather_miss_quant_kernel(MissParams p)
+{
+    __shared__ int s_last;
+    const int n = p.miss_count[0];
+    const int lane = threadIdx.x & 31;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    const int2 *list = p.miss_rows;
+    const int f = p.row_bytes >> 2;
+    const int groups = f >> 2;
+    for (int m0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * R; m0 < n; m0 += n_warps * R) {
+        const uint8_t *sp[R];
+        float *dp[R];
+        float scale[R];
+#pragma unroll
+        for (int jj = 0; jj < R; ++jj) {
+            sp[jj] = nullptr;
+            dp[jj] = nullptr;
+            if (m0 + jj < n) {
+                const int2 e = __ldg(&list[m0 + jj]);
+                sp[jj] = p.host + ((int64_t)e.y % p.n_nodes) * (int64_t)p.host_row_bytes;
+                dp[jj] = reinterpret_cast<float *>(p.dst + (int64_t)e.x * p.row_bytes);
+            }
+        }
+#pragma unroll
+        for (int jj = 0; jj < R; ++jj)
+            if (sp[jj] != nullptr) scale[jj] = *reinterpret_cast<const float *>(sp[jj] + f);
+        for (int g0 = 0; g0 < groups; g0 += 32) {
+            const int g = g0 + lane;
+            uint32_t packed[R];
+#pragma unroll
+            for (int jj = 0; jj < R; ++jj)
+                if (sp[jj] != nullptr && g < groups) packed[jj] = *reinterpret_cast<const uint32_t *>(sp[jj] + g * 4);
+#pragma unroll
+            for (int jj = 0; jj < R; ++jj) {
+                if (sp[jj] != nullptr && g < groups) {
+                    float4 o;
+                    o.x = __fmul_rn(decode_code<CODEC>((uint8_t)(packed[jj])), scale[jj]);
+                    o.y = __fmul_rn(decode_code<CODEC>((uint8_t)(packed[jj] >> 8)), scale[jj]);
+                    o.z = __fmul_rn(decode_code<CODEC>((uint8_t)(packed[jj] >> 16)), scale[jj]);
+                    o.w = __fmul_rn(decode_code<CODEC>((uint8_t)(packed[jj] >> 24)), scale[jj]);
+                    __stcs(reinterpret_cast<float4 *>(dp[jj]) + g, o);
+                }
+            }
+        }
+    }
+    miss_list_done(p, &s_last);
+}
 
 template <int R>
 __global__ void __launch_bounds__(1024) gather_miss_kernel(MissParams p)
@@ -712,6 +779,7 @@ int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c)
     mp.n_nodes = c->n_nodes;
     mp.dst = (uint8_t *)p->features[pipe];
     mp.row_bytes = p->row_bytes_out;
+    mp.host_row_bytes = c->host_codec != LEGION_CODEC_RAW ? c->slot_bytes : p->row_bytes_out;
     // 4 rows per warp and pass.  Shapes from 8 to 296 CTAs and 256 to 1024 threads were measured with
     // batches in flight: fewer CTAs slow the fetch itself, none of them keeps co-running kernels from
     // slowing down, and the batch rate stays within 10%; 148 x 256 was the best.
@@ -719,7 +787,9 @@ int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c)
     int cap = g_miss_ctas > 0 ? g_miss_ctas : kMissCtas;
     int threads = g_miss_threads > 0 ? g_miss_threads : kMissThreads;
     int grid = (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
-    gather_miss_kernel<4><<<grid, threads, 0, s>>>(mp);
+    if (c->host_codec == LEGION_CODEC_INT8) gather_miss_quant_kernel<LEGION_CODEC_INT8, 8><<<grid, threads, 0, s>>>(mp);
+    else if (c->host_codec == LEGION_CODEC_E4M3) gather_miss_quant_kernel<LEGION_CODEC_E4M3, 8><<<grid, threads, 0, s>>>(mp);
+    else gather_miss_kernel<4><<<grid, threads, 0, s>>>(mp);
     LG_LAUNCH_CHECK();
     return LEGION_OK;
 }
@@ -880,6 +950,7 @@ extern "C" int legion_gather_rows_noalloc(void *stream, int32_t dev_id, const in
         mp.n_nodes = n_nodes;
         mp.dst = (uint8_t *)out_dev;
         mp.row_bytes = row_bytes;
+        mp.host_row_bytes = row_bytes;
         int64_t m64 = (n_rows + 31) / 32;
         int mgrid = (int)(m64 < 1 ? 1 : (m64 > (int64_t)sms * 2 ? (int64_t)sms * 2 : m64));
         gather_miss_kernel<4><<<mgrid, 256, 0, s>>>(mp);

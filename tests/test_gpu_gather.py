@@ -326,6 +326,81 @@ def test_compressed_cache(oracle_mod, codec, feat_len):
     rig.close()
 
 
+@pytest.mark.parametrize("codec", [L.CODEC_INT8, L.CODEC_E4M3])
+@pytest.mark.parametrize("feat_len,kg", [(128, 1), (100, 1), (256, 1), (128, 2)])
+def test_compressed_host_table(oracle_mod, codec, feat_len, kg):
+    """Host table held as compressed rows: the table encoder matches the host quantiser byte for byte,
+    the cache is filled with copies of those rows, and hits, peer hits, replicas and host-link misses all
+    decode to the host dequantiser's values."""
+    import torch
+    rng = np.random.default_rng(codec * 100 + feat_len)
+    indptr, _ = small_graph(3000, 40000, 9)
+    n = len(indptr) - 1
+    table = rng.standard_normal((n, feat_len)).astype(np.float32)
+    table[5] = 0.0
+    table[6, :2] = (1e-30, 300.0)
+    rq = oracle_mod.quant_row_bytes(feat_len)
+    want_rows = oracle_mod.quant_rows(table, codec)
+    src = torch.from_numpy(table).pin_memory()
+    stored = torch.zeros((n, rq), dtype=torch.uint8).pin_memory()
+    L.quantize_table(0, codec, src, n, feat_len, stored)
+    np.testing.assert_array_equal(stored.numpy(), want_rows)
+    with pytest.raises(L.LegionError, match="feature_len % 4"):
+        L.quantize_table(0, codec, src, n, 3, stored)
+
+    ids_list = rng.integers(0, n, 4000).astype(np.int32)
+    ids_list[:8] = np.arange(8)
+    ids_list[9] = -1
+    ids = torch.from_numpy(ids_list).cuda()
+    lab = torch.zeros_like(ids)
+    cap = n // (3 * kg)
+    order_np = oracle_mod.degree_order(indptr)
+    order = torch.from_numpy(order_np.astype(np.int32)).cuda()
+    feats = L.FeatureStorage(0, n, feat_len * 4, stored)
+    feats.set_split(L.TRAINMODE, ids, lab)
+    caches, pools = [], []
+    for ki in range(kg):
+        c = L.UnifiedCache(0, n, feat_len * 4, cap, kg, ki, codec)
+        c.set_host_codec(codec)
+        c.fill_static(order, stored)
+        caches.append(c)
+        pools.append(L.MemoryPool(0, 4000, [], feat_len * 4, 2))
+    with pytest.raises(L.LegionError, match="same codec"):
+        raw = L.UnifiedCache(0, n, feat_len * 4, cap, 1, 0, L.CODEC_RAW)
+        try:
+            raw.set_host_codec(codec)
+        finally:
+            raw.close()
+    for a in range(kg):
+        for b in range(kg):
+            if a != b:
+                caches[a].set_peer(b, caches[b].partition()[0])
+    if kg > 1:
+        caches[0].add_replicas(order, cap // 2)
+    # every member's partition is a copy of the stored rows
+    for ki in range(kg):
+        p, b = caches[ki].partition()
+        got_part = np.empty(b, np.uint8)
+        L._check(L.lib().legion_copy(got_part.ctypes.data_as(L.C.c_void_p), L.C.c_void_p(p), L.C.c_int64(b), L.C.c_int32(2)))
+        np.testing.assert_array_equal(got_part.reshape(cap, rq), want_rows[order_np[ki:cap * kg:kg]])
+    valid = ids_list >= 0
+    want = oracle_mod.dequant_rows(want_rows[ids_list[valid]], feat_len, codec)
+    for ki in range(kg):
+        pools[ki].set_batch(0, L.TRAINMODE, 0, 0)
+        L.BatchGenerate(None, feats, caches[ki], pools[ki], 4000, 0, 0, 0, L.TRAINMODE, False, 0)
+        L.FeatureCacheLookup(None, caches[ki], pools[ki], 1, 0)
+        L.IOComplete(None, caches[ki], pools[ki], 0, L.TRAINMODE)
+        got = pools[ki].read(L.BUF_FEATURES, 0, 4000 * feat_len * 4, np.uint8).view(np.float32).reshape(4000, feat_len)
+        np.testing.assert_array_equal(got[valid].view(np.uint32), want.view(np.uint32))
+        st = caches[ki].stats()
+        assert st["misses"] > 0 and st["local_hits"] > 0 and (kg == 1 or st["peer_hits"] > 0)
+    for c in caches:
+        c.close()
+    for p_ in pools:
+        p_.close()
+    feats.close()
+
+
 @pytest.mark.parametrize("ways,sets,feat_len", [(8, 64, 128), (4, 100, 32), (32, 7, 128), (1, 50, 4), (16, 33, 384)])
 def test_lru_cache_sequence(oracle_mod, ways, sets, feat_len):
     """Hot-set workload of the reference's stale dynamic-cache smoke test (1000 nodes, 130 hot ids
