@@ -560,7 +560,12 @@ def main():
         roofline_nvlink = {"bound": "nvlink", "kernel": kname, "achieved": nv, "peak": 770.0, "unit": "GB/s",
                            "frac": nv / 770.0, "peak_source": "peer copy measured on this pool, per direction",
                            "peer_rows_per_batch": d["peer_hits"] / args.steps}
-    link_peak = host_link_peak(table)
+    # one rank at a time: the ranks' host links share the host's memory and root ports
+    link_peak = 0.0
+    for k in range(world):
+        if k == rank:
+            link_peak = host_link_peak(table)
+        barrier()
     link_achieved = d["misses"] * host_row_bytes / miss_s / 1e9 if miss_s > 0 else 0.0
     roofline_host = {"bound": "host_link", "kernel": "gather_miss_kernel (zero-copy fetch of missed rows)",
                      "achieved": link_achieved, "peak": link_peak, "unit": "GB/s",
