@@ -60,7 +60,7 @@ CONFIGS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum of gather_vec_kernel per row served from GPU memory, from the
 # profiler capture of the "mid" config summarised in profiles/gather_kernels_mid_config.md
-NCU_DRAM_BYTES_PER_HIT_ROW = 799
+NCU_DRAM_BYTES_PER_HIT_ROW = 811
 
 
 def load_pkg():
@@ -585,19 +585,22 @@ def main():
     max_nodes, max_edges = bounds(cfg["batch"], cfg["fanout"])
     seeds_h = mine.cpu().numpy()
     labels_h = mine_labels.cpu().numpy()
-    ids_o = torch.empty(max_nodes, dtype=torch.int32).pin_memory().numpy()
-    lab_o = np.empty(cfg["batch"], np.int32)
-    src_o = torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy()
-    dst_o = torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy()
+    # one set of page-locked output arrays per batch in flight; the batch itself writes into them
+    outs = [dict(ids=torch.empty(max_nodes, dtype=torch.int32).pin_memory().numpy(),
+                 lab=torch.empty(cfg["batch"], dtype=torch.int32).pin_memory().numpy(),
+                 src=torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy(),
+                 dst=torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy()) for _ in range(2)]
     nc_o, ec_o = np.zeros(16, np.int32), np.zeros(16, np.int32)
     b = cfg["batch"]
 
     def submit(i):
         it = i % n_iters
-        runner.submit_host(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i)
+        o = outs[i % 2]
+        runner.submit_host_to(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i, o["ids"], o["lab"], o["src"],
+                              o["dst"])
 
     def collect():
-        return runner.collect_host(ids_o, lab_o, src_o, dst_o, nc_o, ec_o, None)
+        return runner.collect_host(None, None, None, None, nc_o, ec_o, None)
 
     # two batches in flight: the copies of batch k overlap the device work of batch k+1
     submit(0)
@@ -620,8 +623,8 @@ def main():
     barrier()
     e2e = {"value": args.steps * world / e2e_s, "unit": "batches/s", "h2d_bytes_per_step": 8 * b,
            "d2h_bytes_per_step": d2h // args.steps,
-           "api": "legion_runner_submit_host / legion_runner_collect_host, two batches in flight",
-           "note": "seeds+labels copied in from host memory, ids/labels/edge lists/counters copied out to host "
+           "api": "legion_runner_submit_host_to / legion_runner_collect_host, two batches in flight",
+           "note": "seeds+labels copied in from host memory, ids/labels/edge lists/counters written to page-locked host "
                    "memory every step; gathered rows stay in the device hand-off buffer where the trainer reads "
                    "them; missed rows cross the host link inside the gather"}
 

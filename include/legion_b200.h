@@ -386,6 +386,15 @@ int legion_runner_sync(LegionRunner *r);
  * LEGION_E_STATE otherwise.  Pinned output buffers make the copies asynchronous. */
 int legion_runner_submit_host(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
                               int32_t global_batch_id);
+/* submit with the output buffers named up front: ids, labels and both edge lists of the batch are
+ * written into these page-locked host buffers (cudaHostAlloc / cudaHostRegister, 16-byte aligned, sized
+ * for the pool's limits; NULL skips one) by the batch itself, as soon as its sampling is over and
+ * while its rows are still being gathered.  The matching legion_runner_collect_host only waits and
+ * returns the counters (its array arguments are ignored), so the host never sits between "sizes
+ * known" and "copy issued".  The buffers belong to the batch until that collect returns. */
+int legion_runner_submit_host_to(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                                 int32_t global_batch_id, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
+                                 int32_t *agg_dst_out);
 int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
                                int32_t *agg_dst_out, int32_t node_counter_out[16], int32_t edge_counter_out[16],
                                void *features_out);

@@ -410,6 +410,13 @@ class Runner:
         _check(lib().legion_runner_submit_host(self.h, _ptr(seeds), _ptr(labels), C.c_int32(len(seeds)),
                                                C.c_int32(global_batch_id)))
 
+    def submit_host_to(self, seeds, labels, global_batch_id, ids_out, labels_out, agg_src_out, agg_dst_out):
+        """submit_host with the (page-locked) output arrays named up front: the batch writes ids, labels and
+        edge lists into them itself; the matching collect_host(None, None, None, None, nc, ec) only waits."""
+        _check(lib().legion_runner_submit_host_to(self.h, _ptr(seeds), _ptr(labels), C.c_int32(len(seeds)),
+                                                  C.c_int32(global_batch_id), _ptr(ids_out), _ptr(labels_out),
+                                                  _ptr(agg_src_out), _ptr(agg_dst_out)))
+
     def collect_host(self, ids_out, labels_out, agg_src_out, agg_dst_out, nc_out, ec_out, features_out=None):
         """Wait for the oldest submitted batch and copy it out; returns (n_nodes, n_edges)."""
         _check(lib().legion_runner_collect_host(self.h, _ptr(ids_out), _ptr(labels_out), _ptr(agg_src_out),

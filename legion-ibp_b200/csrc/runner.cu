@@ -55,6 +55,39 @@ struct PipeGraph {
 
 }  // namespace
 
+struct HostOut {
+    int32_t *ids, *labels, *agg_src, *agg_dst;
+};
+
+namespace legion {
+// Block structure of a finished sampling pass, written straight into pinned host memory (zero-copy
+// stores, 16 bytes per thread) with the sizes read from the device counters: no host round trip
+// between "sizes known" and "copy issued", which is what a cudaMemcpy of the exact sizes would need.
+__global__ void export_host_kernel(const int32_t *__restrict__ nc, const int32_t *__restrict__ ec,
+                                   const int32_t *__restrict__ ids, const int32_t *__restrict__ labels,
+                                   const int32_t *__restrict__ agg_src, const int32_t *__restrict__ agg_dst,
+                                   int32_t n_seeds, HostOut out)
+{
+    const int hops = nc[LEGION_INTRABATCH_CON * 3 - 1];
+    const int n_nodes = nc[LEGION_INTRABATCH_CON * 3 + hops];
+    const int n_edges = ec[0] + ec[1];
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+    const int nthr = gridDim.x * blockDim.x;
+    const int32_t *src[4] = { ids, labels, agg_src, agg_dst };
+    int32_t *dst[4] = { out.ids, out.labels, out.agg_src, out.agg_dst };
+    const int cnt[4] = { n_nodes, n_seeds, n_edges, n_edges };
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        if (dst[a] == nullptr) continue;
+        const int n4 = cnt[a] >> 2;  // device arrays and pinned buffers are 16-byte aligned
+        const int4 *s4 = reinterpret_cast<const int4 *>(src[a]);
+        int4 *d4 = reinterpret_cast<int4 *>(dst[a]);
+        for (int i = tid; i < n4; i += nthr) d4[i] = s4[i];
+        for (int i = (n4 << 2) + tid; i < cnt[a]; i += nthr) dst[a][i] = src[a][i];
+    }
+}
+}  // namespace legion
+
 struct LegionRunner {
     int32_t dev_id;
     LegionGraph *graph;
@@ -88,6 +121,10 @@ struct LegionRunner {
     int32_t host_seeds[LEGION_INTERBATCH_CON];
     int host_pending;
     cudaStream_t s_copy;
+    // pinned host buffers that the batch on a pipe exports its block structure into (submit_host_to)
+    HostOut host_out[LEGION_INTERBATCH_CON];
+    bool host_bound[LEGION_INTERBATCH_CON];   // of the submitted batches, oldest first (parallel to host_fifo)
+    cudaEvent_t sampled[LEGION_INTERBATCH_CON], exported[LEGION_INTERBATCH_CON];
 };
 
 using namespace legion;
@@ -134,6 +171,12 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     r->served_us = 0.0;
     r->host_pending = 0;
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_copy, cudaStreamNonBlocking));
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+        LG_CUDA(cudaEventCreateWithFlags(&r->sampled[i], cudaEventDisableTiming));
+        LG_CUDA(cudaEventCreateWithFlags(&r->exported[i], cudaEventDisableTiming));
+        r->host_out[i] = HostOut{ nullptr, nullptr, nullptr, nullptr };
+        r->host_bound[i] = false;
+    }
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_sample, cudaStreamNonBlocking));
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_gather, cudaStreamNonBlocking));
     {
@@ -304,7 +347,7 @@ static int capture_pipe(LegionRunner *r, int pipe, const BatchCtl &v)
 // Enqueues one batch described by `v` on the current pipe.  host_seeds > 0: the seeds and labels
 // wait in the pipe's pinned staging area and are copied in first, and both counter arrays are
 // copied back to it behind the batch.
-static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
+static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, const HostOut *bound = nullptr)
 {
     LegionPool *p = r->pool;
     LegionCache *c = r->cache;
@@ -353,6 +396,17 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
     }
     if (se.b) LG_CUDA(cudaEventRecord(se.b, front));
     if (se.a && se.b) r->sample_ev.push_back(se);
+    if (bound != nullptr) {
+        // ids and edge lists are final once sampling is over: they leave for the host on a stream of
+        // their own while the gather and the host-link fetch of the same batch run
+        LG_CUDA(cudaEventRecord(r->sampled[pipe], front));
+        LG_CUDA(cudaStreamWaitEvent(r->s_copy, r->sampled[pipe], 0));
+        export_host_kernel<<<2 * p->sm_count, 256, 0, r->s_copy>>>(p->node_counter[pipe], p->edge_counter[pipe], p->ids[pipe],
+                                                                  p->labels[pipe], p->agg_src[pipe], p->agg_dst[pipe],
+                                                                  host_seeds, *bound);
+        LG_LAUNCH_CHECK();
+        LG_CUDA(cudaEventRecord(r->exported[pipe], r->s_copy));
+    }
     if (early_sampling && r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
     rc = issue_gather(r, front);
     if (rc != LEGION_OK) return rc;
@@ -365,6 +419,7 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds)
         LG_CUDA(cudaMemcpyAsync(hc, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_miss));
         LG_CUDA(cudaMemcpyAsync(hc + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_miss));
     }
+    if (bound != nullptr) LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->exported[pipe], 0));
     LG_CUDA(cudaEventRecord(r->pipe_done[pipe], r->s_miss));
     if (lru) c->clock += 1;
     r->pipe_busy[pipe] = true;
@@ -403,8 +458,39 @@ extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, i
 // collect waits for the oldest submitted batch and copies its block structure (and, optionally, its
 // gathered rows) out.  Up to `pipes` batches may be submitted before the first collect, so the copies
 // of one batch overlap the sampling and gathering of the next.
+static int submit_host_impl(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                            int32_t global_batch_id, const HostOut *bound);
+
 extern "C" int legion_runner_submit_host(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
                                          int32_t global_batch_id)
+{
+    return submit_host_impl(r, seeds, labels, n_seeds, global_batch_id, nullptr);
+}
+
+static bool device_can_write(const void *p)
+{
+    if (p == nullptr) return true;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return (a.type == cudaMemoryTypeHost || a.type == cudaMemoryTypeManaged) && ((uintptr_t)p & 15) == 0;
+}
+
+extern "C" int legion_runner_submit_host_to(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                                            int32_t global_batch_id, int32_t *ids_out, int32_t *labels_out,
+                                            int32_t *agg_src_out, int32_t *agg_dst_out)
+{
+    LG_ARG(device_can_write(ids_out) && device_can_write(labels_out) && device_can_write(agg_src_out) &&
+               device_can_write(agg_dst_out),
+           "output buffers must be page-locked host memory (cudaHostAlloc / cudaHostRegister), 16-byte aligned");
+    HostOut b{ ids_out, labels_out, agg_src_out, agg_dst_out };
+    return submit_host_impl(r, seeds, labels, n_seeds, global_batch_id, &b);
+}
+
+static int submit_host_impl(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                            int32_t global_batch_id, const HostOut *bound)
 {
     LG_ARG(r != nullptr && seeds != nullptr && labels != nullptr, "NULL pointer");
     LegionPool *p = r->pool;
@@ -419,8 +505,10 @@ extern "C" int legion_runner_submit_host(LegionRunner *r, const int32_t *seeds, 
     if (rc != LEGION_OK) return rc;
     memcpy(p->h_stage[pipe], seeds, sizeof(int32_t) * n_seeds);
     memcpy(p->h_stage[pipe] + p->batch_size, labels, sizeof(int32_t) * n_seeds);
-    rc = enqueue_ctl(r, make_batch_ctl(p, r->cache, p->seed_stage[pipe], p->label_stage[pipe], n_seeds, 0, n_seeds), n_seeds);
+    rc = enqueue_ctl(r, make_batch_ctl(p, r->cache, p->seed_stage[pipe], p->label_stage[pipe], n_seeds, 0, n_seeds), n_seeds,
+                     bound);
     if (rc != LEGION_OK) return rc;
+    r->host_bound[r->host_pending] = bound != nullptr;
     r->host_fifo[r->host_pending] = pipe;
     r->host_seeds[r->host_pending] = n_seeds;
     r->host_pending += 1;
@@ -440,9 +528,11 @@ extern "C" int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int
     LegionPool *p = r->pool;
     const int pipe = r->host_fifo[0];
     const int32_t n_seeds = r->host_seeds[0];
+    const bool bound = r->host_bound[0];
     for (int i = 1; i < r->host_pending; ++i) {
         r->host_fifo[i - 1] = r->host_fifo[i];
         r->host_seeds[i - 1] = r->host_seeds[i];
+        r->host_bound[i - 1] = r->host_bound[i];
     }
     r->host_pending -= 1;
     LG_CUDA(cudaEventSynchronize(r->pipe_done[pipe]));
@@ -453,6 +543,11 @@ extern "C" int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int
     const int64_t n_nodes = hc[LEGION_INTRABATCH_CON * 3 + hops];
     const int64_t n_edges = (int64_t)hc[16] + hc[17];
     cudaStream_t s = r->s_copy;
+    if (bound) {
+        // the batch wrote its block structure into the buffers named at submit time
+        if (features_out == nullptr) return LEGION_OK;
+        ids_out = labels_out = agg_src_out = agg_dst_out = nullptr;
+    }
     if (ids_out) LG_CUDA(cudaMemcpyAsync(ids_out, p->ids[pipe], 4 * n_nodes, cudaMemcpyDeviceToHost, s));
     if (labels_out) LG_CUDA(cudaMemcpyAsync(labels_out, p->labels[pipe], 4 * (int64_t)n_seeds, cudaMemcpyDeviceToHost, s));
     if (agg_src_out) LG_CUDA(cudaMemcpyAsync(agg_src_out, p->agg_src[pipe], 4 * n_edges, cudaMemcpyDeviceToHost, s));
@@ -669,6 +764,7 @@ extern "C" int legion_runner_destroy(LegionRunner *r)
     cudaStreamDestroy(r->s_gather);
     cudaStreamDestroy(r->s_miss);
     cudaStreamDestroy(r->s_copy);
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) { cudaEventDestroy(r->sampled[i]); cudaEventDestroy(r->exported[i]); }
     delete r;
     return LEGION_OK;
 }

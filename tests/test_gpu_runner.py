@@ -199,6 +199,61 @@ def test_submit_collect_host_pipelined(oracle_mod, use_graph):
     r.Finalize()
 
 
+@pytest.mark.parametrize("use_graph", [True, False])
+def test_submit_host_to_writes_pinned_buffers(oracle_mod, use_graph):
+    """Output arrays named at submit time: the batch writes ids, labels and edge lists into the
+    page-locked buffers itself and collect only returns the counters; contents match the replay."""
+    import torch
+    w = _world(oracle_mod, seed=5)
+    pool = w["pool"]
+    r = L.Runner(0, w["g"], w["f"], w["cache"], pool, None)
+    r.set_options(use_graph=use_graph)
+    b = w["batch"]
+
+    def pinned(n):
+        return torch.full((n,), -7, dtype=torch.int32).pin_memory().numpy()
+    outs = [dict(ids=pinned(pool.max_nodes), lab=pinned(b), src=pinned(pool.max_edges), dst=pinned(pool.max_edges))
+            for _ in range(2)]
+    nc = np.zeros(16, np.int32); ec = np.zeros(16, np.int32)
+
+    def submit(it):
+        o = outs[it % 2]
+        r.submit_host_to(w["train"][it * b:(it + 1) * b], w["labels"][it * b:(it + 1) * b], 30 + it, o["ids"], o["lab"],
+                         o["src"], o["dst"])
+
+    def collect_and_check(it):
+        n_nodes, n_edges = r.collect_host(None, None, None, None, nc, ec, None)
+        o = outs[it % 2]
+        ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], b, it, w["fanout"], 30 + it, 99)
+        assert n_nodes == len(ref["ids"]) and n_edges == len(ref["agg_src"])
+        np.testing.assert_array_equal(nc, ref["node_counter"])
+        np.testing.assert_array_equal(ec, ref["edge_counter"])
+        np.testing.assert_array_equal(o["ids"][:n_nodes], ref["ids"])
+        np.testing.assert_array_equal(o["src"][:n_edges], ref["agg_src"])
+        np.testing.assert_array_equal(o["dst"][:n_edges], ref["agg_dst"])
+        np.testing.assert_array_equal(o["lab"][:b], ref["labels"])
+        assert o["ids"][n_nodes] == -7 or n_nodes == len(o["ids"])      # nothing past the end
+        # the gathered rows stay in the device hand-off buffer of the batch's pipe
+        feat = pool.read(L.BUF_FEATURES, it % 2, n_nodes * w["table"].shape[1], np.float32)
+        np.testing.assert_array_equal(feat.reshape(n_nodes, -1), w["table"][ref["ids"]])
+        for a in o.values():
+            a[:] = -7
+
+    submit(0)
+    for it in range(1, 5):
+        submit(it)
+        collect_and_check(it - 1)
+    collect_and_check(4)
+    # a NULL array is skipped; pageable memory is refused
+    o = outs[1]
+    r.submit_host_to(w["train"][:b], w["labels"][:b], 30, o["ids"], None, None, o["dst"])
+    r.collect_host(None, None, None, None, nc, ec, None)
+    assert (o["src"] == -7).all() and (o["lab"] == -7).all() and o["ids"][0] == w["train"][0]
+    with pytest.raises(L.LegionError, match="page-locked"):
+        r.submit_host_to(w["train"][:b], w["labels"][:b], 30, np.empty(pool.max_nodes, np.int32), None, None, None)
+    r.Finalize()
+
+
 CONSUMER = r'''
 import ctypes as C, sys, os, mmap, numpy as np
 sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
