@@ -164,7 +164,11 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
     const int64_t pad_nodes = round_up(nodes, kTile) + kTile;
     const int64_t pad_edges = round_up(edges > 0 ? edges : 1, kTile) + kTile;
     const int64_t pad_hop_edges = round_up(max_hop_edges > 0 ? max_hop_edges : 1, kTile) + kTile;
-    const int64_t tiles = max_inputs / kTile + 2 + max_hop_edges / kTile + 2;
+    // node tiles: 1024 inputs each, except the seed hop, which may count in 256-seed tiles
+    int64_t input_tiles = max_inputs / kTile + 2;
+    if (batch_size / 256 + 2 > input_tiles) input_tiles = batch_size / 256 + 2;
+    p->input_tiles = input_tiles;
+    const int64_t tiles = input_tiles + max_hop_edges / kTile + 2;
 
     cudaError_t e = cudaSuccess;
     for (int i = 0; i < pipes && e == cudaSuccess; ++i) {

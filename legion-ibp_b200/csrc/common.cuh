@@ -156,6 +156,7 @@ struct LegionPool {
     int32_t row_bytes_out;
     int32_t pipes;
     int64_t max_nodes, max_edges, max_hop_edges, max_inputs;
+    int64_t input_tiles;  // entries of tile_sum / tile_off reserved for the counting kernels (edge tiles follow)
     int64_t feat_rows;
     // per pipe outputs
     int32_t *ids[LEGION_INTERBATCH_CON];

@@ -247,23 +247,26 @@ hop_count_kernel(const int64_t *__restrict__ indptr, int32_t *ids, int32_t fanou
                  NodeRec *rec, int32_t *tile_sum, int32_t *tile_off, int32_t *ctl, int64_t max_edges,
                  const BatchCtl *__restrict__ b, int32_t *labels, MapSlot *map, uint32_t mask, int32_t *nc, int32_t *ec)
 {
+    // the seeds are few (one batch): one item per thread and 256-node tiles give that launch 4 x the CTAs
+    constexpr int IPT = FIRST ? 1 : 4;
+    constexpr int TILE = kScanThreads * IPT;
     __shared__ int smem[kScanThreads / 32];
     __shared__ int s_flag;
     const int n = FIRST ? b->size : ctl[CTL_N_NODES];
-    const int n_tiles = (n + kTile - 1) / kTile;
+    const int n_tiles = (n + TILE - 1) / TILE;
     if (FIRST && blockIdx.x == 0 && threadIdx.x == 0) {
         counter_update(nc, ec, 0, n, b->hop_num);
         ctl[CTL_N_NODES] = n;
         ctl[CTL_E_TOTAL] = 0;
     }
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int base = tile * kTile + threadIdx.x * 4;
+        const int base = tile * TILE + threadIdx.x * IPT;
         int32_t v[4];
         if (FIRST) {
             const int32_t total_cap = b->total_cap;
             const int64_t first = b->first;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < IPT; ++j) {
                 v[j] = -1;
                 const int idx = base + j;
                 if (idx < n) {
@@ -285,7 +288,7 @@ hop_count_kernel(const int64_t *__restrict__ indptr, int32_t *ids, int32_t fanou
         int64_t start[4];
         int32_t deg[4], cnt[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < IPT; ++j) {
             start[j] = 0; deg[j] = 0; cnt[j] = 0;
             if (base + j < n && v[j] >= 0) {
                 int64_t s = indptr[v[j]];
@@ -295,11 +298,13 @@ hop_count_kernel(const int64_t *__restrict__ indptr, int32_t *ids, int32_t fanou
                 cnt[j] = min(deg[j], fanout);
             }
         }
-        int tsum = cnt[0] + cnt[1] + cnt[2] + cnt[3];
+        int tsum = 0;
+#pragma unroll
+        for (int j = 0; j < IPT; ++j) tsum += cnt[j];
         int total;
         int ex = block_excl_scan(tsum, &total, smem);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < IPT; ++j) {
             if (base + j < n) {
                 NodeRec r;
                 r.start = start[j];
@@ -325,7 +330,7 @@ __global__ void __launch_bounds__(256)
 hop_sample_kernel(const int32_t *__restrict__ indices, const NodeRec *__restrict__ rec,
                   const int32_t *__restrict__ tile_off, int32_t fanout, uint32_t hop,
                   const BatchCtl *__restrict__ b, int32_t *src_global, int32_t *agg_dst,
-                  int32_t *eslot, MapSlot *map, uint32_t mask, int32_t *ctl)
+                  int32_t *eslot, MapSlot *map, uint32_t mask, int32_t *ctl, int tile_shift)
 {
     if (ctl[CTL_ERROR] != DERR_NONE) return;
     const uint32_t batch_id = b->global_batch, k0 = b->k0, k1 = b->k1;
@@ -340,7 +345,7 @@ hop_sample_kernel(const int32_t *__restrict__ indices, const NodeRec *__restrict
         NodeRec r = *reinterpret_cast<NodeRec *>(&raw);
         const uint32_t deg = (uint32_t)r.deg;
         if (deg == 0) continue;
-        const int eh0 = __ldg(&tile_off[i >> 10]) + r.loff;
+        const int eh0 = __ldg(&tile_off[i >> tile_shift]) + r.loff;  // tile of the counting kernel that ran before
         int out_slot = -1;   // slot of this lane's first edge, second edge in out_slot2
         int out_slot2 = -1;
         int64_t pos = 0, pos2 = 0;
@@ -535,7 +540,7 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
     int32_t *ctl = p->ctl[pipe];
     if (seeds_pending) {
         LG_ARG(hop == 0, "only the first hop can take the seed slice");
-        hop_count_kernel<true><<<grid_for(inputs, kTile, cap), kScanThreads, 0, s>>>(
+        hop_count_kernel<true><<<grid_for(inputs, kScanThreads, cap), kScanThreads, 0, s>>>(
             g->indptr, p->ids[pipe], fanout, p->node_rec[pipe], p->tile_sum[pipe], p->tile_off[pipe], ctl, p->max_edges,
             p->bctl[pipe], p->labels[pipe], p->map[pipe], p->map_mask, p->node_counter[pipe], p->edge_counter[pipe]);
     } else {
@@ -546,10 +551,11 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
     LG_LAUNCH_CHECK();
     hop_sample_kernel<<<grid_for(inputs, 8, cap), 256, 0, s>>>(
         g->indices, p->node_rec[pipe], p->tile_off[pipe], fanout, (uint32_t)hop, p->bctl[pipe], p->src_global[pipe],
-        p->agg_dst[pipe], p->eslot[pipe], p->map[pipe], p->map_mask, ctl);
+        p->agg_dst[pipe], p->eslot[pipe], p->map[pipe], p->map_mask, ctl, seeds_pending ? 8 : 10);
     LG_LAUNCH_CHECK();
-    int32_t *tile_sum2 = p->tile_sum[pipe] + p->max_inputs / kTile + 2;
-    int32_t *tile_off2 = p->tile_off[pipe] + p->max_inputs / kTile + 2;
+    static_assert(kScanThreads == 256 && kTile == 1024, "tile shifts above assume 256-thread scans over 1024-item tiles");
+    int32_t *tile_sum2 = p->tile_sum[pipe] + p->input_tiles;
+    int32_t *tile_off2 = p->tile_off[pipe] + p->input_tiles;
     hop_flag_kernel<<<grid_for(edges, kTile, cap), kScanThreads, 0, s>>>(p->eslot[pipe], p->map[pipe], p->erank[pipe],
                                                                          tile_sum2, tile_off2, ctl, p->max_nodes);
     LG_LAUNCH_CHECK();
