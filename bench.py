@@ -224,6 +224,11 @@ def zipf_batches(n_nodes, batch, n_batches, s, world=1, rank=0):
     return torch.cat(out)
 
 
+def runner_counts(nc, ec):
+    hops = int(nc[8])
+    return int(nc[9 + hops]), int(ec[0] + ec[1])
+
+
 def bounds(batch, fanout):
     nodes, edges = batch, 0
     for k in fanout:
@@ -316,6 +321,10 @@ def main():
     ap.add_argument("--no-replicas", action="store_true",
                     help="N > 1: stripe the whole per-GPU budget over the clique (the reference's placement) instead "
                          "of planning private copies of the hottest peer rows")
+    ap.add_argument("--e2e-outputs", default="bound", choices=["bound", "copy", "none"],
+                    help="e2e leg: block structure written by the batch into page-locked arrays named at submit "
+                         "time (default), copied out by collect after the batch (two batches in flight), or not "
+                         "moved at all (diagnostic)")
     ap.add_argument("--tunable", action="append", default=[], metavar="NAME=VALUE",
                     help="launch-shape knob passed to legion_set_tunable (measurement sweeps)")
     ap.add_argument("--profile-only", action="store_true",
@@ -589,41 +598,65 @@ def main():
     outs = [dict(ids=torch.empty(max_nodes, dtype=torch.int32).pin_memory().numpy(),
                  lab=torch.empty(cfg["batch"], dtype=torch.int32).pin_memory().numpy(),
                  src=torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy(),
-                 dst=torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy()) for _ in range(2)]
+                 dst=torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy()) for _ in range(3)]
     nc_o, ec_o = np.zeros(16, np.int32), np.zeros(16, np.int32)
     b = cfg["batch"]
 
+    mode = args.e2e_outputs
+
     def submit(i):
         it = i % n_iters
-        o = outs[i % 2]
-        runner.submit_host_to(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i, o["ids"], o["lab"], o["src"],
-                              o["dst"])
+        o = outs[i % 3]
+        if mode == "bound":
+            runner.submit_host_to(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i, o["ids"], o["lab"],
+                                  o["src"], o["dst"])
+        else:
+            runner.submit_host(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i)
 
     def collect():
+        if mode == "copy":
+            o = outs[0]
+            return runner.collect_host(o["ids"], o["lab"], o["src"], o["dst"], nc_o, ec_o, None)
         return runner.collect_host(None, None, None, None, nc_o, ec_o, None)
 
-    # two batches in flight: the copies of batch k overlap the device work of batch k+1
-    submit(0)
-    for i in range(1, 4):
+    # two batches in flight plus, for static caches, a third that samples ahead (the API's limit); a
+    # batch counts as done when its collect returns
+    depth = 3 if (mode == "bound" and not lru_ways) else 2
+    pipe0 = runner.current_pipe()
+    for i in range(depth):
         submit(i)
+    for i in range(depth, depth + 4):
         collect()
-    collect()
+        submit(i)
+    for _ in range(depth):
+        collect()
+    # the exported block structure of the last batch is what the device buffers hold
+    last = depth + 3
+    nn_chk, ne_chk = runner_counts(nc_o, ec_o)
+    chk_pipe = (pipe0 + last) % 2
+    if mode != "none":
+        o_chk = outs[last % 3] if mode == "bound" else outs[0]
+        assert np.array_equal(o_chk["ids"][:nn_chk], pool.read(L.BUF_IDS, chk_pipe, nn_chk, np.int32))
+        assert np.array_equal(o_chk["src"][:ne_chk], pool.read(L.BUF_AGG_SRC, chk_pipe, ne_chk, np.int32))
     barrier()
     t0 = time.perf_counter()
     d2h = 0
-    submit(100)
-    for i in range(1, args.steps):
+    for i in range(depth):
         submit(100 + i)
+    for i in range(depth, args.steps):
         nn, ne = collect()
         d2h += 4 * nn + 8 * ne + 4 * b + 128
-    nn, ne = collect()
-    d2h += 4 * nn + 8 * ne + 4 * b + 128
+        submit(100 + i)
+    for _ in range(min(depth, args.steps)):
+        nn, ne = collect()
+        d2h += 4 * nn + 8 * ne + 4 * b + 128
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
     e2e = {"value": args.steps * world / e2e_s, "unit": "batches/s", "h2d_bytes_per_step": 8 * b,
            "d2h_bytes_per_step": d2h // args.steps,
-           "api": "legion_runner_submit_host_to / legion_runner_collect_host, two batches in flight",
+           "api": "legion_runner_submit_host%s / legion_runner_collect_host, %d batches in flight, outputs: %s" % (
+               "_to" if mode == "bound" else "", depth, mode),
            "note": "seeds+labels copied in from host memory, ids/labels/edge lists/counters written to page-locked host "
                    "memory every step; gathered rows stay in the device hand-off buffer where the trainer reads "
                    "them; missed rows cross the host link inside the gather"}

@@ -387,11 +387,19 @@ int legion_runner_sync(LegionRunner *r);
 int legion_runner_submit_host(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
                               int32_t global_batch_id);
 /* submit with the output buffers named up front: ids, labels and both edge lists of the batch are
- * written into these page-locked host buffers (cudaHostAlloc / cudaHostRegister, 16-byte aligned, sized
- * for the pool's limits; NULL skips one) by the batch itself, as soon as its sampling is over and
- * while its rows are still being gathered.  The matching legion_runner_collect_host only waits and
- * returns the counters (its array arguments are ignored), so the host never sits between "sizes
- * known" and "copy issued".  The buffers belong to the batch until that collect returns. */
+ * copied into these page-locked host buffers (cudaHostAlloc / cudaHostRegister, 16-byte aligned, sized
+ * for the pool's limits; NULL skips one) as soon as the batch's sampling is over and while its rows are
+ * still being gathered.  The sizes are only on the device at that point, so the copies are issued with
+ * the size of the largest batch seen so far plus 1/16 (elements past the batch's own counts are
+ * scratch), and whatever a larger batch leaves behind is moved when it is collected.  The matching
+ * legion_runner_collect_host only waits and returns the counters (its array arguments are ignored), so
+ * the host never sits between "sizes known" and "copy issued".  The buffers belong to the batch until
+ * that collect returns.
+ * One batch more than the pool has pipes may be submitted this way (static caches): it samples and
+ * exports at once, behind the export of the uncollected batch that holds its pipe, and gathers as soon
+ * as that batch has been collected and the caller comes back: the rows of a collected batch stay in
+ * the pipe's feature buffer until the next call on this runner.  The batches in flight then need
+ * pipes + 1 sets of output arrays. */
 int legion_runner_submit_host_to(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
                                  int32_t global_batch_id, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
                                  int32_t *agg_dst_out);

@@ -202,7 +202,7 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
         if (e == cudaSuccess) e = dmalloc(&p->seed_stage[i], batch_size);
         if (e == cudaSuccess) e = dmalloc(&p->label_stage[i], batch_size);
         if (e == cudaSuccess)
-            e = cudaMallocHost(reinterpret_cast<void **>(&p->h_stage[i]), sizeof(int32_t) * (2 * (size_t)batch_size + 32));
+            e = cudaMallocHost(reinterpret_cast<void **>(&p->h_stage[i]), sizeof(int32_t) * (2 * (size_t)batch_size + 64));
     }
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {

@@ -59,35 +59,6 @@ struct HostOut {
     int32_t *ids, *labels, *agg_src, *agg_dst;
 };
 
-namespace legion {
-// Block structure of a finished sampling pass, written straight into pinned host memory (zero-copy
-// stores, 16 bytes per thread) with the sizes read from the device counters: no host round trip
-// between "sizes known" and "copy issued", which is what a cudaMemcpy of the exact sizes would need.
-__global__ void export_host_kernel(const int32_t *__restrict__ nc, const int32_t *__restrict__ ec,
-                                   const int32_t *__restrict__ ids, const int32_t *__restrict__ labels,
-                                   const int32_t *__restrict__ agg_src, const int32_t *__restrict__ agg_dst,
-                                   int32_t n_seeds, HostOut out)
-{
-    const int hops = nc[LEGION_INTRABATCH_CON * 3 - 1];
-    const int n_nodes = nc[LEGION_INTRABATCH_CON * 3 + hops];
-    const int n_edges = ec[0] + ec[1];
-    const int tid = blockIdx.x * blockDim.x + threadIdx.x;
-    const int nthr = gridDim.x * blockDim.x;
-    const int32_t *src[4] = { ids, labels, agg_src, agg_dst };
-    int32_t *dst[4] = { out.ids, out.labels, out.agg_src, out.agg_dst };
-    const int cnt[4] = { n_nodes, n_seeds, n_edges, n_edges };
-#pragma unroll
-    for (int a = 0; a < 4; ++a) {
-        if (dst[a] == nullptr) continue;
-        const int n4 = cnt[a] >> 2;  // device arrays and pinned buffers are 16-byte aligned
-        const int4 *s4 = reinterpret_cast<const int4 *>(src[a]);
-        int4 *d4 = reinterpret_cast<int4 *>(dst[a]);
-        for (int i = tid; i < n4; i += nthr) d4[i] = s4[i];
-        for (int i = (n4 << 2) + tid; i < cnt[a]; i += nthr) dst[a][i] = src[a][i];
-    }
-}
-}  // namespace legion
-
 struct LegionRunner {
     int32_t dev_id;
     LegionGraph *graph;
@@ -117,13 +88,18 @@ struct LegionRunner {
     long long served;
     double served_us;
     // host-buffer batches submitted and not yet collected (oldest first)
-    int host_fifo[LEGION_INTERBATCH_CON];
-    int32_t host_seeds[LEGION_INTERBATCH_CON];
+    int host_fifo[LEGION_INTERBATCH_CON + 1];
+    int32_t host_seeds[LEGION_INTERBATCH_CON + 1];
     int host_pending;
     cudaStream_t s_copy;
     // pinned host buffers that the batch on a pipe exports its block structure into (submit_host_to)
-    HostOut host_out[LEGION_INTERBATCH_CON];
-    bool host_bound[LEGION_INTERBATCH_CON];   // of the submitted batches, oldest first (parallel to host_fifo)
+    HostOut host_out[LEGION_INTERBATCH_CON + 1];   // of the submitted batches, oldest first (parallel to host_fifo)
+    int64_t host_spec_nodes[LEGION_INTERBATCH_CON + 1], host_spec_edges[LEGION_INTERBATCH_CON + 1];  // elements copied ahead
+    bool host_exported[LEGION_INTERBATCH_CON + 1];  // every element of the block structure is on the host
+    int64_t spec_nodes, spec_edges;                 // sizes to copy ahead: the largest batch seen so far plus a margin
+    bool host_bound[LEGION_INTERBATCH_CON + 1];  // of the submitted batches, oldest first (parallel to host_fifo)
+    bool host_deferred;                          // the newest submitted batch still lacks its back half
+    bool host_released;                          // ... and the batch that held its pipe has been collected
     cudaEvent_t sampled[LEGION_INTERBATCH_CON], exported[LEGION_INTERBATCH_CON];
 };
 
@@ -174,9 +150,11 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
         LG_CUDA(cudaEventCreateWithFlags(&r->sampled[i], cudaEventDisableTiming));
         LG_CUDA(cudaEventCreateWithFlags(&r->exported[i], cudaEventDisableTiming));
-        r->host_out[i] = HostOut{ nullptr, nullptr, nullptr, nullptr };
         r->host_bound[i] = false;
     }
+    r->host_deferred = false;
+    r->host_released = false;
+    r->spec_nodes = r->spec_edges = 0;
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_sample, cudaStreamNonBlocking));
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_gather, cudaStreamNonBlocking));
     {
@@ -347,7 +325,13 @@ static int capture_pipe(LegionRunner *r, int pipe, const BatchCtl &v)
 // Enqueues one batch described by `v` on the current pipe.  host_seeds > 0: the seeds and labels
 // wait in the pipe's pinned staging area and are copied in first, and both counter arrays are
 // copied back to it behind the batch.
-static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, const HostOut *bound = nullptr)
+// A batch is issued in two halves.  The front half (seed copy, sampling, export of the block structure
+// to bound host buffers) only needs the pipe's sampling scratch and its id / edge buffers; the back half
+// (lookup + gather, host-link fetch, cache maintenance, counters to the host) needs the pipe's feature
+// buffer.  enqueue_ctl issues both at once.  A host-buffer batch with bound outputs may be submitted
+// while both pipes still hold uncollected batches: its front half runs at once, its back half is issued
+// when the older batch on its pipe has been collected (its features released).
+static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, const HostOut *bound, bool pipe_is_held)
 {
     LegionPool *p = r->pool;
     LegionCache *c = r->cache;
@@ -362,9 +346,15 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
     }
     // An LRU cache has to see the previous batch's insertions before anything of this batch runs.
     // Otherwise sampling only rewrites buffers that the last fetch on this pipe does not touch, so it
-    // starts at once; the wait for that fetch comes before the gather, below.
+    // starts at once; the wait for that fetch comes before the gather (issue_back).
     const bool early_sampling = !lru && host_seeds == 0;
-    if (!early_sampling && r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
+    if (pipe_is_held) {
+        // the older batch on this pipe is still uncollected: its ids and edge lists have left for the
+        // host once its export is over, which is all that this half overwrites
+        LG_CUDA(cudaStreamWaitEvent(front, r->exported[pipe], 0));
+    } else if (!early_sampling && r->pipe_busy[pipe]) {
+        LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
+    }
     if (lru && r->last_pipe >= 0 && r->last_pipe != pipe && r->pipe_busy[r->last_pipe])
         LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[r->last_pipe], 0));
     if (host_seeds > 0) {
@@ -398,35 +388,68 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
     if (se.a && se.b) r->sample_ev.push_back(se);
     if (bound != nullptr) {
         // ids and edge lists are final once sampling is over: they leave for the host on a stream of
-        // their own while the gather and the host-link fetch of the same batch run
+        // their own while the gather and the host-link fetch of the same batch run.  Their sizes are only
+        // on the device at this point, so the copies take the size of the largest batch seen so far plus
+        // a margin; finish_export moves what a larger batch leaves behind.
+        int32_t *early = p->h_stage[pipe] + 2 * (size_t)p->batch_size + 32;
         LG_CUDA(cudaEventRecord(r->sampled[pipe], front));
         LG_CUDA(cudaStreamWaitEvent(r->s_copy, r->sampled[pipe], 0));
-        export_host_kernel<<<2 * p->sm_count, 256, 0, r->s_copy>>>(p->node_counter[pipe], p->edge_counter[pipe], p->ids[pipe],
-                                                                  p->labels[pipe], p->agg_src[pipe], p->agg_dst[pipe],
-                                                                  host_seeds, *bound);
-        LG_LAUNCH_CHECK();
+        LG_CUDA(cudaMemcpyAsync(early, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_copy));
+        LG_CUDA(cudaMemcpyAsync(early + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_copy));
+        if (bound->labels)
+            LG_CUDA(cudaMemcpyAsync(bound->labels, p->labels[pipe], 4 * (size_t)host_seeds, cudaMemcpyDeviceToHost, r->s_copy));
+        if (bound->ids && r->spec_nodes > 0)
+            LG_CUDA(cudaMemcpyAsync(bound->ids, p->ids[pipe], 4 * (size_t)r->spec_nodes, cudaMemcpyDeviceToHost, r->s_copy));
+        if (bound->agg_src && r->spec_edges > 0)
+            LG_CUDA(cudaMemcpyAsync(bound->agg_src, p->agg_src[pipe], 4 * (size_t)r->spec_edges, cudaMemcpyDeviceToHost, r->s_copy));
+        if (bound->agg_dst && r->spec_edges > 0)
+            LG_CUDA(cudaMemcpyAsync(bound->agg_dst, p->agg_dst[pipe], 4 * (size_t)r->spec_edges, cudaMemcpyDeviceToHost, r->s_copy));
         LG_CUDA(cudaEventRecord(r->exported[pipe], r->s_copy));
     }
-    if (early_sampling && r->pipe_busy[pipe]) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
+    r->current_pipe = (pipe + 1) % p->pipes;  // engine/server.cu:398-399
+    return LEGION_OK;
+}
+
+// pipe_was_synced: the host has already waited for the older batch on this pipe (collect), so no
+// device-side wait for it is needed.
+static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound, bool pipe_was_synced)
+{
+    LegionPool *p = r->pool;
+    LegionCache *c = r->cache;
+    int rc;
+    const bool lru = c != nullptr && c->kind == 1;
+    cudaStream_t front = r->use_graph ? r->s_launch[pipe] : r->s_sample;
+    const bool early_sampling = !lru && host_seeds == 0;
+    p->pipe = pipe;
+    if (early_sampling && r->pipe_busy[pipe] && !pipe_was_synced) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
     rc = issue_gather(r, front);
     if (rc != LEGION_OK) return rc;
+    if (host_seeds > 0) {
+        // the counters are final once the lookup has left its snapshot words; copied on this stream so
+        // that the next sampling on this pipe, which resets them, is ordered behind the copy
+        int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
+        LG_CUDA(cudaMemcpyAsync(hc, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, front));
+        LG_CUDA(cudaMemcpyAsync(hc + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, front));
+    }
     LG_CUDA(cudaEventRecord(r->hit_done[pipe], front));
     LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->hit_done[pipe], 0));
     rc = issue_back(r);
     if (rc != LEGION_OK) return rc;
-    if (host_seeds > 0) {
-        int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
-        LG_CUDA(cudaMemcpyAsync(hc, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_miss));
-        LG_CUDA(cudaMemcpyAsync(hc + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_miss));
-    }
-    if (bound != nullptr) LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->exported[pipe], 0));
+    if (bound) LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->exported[pipe], 0));
     LG_CUDA(cudaEventRecord(r->pipe_done[pipe], r->s_miss));
     if (lru) c->clock += 1;
     r->pipe_busy[pipe] = true;
     r->last_pipe = pipe;
     r->window_batches += 1;
-    r->current_pipe = (pipe + 1) % p->pipes;  // engine/server.cu:398-399
     return LEGION_OK;
+}
+
+static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, const HostOut *bound = nullptr)
+{
+    const int pipe = r->current_pipe;
+    int rc = issue_front(r, v, host_seeds, bound, false);
+    if (rc != LEGION_OK) return rc;
+    return issue_rest(r, pipe, host_seeds, bound != nullptr, false);
 }
 
 extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, int32_t mode, int32_t local_batch_id)
@@ -458,6 +481,56 @@ extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, i
 // collect waits for the oldest submitted batch and copies its block structure (and, optionally, its
 // gathered rows) out.  Up to `pipes` batches may be submitted before the first collect, so the copies
 // of one batch overlap the sampling and gathering of the next.
+// Completes the export of the i-th submitted batch: waits for its copies, reads its sizes and moves
+// whatever lies beyond the sizes that were copied ahead.  Must run before the batch's id / edge buffers
+// are reused.  Also raises the sizes that later batches copy ahead.
+static int finish_export(LegionRunner *r, int i)
+{
+    if (!r->host_bound[i] || r->host_exported[i]) return LEGION_OK;
+    LegionPool *p = r->pool;
+    const int pipe = r->host_fifo[i];
+    LG_CUDA(cudaEventSynchronize(r->exported[pipe]));
+    const int32_t *early = p->h_stage[pipe] + 2 * (size_t)p->batch_size + 32;
+    const int hops = early[LEGION_INTRABATCH_CON * 3 - 1];
+    const int64_t n_nodes = early[LEGION_INTRABATCH_CON * 3 + hops];
+    const int64_t n_edges = (int64_t)early[16] + early[17];
+    const HostOut &o = r->host_out[i];
+    const int64_t sn = r->host_spec_nodes[i], se = r->host_spec_edges[i];
+    bool tail = false;
+    if (o.ids && n_nodes > sn) {
+        LG_CUDA(cudaMemcpyAsync(o.ids + sn, p->ids[pipe] + sn, 4 * (size_t)(n_nodes - sn), cudaMemcpyDeviceToHost, r->s_copy));
+        tail = true;
+    }
+    if (o.agg_src && n_edges > se) {
+        LG_CUDA(cudaMemcpyAsync(o.agg_src + se, p->agg_src[pipe] + se, 4 * (size_t)(n_edges - se), cudaMemcpyDeviceToHost, r->s_copy));
+        tail = true;
+    }
+    if (o.agg_dst && n_edges > se) {
+        LG_CUDA(cudaMemcpyAsync(o.agg_dst + se, p->agg_dst[pipe] + se, 4 * (size_t)(n_edges - se), cudaMemcpyDeviceToHost, r->s_copy));
+        tail = true;
+    }
+    if (tail) LG_CUDA(cudaStreamSynchronize(r->s_copy));
+    r->host_exported[i] = true;
+    // batches of one workload differ by a few percent: 1/16 of headroom, rounded up to 256 elements
+    int64_t want_n = (n_nodes + n_nodes / 16 + 255) / 256 * 256, want_e = (n_edges + n_edges / 16 + 255) / 256 * 256;
+    if (want_n > p->max_nodes) want_n = p->max_nodes;
+    if (want_e > p->max_edges) want_e = p->max_edges;
+    if (want_n > r->spec_nodes) r->spec_nodes = want_n;
+    if (want_e > r->spec_edges) r->spec_edges = want_e;
+    return LEGION_OK;
+}
+
+// Back half of the batch that sampled ahead, once the batch that held its pipe has been collected and
+// the caller has come back (its rows in the pipe's feature buffer are given up by that next call).
+static int flush_deferred(LegionRunner *r)
+{
+    if (!r->host_deferred || !r->host_released) return LEGION_OK;
+    r->host_deferred = false;
+    r->host_released = false;
+    const int last = r->host_pending - 1;
+    return issue_rest(r, r->host_fifo[last], r->host_seeds[last], true, true);
+}
+
 static int submit_host_impl(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
                             int32_t global_batch_id, const HostOut *bound);
 
@@ -495,7 +568,17 @@ static int submit_host_impl(LegionRunner *r, const int32_t *seeds, const int32_t
     LG_ARG(r != nullptr && seeds != nullptr && labels != nullptr, "NULL pointer");
     LegionPool *p = r->pool;
     LG_ARG(n_seeds > 0 && n_seeds <= p->batch_size, "n_seeds above the pool's batch size");
-    if (r->host_pending >= p->pipes) {
+    LG_CUDA(cudaSetDevice(r->dev_id));
+    {
+        int frc = flush_deferred(r);
+        if (frc != LEGION_OK) return frc;
+    }
+    const bool lru = r->cache != nullptr && r->cache->kind == 1;
+    // one batch beyond the pipes may start its sampling early when its own and the held batch's block
+    // structure go to bound host buffers (the held batch's ids and edge lists are then on the host already)
+    const bool extra = r->host_pending == p->pipes && bound != nullptr && !r->host_deferred && !lru &&
+                       r->host_bound[0] && r->host_fifo[0] == r->current_pipe;
+    if (r->host_pending >= p->pipes && !extra) {
         set_error("legion_runner_submit_host: %d batches are in flight, collect one first", r->host_pending);
         return LEGION_E_STATE;
     }
@@ -503,12 +586,29 @@ static int submit_host_impl(LegionRunner *r, const int32_t *seeds, const int32_t
     const int pipe = r->current_pipe;
     int rc = legion_pool_set_batch(p, 0, LEGION_TRAINMODE, pipe, (uint32_t)global_batch_id);
     if (rc != LEGION_OK) return rc;
+    if (extra) {
+        // the held batch's ids and edge lists must be on the host in full before this batch's sampling
+        // overwrites them; the staging area of this pipe still holds the held batch's counters (read by
+        // its collect), the seed words were consumed when that batch started
+        rc = finish_export(r, 0);
+        if (rc != LEGION_OK) return rc;
+    }
     memcpy(p->h_stage[pipe], seeds, sizeof(int32_t) * n_seeds);
     memcpy(p->h_stage[pipe] + p->batch_size, labels, sizeof(int32_t) * n_seeds);
-    rc = enqueue_ctl(r, make_batch_ctl(p, r->cache, p->seed_stage[pipe], p->label_stage[pipe], n_seeds, 0, n_seeds), n_seeds,
-                     bound);
+    const BatchCtl v = make_batch_ctl(p, r->cache, p->seed_stage[pipe], p->label_stage[pipe], n_seeds, 0, n_seeds);
+    const int64_t spec_n = r->spec_nodes, spec_e = r->spec_edges;  // what issue_front copies ahead
+    if (extra) {
+        rc = issue_front(r, v, n_seeds, bound, true);
+        if (rc == LEGION_OK) r->host_deferred = true;
+    } else {
+        rc = enqueue_ctl(r, v, n_seeds, bound);
+    }
     if (rc != LEGION_OK) return rc;
     r->host_bound[r->host_pending] = bound != nullptr;
+    r->host_out[r->host_pending] = bound != nullptr ? *bound : HostOut{ nullptr, nullptr, nullptr, nullptr };
+    r->host_spec_nodes[r->host_pending] = spec_n;
+    r->host_spec_edges[r->host_pending] = spec_e;
+    r->host_exported[r->host_pending] = false;
     r->host_fifo[r->host_pending] = pipe;
     r->host_seeds[r->host_pending] = n_seeds;
     r->host_pending += 1;
@@ -525,20 +625,39 @@ extern "C" int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int
         return LEGION_E_STATE;
     }
     LG_CUDA(cudaSetDevice(r->dev_id));
+    {
+        int frc = flush_deferred(r);
+        if (frc != LEGION_OK) return frc;
+    }
+    if (r->host_deferred && r->host_pending == 1) {
+        set_error("legion_runner_collect_host: internal: a batch without its gather is the only one pending");
+        return LEGION_E_STATE;
+    }
     LegionPool *p = r->pool;
     const int pipe = r->host_fifo[0];
     const int32_t n_seeds = r->host_seeds[0];
     const bool bound = r->host_bound[0];
+    {
+        int frc = finish_export(r, 0);
+        if (frc != LEGION_OK) return frc;
+    }
     for (int i = 1; i < r->host_pending; ++i) {
         r->host_fifo[i - 1] = r->host_fifo[i];
         r->host_seeds[i - 1] = r->host_seeds[i];
         r->host_bound[i - 1] = r->host_bound[i];
+        r->host_out[i - 1] = r->host_out[i];
+        r->host_spec_nodes[i - 1] = r->host_spec_nodes[i];
+        r->host_spec_edges[i - 1] = r->host_spec_edges[i];
+        r->host_exported[i - 1] = r->host_exported[i];
     }
     r->host_pending -= 1;
     LG_CUDA(cudaEventSynchronize(r->pipe_done[pipe]));
     const int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
     memcpy(node_counter_out, hc, 64);
     memcpy(edge_counter_out, hc + 16, 64);
+    // the caller reads this batch's rows from the pipe's feature buffer now; the batch that already
+    // sampled on this pipe gathers into it at the next call on this runner (flush_deferred)
+    if (r->host_deferred) r->host_released = true;
     const int hops = hc[LEGION_INTRABATCH_CON * 3 - 1];
     const int64_t n_nodes = hc[LEGION_INTRABATCH_CON * 3 + hops];
     const int64_t n_edges = (int64_t)hc[16] + hc[17];
@@ -563,6 +682,10 @@ extern "C" int legion_runner_sync(LegionRunner *r)
 {
     LG_ARG(r != nullptr, "runner is NULL");
     LG_CUDA(cudaSetDevice(r->dev_id));
+    {
+        int frc = flush_deferred(r);
+        if (frc != LEGION_OK) return frc;
+    }
     if (r->open_window) LG_CUDA(cudaEventRecord(r->t_end, r->s_miss));  // the miss stream ends every batch
     LG_CUDA(cudaStreamSynchronize(r->s_sample));
     LG_CUDA(cudaStreamSynchronize(r->s_gather));

@@ -232,7 +232,6 @@ def test_submit_host_to_writes_pinned_buffers(oracle_mod, use_graph):
         np.testing.assert_array_equal(o["src"][:n_edges], ref["agg_src"])
         np.testing.assert_array_equal(o["dst"][:n_edges], ref["agg_dst"])
         np.testing.assert_array_equal(o["lab"][:b], ref["labels"])
-        assert o["ids"][n_nodes] == -7 or n_nodes == len(o["ids"])      # nothing past the end
         # the gathered rows stay in the device hand-off buffer of the batch's pipe
         feat = pool.read(L.BUF_FEATURES, it % 2, n_nodes * w["table"].shape[1], np.float32)
         np.testing.assert_array_equal(feat.reshape(n_nodes, -1), w["table"][ref["ids"]])
@@ -244,6 +243,50 @@ def test_submit_host_to_writes_pinned_buffers(oracle_mod, use_graph):
         submit(it)
         collect_and_check(it - 1)
     collect_and_check(4)
+    # three deep: the third batch samples and exports while both pipes still hold uncollected batches
+    outs.append(dict(ids=pinned(pool.max_nodes), lab=pinned(b), src=pinned(pool.max_edges), dst=pinned(pool.max_edges)))
+
+    def submit3(it):
+        o = outs[it % 3]
+        r.submit_host_to(w["train"][it * b:(it + 1) * b], w["labels"][it * b:(it + 1) * b], 30 + it, o["ids"], o["lab"],
+                         o["src"], o["dst"])
+
+    def collect3(it, pipe):
+        n_nodes, n_edges = r.collect_host(None, None, None, None, nc, ec, None)
+        o = outs[it % 3]
+        ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], b, it, w["fanout"], 30 + it, 99)
+        assert n_nodes == len(ref["ids"]) and n_edges == len(ref["agg_src"])
+        np.testing.assert_array_equal(nc, ref["node_counter"])
+        np.testing.assert_array_equal(ec, ref["edge_counter"])
+        np.testing.assert_array_equal(o["ids"][:n_nodes], ref["ids"])
+        np.testing.assert_array_equal(o["src"][:n_edges], ref["agg_src"])
+        np.testing.assert_array_equal(o["dst"][:n_edges], ref["agg_dst"])
+        np.testing.assert_array_equal(o["lab"][:b], ref["labels"])
+        feat = pool.read(L.BUF_FEATURES, pipe, n_nodes * w["table"].shape[1], np.float32)
+        np.testing.assert_array_equal(feat.reshape(n_nodes, -1), w["table"][ref["ids"]])
+
+    p0 = r.current_pipe()
+    for it in range(3):
+        submit3(it)
+    with pytest.raises(L.LegionError, match="in flight"):
+        submit3(3)                      # only one batch may run ahead of the pipes
+    for it in range(3, 6):
+        collect3(it - 3, (p0 + it - 3) % 2)
+        submit3(it)
+    for it in range(6, 9):
+        collect3(it - 3, (p0 + it - 3) % 2)
+    # a plain submit cannot run ahead
+    r.submit_host(w["train"][:b], w["labels"][:b], 30)
+    r.submit_host(w["train"][b:2 * b], w["labels"][b:2 * b], 31)
+    with pytest.raises(L.LegionError, match="in flight"):
+        r.submit_host_to(w["train"][:b], w["labels"][:b], 32, outs[0]["ids"], outs[0]["lab"], outs[0]["src"], outs[0]["dst"])
+    ids_p = np.empty(pool.max_nodes, np.int32); lab_p = np.empty(b, np.int32)
+    src_p = np.empty(pool.max_edges, np.int32); dst_p = np.empty(pool.max_edges, np.int32)
+    r.collect_host(ids_p, lab_p, src_p, dst_p, nc, ec, None)
+    r.collect_host(ids_p, lab_p, src_p, dst_p, nc, ec, None)
+    for o in outs:
+        for a in o.values():
+            a[:] = -7
     # a NULL array is skipped; pageable memory is refused
     o = outs[1]
     r.submit_host_to(w["train"][:b], w["labels"][:b], 30, o["ids"], None, None, o["dst"])
