@@ -524,7 +524,6 @@ def main():
     hits = d["local_hits"] + d["peer_hits"]
     rows = hits + d["misses"]
     gather_launches = tm["timed"]  # one lookup + gather launch per batch
-    timed_frac = tm["timed"] / float(args.steps)
     # a hit reads its cache slot (the raw row; codes + scale; for the LRU cache also the keys of its set
     # and one stamp) and writes the fp32 row
     hit_read = slot_bytes + (4 * lru_ways + 4 if lru_ways else 0)
@@ -638,23 +637,26 @@ def main():
         o_chk = outs[last % 3] if mode == "bound" else outs[0]
         assert np.array_equal(o_chk["ids"][:nn_chk], pool.read(L.BUF_IDS, chk_pipe, nn_chk, np.int32))
         assert np.array_equal(o_chk["src"][:ne_chk], pool.read(L.BUF_AGG_SRC, chk_pipe, ne_chk, np.int32))
+    # wall clock needs a longer window than the device-timed leg: 40 steps of 0.2 ms are 8 ms, which one
+    # descheduled rank out of eight distorts; the steps are the same steps
+    e2e_steps = max(args.steps, 200)
     barrier()
     t0 = time.perf_counter()
     d2h = 0
     for i in range(depth):
         submit(100 + i)
-    for i in range(depth, args.steps):
+    for i in range(depth, e2e_steps):
         nn, ne = collect()
         d2h += 4 * nn + 8 * ne + 4 * b + 128
         submit(100 + i)
-    for _ in range(min(depth, args.steps)):
+    for _ in range(depth):
         nn, ne = collect()
         d2h += 4 * nn + 8 * ne + 4 * b + 128
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
-    e2e = {"value": args.steps * world / e2e_s, "unit": "batches/s", "h2d_bytes_per_step": 8 * b,
-           "d2h_bytes_per_step": d2h // args.steps,
+    e2e = {"value": e2e_steps * world / e2e_s, "unit": "batches/s", "h2d_bytes_per_step": 8 * b,
+           "d2h_bytes_per_step": d2h // e2e_steps, "steps": e2e_steps,
            "api": "legion_runner_submit_host%s / legion_runner_collect_host, %d batches in flight, outputs: %s" % (
                "_to" if mode == "bound" else "", depth, mode),
            "note": "seeds+labels copied in from host memory, ids/labels/edge lists/counters written to page-locked host "

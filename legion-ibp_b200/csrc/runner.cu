@@ -50,7 +50,6 @@ struct PipeGraph {
     void *args[7];
     bool valid;
     bool launched;  // since the last sync
-    EvPair hit[LEGION_MAX_HOPS + 1];
 };
 
 }  // namespace
@@ -68,9 +67,7 @@ struct LegionRunner {
     LegionIpcEnv *env;
     cudaStream_t s_sample, s_gather, s_miss;
     cudaStream_t s_launch[LEGION_INTERBATCH_CON];
-    cudaEvent_t seg_ready[LEGION_MAX_HOPS + 1];
-    cudaEvent_t hit_done[LEGION_MAX_HOPS + 1];
-    cudaEvent_t join_ev, cross_ev;
+    cudaEvent_t hit_done[LEGION_INTERBATCH_CON];   // lookup + gather of the pipe's batch is over
     cudaEvent_t pipe_done[LEGION_INTERBATCH_CON];
     bool pipe_busy[LEGION_INTERBATCH_CON];
     int current_pipe, last_pipe;
@@ -164,21 +161,13 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
         LG_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
         LG_CUDA(cudaStreamCreateWithPriority(&r->s_miss, cudaStreamNonBlocking, hi));
     }
-    for (int i = 0; i <= LEGION_MAX_HOPS; ++i) {
-        LG_CUDA(cudaEventCreateWithFlags(&r->seg_ready[i], cudaEventDisableTiming));
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i)
         LG_CUDA(cudaEventCreateWithFlags(&r->hit_done[i], cudaEventDisableTiming));
-    }
-    LG_CUDA(cudaEventCreateWithFlags(&r->join_ev, cudaEventDisableTiming));
-    LG_CUDA(cudaEventCreateWithFlags(&r->cross_ev, cudaEventDisableTiming));
     for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
         LG_CUDA(cudaStreamCreateWithFlags(&r->s_launch[i], cudaStreamNonBlocking));
         LG_CUDA(cudaEventCreateWithFlags(&r->pipe_done[i], cudaEventDisableTiming));
         r->pipe_busy[i] = false;
         memset(&r->pg[i], 0, sizeof(PipeGraph));
-        for (int s = 0; s <= LEGION_MAX_HOPS; ++s) {
-            LG_CUDA(cudaEventCreate(&r->pg[i].hit[s].a));
-            LG_CUDA(cudaEventCreate(&r->pg[i].hit[s].b));
-        }
     }
     LG_CUDA(cudaEventCreate(&r->t_begin));
     LG_CUDA(cudaEventCreate(&r->t_end));
@@ -871,15 +860,10 @@ extern "C" int legion_runner_destroy(LegionRunner *r)
     for (auto &pr : r->miss_ev) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
     for (auto &pr : r->sample_ev) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
     for (auto e : r->ev_free) cudaEventDestroy(e);
-    for (int i = 0; i <= LEGION_MAX_HOPS; ++i) { cudaEventDestroy(r->seg_ready[i]); cudaEventDestroy(r->hit_done[i]); }
-    cudaEventDestroy(r->join_ev);
-    cudaEventDestroy(r->cross_ev);
+    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) cudaEventDestroy(r->hit_done[i]);
     for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
         cudaEventDestroy(r->pipe_done[i]);
         cudaStreamDestroy(r->s_launch[i]);
-        for (int s = 0; s <= LEGION_MAX_HOPS; ++s) {
-            cudaEventDestroy(r->pg[i].hit[s].a); cudaEventDestroy(r->pg[i].hit[s].b);
-        }
     }
     cudaEventDestroy(r->t_begin);
     cudaEventDestroy(r->t_end);
