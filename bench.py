@@ -295,7 +295,8 @@ def workload_config(cfg, n_gpus):
         if cfg.get("host_codec"):
             kind += ", host table held as the same compressed rows"
     else:
-        kind = "static degree-ordered cache %d%% of the table per GPU" % int(cfg["cache_frac"] * 100)
+        kind = "static %s-ordered cache %d%% of the table per GPU" % (cfg.get("cache_order", "degree"),
+                                                                    int(cfg["cache_frac"] * 100))
     return {"workload": "%s: %d nodes, fp32 dim %d, batch %d, fanout %s, %s, misses by zero-copy from pinned host "
                         "memory" % (cfg["name"], cfg["n_nodes"], cfg["feat_len"], cfg["batch"], cfg["fanout"], kind),
             "batch_per_gpu": cfg["batch"], "fanout": cfg["fanout"], "feat_len": cfg["feat_len"],
@@ -321,6 +322,9 @@ def main():
     ap.add_argument("--no-replicas", action="store_true",
                     help="N > 1: stripe the whole per-GPU budget over the clique (the reference's placement) instead "
                          "of planning private copies of the hottest peer rows")
+    ap.add_argument("--cache-order", default="degree", choices=["degree", "hotness"],
+                    help="ranking behind the static cache: node degree (what the configs name) or the reference's "
+                         "own policy, access counts of one presampled epoch (engine/server.cu:94-122)")
     ap.add_argument("--e2e-outputs", default="bound", choices=["bound", "copy", "none"],
                     help="e2e leg: block structure written by the batch into page-locked arrays named at submit "
                          "time (default), copied out by collect after the batch (two batches in flight), or not "
@@ -333,6 +337,7 @@ def main():
     cfg = dict(CONFIGS[args.config])
     if args.cache_frac is not None:
         cfg["cache_frac"] = args.cache_frac
+    cfg["cache_order"] = args.cache_order
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
@@ -378,7 +383,22 @@ def main():
     fs = L.FeatureStorage(dev, n, row_bytes, table)
     fs.set_split(L.TRAINMODE, mine, mine_labels)
     order = torch.empty(n, dtype=torch.int32, device="cuda")
-    L.UnifiedCache.degree_order(dev, indptr, order)
+    counts = None
+    if args.cache_order == "hotness":
+        # PreSc: one epoch of sampling only, every touched node counted; counts of all ranks added up
+        pre_pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, 2)
+        pre_pool.set_rng(0xC0FFEE + rank, 64)  # not the measured runs' stream: those batches must be new to the cache
+        pre = L.Runner(dev, g, fs, None, pre_pool, None)
+        counts = torch.zeros(n, dtype=torch.int32, device="cuda")
+        pre.presample(0, max(1, (int(mine.numel()) - 1) // cfg["batch"]), counts)
+        torch.cuda.synchronize()
+        pre.Finalize()
+        pre_pool.close()
+        if dist is not None:
+            dist.all_reduce(counts)
+        L.UnifiedCache.hotness_order(dev, counts, order)
+    else:
+        L.UnifiedCache.degree_order(dev, indptr, order)
     codec_name = cfg.get("codec", "raw")
     codec = {"raw": L.CODEC_RAW, "int8": L.CODEC_INT8, "e4m3": L.CODEC_E4M3}[codec_name]
     slot_bytes = row_bytes if codec == L.CODEC_RAW else (f + 4 + 15) // 16 * 16
@@ -408,7 +428,9 @@ def main():
             barrier0()
         if world > 1 and not args.no_replicas:
             from legion_ibp_b200 import server
-            cap, replica_rows = server.plan_clique_cache(server.degree_mass(indptr, order), n, budget, world)
+            mass = server.degree_mass(indptr, order) if counts is None else server.weight_mass(counts, order)
+            cap, replica_rows = server.plan_clique_cache(mass, n, budget, world)
+            del mass
         cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank, codec=codec)
         if args.host_layout == "seeds_first":
             row_of = host_rows_seeds_first(order, train, cap * world)
@@ -417,7 +439,7 @@ def main():
         cache.fill_static(order, table if stored is None else stored, row_of_id=row_of)
         if replica_rows > 0:
             cache.add_replicas(order, replica_rows, row_of_id=row_of)
-    del order
+    del order, counts
     share = None
     if world > 1 and not lru_ways:
         from legion_ibp_b200 import server

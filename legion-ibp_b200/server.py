@@ -70,11 +70,11 @@ def plan_clique_cache(mass, n_nodes, budget_rows, world, cost=ROW_COST, steps=64
     return stripe, r
 
 
-def degree_mass(indptr, order):
-    """mass(x) for plan_clique_cache from node degrees: a node is sampled as a neighbour in proportion
-    to its degree, and neighbours are ~96% of the rows of a [25, 10] batch."""
-    deg = (indptr[1:] - indptr[:-1])[order.long()].to(torch.float64)
-    cum = torch.cumsum(deg, 0)
+def weight_mass(weights, order):
+    """mass(x) for plan_clique_cache: share of the total weight held by the x first nodes of `order`
+    (weights: one non-negative number per node, e.g. presampled access counts)."""
+    w = weights[order.long()].to(torch.float64)
+    cum = torch.cumsum(w, 0)
     total = float(cum[-1].item()) if cum.numel() else 0.0
     n = int(cum.numel())
 
@@ -84,6 +84,12 @@ def degree_mass(indptr, order):
             return 0.0
         return float(cum[x - 1].item()) / total
     return mass
+
+
+def degree_mass(indptr, order):
+    """mass(x) from node degrees: a node is sampled as a neighbour in proportion to its degree, and
+    neighbours are ~96% of the rows of a [25, 10] batch."""
+    return weight_mass(indptr[1:] - indptr[:-1], order)
 
 
 def all_gather_ints(values, dist, device="cpu"):

@@ -477,3 +477,32 @@ def test_gather_full_size_rows_roundtrip(oracle_mod):
     lut = oracle_mod.static_cache_lut(order, cap, 1)
     assert st["local_hits"] == int((lut[ids_list] >= 0).sum())
     rig.close()
+
+
+def test_host_register_makes_plain_memory_readable_by_kernels(oracle_mod):
+    """Host memory that CUDA did not allocate (here a numpy array standing for a shared segment) is
+    page-locked once and then serves as the host table; registering it again is not an error."""
+    import torch
+    rng = np.random.default_rng(77)
+    n, f = 3000, 64
+    table = rng.standard_normal((n, f)).astype(np.float32)          # pageable
+    t = torch.from_numpy(table)
+    L.host_register(0, t)
+    L.host_register(0, t)
+    ids_list = rng.integers(0, n, 2000).astype(np.int32)
+    ids = torch.from_numpy(ids_list).cuda()
+    feats = L.FeatureStorage(0, n, f * 4, t)
+    feats.set_split(L.TRAINMODE, ids, torch.zeros_like(ids))
+    cache = L.UnifiedCache(0, n, f * 4, 0)
+    cache.set_host_table(t)
+    pool = L.MemoryPool(0, 2000, [], f * 4, 2)
+    pool.set_batch(0, L.TRAINMODE, 0, 0)
+    L.BatchGenerate(None, feats, cache, pool, 2000, 0, 0, 0, L.TRAINMODE, False, 0)
+    L.FeatureCacheLookup(None, cache, pool, 1, 0)
+    L.IOComplete(None, cache, pool, 0, L.TRAINMODE)
+    got = pool.read(L.BUF_FEATURES, 0, 2000 * f, np.float32).reshape(2000, f)
+    np.testing.assert_array_equal(got, table[ids_list])
+    with pytest.raises(L.LegionError):
+        L._check(L.lib().legion_host_register(L.C.c_int32(0), L.C.c_void_p(0), L.C.c_int64(4096)))
+    pool.close(); cache.close(); feats.close()
+    assert int(torch.cuda.cudart().cudaHostUnregister(t.data_ptr())) == 0
