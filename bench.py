@@ -322,9 +322,10 @@ def main():
     ap.add_argument("--no-replicas", action="store_true",
                     help="N > 1: stripe the whole per-GPU budget over the clique (the reference's placement) instead "
                          "of planning private copies of the hottest peer rows")
-    ap.add_argument("--cache-order", default="degree", choices=["degree", "hotness"],
-                    help="ranking behind the static cache: node degree (what the configs name) or the reference's "
-                         "own policy, access counts of one presampled epoch (engine/server.cu:94-122)")
+    ap.add_argument("--cache-order", default="degree", choices=["degree", "hotness", "seeds_degree"],
+                    help="ranking behind the static cache: node degree (what the configs name); the reference's own "
+                         "policy, access counts of one presampled epoch (engine/server.cu:94-122); or the training "
+                         "seeds (every one of them is read once per epoch) followed by the other nodes by degree")
     ap.add_argument("--e2e-outputs", default="bound", choices=["bound", "copy", "none"],
                     help="e2e leg: block structure written by the batch into page-locked arrays named at submit "
                          "time (default), copied out by collect after the batch (two batches in flight), or not "
@@ -399,6 +400,12 @@ def main():
         L.UnifiedCache.hotness_order(dev, counts, order)
     else:
         L.UnifiedCache.degree_order(dev, indptr, order)
+        if args.cache_order == "seeds_degree":
+            is_seed = torch.zeros(n, dtype=torch.bool, device="cuda")
+            is_seed[train.long()] = True
+            first = is_seed[order.long()]
+            order = torch.cat([order[first], order[~first]]).contiguous()
+            del is_seed, first
     codec_name = cfg.get("codec", "raw")
     codec = {"raw": L.CODEC_RAW, "int8": L.CODEC_INT8, "e4m3": L.CODEC_E4M3}[codec_name]
     slot_bytes = row_bytes if codec == L.CODEC_RAW else (f + 4 + 15) // 16 * 16

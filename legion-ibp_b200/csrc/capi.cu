@@ -102,7 +102,7 @@ extern "C" int legion_pool_destroy(LegionPool *p)
         cudaFree(p->cache_index[i]); cudaFree(p->src_global[i]); cudaFree(p->map[i]); cudaFree(p->node_rec[i]);
         cudaFree(p->tile_sum[i]); cudaFree(p->tile_off[i]); cudaFree(p->eslot[i]); cudaFree(p->erank[i]);
         cudaFree(p->lru_victim[i]); cudaFree(p->ctl[i]); cudaFree(p->bctl[i]);
-        cudaFree(p->seed_stage[i]); cudaFree(p->label_stage[i]);
+        cudaFree(p->seed_stage[i]);
         if (p->h_stage[i]) cudaFreeHost(p->h_stage[i]);
     }
     delete p;
@@ -199,8 +199,9 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
         if (e == cudaSuccess) e = cudaMemset(p->ctl[i], 0, sizeof(int32_t) * CTL_WORDS);
         if (e == cudaSuccess) e = cudaMemset(p->bctl[i], 0, sizeof(BatchCtl));
         if (e == cudaSuccess) e = cudaMemset(p->eslot[i], 0, sizeof(int32_t) * pad_hop_edges);
-        if (e == cudaSuccess) e = dmalloc(&p->seed_stage[i], batch_size);
-        if (e == cudaSuccess) e = dmalloc(&p->label_stage[i], batch_size);
+        // seeds and labels of a host-provided batch: one allocation, so that one copy brings both in
+        if (e == cudaSuccess) e = dmalloc(&p->seed_stage[i], 2 * (int64_t)batch_size);
+        if (e == cudaSuccess) p->label_stage[i] = p->seed_stage[i] + batch_size;
         if (e == cudaSuccess)
             e = cudaMallocHost(reinterpret_cast<void **>(&p->h_stage[i]), sizeof(int32_t) * (2 * (size_t)batch_size + 64));
     }

@@ -348,8 +348,8 @@ static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
         LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[r->last_pipe], 0));
     if (host_seeds > 0) {
         int32_t *hs = p->h_stage[pipe];
-        LG_CUDA(cudaMemcpyAsync(p->seed_stage[pipe], hs, sizeof(int32_t) * host_seeds, cudaMemcpyHostToDevice, front));
-        LG_CUDA(cudaMemcpyAsync(p->label_stage[pipe], hs + p->batch_size, sizeof(int32_t) * host_seeds,
+        // seeds and labels sit at [0, B) and [B, 2B) of both the pinned staging area and the device one
+        LG_CUDA(cudaMemcpyAsync(p->seed_stage[pipe], hs, sizeof(int32_t) * ((size_t)p->batch_size + host_seeds),
                                 cudaMemcpyHostToDevice, front));
     }
     EvPair se = { nullptr, nullptr };
