@@ -65,6 +65,10 @@ int legion_host_register(int32_t dev_id, void *ptr, int64_t bytes);
 /* Launch-shape knobs for measurements (the reference hard-codes its grids, e.g. cache/cache.cu:746-752).
  * "miss_ctas": CTAs of the host-link fetch kernel, 0 = one per SM. */
 int legion_set_tunable(const char *name, int32_t value);
+/* Names: "miss_ctas", "miss_threads" (launch shape of the host-link fetch); "gather_ctas_per_sm",
+ * "gather_rows_in_flight" (2/4/8/16, register path); "gather_engine" 0 = rows move through registers,
+ * 1 = rows move by bulk asynchronous copies through shared memory (start value from the environment
+ * variable LEGION_GATHER_ENGINE). */
 
 /* EnableP2PAccess (storage/storage_management.cu:9-27) for one ordered pair of devices of this
  * process; needed when the clique's partitions are allocated by threads of one process. */

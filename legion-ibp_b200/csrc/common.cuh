@@ -60,7 +60,8 @@ enum Ctl {
     CTL_WORDS = 16
 };
 
-enum DeviceError { DERR_NONE = 0, DERR_MAP_FULL = 1, DERR_EDGE_OVERFLOW = 2, DERR_NODE_OVERFLOW = 3 };
+enum DeviceError { DERR_NONE = 0, DERR_MAP_FULL = 1, DERR_EDGE_OVERFLOW = 2, DERR_NODE_OVERFLOW = 3,
+                   DERR_BULK_TIMEOUT = 4 };  // a bulk copy of the gather did not complete within its wait limit
 
 struct NodeRec {  // per input node of a hop, written by the count kernel
     int64_t start;  // first CSR position of the adjacency list

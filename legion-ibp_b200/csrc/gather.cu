@@ -12,6 +12,7 @@
 // 743-781; cache/cache_impl.cuh:239-303: thread-per-float, 4-byte loads, 32-64 CTAs) and
 // static_retrieve_kernel + static_transfer_kernel (comp_cache/static_cache_kernel.cuh:185-266).
 #include "common.cuh"
+#include <cstdlib>
 
 #include <cuda_fp8.h>
 #include <string.h>
@@ -37,6 +38,7 @@ struct GatherParams {
     int32_t feature_len; // elements per row (quantised codecs)
     int2 *miss_rows;     // (position in ids, host table row) of rows whose source is the host table
     int32_t *miss_count; // [0] number of entries
+    int32_t *err;        // device error word of the pipe (sticky), or nullptr
 };
 
 __device__ __forceinline__ const uint8_t *shfl_ptr(const uint8_t *p, int src)
@@ -219,6 +221,109 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
             }
         }
     }
+}
+
+// ---- the same gather with the copy engine of the SM (bulk asynchronous copies) -----------------------
+//
+// A warp looks 32 ids up, one per lane, as above; then every lane whose row is held in GPU memory issues
+// ONE bulk copy global -> shared for its whole row (cp.async.bulk, completion counted in bytes on the
+// warp's mbarrier), the warp waits for the barrier, and every lane issues ONE bulk copy shared -> global
+// into the output row.  No row data passes through registers, so a warp keeps 32 rows (16 KB for
+// 512-byte rows) in flight with a handful of registers, and three CTAs of four warps hold 192 KB of
+// reads in flight per SM.  Rows, shared-memory slots and output rows are 16-byte aligned and a multiple
+// of 16 bytes long, which is all that the untiled bulk copy asks for; no multicast, no tensor map.
+// Every wait is bounded: on a timeout the kernel raises DERR_BULK_TIMEOUT, drains what it issued (again
+// bounded) and returns.
+constexpr int kBulkWarps = 4;
+constexpr int kBulkWaitLimit = 1 << 20;
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    for (int spin = 0; spin < kBulkWaitLimit; ++spin) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(kBulkWarps * 32) gather_bulk_kernel(GatherParams p)
+{
+    extern __shared__ __align__(128) uint8_t bulk_smem[];          // [warp][32 rows][row_bytes]
+    __shared__ __align__(8) unsigned long long bars[kBulkWarps];
+    int off, n;
+    segment_of(p.nc, p.op_id, off, n);
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    const uint32_t row_bytes = (uint32_t)p.row_bytes;
+    uint8_t *my_rows = bulk_smem + (size_t)warp * 32 * row_bytes;
+    const uint32_t my_slot = smem_addr(my_rows + (size_t)lane * row_bytes);
+    const uint32_t bar = smem_addr(&bars[warp]);
+    if (lane == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    uint32_t parity = 0;
+    bool store_pending = false;
+    int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (c * 32 < n) {
+        int32_t id = (c * 32 + lane < n) ? __ldg(&p.ids[off + c * 32 + lane]) : -1;
+        int32_t raw = lookup_raw(p, id);
+        for (; c * 32 < n; c += n_warps) {
+            const int r = c * 32 + lane;
+            int32_t gidx, host_row;
+            int where;
+            const uint8_t *src = decode_raw(p, id, raw, gidx, where, host_row);
+            if (r < n) p.cache_index[off + r] = gidx;
+            add_stats(p.stats, where, lane);
+            defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
+            const int rn = (c + n_warps) * 32 + lane;
+            id = (rn < n) ? __ldg(&p.ids[off + rn]) : -1;
+            const unsigned hits = __ballot_sync(kFull, src != nullptr);
+            // the previous chunk's stores must have read their rows out of shared memory
+            if (store_pending) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+            if (hits != 0u) {
+                if (lane == 0) {
+                    const uint32_t tx = (uint32_t)__popc(hits) * row_bytes;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(tx) : "memory");
+                }
+                __syncwarp();
+                if (src != nullptr)
+                    asm volatile(
+                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                        :: "r"(my_slot), "l"(src), "r"(row_bytes), "r"(bar) : "memory");
+            }
+            raw = lookup_raw(p, id);  // the next chunk's table entries travel while the rows do
+            if (hits != 0u) {
+                const bool done = mbar_wait(bar, parity);
+                parity ^= 1u;
+                if (!__all_sync(kFull, done)) {
+                    if (lane == 0 && p.err != nullptr) atomicCAS(p.err, DERR_NONE, DERR_BULK_TIMEOUT);
+                    mbar_wait(bar, parity ^ 1u);  // one more bounded wait for the copies that are still on their way
+                    break;
+                }
+                if (src != nullptr) {
+                    uint8_t *dst = p.dst + (int64_t)(off + r) * p.row_bytes;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 :: "l"(dst), "r"(my_slot), "r"(row_bytes) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    store_pending = true;
+                }
+            }
+        }
+    }
+    // nothing of this CTA may still be in flight when its shared memory is given back
+    if (store_pending) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 // Any row size that is a multiple of 4 bytes (rows of F floats with F odd, ...).
@@ -654,6 +759,14 @@ static void launch_lru(int grid, cudaStream_t s, const LruParams &lp)
     gather_lru_kernel<VPL, R><<<grid, 256, 0, s>>>(lp);
 }
 
+// 0: loads and stores through registers; 1: bulk asynchronous copies through shared memory.  The
+// environment variable LEGION_GATHER_ENGINE sets the start value (legion_set_tunable overrides it).
+static int gather_engine_from_env()
+{
+    const char *v = getenv("LEGION_GATHER_ENGINE");
+    return (v != nullptr && v[0] == '1' && v[1] == 0) ? 1 : 0;
+}
+int g_gather_engine = gather_engine_from_env();
 int g_gather_cps = 0;  // CTAs per SM of the hit gathers (0 = default); see legion_set_tunable
 int g_gather_rows = 0; // rows in flight per warp for 512-byte-class rows (0 = default)
 
@@ -731,6 +844,29 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
     gp.feature_len = row_bytes / 4;
     gp.miss_rows = p->miss_rows[pipe];
     gp.miss_count = p->miss_count[pipe];
+    gp.err = p->ctl[pipe] + CTL_ERROR;
+
+    if (g_gather_engine == 1 && (c == nullptr || c->codec == LEGION_CODEC_RAW) && row_bytes % 16 == 0 && row_bytes <= 1024 &&
+        gp.slot_bytes == row_bytes) {
+        // 32 rows per warp in shared memory: 64 KB per CTA for 512-byte rows, three CTAs per SM
+        const size_t smem = (size_t)kBulkWarps * 32 * row_bytes;
+        static bool attr_set[64] = { false };
+        if (p->dev_id >= 0 && p->dev_id < 64 && !attr_set[p->dev_id]) {
+            LG_CUDA(cudaFuncSetAttribute(gather_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
+            attr_set[p->dev_id] = true;
+        }
+        int64_t rows = 0;
+        segment_grid(p, op_id, &rows);
+        int64_t want = (rows + 32 * kBulkWarps - 1) / (32 * kBulkWarps);
+        int per_sm = (int)(200 * 1024 / (smem + 1024));
+        if (per_sm < 1) per_sm = 1;
+        if (g_gather_cps > 0 && g_gather_cps < per_sm) per_sm = g_gather_cps;
+        int64_t cap = (int64_t)p->sm_count * per_sm;
+        int bgrid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+        gather_bulk_kernel<<<bgrid, kBulkWarps * 32, smem, s>>>(gp);
+        LG_LAUNCH_CHECK();
+        return LEGION_OK;
+    }
 
     if (c != nullptr && c->codec != LEGION_CODEC_RAW) {
         LG_ARG(gp.feature_len % 4 == 0, "compressed rows need a feature length that is a multiple of 4");
@@ -919,6 +1055,7 @@ extern "C" int legion_gather_rows_noalloc(void *stream, int32_t dev_id, const in
     gp.dst = (uint8_t *)out_dev;
     gp.cache_index = reinterpret_cast<int32_t *>(scratch + kNaCacheIndex);
     gp.stats = nullptr;
+    gp.err = nullptr;
     gp.row_bytes = row_bytes;
     gp.slot_bytes = row_bytes;
     gp.feature_len = row_bytes / 4;
@@ -972,6 +1109,11 @@ extern "C" int legion_set_tunable(const char *name, int32_t value)
     if (strcmp(name, "miss_threads") == 0) {
         LG_ARG(value == 0 || (value >= 32 && value <= 1024 && value % 32 == 0), "miss_threads must be a multiple of 32 up to 1024");
         g_miss_threads = value;
+        return LEGION_OK;
+    }
+    if (strcmp(name, "gather_engine") == 0) {
+        LG_ARG(value == 0 || value == 1, "gather_engine must be 0 (registers) or 1 (bulk copies)");
+        g_gather_engine = value;
         return LEGION_OK;
     }
     if (strcmp(name, "gather_ctas_per_sm") == 0) {

@@ -506,3 +506,43 @@ def test_host_register_makes_plain_memory_readable_by_kernels(oracle_mod):
         L._check(L.lib().legion_host_register(L.C.c_int32(0), L.C.c_void_p(0), L.C.c_int64(4096)))
     pool.close(); cache.close(); feats.close()
     assert int(torch.cuda.cudart().cudaHostUnregister(t.data_ptr())) == 0
+
+
+@pytest.mark.parametrize("feat_len,dtype,kg", [(128, np.float32, 1), (100, np.float32, 1), (256, np.float32, 1),
+                                               (768, np.float16, 1), (128, np.float32, 4)])
+def test_bulk_copy_engine_gathers_the_same_rows(oracle_mod, feat_len, dtype, kg):
+    """The gather that moves rows by bulk asynchronous copies through shared memory (opt-in engine 1):
+    same rows, same hit / miss index and same counters as the register path, and no device error."""
+    rng = np.random.default_rng(500 + feat_len + kg)
+    indptr, _ = small_graph(6000, 80000, 5)
+    n = len(indptr) - 1
+    table = rng.standard_normal((n, feat_len)).astype(dtype)
+    ids_list = rng.integers(0, n, 5000).astype(np.int32)
+    ids_list[7] = -1
+    cap = n // (kg * 3)
+    order = oracle_mod.degree_order(indptr)
+    rigs = [Rig(table, ids_list, 5000, capacity=cap, kg=kg, ki=ki, order=order) for ki in range(kg)]
+    for a in range(kg):
+        for b in range(kg):
+            if a != b:
+                rigs[a].cache.set_peer(b, rigs[b].cache.partition()[0])
+    valid = ids_list >= 0
+    try:
+        L._check(L.lib().legion_set_tunable(b"gather_engine", 0))
+        cnt0, feat0, nc0 = rigs[0].gather(0)
+        ci0 = rigs[0].pool.read(L.BUF_CACHE_INDEX, 0, cnt0, np.int32)
+        L._check(L.lib().legion_set_tunable(b"gather_engine", 1))
+        cnt1, feat1, nc1 = rigs[0].gather(0, pipe=1)   # the other pipe's buffers: nothing left over from engine 0
+        ci1 = rigs[0].pool.read(L.BUF_CACHE_INDEX, 1, cnt1, np.int32)
+    finally:
+        L._check(L.lib().legion_set_tunable(b"gather_engine", 0))
+    assert cnt0 == cnt1
+    np.testing.assert_array_equal(feat1[valid], feat0[valid])
+    np.testing.assert_array_equal(feat1[valid], table[ids_list[valid]].view(np.uint8).reshape(int(valid.sum()), -1))
+    np.testing.assert_array_equal(ci1, ci0)
+    np.testing.assert_array_equal(nc1, nc0)
+    assert rigs[0].pool.device_error() == 0
+    with pytest.raises(L.LegionError):
+        L._check(L.lib().legion_set_tunable(b"gather_engine", 2))
+    for r in rigs:
+        r.close()
