@@ -68,7 +68,10 @@ int legion_set_tunable(const char *name, int32_t value);
 /* Names: "miss_ctas", "miss_threads" (launch shape of the host-link fetch); "gather_ctas_per_sm",
  * "gather_rows_in_flight" (2/4/8/16, register path); "gather_engine" 0 = rows move through registers,
  * 1 = rows move by bulk asynchronous copies through shared memory (start value from the environment
- * variable LEGION_GATHER_ENGINE). */
+ * variable LEGION_GATHER_ENGINE); "pdl" 1 = the sampling kernels of a batch are launched as programmatic
+ * dependents of one another (start value from LEGION_PDL; applies to runners created afterwards);
+ * "map_front_shift" s: the front region of a pool's id map gets 1 / 2^s of the worst-case slots
+ * (default 3; pools created afterwards). */
 
 /* EnableP2PAccess (storage/storage_management.cu:9-27) for one ordered pair of devices of this
  * process; needed when the clique's partitions are allocated by threads of one process. */

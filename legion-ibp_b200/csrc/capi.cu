@@ -160,6 +160,17 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
     uint32_t cap = 1024;
     while ((int64_t)cap * 5 < nodes * 8) cap <<= 1;  // load factor <= 0.625 in the worst case
     p->map_mask = cap - 1;
+    // front region: what batches actually need is far below the worst case (a paper100M-shaped batch finds
+    // ~2 x 10^5 of its 2.3 x 10^6 possible nodes), so an eighth of the worst-case size stays half empty
+    uint32_t front = cap >> (g_map_front_shift >= 0 && g_map_front_shift < 31 ? g_map_front_shift : 3);
+    if (front < 64) front = 64;
+    if (front > cap) front = cap;
+    p->map_front_mask = front - 1;
+    if ((int64_t)front + cap >= (1ll << 31)) {  // slots are named by int32 indices
+        set_error("legion_pool_create: a batch of up to %lld nodes needs an id map beyond 2^31 slots", (long long)nodes);
+        delete p;
+        return LEGION_E_LIMIT;
+    }
 
     const int64_t pad_nodes = round_up(nodes, kTile) + kTile;
     const int64_t pad_edges = round_up(edges > 0 ? edges : 1, kTile) + kTile;
@@ -187,7 +198,7 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
         if (e == cudaSuccess) e = cudaMemset(p->miss_count[i], 0, 32);
         if (e == cudaSuccess) e = dmalloc(&p->cache_index[i], pad_nodes);
         if (e == cudaSuccess) e = dmalloc(&p->src_global[i], pad_edges);
-        if (e == cudaSuccess) e = dmalloc(&p->map[i], (int64_t)cap);
+        if (e == cudaSuccess) e = dmalloc(&p->map[i], (int64_t)front + cap);
         if (e == cudaSuccess) e = dmalloc(&p->node_rec[i], pad_nodes);
         if (e == cudaSuccess) e = dmalloc(&p->tile_sum[i], tiles);
         if (e == cudaSuccess) e = dmalloc(&p->tile_off[i], tiles);
@@ -197,6 +208,11 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
         if (e == cudaSuccess) e = dmalloc(&p->ctl[i], CTL_WORDS);
         if (e == cudaSuccess) e = dmalloc(&p->bctl[i], 1);
         if (e == cudaSuccess) e = cudaMemset(p->ctl[i], 0, sizeof(int32_t) * CTL_WORDS);
+        if (e == cudaSuccess) {
+            // the back region of a new map is not empty yet: the first batch has to clear it
+            const int32_t one = 1;
+            e = cudaMemcpy(p->ctl[i] + CTL_BACK_DIRTY, &one, sizeof(one), cudaMemcpyHostToDevice);
+        }
         if (e == cudaSuccess) e = cudaMemset(p->bctl[i], 0, sizeof(BatchCtl));
         if (e == cudaSuccess) e = cudaMemset(p->eslot[i], 0, sizeof(int32_t) * pad_hop_edges);
         // seeds and labels of a host-provided batch: one allocation, so that one copy brings both in

@@ -57,6 +57,8 @@ enum Ctl {
     CTL_TICKET_C = 6,
     CTL_ERROR = 7,     // first error raised by a kernel (0 = none)
     CTL_MISS_COUNT = 8,
+    CTL_BACK_DIRTY = 9,  // the back region of the id map holds entries (kept across batches until it is cleared)
+    CTL_TICKET_D = 10,
     CTL_WORDS = 16
 };
 
@@ -74,6 +76,16 @@ struct MapSlot {
     int32_t key;
     int32_t val;
 };
+
+// The id map of a pipe is one array of slots in two regions.  The front region is sized for the
+// batches that actually occur (an eighth of the worst case), so that it stays in L2 and costs little to
+// clear; a key whose first kFrontProbes slots there are taken goes to the back region, which is sized
+// for the worst case and is only cleared after a batch that used it.
+struct MapDims {
+    uint32_t front_mask;  // front slots - 1 (power of two)
+    uint32_t back_mask;   // back slots - 1 (power of two); the back region starts at slot front_mask + 1
+};
+constexpr int kFrontProbes = 32;
 
 // Per-batch parameters, kept in device memory (one copy per pipe) so that the launch sequence of a
 // batch does not depend on them and can be replayed as a CUDA graph: only the kernel that writes
@@ -171,7 +183,8 @@ struct LegionPool {
     int64_t *cache_index[LEGION_INTERBATCH_CON];      // one entry per node of the batch
     int32_t *src_global[LEGION_INTERBATCH_CON];       // sampled neighbour ids, all hops
     legion::MapSlot *map[LEGION_INTERBATCH_CON];      // batch-local id map
-    uint32_t map_mask;
+    uint32_t map_mask;        // back region of the id map: slots - 1
+    uint32_t map_front_mask;  // front region: slots - 1
     legion::NodeRec *node_rec[LEGION_INTERBATCH_CON];
     int32_t *tile_sum[LEGION_INTERBATCH_CON], *tile_off[LEGION_INTERBATCH_CON];
     int32_t *eslot[LEGION_INTERBATCH_CON], *erank[LEGION_INTERBATCH_CON];
@@ -192,6 +205,8 @@ struct LegionPool {
 
 namespace legion {
 // kernel launchers (defined in sample.cu / gather.cu / cache.cu)
+extern int g_pdl;
+extern int g_map_front_shift;
 int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &ctl, bool defer_seeds = false);
 BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t *all_ids, const int32_t *all_labels,
                         int32_t total_cap, int64_t first, int32_t size);

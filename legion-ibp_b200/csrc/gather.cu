@@ -1111,6 +1111,16 @@ extern "C" int legion_set_tunable(const char *name, int32_t value)
         g_miss_threads = value;
         return LEGION_OK;
     }
+    if (strcmp(name, "map_front_shift") == 0) {
+        LG_ARG(value >= 0 && value <= 30, "map_front_shift must be 0..30");
+        g_map_front_shift = value;  // pools created afterwards
+        return LEGION_OK;
+    }
+    if (strcmp(name, "pdl") == 0) {
+        LG_ARG(value == 0 || value == 1, "pdl must be 0 or 1");
+        g_pdl = value;  // takes effect for runners created (graphs captured) afterwards
+        return LEGION_OK;
+    }
     if (strcmp(name, "gather_engine") == 0) {
         LG_ARG(value == 0 || value == 1, "gather_engine must be 0 (registers) or 1 (bulk copies)");
         g_gather_engine = value;

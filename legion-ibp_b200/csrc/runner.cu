@@ -43,11 +43,11 @@ struct PipeGraph {
     cudaKernelNodeParams ctl_params;
     // argument storage of the first kernel (kept alive for cudaGraphExecKernelNodeSetParams)
     uint4 *a_slots;
-    int64_t a_pairs;
+    int64_t a_pairs, a_back_pairs;
     int32_t *a_ctl, *a_nc, *a_ec;
     legion::BatchCtl *a_bctl;
     legion::BatchCtl a_value;
-    void *args[7];
+    void *args[8];
     bool valid;
     bool launched;  // since the last sync
 };
@@ -293,6 +293,7 @@ static int capture_pipe(LegionRunner *r, int pipe, const BatchCtl &v)
             g.a_ec = *(int32_t **)kp.kernelParams[4];
             g.a_bctl = *(BatchCtl **)kp.kernelParams[5];
             g.a_value = v;
+            g.a_back_pairs = *(int64_t *)kp.kernelParams[7];
             found = true;
         }
     }
@@ -302,7 +303,7 @@ static int capture_pipe(LegionRunner *r, int pipe, const BatchCtl &v)
         return LEGION_E_STATE;
     }
     g.args[0] = &g.a_slots; g.args[1] = &g.a_pairs; g.args[2] = &g.a_ctl; g.args[3] = &g.a_nc;
-    g.args[4] = &g.a_ec; g.args[5] = &g.a_bctl; g.args[6] = &g.a_value;
+    g.args[4] = &g.a_ec; g.args[5] = &g.a_bctl; g.args[6] = &g.a_value; g.args[7] = &g.a_back_pairs;
     g.ctl_params.kernelParams = g.args;
     g.ctl_params.extra = nullptr;
     LG_CUDA(cudaGraphInstantiate(&g.exec, graph, 0));

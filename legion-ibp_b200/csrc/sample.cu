@@ -18,10 +18,20 @@
 // position_map become a batch-local open-addressing map that stays in L2, the fixed <<<16,512>>>
 // grid becomes a grid sized from the SM count, and the blocking counter read-backs disappear.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace legion {
 
 static constexpr unsigned kFull = 0xFFFFFFFFu;
+
+// Programmatic dependent launch.  A kernel launched with the attribute may be scheduled while its
+// predecessor in the stream is still running; it must not touch the predecessor's results before
+// pdl_wait() returns (all prerequisite grids complete, their writes visible).  pdl_trigger() lets the
+// successor of THIS kernel be scheduled as soon as every CTA of this kernel has started.  Both are
+// no-ops for a kernel launched the ordinary way.  The point: a hop is four 8-20 us kernels, and the
+// drain / launch / ramp-up between two of them costs as much as a quarter of one.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t mix32(uint32_t h)
 {
@@ -31,11 +41,16 @@ __device__ __forceinline__ uint32_t mix32(uint32_t h)
 
 // Enters `key` and lowers its value to `cand`; returns the slot.  Keys never change once
 // written during a batch, so a stale read can only show "empty", which the CAS then corrects.
-__device__ __forceinline__ int32_t map_insert_min(MapSlot *map, uint32_t mask, int32_t key, int32_t cand,
+// The front region is tried first (kFrontProbes slots from the key's home slot).  Slots never empty
+// during a batch, so every thread that carries the same key sees the same first usable slot there, or
+// finds all of them taken by other keys and moves on to the back region, like every other thread
+// with that key.
+__device__ __forceinline__ int32_t map_insert_min(MapSlot *map, MapDims dims, int32_t key, int32_t cand,
                                                   int32_t *ctl)
 {
-    uint32_t s = mix32((uint32_t)key) & mask;
-    for (uint32_t probe = 0; probe <= mask; ++probe) {
+    const uint32_t h = mix32((uint32_t)key);
+    uint32_t s = h & dims.front_mask;
+    for (int probe = 0; probe < kFrontProbes; ++probe) {
         int32_t k = __ldcg(&map[s].key);
         if (k == kEmptyKey) {
             int32_t old = atomicCAS(&map[s].key, kEmptyKey, key);
@@ -45,7 +60,22 @@ __device__ __forceinline__ int32_t map_insert_min(MapSlot *map, uint32_t mask, i
             atomicMin(&map[s].val, cand);
             return (int32_t)s;
         }
-        s = (s + 1) & mask;
+        s = (s + 1) & dims.front_mask;
+    }
+    if (ctl[CTL_BACK_DIRTY] == 0) ctl[CTL_BACK_DIRTY] = 1;
+    MapSlot *back = map + dims.front_mask + 1;
+    s = mix32(h ^ 0x9E3779B9u) & dims.back_mask;
+    for (uint32_t probe = 0; probe <= dims.back_mask; ++probe) {
+        int32_t k = __ldcg(&back[s].key);
+        if (k == kEmptyKey) {
+            int32_t old = atomicCAS(&back[s].key, kEmptyKey, key);
+            k = (old == kEmptyKey) ? key : old;
+        }
+        if (k == key) {
+            atomicMin(&back[s].val, cand);
+            return (int32_t)(dims.front_mask + 1 + s);
+        }
+        s = (s + 1) & dims.back_mask;
     }
     atomicCAS(&ctl[CTL_ERROR], DERR_NONE, DERR_MAP_FULL);
     return 0;
@@ -193,26 +223,45 @@ __device__ __forceinline__ void counter_update(int32_t *nc, int32_t *ec, int op_
 // ---- batch start -----------------------------------------------------------------------------
 
 // First kernel of every batch: empties the id map, zeroes the counters and stores the batch's
-// parameters, the only values of the batch that are passed by value.
+// parameters, the only values of the batch that are passed by value.  The front region of the map is
+// always cleared; the back region only if the last batch on this pipe put anything there.
 __global__ void map_clear_kernel(uint4 *slots2, int64_t n_pairs, int32_t *ctl, int32_t *nc, int32_t *ec,
-                                 BatchCtl *bctl, BatchCtl value)
+                                 BatchCtl *bctl, BatchCtl value, int64_t back_pairs)
 {
+    __shared__ int s_last;
+    const bool back_dirty = ctl[CTL_BACK_DIRTY] != 0;  // final since the end of the last batch's sampling
     if (blockIdx.x == 0 && threadIdx.x == 32) *bctl = value;
     const uint4 empty = make_uint4((uint32_t)kEmptyKey, (uint32_t)kEmptyVal, (uint32_t)kEmptyKey,
                                    (uint32_t)kEmptyVal);
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_pairs;
+    const int64_t total = n_pairs + (back_dirty ? back_pairs : 0);
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x)
         slots2[i] = empty;
     if (blockIdx.x == 0 && threadIdx.x < 16) {
-        if (threadIdx.x != CTL_ERROR) ctl[threadIdx.x] = 0;  // the error word is sticky
+        // the error word is sticky; the dirty flag and its ticket are read by every CTA of this kernel
+        if (threadIdx.x != CTL_ERROR && threadIdx.x != CTL_BACK_DIRTY && threadIdx.x != CTL_TICKET_D) ctl[threadIdx.x] = 0;
         nc[threadIdx.x] = 0;  // cudaMemsetAsync of both counters, operator_impl.cu:158-159
         ec[threadIdx.x] = 0;
+    }
+    // the last CTA to get here lowers the flag: every CTA has read it by then, and nothing enters the
+    // map before the next kernel
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = atomicAdd(&ctl[CTL_TICKET_D], 1);
+        s_last = (t == (int)gridDim.x - 1);
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        ctl[CTL_BACK_DIRTY] = 0;
+        ctl[CTL_TICKET_D] = 0;
     }
 }
 
 __global__ void batch_generate_kernel(const BatchCtl *__restrict__ b, int32_t *ids, int32_t *labels, MapSlot *map,
-                                      uint32_t mask, int32_t *ctl, int32_t *nc, int32_t *ec)
+                                      MapDims mask, int32_t *ctl, int32_t *nc, int32_t *ec)
 {
+    pdl_wait();
+    pdl_trigger();
     const int32_t *__restrict__ all_ids = b->all_ids;
     const int32_t *__restrict__ all_labels = b->all_labels;
     const int32_t total_cap = b->total_cap, size = b->size, hop_num = b->hop_num;
@@ -245,8 +294,10 @@ template <bool FIRST>
 __global__ void __launch_bounds__(kScanThreads)
 hop_count_kernel(const int64_t *__restrict__ indptr, int32_t *ids, int32_t fanout,
                  NodeRec *rec, int32_t *tile_sum, int32_t *tile_off, int32_t *ctl, int64_t max_edges,
-                 const BatchCtl *__restrict__ b, int32_t *labels, MapSlot *map, uint32_t mask, int32_t *nc, int32_t *ec)
+                 const BatchCtl *__restrict__ b, int32_t *labels, MapSlot *map, MapDims mask, int32_t *nc, int32_t *ec)
 {
+    pdl_wait();
+    pdl_trigger();
     // the seeds are few (one batch): one item per thread and 256-node tiles give that launch 4 x the CTAs
     constexpr int IPT = FIRST ? 1 : 4;
     constexpr int TILE = kScanThreads * IPT;
@@ -330,8 +381,10 @@ __global__ void __launch_bounds__(256)
 hop_sample_kernel(const int32_t *__restrict__ indices, const NodeRec *__restrict__ rec,
                   const int32_t *__restrict__ tile_off, int32_t fanout, uint32_t hop,
                   const BatchCtl *__restrict__ b, int32_t *src_global, int32_t *agg_dst,
-                  int32_t *eslot, MapSlot *map, uint32_t mask, int32_t *ctl, int tile_shift)
+                  int32_t *eslot, MapSlot *map, MapDims mask, int32_t *ctl, int tile_shift)
 {
+    pdl_wait();
+    pdl_trigger();
     if (ctl[CTL_ERROR] != DERR_NONE) return;
     const uint32_t batch_id = b->global_batch, k0 = b->k0, k1 = b->k1;
     const int max_rounds = b->max_rounds;
@@ -390,6 +443,8 @@ __global__ void __launch_bounds__(kScanThreads)
 hop_flag_kernel(const int32_t *__restrict__ eslot, const MapSlot *map, int32_t *erank, int32_t *tile_sum,
                 int32_t *tile_off, int32_t *ctl, int64_t max_nodes)
 {
+    pdl_wait();
+    pdl_trigger();
     __shared__ int smem[kScanThreads / 32];
     __shared__ int s_flag;
     const int n_edges = ctl[CTL_E_HOP];
@@ -433,6 +488,8 @@ __global__ void hop_finish_kernel(const int32_t *__restrict__ erank, const int32
                                   int32_t *ids, MapSlot *map, int32_t *agg_src, int32_t *ctl, int32_t *nc, int32_t *ec,
                                   int op_id)
 {
+    pdl_wait();
+    pdl_trigger();
     __shared__ int s_flag;
     const int n_edges = ctl[CTL_E_HOP];
     const int n0 = ctl[CTL_N_NODES];
@@ -482,6 +539,32 @@ __global__ void hop_finish_kernel(const int32_t *__restrict__ erank, const int32
 
 // ---- launchers -----------------------------------------------------------------------------------
 
+// 1: the kernels of a batch after its first are launched as programmatic dependents (legion_set_tunable
+// "pdl"; start value from the environment variable LEGION_PDL)
+static int pdl_from_env()
+{
+    const char *v = getenv("LEGION_PDL");
+    return (v != nullptr && v[0] == '1' && v[1] == 0) ? 1 : 0;
+}
+int g_pdl = pdl_from_env();
+int g_map_front_shift = 3;  // front region of the id map = worst-case slots >> this (legion_set_tunable "map_front_shift")
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_dep(void (*kernel)(KArgs...), int grid, int block, cudaStream_t s, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = g_pdl ? at : nullptr;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int grid_for(int64_t items, int per_cta, int cap)
 {
     int64_t g = (items + per_cta - 1) / per_cta;
@@ -515,16 +598,17 @@ BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t
 int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &v, bool defer_seeds)
 {
     const int pipe = p->pipe;
-    int64_t n_pairs = ((int64_t)p->map_mask + 1) / 2;
+    const int64_t n_pairs = ((int64_t)p->map_front_mask + 1) / 2;
+    const int64_t back_pairs = ((int64_t)p->map_mask + 1) / 2;
+    // sized for the front region; when the back region has to be cleared too, the CTAs loop longer
     map_clear_kernel<<<grid_for(n_pairs, 256 * 4, p->sm_count * 8), 256, 0, s>>>(
         reinterpret_cast<uint4 *>(p->map[pipe]), n_pairs, p->ctl[pipe], p->node_counter[pipe], p->edge_counter[pipe],
-        p->bctl[pipe], v);
+        p->bctl[pipe], v, back_pairs);
     LG_LAUNCH_CHECK();
     if (defer_seeds) return LEGION_OK;
-    batch_generate_kernel<<<grid_for(p->batch_size, 256, 1 << 20), 256, 0, s>>>(
-        p->bctl[pipe], p->ids[pipe], p->labels[pipe], p->map[pipe], p->map_mask, p->ctl[pipe], p->node_counter[pipe],
-        p->edge_counter[pipe]);
-    LG_LAUNCH_CHECK();
+    LG_CUDA(launch_dep(batch_generate_kernel, grid_for(p->batch_size, 256, 1 << 20), 256, s, p->bctl[pipe], p->ids[pipe],
+                       p->labels[pipe], p->map[pipe], MapDims{ p->map_front_mask, p->map_mask }, p->ctl[pipe], p->node_counter[pipe],
+                       p->edge_counter[pipe]));
     return LEGION_OK;
 }
 
@@ -540,30 +624,26 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
     int32_t *ctl = p->ctl[pipe];
     if (seeds_pending) {
         LG_ARG(hop == 0, "only the first hop can take the seed slice");
-        hop_count_kernel<true><<<grid_for(inputs, kScanThreads, cap), kScanThreads, 0, s>>>(
-            g->indptr, p->ids[pipe], fanout, p->node_rec[pipe], p->tile_sum[pipe], p->tile_off[pipe], ctl, p->max_edges,
-            p->bctl[pipe], p->labels[pipe], p->map[pipe], p->map_mask, p->node_counter[pipe], p->edge_counter[pipe]);
+        LG_CUDA(launch_dep(hop_count_kernel<true>, grid_for(inputs, kScanThreads, cap), kScanThreads, s, g->indptr,
+                           p->ids[pipe], fanout, p->node_rec[pipe], p->tile_sum[pipe], p->tile_off[pipe], ctl, p->max_edges,
+                           p->bctl[pipe], p->labels[pipe], p->map[pipe], MapDims{ p->map_front_mask, p->map_mask }, p->node_counter[pipe],
+                           p->edge_counter[pipe]));
     } else {
-        hop_count_kernel<false><<<grid_for(inputs, kTile, cap), kScanThreads, 0, s>>>(
-            g->indptr, p->ids[pipe], fanout, p->node_rec[pipe], p->tile_sum[pipe], p->tile_off[pipe], ctl, p->max_edges,
-            p->bctl[pipe], p->labels[pipe], p->map[pipe], p->map_mask, p->node_counter[pipe], p->edge_counter[pipe]);
+        LG_CUDA(launch_dep(hop_count_kernel<false>, grid_for(inputs, kTile, cap), kScanThreads, s, g->indptr, p->ids[pipe],
+                           fanout, p->node_rec[pipe], p->tile_sum[pipe], p->tile_off[pipe], ctl, p->max_edges, p->bctl[pipe],
+                           p->labels[pipe], p->map[pipe], MapDims{ p->map_front_mask, p->map_mask }, p->node_counter[pipe], p->edge_counter[pipe]));
     }
-    LG_LAUNCH_CHECK();
-    hop_sample_kernel<<<grid_for(inputs, 8, cap), 256, 0, s>>>(
-        g->indices, p->node_rec[pipe], p->tile_off[pipe], fanout, (uint32_t)hop, p->bctl[pipe], p->src_global[pipe],
-        p->agg_dst[pipe], p->eslot[pipe], p->map[pipe], p->map_mask, ctl, seeds_pending ? 8 : 10);
-    LG_LAUNCH_CHECK();
+    LG_CUDA(launch_dep(hop_sample_kernel, grid_for(inputs, 8, cap), 256, s, g->indices, p->node_rec[pipe], p->tile_off[pipe],
+                       fanout, (uint32_t)hop, p->bctl[pipe], p->src_global[pipe], p->agg_dst[pipe], p->eslot[pipe],
+                       p->map[pipe], MapDims{ p->map_front_mask, p->map_mask }, ctl, seeds_pending ? 8 : 10));
     static_assert(kScanThreads == 256 && kTile == 1024, "tile shifts above assume 256-thread scans over 1024-item tiles");
     int32_t *tile_sum2 = p->tile_sum[pipe] + p->input_tiles;
     int32_t *tile_off2 = p->tile_off[pipe] + p->input_tiles;
-    hop_flag_kernel<<<grid_for(edges, kTile, cap), kScanThreads, 0, s>>>(p->eslot[pipe], p->map[pipe], p->erank[pipe],
-                                                                         tile_sum2, tile_off2, ctl, p->max_nodes);
-    LG_LAUNCH_CHECK();
-    hop_finish_kernel<<<grid_for(edges, 256 * 4, cap), 256, 0, s>>>(p->erank[pipe], tile_off2, p->eslot[pipe],
-                                                                   p->src_global[pipe], p->ids[pipe], p->map[pipe],
-                                                                   p->agg_src[pipe], ctl, p->node_counter[pipe],
-                                                                   p->edge_counter[pipe], op_id);
-    LG_LAUNCH_CHECK();
+    LG_CUDA(launch_dep(hop_flag_kernel, grid_for(edges, kTile, cap), kScanThreads, s, p->eslot[pipe], p->map[pipe],
+                       p->erank[pipe], tile_sum2, tile_off2, ctl, p->max_nodes));
+    LG_CUDA(launch_dep(hop_finish_kernel, grid_for(edges, 256 * 4, cap), 256, s, p->erank[pipe], tile_off2, p->eslot[pipe],
+                       p->src_global[pipe], p->ids[pipe], p->map[pipe], p->agg_src[pipe], ctl, p->node_counter[pipe],
+                       p->edge_counter[pipe], op_id));
     return LEGION_OK;
 }
 

@@ -90,6 +90,30 @@ def test_batch_matches_host_replay(oracle_mod, n_nodes, n_pairs, batch, fanout, 
     pool.close(); f.close(); g.close()
 
 
+@pytest.mark.parametrize("shift", [20, 6, 0])
+def test_id_map_front_and_back_regions(oracle_mod, shift):
+    """The id map tries a small front region first and falls back to the worst-case-sized back region.
+    With a front of 64 slots nearly every node lands in the back region, which must then be cleared
+    before the next batch on the same pipe; with shift 0 the front alone is as large as the worst case."""
+    n_nodes, n_pairs, batch, fanout, seed = 3000, 40000, 128, [15, 10, 5], 7
+    indptr, indices = small_graph(n_nodes, n_pairs, seed)
+    rng = np.random.default_rng(seed)
+    train = rng.permutation(n_nodes)[: batch * 6].astype(np.int32)
+    labels = rng.integers(0, 47, len(train)).astype(np.int32)
+    L._check(L.lib().legion_set_tunable(b"map_front_shift", shift))
+    try:
+        g, f, pool = _setup(indptr, indices, train, labels, batch, fanout)
+    finally:
+        L._check(L.lib().legion_set_tunable(b"map_front_shift", 3))
+    pool.set_rng(77, 64)
+    for it in range(6):
+        pipe = 0 if it < 4 else 1          # four batches in a row on one pipe, then the other
+        _run_ops(g, f, pool, batch, it, fanout, global_batch=it, pipe=pipe)
+        _compare(_fetch(pool, pipe), oracle_mod.run_batch(indptr, indices, train, labels, batch, it, fanout, it, 77))
+        assert pool.device_error() == 0
+    pool.close(); f.close(); g.close()
+
+
 @pytest.mark.parametrize("max_rounds", [1, 2, 3])
 def test_fallback_after_few_rounds(oracle_mod, max_rounds):
     """With the rejection rounds cut short the lane-ordered fallback settles the draws."""
