@@ -71,7 +71,8 @@ int legion_set_tunable(const char *name, int32_t value);
  * variable LEGION_GATHER_ENGINE); "pdl" 1 = the sampling kernels of a batch are launched as programmatic
  * dependents of one another (start value from LEGION_PDL; applies to runners created afterwards);
  * "map_front_shift" s: the front region of a pool's id map gets 1 / 2^s of the worst-case slots
- * (default 3; pools created afterwards). */
+ * (-1, the default: an eighth, but at least 2^20 slots where the worst case has that many; pools
+ * created afterwards). */
 
 /* EnableP2PAccess (storage/storage_management.cu:9-27) for one ordered pair of devices of this
  * process; needed when the clique's partitions are allocated by threads of one process. */

@@ -1112,7 +1112,7 @@ extern "C" int legion_set_tunable(const char *name, int32_t value)
         return LEGION_OK;
     }
     if (strcmp(name, "map_front_shift") == 0) {
-        LG_ARG(value >= 0 && value <= 30, "map_front_shift must be 0..30");
+        LG_ARG(value >= -1 && value <= 30, "map_front_shift must be -1 (automatic) or 0..30");
         g_map_front_shift = value;  // pools created afterwards
         return LEGION_OK;
     }

@@ -547,7 +547,9 @@ static int pdl_from_env()
     return (v != nullptr && v[0] == '1' && v[1] == 0) ? 1 : 0;
 }
 int g_pdl = pdl_from_env();
-int g_map_front_shift = 3;  // front region of the id map = worst-case slots >> this (legion_set_tunable "map_front_shift")
+// front region of the id map = worst-case slots >> this; -1: sized by legion_pool_create's own rule
+// (legion_set_tunable "map_front_shift")
+int g_map_front_shift = -1;
 
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_dep(void (*kernel)(KArgs...), int grid, int block, cudaStream_t s, Args... args)

@@ -104,7 +104,7 @@ def test_id_map_front_and_back_regions(oracle_mod, shift):
     try:
         g, f, pool = _setup(indptr, indices, train, labels, batch, fanout)
     finally:
-        L._check(L.lib().legion_set_tunable(b"map_front_shift", 3))
+        L._check(L.lib().legion_set_tunable(b"map_front_shift", -1))
     pool.set_rng(77, 64)
     for it in range(6):
         pipe = 0 if it < 4 else 1          # four batches in a row on one pipe, then the other
