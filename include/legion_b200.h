@@ -331,6 +331,13 @@ int legion_ipc_open_semaphores(LegionIpcEnv *e, int32_t dev_id, int32_t pipes);
  * reference; otherwise LEGION_E_TIMEOUT is returned when the trainer does not answer. */
 int legion_ipc_wait(LegionIpcEnv *e, int32_t dev_id, int32_t pipe, int32_t timeout_ms);
 int legion_ipc_post(LegionIpcEnv *e, int32_t dev_id, int32_t pipe);
+/* Counter words of the batch just finished on (dev, pipe), written to the companion host segment
+ * "<segment name>_ctr" (int32 [8][2][32]: node_counter then edge_counter) before the batch is posted.
+ * The reference's trainer reads both arrays from the device with two blocking copies per batch
+ * (training_backend/ipc_cuda_kernel.cu:194-203); a consumer that knows the segment (legion_client_*)
+ * reads them from host memory instead, one that does not is unaffected.  The runner calls this itself. */
+int legion_ipc_publish_counters(LegionIpcEnv *e, int32_t dev_id, int32_t pipe, const int32_t *node_counter,
+                                const int32_t *edge_counter);
 /* Finalize (engine/ipc_service.cu:293-320): closes and unlinks semaphores and the segment. */
 int legion_ipc_destroy(LegionIpcEnv *e);
 /* Byte layout of the shared segment, for consumers written in other languages. */
@@ -370,6 +377,9 @@ typedef struct LegionClient LegionClient;
 int legion_client_open(LegionClient **out, int32_t dev_id, const char *shm_name);
 int legion_client_steps(LegionClient *c, int32_t steps[3]);                                   /* get_steps */
 int legion_client_get_next(LegionClient *c, int32_t timeout_ms, LegionBatchView *out);       /* get_next */
+/* 1 when legion_client_get_next takes the counters from the server's host segment, 0 when it reads
+ * them from the device buffers (a server without the segment). */
+int legion_client_counters_on_host(LegionClient *c);
 int legion_client_synchronize(LegionClient *c);                                              /* synchronize */
 int legion_client_close(LegionClient *c);                                                    /* finalize */
 

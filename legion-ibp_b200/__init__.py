@@ -336,6 +336,12 @@ class IPCEnv:
         name = shm_name.encode() if shm_name else None
         _check(lib().legion_ipc_create(C.byref(self.h), C.c_int32(device_count), name))
 
+    def publish_counters(self, dev_id, pipe, node_counter, edge_counter):
+        """Counter words of a finished batch into the companion host segment (the runner does this itself)."""
+        nc = (C.c_int32 * 16)(*[int(v) for v in node_counter])
+        ec = (C.c_int32 * 16)(*[int(v) for v in edge_counter])
+        _check(lib().legion_ipc_publish_counters(self.h, C.c_int32(dev_id), C.c_int32(pipe), nc, ec))
+
     def Coordinate(self, train_num, valid_num, test_num, raw_batch_size, epochs):
         n = len(train_num)
         arr = lambda v: (C.c_int32 * n)(*v)
@@ -553,6 +559,10 @@ class ipc_service:
         for j in range(v.hop_num):
             out += [v.block_src[j], v.block_dst[j]]
         return out
+
+    def counters_on_host(self):
+        """True when get_next reads the counters from the server's host segment (no device copy)."""
+        return bool(lib().legion_client_counters_on_host(self.h))
 
     def synchronize(self):
         _check(lib().legion_client_synchronize(self.h))

@@ -34,6 +34,11 @@ struct LegionIpcEnv {
     std::string sem_prefix;
     int shm_fd;
     volatile legion::ShmLayout *shm;
+    // companion segment "<name>_ctr": the counter words of every finished batch in host memory, so that a
+    // consumer need not read them from the device (the reference's trainer does two blocking device-to-host
+    // copies per batch, training_backend/ipc_cuda_kernel.cu:194-203); consumers that do not know it ignore it
+    int ctr_fd;
+    volatile int32_t *ctr;  // [device][pipe][32]: node_counter[16], edge_counter[16]
     sem_t *semr[LEGION_MAX_DEVICE][LEGION_INTERBATCH_CON];
     sem_t *semw[LEGION_MAX_DEVICE][LEGION_INTERBATCH_CON];
     int32_t pipes[LEGION_MAX_DEVICE];
@@ -45,6 +50,7 @@ struct LegionIpcEnv {
 using namespace legion;
 
 static const char kDefaultShm[] = "simpleIPCshm";  // engine/ipc_service.cu:37
+static constexpr size_t kCtrBytes = sizeof(int32_t) * LEGION_MAX_DEVICE * LEGION_INTERBATCH_CON * 32;
 
 extern "C" int legion_ipc_layout(int64_t *segment_bytes, int64_t *handle_bytes, int64_t *handles_offset)
 {
@@ -93,7 +99,33 @@ extern "C" int legion_ipc_create(LegionIpcEnv **out, int32_t device_count, const
     }
     e->shm = (volatile ShmLayout *)addr;
     memset((void *)e->shm, 0, sizeof(ShmLayout));  // engine/ipc_service.cu:45
+    // the companion segment is an extra: a failure here only means that consumers read the device counters
+    e->ctr = nullptr;
+    e->ctr_fd = shm_open((e->shm_name + "_ctr").c_str(), O_RDWR | O_CREAT, 0777);
+    if (e->ctr_fd >= 0 && ftruncate(e->ctr_fd, kCtrBytes) == 0) {
+        void *ca = mmap(nullptr, kCtrBytes, PROT_READ | PROT_WRITE, MAP_SHARED, e->ctr_fd, 0);
+        if (ca != MAP_FAILED) {
+            e->ctr = (volatile int32_t *)ca;
+            memset((void *)e->ctr, 0, kCtrBytes);
+        }
+    }
     *out = e;
+    return LEGION_OK;
+}
+
+// Counter words of the batch that was just finished on (dev, pipe), for consumers that read them from
+// host memory; call before posting the batch.
+extern "C" int legion_ipc_publish_counters(LegionIpcEnv *e, int32_t dev_id, int32_t pipe, const int32_t *node_counter,
+                                           const int32_t *edge_counter)
+{
+    LG_ARG(e != nullptr && node_counter != nullptr && edge_counter != nullptr, "NULL pointer");
+    LG_ARG(dev_id >= 0 && dev_id < LEGION_MAX_DEVICE && pipe >= 0 && pipe < LEGION_INTERBATCH_CON, "bad device or pipe");
+    if (e->ctr == nullptr) return LEGION_OK;
+    volatile int32_t *dst = e->ctr + ((size_t)dev_id * LEGION_INTERBATCH_CON + pipe) * 32;
+    for (int i = 0; i < 16; ++i) {
+        dst[i] = node_counter[i];
+        dst[16 + i] = edge_counter[i];
+    }
     return LEGION_OK;
 }
 
@@ -270,6 +302,9 @@ extern "C" int legion_ipc_destroy(LegionIpcEnv *e)
     if (e->shm) munmap((void *)e->shm, sizeof(ShmLayout));
     if (e->shm_fd >= 0) close(e->shm_fd);
     shm_unlink(e->shm_name.c_str());
+    if (e->ctr) munmap((void *)e->ctr, kCtrBytes);
+    if (e->ctr_fd >= 0) close(e->ctr_fd);
+    shm_unlink((e->shm_name + "_ctr").c_str());
     delete e;
     return LEGION_OK;
 }
@@ -316,6 +351,8 @@ struct LegionClient {
     sem_t *semr[LEGION_INTERBATCH_CON], *semw[LEGION_INTERBATCH_CON];
     int current_pipe;
     int32_t *h_counters;  // pinned, 32 ints
+    int ctr_fd;
+    volatile int32_t *ctr;  // the server's companion segment, when there is one
 };
 
 extern "C" int legion_client_close(LegionClient *c)
@@ -328,6 +365,8 @@ extern "C" int legion_client_close(LegionClient *c)
         if (c->semw[i]) sem_close(c->semw[i]);
     }
     if (c->h_counters) cudaFreeHost(c->h_counters);
+    if (c->ctr) munmap((void *)c->ctr, kCtrBytes);
+    if (c->ctr_fd >= 0) close(c->ctr_fd);
     if (c->shm) munmap((void *)c->shm, sizeof(ShmLayout));
     if (c->shm_fd >= 0) close(c->shm_fd);
     delete c;
@@ -347,6 +386,8 @@ extern "C" int legion_client_open(LegionClient **out, int32_t dev_id, const char
     c->shm = nullptr;
     c->current_pipe = 0;
     c->h_counters = nullptr;
+    c->ctr = nullptr;
+    c->ctr_fd = -1;
     memset(c->buf, 0, sizeof(c->buf));
     for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) c->semr[i] = c->semw[i] = nullptr;
     c->shm_fd = shm_open(c->shm_name.c_str(), O_RDWR | O_CREAT, 0777);  // sharedMemoryCreate, as the trainer calls it
@@ -362,6 +403,15 @@ extern "C" int legion_client_open(LegionClient **out, int32_t dev_id, const char
         return LEGION_E_SYS;
     }
     c->shm = (volatile ShmLayout *)addr;
+    // a server of this library also publishes the counters in host memory; the reference's does not
+    c->ctr_fd = shm_open((c->shm_name + "_ctr").c_str(), O_RDONLY, 0);
+    if (c->ctr_fd >= 0) {
+        struct stat st;
+        if (fstat(c->ctr_fd, &st) == 0 && (size_t)st.st_size >= kCtrBytes) {
+            void *ca = mmap(nullptr, kCtrBytes, PROT_READ, MAP_SHARED, c->ctr_fd, 0);
+            if (ca != MAP_FAILED) c->ctr = (volatile int32_t *)ca;
+        }
+    }
     for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
         for (int k = 0; k < LEGION_MEMORY_USAGE; ++k) {
             cudaIpcMemHandle_t h;
@@ -431,12 +481,21 @@ extern "C" int legion_client_get_next(LegionClient *c, int32_t timeout_ms, Legio
     }
     LG_CUDA(cudaSetDevice(c->dev_id));
     void **b = c->buf[c->current_pipe];
-    LG_CUDA(cudaMemcpyAsync(c->h_counters, b[5], 64, cudaMemcpyDeviceToHost, 0));
-    LG_CUDA(cudaMemcpyAsync(c->h_counters + 16, b[6], 64, cudaMemcpyDeviceToHost, 0));
-    LG_CUDA(cudaStreamSynchronize(0));
     memset(out, 0, sizeof(*out));
-    memcpy(out->node_counter, c->h_counters, 64);
-    memcpy(out->edge_counter, c->h_counters + 16, 64);
+    if (c->ctr != nullptr) {
+        // written by the server before it posted this batch; the semaphore orders the two sides
+        const volatile int32_t *src = c->ctr + ((size_t)c->dev_id * LEGION_INTERBATCH_CON + c->current_pipe) * 32;
+        for (int i = 0; i < 16; ++i) {
+            out->node_counter[i] = src[i];
+            out->edge_counter[i] = src[16 + i];
+        }
+    } else {
+        LG_CUDA(cudaMemcpyAsync(c->h_counters, b[5], 64, cudaMemcpyDeviceToHost, 0));
+        LG_CUDA(cudaMemcpyAsync(c->h_counters + 16, b[6], 64, cudaMemcpyDeviceToHost, 0));
+        LG_CUDA(cudaStreamSynchronize(0));
+        memcpy(out->node_counter, c->h_counters, 64);
+        memcpy(out->edge_counter, c->h_counters + 16, 64);
+    }
     const int32_t *nc = out->node_counter, *ec = out->edge_counter;
     const int hops = nc[LEGION_INTRABATCH_CON * 3 - 1];
     if (hops < 0 || hops > LEGION_MAX_HOPS) {
@@ -458,6 +517,9 @@ extern "C" int legion_client_get_next(LegionClient *c, int32_t timeout_ms, Legio
     }
     return LEGION_OK;
 }
+
+// 1 when get_next takes the counters from the server's host segment, 0 when it reads the device buffers
+extern "C" int legion_client_counters_on_host(LegionClient *c) { return (c != nullptr && c->ctr != nullptr) ? 1 : 0; }
 
 // synchronize (ipc_service.cpp:89-91, ipc_cuda_kernel.cu:102-106): release the slot, move to the next
 extern "C" int legion_client_synchronize(LegionClient *c)

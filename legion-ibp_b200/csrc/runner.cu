@@ -107,6 +107,17 @@ extern "C" int legion_ipc_post(LegionIpcEnv *e, int32_t dev_id, int32_t pipe);
 extern "C" int legion_ipc_current_batchsize(LegionIpcEnv *e, int32_t dev_id, int32_t mode);
 extern "C" int legion_ipc_current_mode(LegionIpcEnv *e, int32_t global_batch_id);
 extern "C" int legion_ipc_local_batch_id(LegionIpcEnv *e, int32_t global_batch_id);
+extern "C" int legion_ipc_publish_counters(LegionIpcEnv *e, int32_t dev_id, int32_t pipe, const int32_t *node_counter,
+                                           const int32_t *edge_counter);
+
+// The finished batch of `pipe` goes to the consumer: counters into the host segment, then the post.
+static int post_batch(LegionRunner *r, int pipe)
+{
+    const int32_t *hc = r->pool->h_stage[pipe] + 2 * (size_t)r->pool->batch_size;
+    int rc = legion_ipc_publish_counters(r->env, r->dev_id, pipe, hc, hc + 16);
+    if (rc != LEGION_OK) return rc;
+    return legion_ipc_post(r->env, r->dev_id, pipe);
+}
 
 static cudaEvent_t take_event(LegionRunner *r)
 {
@@ -414,7 +425,7 @@ static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound,
     if (early_sampling && r->pipe_busy[pipe] && !pipe_was_synced) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
     rc = issue_gather(r, front);
     if (rc != LEGION_OK) return rc;
-    if (host_seeds > 0) {
+    if (host_seeds > 0 || r->env != nullptr) {
         // the counters are final once the lookup has left its snapshot words; copied on this stream so
         // that the next sampling on this pipe, which resets them, is ordered behind the copy
         int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
@@ -779,7 +790,7 @@ extern "C" int legion_runner_run_once(LegionRunner *r, int32_t global_batch_id, 
     r->served_us += (t1.tv_sec - t0.tv_sec) * 1e6 + (t1.tv_nsec - t0.tv_nsec) * 1e-3;
     r->served += 1;
     if (r->env != nullptr) {
-        rc = legion_ipc_post(r->env, r->dev_id, pipe);  // engine/server.cu:377
+        rc = post_batch(r, pipe);  // engine/server.cu:377
         if (rc != LEGION_OK) return rc;
     }
     if (r->served % 1000 == 0 && r->dev_id == 0) {  // engine/server.cu:378-379
@@ -807,14 +818,14 @@ extern "C" int legion_runner_serve(LegionRunner *r, int32_t first_global_batch, 
         if (rc != LEGION_OK) return rc;
         if (prev_pipe >= 0) {
             LG_CUDA(cudaEventSynchronize(r->pipe_done[prev_pipe]));
-            rc = legion_ipc_post(r->env, r->dev_id, prev_pipe);
+            rc = post_batch(r, prev_pipe);
             if (rc != LEGION_OK) return rc;
         }
         prev_pipe = pipe;
     }
     if (prev_pipe >= 0) {
         LG_CUDA(cudaEventSynchronize(r->pipe_done[prev_pipe]));
-        int rc = legion_ipc_post(r->env, r->dev_id, prev_pipe);
+        int rc = post_batch(r, prev_pipe);
         if (rc != LEGION_OK) return rc;
     }
     return legion_runner_sync(r);

@@ -491,6 +491,7 @@ import conftest
 import legion_ibp_b200 as L
 shm_name, n_batches, feat_len, out_path = sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
 svc = L.ipc_service(0, shm_name)
+assert svc.counters_on_host()
 def d2h(ptr, count, dtype):
     out = np.empty(count, dtype)
     if out.nbytes:
@@ -578,6 +579,7 @@ def test_sampling_server_binary_end_to_end(oracle_mod, tmp_path):
             if select.select([proc.stdout], [], [], 1.0)[0]:
                 seen += os.read(proc.stdout.fileno(), 4096)
         svc = L.ipc_service(0, shm)
+        assert svc.counters_on_host()     # this library's server publishes them; no device copy per batch
         train, valid, test = ref["train"], ref["valid"], ref["test"]
         steps, vbs, tbs = oracle_mod.coordinate([len(train)], [len(valid)], [len(test)], 24)
         assert svc.get_steps() == list(steps)

@@ -41,6 +41,31 @@ def test_segment_layout_and_steps(oracle_mod):
     assert not os.path.exists("/dev/shm/" + name)
 
 
+def test_counters_are_published_in_a_companion_host_segment():
+    """Next to the reference's segment the server keeps "<name>_ctr": int32 [8][2][32], node_counter then
+    edge_counter of the last batch finished on (device, pipe); it goes away with the environment."""
+    name = _name("ctr")
+    env = L.IPCEnv(2, name)
+    try:
+        path = "/dev/shm/" + name + "_ctr"
+        assert os.path.getsize(path) == 8 * 2 * 32 * 4
+        seg = np.memmap(path, dtype=np.int32, mode="r", shape=(8, 2, 32))
+        assert not seg.any()
+        nc, ec = np.arange(16, dtype=np.int32) + 100, np.arange(16, dtype=np.int32) + 200
+        env.publish_counters(1, 0, nc, ec)
+        env.publish_counters(0, 1, ec, nc)
+        np.testing.assert_array_equal(seg[1, 0], np.concatenate([nc, ec]))
+        np.testing.assert_array_equal(seg[0, 1], np.concatenate([ec, nc]))
+        assert not seg[0, 0].any() and not seg[1, 1].any()
+        import pytest
+        with pytest.raises(L.LegionError):
+            env.publish_counters(0, 2, nc, ec)
+        del seg
+    finally:
+        env.Finalize()
+    assert not os.path.exists("/dev/shm/" + name + "_ctr")
+
+
 def _trainer(name, n_batches, q):
     """The trainer's half of the protocol (ipc_cuda_kernel.cu:70-106): post sem_r once per pipe,
     then wait sem_w / post sem_r while rotating the pipe."""
