@@ -172,6 +172,15 @@ int legion_cache_set_host_codec(LegionCache *c, int32_t codec);
  * (feature_len + 4) bytes rounded up to 16, with the quantiser the caches use. */
 int legion_quantize_table(int32_t dev_id, int32_t codec, const void *rows, int64_t n_rows, int32_t feature_len,
                           void *out_rows, void *stream);
+/* The capacity split of the reference's cost model (CandidateSelection / CostModel, cache/cache.cu:354-557)
+ * for a clique of one process per GPU: how many rows of a per-GPU budget go to this GPU's stripe of
+ * the clique's cache and how many to private copies of hot rows held by peers.  Node weights in rank
+ * order come from the degrees (indptr_dev) or from presampled access counts (counts_dev; one of the two
+ * may be NULL); cost_local_peer_host gives the relative cost of a row served locally / by a peer / by
+ * the host table (NULL: 0.16, 1, 15 as measured on B200).  Every rank computes the same plan. */
+int legion_cache_plan(int32_t dev_id, const int32_t *order_dev, const int64_t *indptr_dev, const uint32_t *counts_dev,
+                      int64_t n_nodes, int64_t budget_rows, int32_t world, const double cost_local_peer_host[3],
+                      int64_t *stripe_rows, int64_t *replica_rows, void *stream);
 /* Private copies of the hottest rows that the striping gave to OTHER clique members, so that this
  * GPU serves them from its own memory instead of over NVLink.  The reference stripes only
  * (cache/cache_impl.cuh:104-109): when the clique's budget exceeds the table (8 GPUs x 20%), its

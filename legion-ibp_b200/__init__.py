@@ -143,6 +143,16 @@ class UnifiedCache:
         _check(lib().legion_cache_hotness_order(C.c_int32(dev_id), _ptr(counts_dev), C.c_int64(_numel(counts_dev)),
                                                 _ptr(order_out), _stream(stream)))
 
+    @staticmethod
+    def plan(dev_id, order_dev, n_nodes, budget_rows, world, indptr=None, counts=None, cost=None, stream=None):
+        """(stripe_rows, replica_rows) of a per-GPU row budget; weights from degrees or presampled counts."""
+        a, b = C.c_int64(), C.c_int64()
+        cost_arr = (C.c_double * 3)(*cost) if cost is not None else None
+        _check(lib().legion_cache_plan(C.c_int32(dev_id), _ptr(order_dev), _ptr(indptr), _ptr(counts), C.c_int64(n_nodes),
+                                       C.c_int64(budget_rows), C.c_int32(world), cost_arr, C.byref(a), C.byref(b),
+                                       _stream(stream)))
+        return a.value, b.value
+
     def fill_static(self, order_dev, host_table, stream=None, row_of_id=None):
         """row_of_id (device int32 per node): row of host_table that holds each node, for tables that are
         not in id order."""

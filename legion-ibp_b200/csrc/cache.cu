@@ -9,6 +9,7 @@
 #include "common.cuh"
 
 #include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
 #include <cuda_fp8.h>
 
 namespace legion {
@@ -141,6 +142,22 @@ static_fill_kernel(const int32_t *__restrict__ order, int64_t n_order, int32_t c
             for (int i = f + 4 + lane; i < slot_bytes; i += 32) dst[i] = 0;
         }
     }
+}
+
+// weight of the node at every rank: its degree (indptr given) or its presampled access count
+__global__ void ranked_weight_kernel(const int32_t *__restrict__ order, const int64_t *__restrict__ indptr,
+                                     const uint32_t *__restrict__ counts, int64_t n, double *w)
+{
+    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t v = order[t];
+        w[t] = indptr != nullptr ? (double)(indptr[v + 1] - indptr[v]) : (double)counts[v];
+    }
+}
+
+__global__ void pick_kernel(const double *__restrict__ cum, const int64_t *__restrict__ at, int n_at, double *out)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_at) out[i] = at[i] > 0 ? cum[at[i] - 1] : 0.0;
 }
 
 static int grid_stride(int64_t n, int sm_count)
@@ -400,6 +417,101 @@ extern "C" int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev
                                         const void *host_table, void *stream)
 {
     return legion_cache_fill_static_rows(c, order_dev, n_order, host_table, nullptr, stream);
+}
+
+// Splits one GPU's row budget into its stripe of the clique's cache and private copies of hot rows
+// held by peers (legion_cache_add_replicas).  mass(x) = share of all row accesses that go to the x
+// hottest nodes, estimated from the weights in rank order (degree, or presampled counts).  With R
+// replica rows and S = budget - R stripe rows per GPU the clique holds C = min(n, S * world) nodes; the
+// T = R * world / (world - 1) hottest of them are local on every GPU, the others with probability
+// 1 / world; the plan minimises
+//   host * (1 - mass(C)) + peer * (mass(C) - mass(T)) * (world - 1) / world + local * (the rest).
+// R = 0 is the reference's plan (striping only, cache/cache_impl.cuh:104-109).
+extern "C" int legion_cache_plan(int32_t dev_id, const int32_t *order_dev, const int64_t *indptr_dev,
+                                 const uint32_t *counts_dev, int64_t n_nodes, int64_t budget_rows, int32_t world,
+                                 const double cost_local_peer_host[3], int64_t *stripe_rows, int64_t *replica_rows,
+                                 void *stream)
+{
+    LG_ARG(order_dev != nullptr && (indptr_dev != nullptr || counts_dev != nullptr), "NULL pointer");
+    LG_ARG(stripe_rows != nullptr && replica_rows != nullptr, "NULL result pointer");
+    LG_ARG(n_nodes > 0 && n_nodes < (1ll << 31) && world >= 1 && world <= LEGION_MAX_DEVICE, "bad size");
+    if (budget_rows < 0) budget_rows = 0;
+    if (budget_rows > n_nodes) budget_rows = n_nodes;
+    *stripe_rows = budget_rows;
+    *replica_rows = 0;
+    if (world == 1 || budget_rows == 0) return LEGION_OK;
+    const double c_local = cost_local_peer_host ? cost_local_peer_host[0] : 0.16;
+    const double c_peer = cost_local_peer_host ? cost_local_peer_host[1] : 1.0;
+    const double c_host = cost_local_peer_host ? cost_local_peer_host[2] : 15.0;
+    constexpr int kSteps = 64;
+    const int64_t full = (n_nodes + world - 1) / world;
+    int64_t cand_r[kSteps + 1], cand_s[kSteps + 1], at[2 * (kSteps + 1) + 1];
+    for (int i = 0; i <= kSteps; ++i) {
+        int64_t r = budget_rows / 2 * i / kSteps;
+        int64_t stripe = budget_rows - r < full ? budget_rows - r : full;
+        if (r > stripe) r = stripe;
+        int64_t covered = stripe * world < n_nodes ? stripe * world : n_nodes;
+        int64_t local_top = r * world / (world - 1);
+        if (local_top > covered) local_top = covered;
+        cand_r[i] = r;
+        cand_s[i] = stripe;
+        at[2 * i] = covered;
+        at[2 * i + 1] = local_top;
+    }
+    at[2 * (kSteps + 1)] = n_nodes;
+    const int n_at = 2 * (kSteps + 1) + 1;
+
+    LG_CUDA(cudaSetDevice(dev_id));
+    cudaStream_t s = (cudaStream_t)stream;
+    double *w = nullptr, *d_out = nullptr;
+    int64_t *d_at = nullptr;
+    void *tmp = nullptr;
+    size_t tmp_bytes = 0;
+    double h_out[2 * (kSteps + 1) + 1];
+    cudaError_t e = cudaMalloc(&w, sizeof(double) * n_nodes);
+    if (e == cudaSuccess) e = cudaMalloc(&d_out, sizeof(double) * n_at);
+    if (e == cudaSuccess) e = cudaMalloc(&d_at, sizeof(int64_t) * n_at);
+    if (e == cudaSuccess) e = cub::DeviceScan::InclusiveSum(nullptr, tmp_bytes, w, w, (int)n_nodes, s);
+    if (e == cudaSuccess) e = cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1);
+    if (e == cudaSuccess) {
+        ranked_weight_kernel<<<grid_stride(n_nodes, sm_count_of(dev_id)), 256, 0, s>>>(order_dev, indptr_dev, counts_dev, n_nodes, w);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cub::DeviceScan::InclusiveSum(tmp, tmp_bytes, w, w, (int)n_nodes, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_at, at, sizeof(int64_t) * n_at, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) {
+        pick_kernel<<<(n_at + 127) / 128, 128, 0, s>>>(w, d_at, n_at, d_out);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_out, d_out, sizeof(double) * n_at, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(w); cudaFree(d_out); cudaFree(d_at); cudaFree(tmp);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        set_error("legion_cache_plan: %s", cudaGetErrorString(e));
+        return e == cudaErrorMemoryAllocation ? LEGION_E_NOMEM : LEGION_E_CUDA;
+    }
+    const double total = h_out[n_at - 1];
+    int best = 0;
+    double best_cost = 0.0;
+    for (int i = 0; i <= kSteps; ++i) {
+        const double m_c = total > 0.0 ? h_out[2 * i] / total : 0.0;
+        const double m_t = total > 0.0 ? h_out[2 * i + 1] / total : 0.0;
+        const double t = c_host * (1.0 - m_c) + c_peer * (m_c - m_t) * (world - 1) / world +
+                         c_local * (m_t + (m_c - m_t) / world);
+        if (i == 0 || t < best_cost - 1e-12) {
+            best_cost = t;
+            best = i;
+        }
+    }
+    int64_t stripe = cand_s[best], r = cand_r[best];
+    if (stripe == full) {  // memory left over once the stripes cover the table goes to replicas
+        int64_t spare = budget_rows - stripe < stripe ? budget_rows - stripe : stripe;
+        if (spare > r) r = spare;
+    }
+    *stripe_rows = stripe;
+    *replica_rows = r;
+    return LEGION_OK;
 }
 
 extern "C" int legion_cache_set_host_codec(LegionCache *c, int32_t codec)

@@ -546,3 +546,43 @@ def test_bulk_copy_engine_gathers_the_same_rows(oracle_mod, feat_len, dtype, kg)
         L._check(L.lib().legion_set_tunable(b"gather_engine", 2))
     for r in rigs:
         r.close()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_native_cache_plan_matches_the_host_planner(oracle_mod, world):
+    """legion_cache_plan (weights scanned on the device) picks the split that server.plan_clique_cache
+    picks from the same weights, for degree weights and for presampled counts."""
+    import torch
+    from legion_ibp_b200 import server
+    indptr, _ = small_graph(20000, 300000, 13)
+    n = len(indptr) - 1
+    d_indptr = torch.from_numpy(indptr).cuda()
+    order = torch.empty(n, dtype=torch.int32, device="cuda")
+    L.UnifiedCache.degree_order(0, d_indptr, order)
+    rng = np.random.default_rng(world)
+    counts = torch.from_numpy(rng.zipf(1.5, n).clip(0, 10 ** 6).astype(np.int32)).cuda()
+    corder = torch.empty(n, dtype=torch.int32, device="cuda")
+    L.UnifiedCache.hotness_order(0, counts, corder)
+
+    def cost(mass, stripe, rep):
+        c_l, c_p, c_h = server.ROW_COST
+        if world == 1:
+            return c_h * (1 - mass(stripe)) + c_l * mass(stripe)
+        cov = min(n, stripe * world)
+        top = min(cov, rep * world // (world - 1))
+        return (c_h * (1 - mass(cov)) + c_p * (mass(cov) - mass(top)) * (world - 1) / world +
+                c_l * (mass(top) + (mass(cov) - mass(top)) / world))
+
+    for budget in (n // 50, n // 10, n // 5, n):
+        for kind in ("degree", "counts"):
+            if kind == "degree":
+                mass = server.degree_mass(d_indptr, order)
+                got = L.UnifiedCache.plan(0, order, n, budget, world, indptr=d_indptr)
+            else:
+                mass = server.weight_mass(counts, corder)
+                got = L.UnifiedCache.plan(0, corder, n, budget, world, counts=counts)
+            want = server.plan_clique_cache(mass, n, budget, world)
+            assert got[0] + got[1] <= budget and got[1] <= got[0]
+            assert got == tuple(want) or abs(cost(mass, *got) - cost(mass, *want)) <= 1e-9 * max(1.0, cost(mass, *want))
+    with pytest.raises(L.LegionError):
+        L.UnifiedCache.plan(0, order, n, 10, 2)     # neither degrees nor counts
