@@ -178,7 +178,7 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
         LG_CUDA(cudaStreamCreateWithFlags(&r->s_launch[i], cudaStreamNonBlocking));
         LG_CUDA(cudaEventCreateWithFlags(&r->pipe_done[i], cudaEventDisableTiming));
         r->pipe_busy[i] = false;
-        memset(&r->pg[i], 0, sizeof(PipeGraph));
+        r->pg[i] = PipeGraph();
     }
     LG_CUDA(cudaEventCreate(&r->t_begin));
     LG_CUDA(cudaEventCreate(&r->t_end));
