@@ -74,15 +74,40 @@ def load_oracle():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons while the timed region runs.  The region is a few milliseconds, so
+    the driver library is polled from a thread (a sample every millisecond or so); when it cannot be
+    loaded, `nvidia-smi -lms` stands in, which manages a sample per 100 ms."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    # bits of the driver's clocks-event-reasons mask
+    BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, gpu_index=0):
         self.rows, self.proc, self.gpu = [], None, gpu_index
+        self.nv, self.handle, self.polling, self.samples, self.t = None, None, False, [], None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            import torch
+            pr = torch.cuda.get_device_properties(self.gpu)
+            bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+            return pynvml, pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
 
     def start(self):
+        try:
+            self.nv, self.handle = self._nvml_handle()
+            self.nv.nvmlDeviceGetClockInfo(self.handle, self.nv.NVML_CLOCK_SM)
+            self.polling = True
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return
+        except Exception:
+            self.nv = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -92,11 +117,35 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def _poll(self):
+        nv, h = self.nv, self.handle
+        mx = 0.0
+        try:
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        except Exception:
+            pass
+        while self.polling:
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                why = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.samples.append((float(sm), float(mx), int(why)))
+            except Exception:
+                pass
+            time.sleep(0.001)
+
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if self.nv is not None:
+            self.polling = False
+            self.t.join(timeout=2)
+            sm = sorted(s[0] for s in self.samples)
+            reasons = sorted(n for n, bit in self.BITS.items() if any(s[2] & bit for s in self.samples))
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None,
+                    "sm_max_mhz": max(s[1] for s in self.samples) if self.samples else None,
+                    "reasons": reasons, "samples": len(sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -115,7 +164,7 @@ class ClockSampler:
                     if r[5 + i].lower().startswith("active"):
                         reasons.add(nm)
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 def make_graph(cfg, device, seed=0):
@@ -507,7 +556,6 @@ def main():
         step += 1
     runner.sync()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     ms_total = max_over_ranks(runner.timing()["batch_ms"])
     value = args.steps * world / (ms_total * 1e-3)
     assert pool.device_error() == 0, "device-side error flag set"
@@ -538,6 +586,9 @@ def main():
     pipeline = {"window_ms_per_batch": tp["batch_ms"] / args.steps, "miss_ms_per_batch": tp["miss_ms"] / args.steps,
                 "miss_stream_busy_frac": tp["miss_ms"] / tp["batch_ms"] if tp["batch_ms"] > 0 else None}
     runner.set_options(use_graph=True, time_kernels=False)
+    # the timed region is a few milliseconds: the clock samples run on through the kernel-timing passes
+    # above, which replay the same batches
+    clocks = sampler.stop() if rank == 0 else None
     if args.profile_only:
         if rank == 0:
             print(json.dumps({"profile_only": True, "ms_per_step": ms_total / args.steps, "value": value}), flush=True)
