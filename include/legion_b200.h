@@ -194,6 +194,8 @@ int legion_cache_add_replicas(LegionCache *c, const int32_t *order_dev, int64_t 
 /* Pointer tables of the clique (d_float_feature_cache_ptr_, cache/cache.cu:601-622). */
 int legion_cache_partition(LegionCache *c, void **ptr, int64_t *bytes);
 int legion_cache_set_peer(LegionCache *c, int32_t k, const void *partition_ptr);
+/* The lookup table of a cache of uncompressed rows without replicas (LEGION_E_ARG otherwise: such tables
+ * only make sense together with the cache's own slot size and replica region). */
 int legion_cache_lut(LegionCache *c, int32_t **lut_dev);
 /* The same pointer table across processes (one process per GPU).  With kg > 1 the partition is
  * allocated as shareable memory: export it as a POSIX file descriptor (pass it to the peers over a
@@ -248,7 +250,10 @@ int legion_pool_set_batch(LegionPool *p, int32_t iter, int32_t mode, int32_t pip
 int legion_pool_set_rng(LegionPool *p, uint64_t seed, int32_t max_rounds);
 /* First error raised on the device since the last reset (the reference prints and exits,
  * engine/operator_impl.cu:17-25): 0 none, 1 id map full, 2 edge buffer overflow, 3 node buffer
- * overflow.  Synchronises `stream`. */
+ * overflow, 4 a bulk copy of the gather timed out (the pipe's output is invalid; stop issuing on it);
+ * 5 a seed id (or a neighbour id stored in the topology) outside [0, n_nodes) was met: such an id is
+ * never used as an index, its slot in the batch reads -1 like a slot past the end of the seed list
+ * (engine/operator_impl.cu:41-43), and the rest of the batch is complete.  Synchronises `stream`. */
 int legion_pool_device_error(LegionPool *p, void *stream, int32_t *err, int32_t reset);
 
 /* ---- the five operators (engine/operator_impl.cuh:11-69) ---------------------------- */
@@ -283,9 +288,14 @@ int legion_io_complete(void *stream, LegionCache *cache, LegionPool *pool, int32
  * library image, so every GPU that loads the library holds about 3 MB for it until the process
  * exits.  This call, and everything it calls, performs no cudaMalloc / cudaFree.
  *
- *   ids_dev      n_rows int32 node ids on the device (ids < 0 leave their output row untouched)
+ *   dev_id       the GPU to run on; the call makes it the calling thread's current device
+ *                (cudaSetDevice) and leaves it so
+ *   ids_dev      n_rows int32 node ids on the device (ids outside [0, n_nodes) leave their output
+ *                row untouched)
  *   lut_dev      one int32 per node: gpu*capacity + row for a cached node, LEGION_CACHEMISS_FLAG
- *                otherwise (legion_cache_lut); NULL = nothing is cached
+ *                otherwise (legion_cache_lut); NULL = nothing is cached.  capacity, kg and
+ *                partitions must be the ones the table was built for; an entry that names a member
+ *                >= kg or a NULL partition is served from host_table like a miss
  *   partitions   host array of kg device pointers, the clique's cache partitions (uncompressed rows)
  *   host_table   pinned host table that serves the misses, or NULL (missed rows stay untouched)
  *   out_dev      n_rows * row_bytes bytes on the device, rows in the order of ids_dev

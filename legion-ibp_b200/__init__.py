@@ -330,7 +330,9 @@ def gather_rows_noalloc(stream, dev_id, ids_dev, lut_ptr, capacity, kg, ki, part
                         row_bytes, out_dev):
     """Lookup + gather of one id list through the entry point that allocates nothing (its scratch is a
     fixed array inside the library).  For callers that must not allocate device memory when they call in;
-    at most NOALLOC_MAX_ROWS ids per call, calls on one GPU must not overlap."""
+    at most NOALLOC_MAX_ROWS ids per call, calls on one GPU must not overlap.  Makes dev_id the current device."""
+    if lut_ptr and len(partition_ptrs) < kg:
+        raise LegionError("gather_rows_noalloc: %d partition pointers for a clique of %d" % (len(partition_ptrs), kg))
     parts = (C.c_void_p * max(1, len(partition_ptrs)))(*partition_ptrs)
     _check(lib().legion_gather_rows_noalloc(_stream(stream), C.c_int32(dev_id), _ptr(ids_dev),
                                             C.c_int64(ids_dev.numel()), C.c_void_p(lut_ptr), C.c_int32(capacity),

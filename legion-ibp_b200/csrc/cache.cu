@@ -573,6 +573,7 @@ extern "C" int legion_cache_lut(LegionCache *c, int32_t **lut_dev)
 {
     LG_ARG(c != nullptr && c->kind == 0 && lut_dev != nullptr, "not a static cache");
     LG_ARG(c->part[c->kg] == nullptr, "the lookup table of a cache with replicas is only usable through the cache handle");
+    LG_ARG(c->codec == LEGION_CODEC_RAW, "the lookup table of a compressed cache is only usable through the cache handle");
     *lut_dev = c->lut;
     return LEGION_OK;
 }

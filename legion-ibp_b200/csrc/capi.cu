@@ -293,18 +293,23 @@ extern "C" int legion_pool_set_rng(LegionPool *p, uint64_t seed, int32_t max_rou
 }
 
 // First error raised by a kernel of this pool since the last reset (0 = none): 1 id map full,
-// 2 edge buffer overflow, 3 node buffer overflow.  Synchronises the stream.
+// 2 edge buffer overflow, 3 node buffer overflow, 4 bulk copy timed out (these stop the batch);
+// 5 a seed or neighbour id outside [0, n_nodes) was met: it was skipped without being read, the
+// rest of the batch is complete.  Synchronises the stream.
 extern "C" int legion_pool_device_error(LegionPool *p, void *stream, int32_t *err, int32_t reset)
 {
     LG_ARG(p != nullptr && err != nullptr, "NULL pointer");
     LG_CUDA(cudaSetDevice(p->dev_id));
     *err = 0;
     for (int i = 0; i < p->pipes; ++i) {
-        int32_t e = 0;
-        LG_CUDA(cudaMemcpyAsync(&e, p->ctl[i] + CTL_ERROR, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+        int32_t w[CTL_WORDS];
+        LG_CUDA(cudaMemcpyAsync(w, p->ctl[i], sizeof(w), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
         LG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-        if (e != 0 && *err == 0) *err = e;
-        if (reset && e != 0) LG_CUDA(cudaMemsetAsync(p->ctl[i] + CTL_ERROR, 0, 4, (cudaStream_t)stream));
+        // an error that stopped the batch comes before "an id was skipped"
+        const int32_t e = w[CTL_ERROR] != 0 ? w[CTL_ERROR] : (w[CTL_BAD_IDS] != 0 ? (int32_t)DERR_BAD_ID : 0);
+        if (e != 0 && (*err == 0 || *err == DERR_BAD_ID)) *err = e;
+        if (reset && w[CTL_ERROR] != 0) LG_CUDA(cudaMemsetAsync(p->ctl[i] + CTL_ERROR, 0, 4, (cudaStream_t)stream));
+        if (reset && w[CTL_BAD_IDS] != 0) LG_CUDA(cudaMemsetAsync(p->ctl[i] + CTL_BAD_IDS, 0, 4, (cudaStream_t)stream));
     }
     return LEGION_OK;
 }
@@ -331,7 +336,8 @@ extern "C" int legion_batch_generate(void *stream, LegionFeatures *feature, Legi
     int64_t size = ((int64_t)batch_size * (counter + 1) >= total_cap) ? (total_cap - first) : batch_size;
     if (size < 0) size = 0;
     return launch_batch_generate((cudaStream_t)stream, pool,
-                                 make_batch_ctl(pool, cache, all_ids, all_labels, total_cap, first, (int32_t)size));
+                                 make_batch_ctl(pool, cache, all_ids, all_labels, total_cap, first, (int32_t)size,
+                                                feature->n_nodes));
 }
 
 extern "C" int legion_random_sample(void *stream, LegionGraph *graph, LegionCache *cache, LegionPool *pool,
@@ -420,7 +426,7 @@ extern "C" int legion_run_batch_host(LegionGraph *graph, LegionFeatures *feature
     LG_CUDA(cudaMemcpyAsync(pool->label_stage[pipe], hs + pool->batch_size, sizeof(int32_t) * n_seeds,
                             cudaMemcpyHostToDevice, s));
     int rc = launch_batch_generate(s, pool, make_batch_ctl(pool, cache, pool->seed_stage[pipe], pool->label_stage[pipe],
-                                                            n_seeds, 0, n_seeds));
+                                                            n_seeds, 0, n_seeds, graph->n_nodes));
     if (rc != LEGION_OK) return rc;
     rc = run_ops(s, graph, cache, pool, dev_id);
     if (rc != LEGION_OK) return rc;

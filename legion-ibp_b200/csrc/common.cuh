@@ -59,11 +59,13 @@ enum Ctl {
     CTL_MISS_COUNT = 8,
     CTL_BACK_DIRTY = 9,  // the back region of the id map holds entries (kept across batches until it is cleared)
     CTL_TICKET_D = 10,
+    CTL_BAD_IDS = 11,   // sticky: an id outside [0, n_nodes) was met and skipped (reported as DERR_BAD_ID; the batch goes on)
     CTL_WORDS = 16
 };
 
 enum DeviceError { DERR_NONE = 0, DERR_MAP_FULL = 1, DERR_EDGE_OVERFLOW = 2, DERR_NODE_OVERFLOW = 3,
-                   DERR_BULK_TIMEOUT = 4 };  // a bulk copy of the gather did not complete within its wait limit
+                   DERR_BULK_TIMEOUT = 4,  // a bulk copy of the gather did not complete within its wait limit
+                   DERR_BAD_ID = 5 };      // a node id outside [0, n_nodes) reached the path; it was skipped, not read
 
 struct NodeRec {  // per input node of a hop, written by the count kernel
     int64_t start;  // first CSR position of the adjacency list
@@ -101,6 +103,7 @@ struct BatchCtl {
     uint32_t k0, k1;            // RNG key
     int32_t max_rounds;
     int32_t clock;              // LRU batch clock
+    int32_t n_nodes;            // ids outside [0, n_nodes) are skipped and raise DERR_BAD_ID
 };
 
 }  // namespace legion
@@ -209,7 +212,7 @@ extern int g_pdl;
 extern int g_map_front_shift;
 int launch_batch_generate(cudaStream_t s, LegionPool *p, const BatchCtl &ctl, bool defer_seeds = false);
 BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t *all_ids, const int32_t *all_labels,
-                        int32_t total_cap, int64_t first, int32_t size);
+                        int32_t total_cap, int64_t first, int32_t size, int64_t n_nodes);
 const void *map_clear_kernel_address();
 int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32_t fanout, int32_t hop,
                       int32_t op_id, bool seeds_pending = false);

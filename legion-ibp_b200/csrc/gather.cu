@@ -88,13 +88,17 @@ __device__ __forceinline__ const uint8_t *resolve(const GatherParams &p, int32_t
     gidx = LEGION_CACHEMISS_FLAG;
     where = 3;
     host_row = id;
-    if (id < 0) return nullptr;
+    if (id < 0 || id >= p.n_nodes) return nullptr;  // not a node: nothing is read, the output row stays as it is
     if (p.lut != nullptr) gidx = __ldg(&p.lut[id]);
     if (gidx >= 0) {
         int d = gidx / p.capacity;
         int row = gidx - d * p.capacity;
-        where = (d == p.ki || d == p.kg) ? 0 : 1;
-        return p.part[d] + (int64_t)row * p.slot_bytes;
+        const uint8_t *base = d <= LEGION_MAX_DEVICE ? p.part[d] : nullptr;
+        if (base != nullptr) {
+            where = (d == p.ki || d == p.kg) ? 0 : 1;
+            return base + (int64_t)row * p.slot_bytes;
+        }
+        gidx = LEGION_CACHEMISS_FLAG;  // the table names a partition this call was not given: served as a miss
     }
     if (gidx <= -3) host_row = -(gidx + 3);
     gidx = LEGION_CACHEMISS_FLAG;
@@ -138,7 +142,7 @@ __device__ __forceinline__ void add_stats(unsigned long long *stats, int where, 
 // The two halves of resolve(), for callers that fetch the table entry of the next chunk early.
 __device__ __forceinline__ int32_t lookup_raw(const GatherParams &p, int32_t id)
 {
-    return (id >= 0 && p.lut != nullptr) ? __ldg(&p.lut[id]) : LEGION_CACHEMISS_FLAG;
+    return (id >= 0 && id < p.n_nodes && p.lut != nullptr) ? __ldg(&p.lut[id]) : LEGION_CACHEMISS_FLAG;
 }
 __device__ __forceinline__ const uint8_t *decode_raw(const GatherParams &p, int32_t id, int32_t raw, int32_t &gidx,
                                                      int &where, int32_t &host_row)
@@ -146,13 +150,17 @@ __device__ __forceinline__ const uint8_t *decode_raw(const GatherParams &p, int3
     gidx = LEGION_CACHEMISS_FLAG;
     where = 3;
     host_row = id;
-    if (id < 0) return nullptr;
+    if (id < 0 || id >= p.n_nodes) return nullptr;  // not a node: nothing is read, the output row stays as it is
     if (raw >= 0) {
-        gidx = raw;
         int d = raw / p.capacity;
         int row = raw - d * p.capacity;
-        where = (d == p.ki || d == p.kg) ? 0 : 1;
-        return p.part[d] + (int64_t)row * p.slot_bytes;
+        const uint8_t *base = d <= LEGION_MAX_DEVICE ? p.part[d] : nullptr;
+        if (base != nullptr) {
+            gidx = raw;
+            where = (d == p.ki || d == p.kg) ? 0 : 1;
+            return base + (int64_t)row * p.slot_bytes;
+        }
+        // the table names a partition this call was not given: served as a miss
     }
     if (raw <= -3) host_row = -(raw + 3);
     if (p.host != nullptr) {
@@ -232,8 +240,10 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
 // 512-byte rows) in flight with a handful of registers, and three CTAs of four warps hold 192 KB of
 // reads in flight per SM.  Rows, shared-memory slots and output rows are 16-byte aligned and a multiple
 // of 16 bytes long, which is all that the untiled bulk copy asks for; no multicast, no tensor map.
-// Every wait is bounded: on a timeout the kernel raises DERR_BULK_TIMEOUT, drains what it issued (again
-// bounded) and returns.
+// Every wait is bounded: on a timeout the warp raises DERR_BULK_TIMEOUT, waits once more (again bounded) for
+// the copies it issued and leaves.  After that error the pipe's output rows are invalid and the caller must
+// stop issuing work on this context (legion_pool_device_error reports it): a copy that is still on its way
+// when the CTA retires would land in shared memory that no longer belongs to it.
 constexpr int kBulkWarps = 4;
 constexpr int kBulkWaitLimit = 1 << 20;
 
@@ -846,8 +856,9 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
     gp.miss_count = p->miss_count[pipe];
     gp.err = p->ctl[pipe] + CTL_ERROR;
 
-    if (g_gather_engine == 1 && (c == nullptr || c->codec == LEGION_CODEC_RAW) && row_bytes % 16 == 0 && row_bytes <= 1024 &&
-        gp.slot_bytes == row_bytes) {
+    // the bulk-copy engine has only ever read this GPU's own memory: a clique of more than one GPU keeps the register path
+    if (g_gather_engine == 1 && gp.kg == 1 && (c == nullptr || c->codec == LEGION_CODEC_RAW) && row_bytes % 16 == 0 &&
+        row_bytes <= 1024 && gp.slot_bytes == row_bytes) {
         // 32 rows per warp in shared memory: 64 KB per CTA for 512-byte rows, three CTAs per SM
         const size_t smem = (size_t)kBulkWarps * 32 * row_bytes;
         static bool attr_set[64] = { false };
@@ -1069,7 +1080,7 @@ extern "C" int legion_gather_rows_noalloc(void *stream, int32_t dev_id, const in
     if (row_bytes % 16 == 0 && row_bytes <= 2048) {
         int vpl = (row_bytes / 16 + 31) / 32;
         switch (vpl) {
-        case 1: launch_vec<1, 4>(grid, s, gp); break;
+        case 1: launch_vec<1, 8>(grid, s, gp); break;  // the shape the pool-based path launches
         case 2: launch_vec<2, 2>(grid, s, gp); break;
         case 3: launch_vec<3, 2>(grid, s, gp); break;
         default: launch_vec<4, 2>(grid, s, gp); break;

@@ -475,7 +475,7 @@ extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, i
     int64_t size = ((int64_t)bs * (local_batch_id + 1) >= total_cap) ? (total_cap - first) : bs;  // operator_impl.cu:162
     if (size < 0) size = 0;
     return enqueue_ctl(r, make_batch_ctl(p, r->cache, r->feature->ids[mode], r->feature->labels[mode], total_cap, first,
-                                         (int32_t)size), 0);
+                                         (int32_t)size, r->graph->n_nodes), 0);
 }
 
 // Host-buffer interface with batches in flight.  submit copies the seeds in and starts the batch;
@@ -596,7 +596,8 @@ static int submit_host_impl(LegionRunner *r, const int32_t *seeds, const int32_t
     }
     memcpy(p->h_stage[pipe], seeds, sizeof(int32_t) * n_seeds);
     memcpy(p->h_stage[pipe] + p->batch_size, labels, sizeof(int32_t) * n_seeds);
-    const BatchCtl v = make_batch_ctl(p, r->cache, p->seed_stage[pipe], p->label_stage[pipe], n_seeds, 0, n_seeds);
+    const BatchCtl v = make_batch_ctl(p, r->cache, p->seed_stage[pipe], p->label_stage[pipe], n_seeds, 0, n_seeds,
+                                      r->graph->n_nodes);
     const int64_t spec_n = r->spec_nodes, spec_e = r->spec_edges;  // what issue_front copies ahead
     if (extra) {
         rc = issue_front(r, v, n_seeds, bound, true);
@@ -852,7 +853,7 @@ extern "C" int legion_runner_presample(LegionRunner *r, int32_t first_batch, int
         if (size <= 0) break;
         rc = launch_batch_generate(r->s_sample, p, make_batch_ctl(p, r->cache, r->feature->ids[LEGION_TRAINMODE],
                                                                    r->feature->labels[LEGION_TRAINMODE], total_cap, first,
-                                                                   (int32_t)size));
+                                                                   (int32_t)size, r->graph->n_nodes));
         for (int h = 0; h < p->hop_num && rc == LEGION_OK; ++h)
             rc = launch_sample_hop(r->s_sample, p, r->graph, p->fanout[h], h, LEGION_INTRABATCH_CON * (h + 1));
         if (rc == LEGION_OK) rc = launch_hotness(r->s_sample, p, counts_dev);

@@ -239,7 +239,8 @@ __global__ void map_clear_kernel(uint4 *slots2, int64_t n_pairs, int32_t *ctl, i
         slots2[i] = empty;
     if (blockIdx.x == 0 && threadIdx.x < 16) {
         // the error word is sticky; the dirty flag and its ticket are read by every CTA of this kernel
-        if (threadIdx.x != CTL_ERROR && threadIdx.x != CTL_BACK_DIRTY && threadIdx.x != CTL_TICKET_D) ctl[threadIdx.x] = 0;
+        if (threadIdx.x != CTL_ERROR && threadIdx.x != CTL_BAD_IDS && threadIdx.x != CTL_BACK_DIRTY && threadIdx.x != CTL_TICKET_D)
+            ctl[threadIdx.x] = 0;
         nc[threadIdx.x] = 0;  // cudaMemsetAsync of both counters, operator_impl.cu:158-159
         ec[threadIdx.x] = 0;
     }
@@ -274,6 +275,10 @@ __global__ void batch_generate_kernel(const BatchCtl *__restrict__ b, int32_t *i
             labels[idx] = -1;
         } else {
             int32_t id = all_ids[pos % total_cap];
+            if (id >= b->n_nodes) {  // not a node of this graph: skipped like an overrun slot, and reported
+                id = -1;
+                ctl[CTL_BAD_IDS] = 1;
+            }
             ids[idx] = id;
             labels[idx] = all_labels[pos % total_cap];
             if (id >= 0) map_insert_min(map, mask, id, idx, ctl);
@@ -304,6 +309,7 @@ hop_count_kernel(const int64_t *__restrict__ indptr, int32_t *ids, int32_t fanou
     __shared__ int smem[kScanThreads / 32];
     __shared__ int s_flag;
     const int n = FIRST ? b->size : ctl[CTL_N_NODES];
+    const int n_limit = b->n_nodes;
     const int n_tiles = (n + TILE - 1) / TILE;
     if (FIRST && blockIdx.x == 0 && threadIdx.x == 0) {
         counter_update(nc, ec, 0, n, b->hop_num);
@@ -326,6 +332,10 @@ hop_count_kernel(const int64_t *__restrict__ indptr, int32_t *ids, int32_t fanou
                     if (pos < total_cap) {  // operator_impl.cu:41-43
                         v[j] = b->all_ids[pos % total_cap];
                         lab = b->all_labels[pos % total_cap];
+                        if (v[j] >= n_limit) {  // not a node of this graph: skipped like an overrun slot, and reported
+                            v[j] = -1;
+                            ctl[CTL_BAD_IDS] = 1;
+                        }
                     }
                     ids[idx] = v[j];
                     labels[idx] = lab;
@@ -342,11 +352,15 @@ hop_count_kernel(const int64_t *__restrict__ indptr, int32_t *ids, int32_t fanou
         for (int j = 0; j < IPT; ++j) {
             start[j] = 0; deg[j] = 0; cnt[j] = 0;
             if (base + j < n && v[j] >= 0) {
-                int64_t s = indptr[v[j]];
-                int64_t e = indptr[v[j] + 1];
-                start[j] = s;
-                deg[j] = (int32_t)(e - s);
-                cnt[j] = min(deg[j], fanout);
+                if (v[j] < n_limit) {
+                    int64_t s = indptr[v[j]];
+                    int64_t e = indptr[v[j] + 1];
+                    start[j] = s;
+                    deg[j] = (int32_t)(e - s);
+                    cnt[j] = min(deg[j], fanout);
+                } else {  // a neighbour id that the topology itself got wrong is never followed
+                    ctl[CTL_BAD_IDS] = 1;
+                }
             }
         }
         int tsum = 0;
@@ -578,7 +592,7 @@ static inline int grid_for(int64_t items, int per_cta, int cap)
 const void *map_clear_kernel_address() { return (const void *)map_clear_kernel; }
 
 BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t *all_ids, const int32_t *all_labels,
-                        int32_t total_cap, int64_t first, int32_t size)
+                        int32_t total_cap, int64_t first, int32_t size, int64_t n_nodes)
 {
     BatchCtl v;
     v.all_ids = all_ids;
@@ -592,6 +606,7 @@ BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t
     v.k1 = (uint32_t)(p->rng_seed >> 32);
     v.max_rounds = p->max_rounds;
     v.clock = (c != nullptr && c->kind == 1) ? c->clock : 0;
+    v.n_nodes = (n_nodes > 0 && n_nodes < 0x7FFFFFFF) ? (int32_t)n_nodes : 0x7FFFFFFF;
     return v;
 }
 

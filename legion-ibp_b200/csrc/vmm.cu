@@ -10,6 +10,7 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <stdlib.h>
 #include <unistd.h>
 
 namespace legion {
@@ -76,7 +77,10 @@ static CUmemAllocationProp prop_of(int dev)
 int vmm_alloc(int dev, int64_t bytes, VmmBlock *out)
 {
     Driver *d = driver();
-    if (!d->ok) {
+    // LEGION_NO_VMM=1 stands for a platform without the virtual memory management API (tests of the
+    // cudaMalloc + peer-access fallback)
+    const char *off = getenv("LEGION_NO_VMM");
+    if (!d->ok || (off != nullptr && off[0] == '1')) {
         set_error("CUDA virtual memory management entry points are not available");
         return LEGION_E_STATE;
     }
@@ -214,7 +218,17 @@ extern "C" int legion_cache_import_peer(LegionCache *c, int32_t k, int32_t fd, i
 extern "C" int legion_cache_allow_device(LegionCache *c, int32_t dev)
 {
     LG_ARG(c != nullptr && c->kind == 0 && dev >= 0, "not a static cache");
-    if (c->own_block.ptr == nullptr || dev == c->dev_id) return LEGION_OK;
+    if (dev == c->dev_id) return LEGION_OK;
+    if (c->own_block.ptr == nullptr) {
+        // the partition is ordinary cudaMalloc memory (no virtual memory management on this platform):
+        // device `dev` reads it through peer access, or the call fails; it never reports success without
+        // either, because the gather would then dereference a pointer that `dev` cannot reach
+        int cur = -1;
+        LG_CUDA(cudaGetDevice(&cur));
+        int rc = legion_enable_peer_access(dev, c->dev_id);
+        if (cur >= 0) cudaSetDevice(cur);
+        return rc;
+    }
     Driver *d = driver();
     CUmemAccessDesc acc;
     memset(&acc, 0, sizeof(acc));

@@ -610,3 +610,63 @@ def test_sampling_server_binary_end_to_end(oracle_mod, tmp_path):
         if proc.poll() is None:
             proc.kill()
     assert not os.path.exists("/dev/shm/" + shm)
+
+
+def test_seed_ids_outside_the_graph_are_skipped_and_reported(oracle_mod):
+    """A client that hands in a seed id >= n_nodes (or a topology that stores one) must not make any
+    kernel index with it: the slot reads -1 like a slot past the end of the seed list, the rest of the
+    batch equals the batch without that seed, and the pool reports error 5."""
+    w = _world(oracle_mod)
+    r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], None)
+    b = w["batch"]
+    seeds = w["train"][:b].copy()
+    labels = w["labels"][:b].copy()
+    bad = seeds.copy()
+    bad[7] = w["n"]            # first id past the table
+    bad[11] = 2 ** 31 - 5      # far outside
+    f = w["table"].shape[1]
+    outs = {}
+    for name, s in (("bad", bad), ("good", seeds)):
+        mn, me = w["pool"].max_nodes, w["pool"].max_edges
+        ids, lab = np.empty(mn, np.int32), np.empty(b, np.int32)
+        src, dst = np.empty(me, np.int32), np.empty(me, np.int32)
+        nc, ec = np.zeros(16, np.int32), np.zeros(16, np.int32)
+        feat = np.zeros((mn, f), np.float32)
+        r.submit_host(s, labels, 5)
+        nn, ne = r.collect_host(ids, lab, src, dst, nc, ec, feat)
+        outs[name] = (ids[:nn].copy(), src[:ne].copy(), dst[:ne].copy(), feat[:nn].copy())
+        err = w["pool"].device_error()
+        assert err == (5 if name == "bad" else 0), err
+    ids_bad = outs["bad"][0]
+    assert ids_bad[7] == -1 and ids_bad[11] == -1
+    keep = np.ones(b, bool)
+    keep[[7, 11]] = False
+    np.testing.assert_array_equal(ids_bad[:b][keep], seeds[keep])
+    # every node that was found carries its own row, and none of the ids is out of range
+    found = ids_bad >= 0
+    assert ids_bad[found].max() < w["n"]
+    np.testing.assert_array_equal(outs["bad"][3][found], w["table"][ids_bad[found]])
+    # the error word is not sticky for this kind: the next batch is complete again
+    np.testing.assert_array_equal(outs["good"][0][:b], seeds)
+    assert w["pool"].device_error() == 0
+    r.Finalize()
+
+
+def test_partition_without_shareable_memory_needs_peer_access(oracle_mod, monkeypatch):
+    """On a platform without the virtual memory management API a clique partition is plain cudaMalloc
+    memory.  legion_cache_allow_device must then either enable peer access for the reading device or
+    fail; it must never answer OK and leave the reader with a pointer it cannot dereference."""
+    import torch
+    monkeypatch.setenv("LEGION_NO_VMM", "1")
+    c = L.UnifiedCache(0, 1000, 64, 100, kg=2, ki=0)
+    with pytest.raises(L.LegionError):
+        c.export_partition()          # not shareable memory
+    assert L.lib().legion_cache_allow_device(c.h, 0) == 0   # the owner itself: nothing to do
+    rc = L.lib().legion_cache_allow_device(c.h, 1)
+    if torch.cuda.device_count() < 2:
+        assert rc != 0                 # there is no device 1 to enable: refused, with a message
+        assert L.lib().legion_last_error()
+    else:
+        assert rc == 0                 # peer access of device 1 to device 0 is on now
+        assert L.lib().legion_enable_peer_access(1, 0) == 0   # already enabled is not an error
+    c.close()

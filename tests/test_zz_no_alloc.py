@@ -50,15 +50,32 @@ def test_two_calls_match_the_pool_based_entry_point(oracle_mod, feat_len):
     cap = n // 5
     calls = [rng.integers(0, n, 50000).astype(np.int32), rng.integers(0, n, 777).astype(np.int32)]
     calls[1][5] = -1  # an invalid id leaves its row untouched
-    for ids_np in calls:
+    calls[1][9] = n   # and so does an id past the table
+    side = torch.cuda.Stream()
+    # a first call makes the driver load the kernels this row size uses (code is loaded lazily, which takes
+    # device memory once per kernel); the calls below must then leave the device's free memory where it was
+    warm_ids = torch.arange(64, dtype=torch.int32, device="cuda")
+    warm_out = torch.zeros((64, row_bytes), dtype=torch.uint8, device="cuda")
+    L.gather_rows_noalloc(None, 0, warm_ids, 0, 0, 1, 0, [], h_table, n, row_bytes, warm_out)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(warm_out.cpu().numpy().view(np.float32), table[:64])
+    for k, ids_np in enumerate(calls):
         want, ci, cache = _reference_rows(h_table, order, cap, ids_np, n, row_bytes)
         part_ptr, _ = cache.partition()
         d_ids = torch.from_numpy(ids_np).cuda()
         out = torch.full((len(ids_np), row_bytes), 0xA5, dtype=torch.uint8, device="cuda")
-        L.gather_rows_noalloc(None, 0, d_ids, cache.lut_ptr(), cap, 1, 0, [part_ptr], h_table, n, row_bytes, out)
         torch.cuda.synchronize()
+        # the property the entry point exists for: device memory in use does not move across the call
+        # (the second call runs on a stream of its own)
+        free_before, _ = torch.cuda.mem_get_info()
+        reserved_before = torch.cuda.memory_reserved()
+        L.gather_rows_noalloc(side if k == 1 else None, 0, d_ids, cache.lut_ptr(), cap, 1, 0, [part_ptr], h_table, n,
+                              row_bytes, out)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.cuda.memory_reserved() == reserved_before
         got = out.cpu().numpy()
-        valid = ids_np >= 0
+        valid = (ids_np >= 0) & (ids_np < n)
         np.testing.assert_array_equal(got[valid], want[valid])                       # bit-exact
         np.testing.assert_array_equal(got[valid].view(np.float32), table[ids_np[valid]])
         assert (got[~valid] == 0xA5).all()
