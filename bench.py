@@ -5,15 +5,17 @@
     python bench.py --impl reference --steps K --warmup W     # CPU pipeline on the host cores
 
 A step is one mini-batch per GPU: seeds -> neighbour sampling (all hops) -> dedup / relabel ->
-cache lookup -> feature gather, outputs left in the double-buffered hand-off buffers.
+cache lookup -> feature gather, outputs left in the hand-off buffers.
 `value` = batches of all ranks / device time (CUDA events on the runner's streams, max over ranks)
-with all inputs resident; `e2e` = the same batches through the host-buffer C-ABI call, seeds copied
-in from pinned host memory and the block structure copied back inside the timed region.
+with all inputs resident: windows of K batches, each bracketed by a barrier and a synchronize, are
+repeated until half a second has been timed, and the median window is reported.
+`e2e` = the same batches through the host-buffer C-ABI call, seeds copied in from pinned host memory
+and the block structure copied back inside the timed region.
 One JSON line on stdout (rank 0).
 """
 import argparse
+import ctypes
 import json
-import math
 import os
 import subprocess
 import sys
@@ -23,8 +25,11 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# Workloads.  elt: element type of a feature row ("f32" / "f16"); table: "host" = whole table in pinned
+# host memory with a per-GPU cache in front of it, "striped" = no host copy at all, the table is spread
+# over the clique's caches (every rank makes the rows of its own stripe).
 CONFIGS = {
-    # products-shaped (BASELINE.json configs[0]); whole table cached
+    # products-shaped (configs[0]); whole table cached
     "c1": dict(name="products-shaped RMAT", n_nodes=2449029, n_pairs=34000000, feat_len=100, classes=47,
                train_frac=0.08, batch=800, fanout=[25, 10], cache_frac=1.0),
     # paper100M-shaped (configs[1]): the configuration the metric is quoted on
@@ -33,23 +38,36 @@ CONFIGS = {
     # c2 scaled down to a few GB (inputs still larger than L2) for profiler captures
     "mid": dict(name="mid RMAT (profiler capture)", n_nodes=8000000, n_pairs=64000000, feat_len=128, classes=172,
                 train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2),
-    # compressed-cache variant of c2 (configs[3]): the same byte budget holds int8 rows + fp32 scale
-    "c4": dict(name="paper100M-shaped RMAT, int8 cache", n_nodes=111059956, n_pairs=900000000, feat_len=128,
-               classes=172, train_frac=0.011, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="int8"),
+    # MAG240M-shaped (configs[2]): 768 x fp16 rows, 375 GB spread over the caches of 8 GPUs, no host copy;
+    # 7 of 8 rows are read from peer partitions over NVLink
+    "c3": dict(name="MAG240M-shaped RMAT", n_nodes=244160499, n_pairs=875000000, feat_len=768, elt="f16", classes=153,
+               train_frac=0.0046, batch=1024, fanout=[25, 15], table="striped"),
+    # the same layout on a graph that 1-2 GPUs can hold (profiler captures, tests of the harness)
+    "c3s": dict(name="MAG240M-shaped rows on a small RMAT", n_nodes=6000000, n_pairs=48000000, feat_len=768, elt="f16",
+                classes=153, train_frac=0.02, batch=1024, fanout=[25, 15], table="striped"),
+    # compressed-cache variant of configs[0] (configs[3]): int8 codes + fp32 row scale in the byte budget of c1
+    "c4": dict(name="products-shaped RMAT, int8 cache", n_nodes=2449029, n_pairs=34000000, feat_len=100, classes=47,
+               train_frac=0.08, batch=800, fanout=[25, 10], cache_frac=1.0, codec="int8"),
+    # the same codec in front of the paper100M-shaped table, where the cache does not hold everything
+    "c2-int8": dict(name="paper100M-shaped RMAT, int8 cache", n_nodes=111059956, n_pairs=900000000, feat_len=128,
+                    classes=172, train_frac=0.011, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="int8"),
     "mid-int8": dict(name="mid RMAT, int8 cache", n_nodes=8000000, n_pairs=64000000, feat_len=128, classes=172,
                      train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="int8"),
     "mid-e4m3": dict(name="mid RMAT, fp8 e4m3 cache", n_nodes=8000000, n_pairs=64000000, feat_len=128, classes=172,
                      train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="e4m3"),
     # compressed rows in the host table too: a miss moves 144 instead of 512 bytes over the host link
-    "c4h": dict(name="paper100M-shaped RMAT, int8 cache and int8 host table", n_nodes=111059956, n_pairs=900000000,
-                feat_len=128, classes=172, train_frac=0.011, batch=8000, fanout=[25, 10], cache_frac=0.2, codec="int8",
-                host_codec=True),
+    "c2-int8-host": dict(name="paper100M-shaped RMAT, int8 cache and int8 host table", n_nodes=111059956,
+                         n_pairs=900000000, feat_len=128, classes=172, train_frac=0.011, batch=8000, fanout=[25, 10],
+                         cache_frac=0.2, codec="int8", host_codec=True),
     "mid-int8-host": dict(name="mid RMAT, int8 cache and int8 host table", n_nodes=8000000, n_pairs=64000000,
                           feat_len=128, classes=172, train_frac=0.05, batch=8000, fanout=[25, 10], cache_frac=0.2,
                           codec="int8", host_codec=True),
-    # dynamic-LRU stress (configs[4]) scaled 1:25 so that the host table (10 GB) fits any box: Zipf(1.1)
-    # seeds, three hops, set-associative LRU cache of 10% of the table
-    "c5s": dict(name="LRU stress RMAT (configs[4] scaled 1:25)", n_nodes=20000000, n_pairs=80000000, feat_len=128,
+    # dynamic-LRU stress (configs[4]): Zipf(1.1) seeds, three hops, per-GPU set-associative LRU cache of 10% of
+    # the table; the 256 GB host table needs a box with that much memory (else a window of it, see host_window)
+    "c5": dict(name="LRU stress RMAT", n_nodes=500000000, n_pairs=2100000000, feat_len=128, classes=172,
+               train_frac=0.0, batch=4096, fanout=[15, 10, 5], cache_frac=0.1, lru_ways=8, zipf=1.1, zipf_batches=96),
+    # the same workload scaled 1:25 (host table 10 GB)
+    "c5s": dict(name="LRU stress RMAT scaled 1:25", n_nodes=20000000, n_pairs=80000000, feat_len=128,
                 classes=172, train_frac=0.0, batch=4096, fanout=[15, 10, 5], cache_frac=0.1, lru_ways=8,
                 zipf=1.1, zipf_batches=160),
     # reduced copy of c2 for checking the harness itself on small machines (never the default)
@@ -57,10 +75,10 @@ CONFIGS = {
                  train_frac=0.2, batch=2000, fanout=[25, 10], cache_frac=0.2),
 }
 
-
-# dram__bytes_read.sum + dram__bytes_write.sum of gather_vec_kernel per row served from GPU memory, from the
-# profiler capture of the "mid" config summarised in profiles/gather_kernels_mid_config.md
+# dram__bytes_read.sum + dram__bytes_write.sum of gather_vec_kernel per 512-byte row served from GPU memory, from
+# a profiler capture of the "mid" config (the full-size workload is too large for a multi-pass capture)
 NCU_DRAM_BYTES_PER_HIT_ROW = 811
+RNG_SEED = 0x5EED
 
 
 def load_pkg():
@@ -73,14 +91,17 @@ def load_oracle():
     return ge._oracle()
 
 
+def elt_of(cfg):
+    import torch
+    return {"f32": (torch.float32, 4), "f16": (torch.float16, 2)}[cfg.get("elt", "f32")]
+
+
 class ClockSampler:
-    """SM clock and throttle reasons while the timed region runs.  The region is a few milliseconds, so
-    the driver library is polled from a thread (a sample every millisecond or so); when it cannot be
-    loaded, `nvidia-smi -lms` stands in, which manages a sample per 100 ms."""
+    """SM clock and throttle reasons while the timed region runs, polled from the driver library in a
+    thread (a sample every millisecond or so); `nvidia-smi -lms` stands in when it cannot be loaded."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
-    # bits of the driver's clocks-event-reasons mask
     BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, gpu_index=0):
@@ -172,56 +193,58 @@ def make_graph(cfg, device, seed=0):
     return synth.rmat_csr(cfg["n_nodes"], cfg["n_pairs"], seed=seed, device=device)
 
 
-def host_buffer(n_bytes, shared_name, rank, world, dev=0, fill=None):
+def host_memory_bytes():
+    try:
+        return os.sysconf("SC_PAGE_SIZE") * os.sysconf("SC_PHYS_PAGES")
+    except (ValueError, OSError):
+        return 1 << 62
+
+
+def host_buffer(n_bytes, shared_name, rank, world, dev=0, barrier=None):
     """uint8 buffer in host memory that every rank's GPU can read: pinned (one rank) or one POSIX shared
-    segment that rank 0 creates and populates (`fill(buffer)`, else zeros) and every rank page-locks."""
+    segment that rank 0 creates and every rank maps and page-locks.  Not initialised."""
     import torch
     if world == 1:
-        t = torch.empty(n_bytes, dtype=torch.uint8, pin_memory=True)
-        if fill is not None:
-            fill(t)
-        return t
-    import torch.distributed as dist
+        return torch.empty(n_bytes, dtype=torch.uint8, pin_memory=True)
     L = load_pkg()
     path = "/dev/shm/" + shared_name
     if rank == 0:
         t = torch.from_file(path, shared=True, size=n_bytes, dtype=torch.uint8)
-        if fill is not None:
-            fill(t)
-        else:
-            t.zero_()
-    dist.barrier()
+    barrier()
     if rank != 0:
         t = torch.from_file(path, shared=True, size=n_bytes, dtype=torch.uint8)
     try:
         L.host_register(dev, t)
     except L.LegionError as e:
-        # the driver would not page-lock the shared segment: every rank keeps a pinned copy of its own
-        print("rank %d: %s; falling back to a private pinned copy" % (rank, e), file=sys.stderr, flush=True)
-        own = torch.empty(n_bytes, dtype=torch.uint8, pin_memory=True)
-        own.copy_(t)
-        t = own
-    dist.barrier()
+        # the driver would not page-lock the shared segment: every rank keeps a pinned buffer of its own
+        print("rank %d: %s; falling back to a private pinned buffer" % (rank, e), file=sys.stderr, flush=True)
+        t = torch.empty(n_bytes, dtype=torch.uint8, pin_memory=True)
+        t.private = True
+    barrier()
     if rank == 0:
         os.unlink(path)  # the mappings stay valid
     return t
 
 
-def host_table(cfg, shared_name=None, rank=0, world=1, dev=0):
-    """[N, F] fp32 table in host memory, filled by rank 0; pinned / registered for zero-copy reads."""
-    import torch
+def fill_host_rows(table2d, rank, world, barrier, node_of_row=None, private=False):
+    """Every rank writes its share of the rows of a shared table (all rows of a private one): row r holds
+    the features of node r, or of node_of_row[r]."""
     from legion_ibp_b200 import synth
-    n, f = cfg["n_nodes"], cfg["feat_len"]
-    fill = lambda b: synth.features_into(b.view(torch.float32).view(n, f), seed=0)
-    return host_buffer(n * f * 4, shared_name, rank, world, dev, fill).view(torch.float32).view(n, f)
+    n = table2d.shape[0]
+    private = world == 1 or private
+    lo, hi = (0, n) if private else (n * rank // world, n * (rank + 1) // world)
+    synth.features_into(table2d, seed=0, row_ids=node_of_row, first=lo, last=hi)
+    if barrier is not None:
+        barrier()
 
 
-def host_link_peak(table):
-    """GB/s of a plain pinned host -> device copy, the ceiling for zero-copy reads of the host table."""
+def copy_peak(kind, n_bytes=1 << 30):
+    """GB/s of a plain pinned copy over the host link: kind "h2d" (the ceiling for zero-copy reads of the
+    host table) or "d2h" (the ceiling for the export of the block structure)."""
     import torch
-    n = min(table.numel(), 1 << 28)  # 1 GiB of fp32
-    src = table.view(-1)[:n]
-    dst = torch.empty(n, dtype=table.dtype, device="cuda")
+    host = torch.empty(n_bytes, dtype=torch.uint8, pin_memory=True)
+    devt = torch.empty(n_bytes, dtype=torch.uint8, device="cuda")
+    src, dst = (host, devt) if kind == "h2d" else (devt, host)
     for _ in range(2):
         dst.copy_(src, non_blocking=True)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -231,13 +254,13 @@ def host_link_peak(table):
         dst.copy_(src, non_blocking=True)
     b.record()
     torch.cuda.synchronize()
-    return 3 * n * 4 / (a.elapsed_time(b) * 1e-3) / 1e9
+    return 3 * n_bytes / (a.elapsed_time(b) * 1e-3) / 1e9
 
 
 def host_rows_seeds_first(order, seeds, n_cached):
-    """row_of[id] for a host table that holds, in this order: the uncached seed nodes, the other
-    uncached nodes by falling degree, and last the nodes whose rows live in the GPU caches (read once,
-    at fill time).  The synthetic table is random, so it can be taken to be in this order already."""
+    """(row_of[id], node_of[row]) for a host table that holds, in this order: the uncached seed nodes, the
+    other uncached nodes by falling degree, and last the nodes whose rows live in the GPU caches (read
+    once, at fill time)."""
     import torch
     n = order.numel()
     rank_of = torch.empty(n, dtype=torch.int64, device=order.device)
@@ -245,11 +268,11 @@ def host_rows_seeds_first(order, seeds, n_cached):
     cls = torch.ones(n, dtype=torch.int64, device=order.device)
     cls[seeds.long()] = 0
     cls[order[:min(n, n_cached)].long()] = 2
-    perm = torch.argsort(cls * n + rank_of)
+    node_of = torch.argsort(cls * n + rank_of)
     del cls, rank_of
     row_of = torch.empty(n, dtype=torch.int32, device=order.device)
-    row_of[perm] = torch.arange(n, dtype=torch.int32, device=order.device)
-    return row_of
+    row_of[node_of] = torch.arange(n, dtype=torch.int32, device=order.device)
+    return row_of, node_of.to(torch.int32)
 
 
 def zipf_batches(n_nodes, batch, n_batches, s, world=1, rank=0):
@@ -263,11 +286,13 @@ def zipf_batches(n_nodes, batch, n_batches, s, world=1, rank=0):
     draws = draws[:3 * batch * n_batches].view(n_batches, 3 * batch)
     out = []
     for i in range(n_batches):
-        row = draws[i].long()
-        first = torch.full((n_nodes,), 1 << 40, dtype=torch.int64, device=row.device)
-        first.scatter_reduce_(0, row, torch.arange(row.numel(), device=row.device), reduce="amin")
-        keep = first[row] == torch.arange(row.numel(), device=row.device)
-        uniq = row[keep][:batch]
+        row = draws[i]
+        uniq, first = None, None
+        srt, idx = torch.sort(row, stable=True)
+        keep = torch.ones_like(srt, dtype=torch.bool)
+        keep[1:] = srt[1:] != srt[:-1]
+        first = torch.sort(idx[keep]).values  # positions of first appearances, in draw order
+        uniq = row[first][:batch]
         assert uniq.numel() == batch, "not enough distinct Zipf draws for a batch"
         out.append(uniq.to(torch.int32))
     return torch.cat(out)
@@ -287,10 +312,78 @@ def bounds(batch, fanout):
     return nodes, edges
 
 
+def workload_config(cfg, n_gpus):
+    elt = cfg.get("elt", "f32")
+    if cfg.get("table") == "striped":
+        kind = "whole table striped over the caches of the %d GPU(s) (no host copy), peer rows by NVLink loads" % n_gpus
+    elif cfg.get("lru_ways"):
+        kind = ("%d-way set-associative LRU cache of %d%% of the table per GPU, Zipf(%.1f) seeds, misses by zero-copy "
+                "from pinned host memory" % (cfg["lru_ways"], int(cfg["cache_frac"] * 100), cfg.get("zipf", 0.0)))
+    elif cfg.get("codec", "raw") != "raw":
+        kind = "static degree-ordered %s cache (codes + fp32 row scale) in %d%% of the table's bytes per GPU" % (
+            cfg["codec"], int(cfg["cache_frac"] * 100))
+        kind += (", host table held as the same compressed rows" if cfg.get("host_codec") else
+                 ", misses by zero-copy from pinned host memory")
+    else:
+        kind = "static degree-ordered cache %d%% of the table per GPU, misses by zero-copy from pinned host memory" % int(
+            cfg["cache_frac"] * 100)
+    return {"workload": "%s: %d nodes, %s dim %d, batch %d, fanout %s, %s" % (
+                cfg["name"], cfg["n_nodes"], elt, cfg["feat_len"], cfg["batch"], cfg["fanout"], kind),
+            "batch_per_gpu": cfg["batch"], "fanout": cfg["fanout"], "feat_len": cfg["feat_len"],
+            "parallelism": "dp%d, cache striped over %d GPU(s)" % (n_gpus, n_gpus),
+            "l2": "inputs larger than L2 (topology, cache partition and host table are each GBs)"}
+
+
+def time_cpu(fn, cores, first_guess, target_s=3.0):
+    """Runs fn(first_batch, n_batches) once to warm up, once to estimate its rate, and once for about
+    target_s seconds; returns (batches/s, batches, seconds) of the last run."""
+    fn(0, cores)
+    t0 = time.perf_counter()
+    fn(cores, first_guess)
+    rate = first_guess / max(time.perf_counter() - t0, 1e-6)
+    nb = max(first_guess, int(rate * target_s) // cores * cores)
+    t0 = time.perf_counter()
+    fn(cores + first_guess, nb)
+    dt = time.perf_counter() - t0
+    return nb / dt, nb, dt
+
+
+def cpu_arms(O, indptr, indices, seeds, labels, batch, fanout, table, cores, target_s=3.0):
+    """Both CPU pipelines on the same workload: the sampler written for a CPU (Floyd's algorithm, a
+    reusable relabelling map per thread) and the lock-step replay of the GPU's algorithm that the parity
+    tests use.  The faster one is the baseline."""
+    n_iters = max(1, (len(seeds) - 1) // batch)
+
+    def run(fn):
+        return lambda first, nb: fn(indptr, indices, seeds, labels, batch, first % max(1, n_iters - nb), nb, fanout, 1,
+                                    table, cores)
+    native = time_cpu(run(O.cpu_pipeline_native), cores, 2 * cores, target_s)
+    lockstep = time_cpu(run(O.cpu_pipeline), cores, 2 * cores, target_s / 2)
+    best = max(native, lockstep, key=lambda r: r[0])
+    which = "cpu-native" if best is native else "lock-step"
+    return {"value": best[0], "unit": "batches/s", "cores": cores, "kind": "port", "sampler": which,
+            "values": {"cpu-native sampler (Floyd, reusable map per thread)": native[0],
+                       "lock-step replay of the GPU algorithm (the parity checker)": lockstep[0]},
+            "sample": "%d batches of the same workload (sample + relabel + gather), %d threads, %.1f s" % (
+                best[1], cores, best[2])}
+
+
+def reference_table(cfg):
+    """Host table of the CPU arm: the whole table in node-id order, or a window of it (row = id % rows) when
+    the whole table does not fit the box."""
+    import torch
+    from legion_ibp_b200 import synth
+    dtype, esz = elt_of(cfg)
+    n, f = cfg["n_nodes"], cfg["feat_len"]
+    rows = min(n, int(host_memory_bytes() * 0.4) // (f * esz))
+    table = torch.empty((rows, f), dtype=dtype)
+    synth.features_into(table, seed=0)
+    return table.view(torch.uint8).view(rows, f * esz).numpy(), rows
+
+
 def run_reference(args, cfg):
     """CPU arm: the DGL CPU pipeline restated in oracle/ (sample -> relabel -> gather), one batch
     per host thread, on the same synthetic workload."""
-    import numpy as np
     import torch
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -302,56 +395,46 @@ def run_reference(args, cfg):
     indptr, indices = ip.cpu().numpy(), ix.cpu().numpy()
     del ip, ix
     from legion_ibp_b200 import synth
-    labels, train, _, _ = synth.labels_and_split(cfg["n_nodes"], cfg["classes"], cfg["train_frac"], device=dev)
-    train = train.cpu().numpy()
-    tl = labels.cpu().numpy()[train]
-    table = torch.empty((cfg["n_nodes"], cfg["feat_len"]), dtype=torch.float32)
-    synth.features_into(table, seed=0)
-    table = table.numpy()
+    n = cfg["n_nodes"]
+    if cfg.get("zipf"):
+        assert dev == "cuda", "the Zipf seed generator of this config runs on a GPU"
+        train = zipf_batches(n, cfg["batch"], cfg["zipf_batches"], cfg["zipf"]).cpu().numpy()
+        tl = (train % cfg["classes"]).astype("int32")
+    else:
+        labels, train, _, _ = synth.labels_and_split(n, cfg["classes"], cfg["train_frac"], device=dev)
+        train = train.cpu().numpy()
+        tl = labels.cpu().numpy()[train]
     if dev == "cuda":
         torch.cuda.empty_cache()
+    table, rows = reference_table(cfg)
     cores = O.num_threads()
     batch, fanout = cfg["batch"], cfg["fanout"]
     per_step = cores  # one batch per thread and step
     n_iters = (len(train) - 1) // batch
-    it = 0
-    for _ in range(args.warmup):
-        O.cpu_pipeline(indptr, indices, train, tl, batch, it % max(1, n_iters - per_step), per_step, fanout, 1, table, cores)
-        it += per_step
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        O.cpu_pipeline(indptr, indices, train, tl, batch, it % max(1, n_iters - per_step), per_step, fanout, 1, table, cores)
-        it += per_step
-    dt = time.perf_counter() - t0
-    value = args.steps * per_step / dt
+    results = {}
+    for name, fn in (("cpu-native", O.cpu_pipeline_native), ("lock-step", O.cpu_pipeline)):
+        it = 0
+        for _ in range(args.warmup):
+            fn(indptr, indices, train, tl, batch, it % max(1, n_iters - per_step), per_step, fanout, 1, table, cores)
+            it += per_step
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            fn(indptr, indices, train, tl, batch, it % max(1, n_iters - per_step), per_step, fanout, 1, table, cores)
+            it += per_step
+        dt = time.perf_counter() - t0
+        results[name] = (args.steps * per_step / dt, dt)
+    which = max(results, key=lambda k: results[k][0])
+    value, dt = results[which]
     line = {"impl": "reference", "metric": "sampled+gathered mini-batches/sec", "value": value, "unit": "batches/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(cfg, args.gpus),
-            "cpu_baseline": {"value": value, "unit": "batches/s", "cores": cores, "kind": "port",
-                             "sample": "%d batches per step (one per thread), %d steps" % (per_step, args.steps)},
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg.get("elt", "f32"),
+            "data": "synthetic", "config": workload_config(cfg, args.gpus),
+            "cpu_baseline": {"value": value, "unit": "batches/s", "cores": cores, "kind": "port", "sampler": which,
+                             "values": {k: v[0] for k, v in results.items()},
+                             "sample": "%d batches per step (one per thread), %d steps; host table of %d rows in "
+                                       "node-id order" % (per_step, args.steps, rows)},
             "e2e": {"value": value, "unit": "batches/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
-
-
-def workload_config(cfg, n_gpus):
-    if cfg.get("lru_ways"):
-        kind = "%d-way set-associative LRU cache of %d%% of the table per GPU, Zipf(%.1f) seeds" % (
-            cfg["lru_ways"], int(cfg["cache_frac"] * 100), cfg.get("zipf", 0.0))
-    elif cfg.get("codec", "raw") != "raw":
-        kind = "static degree-ordered %s cache (codes + fp32 row scale) in %d%% of the table's bytes per GPU" % (
-            cfg["codec"], int(cfg["cache_frac"] * 100))
-        if cfg.get("host_codec"):
-            kind += ", host table held as the same compressed rows"
-    else:
-        kind = "static %s-ordered cache %d%% of the table per GPU" % (cfg.get("cache_order", "degree"),
-                                                                    int(cfg["cache_frac"] * 100))
-    return {"workload": "%s: %d nodes, fp32 dim %d, batch %d, fanout %s, %s, misses by zero-copy from pinned host "
-                        "memory" % (cfg["name"], cfg["n_nodes"], cfg["feat_len"], cfg["batch"], cfg["fanout"], kind),
-            "batch_per_gpu": cfg["batch"], "fanout": cfg["fanout"], "feat_len": cfg["feat_len"],
-            "parallelism": "dp%d, cache striped over %d GPU(s)" % (n_gpus, n_gpus),
-            "l2": "inputs larger than L2 (topology, cache partition and host table are each GBs)"}
-
 
 
 def main():
@@ -361,33 +444,27 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
-    ap.add_argument("--cpu-sample-batches", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cache-frac", type=float, default=None, help="override the cached fraction of the table")
-    ap.add_argument("--pipes", type=int, default=2, help="batches in flight (the hand-off protocol uses 2)")
+    ap.add_argument("--pipes", type=int, default=0,
+                    help="batches in flight on the device (0: 4 for static caches, 2 for the LRU cache; the hand-off to "
+                         "trainer processes uses 2)")
     ap.add_argument("--host-layout", default="seeds_first", choices=["id", "seeds_first"],
                     help="row order of the pinned host table: node-id order, or uncached seed nodes first and the "
                          "other uncached nodes by falling degree (shorter spans for the zero-copy misses)")
     ap.add_argument("--no-replicas", action="store_true",
                     help="N > 1: stripe the whole per-GPU budget over the clique (the reference's placement) instead "
                          "of planning private copies of the hottest peer rows")
-    ap.add_argument("--cache-order", default="degree", choices=["degree", "hotness", "seeds_degree"],
-                    help="ranking behind the static cache: node degree (what the configs name); the reference's own "
-                         "policy, access counts of one presampled epoch (engine/server.cu:94-122); or the training "
-                         "seeds (every one of them is read once per epoch) followed by the other nodes by degree")
-    ap.add_argument("--e2e-outputs", default="bound", choices=["bound", "copy", "none"],
-                    help="e2e leg: block structure written by the batch into page-locked arrays named at submit "
-                         "time (default), copied out by collect after the batch (two batches in flight), or not "
-                         "moved at all (diagnostic)")
+    ap.add_argument("--no-seed-staging", action="store_true",
+                    help="fetch the rows of uncached seeds like any other miss instead of staging them by the copy engine")
     ap.add_argument("--tunable", action="append", default=[], metavar="NAME=VALUE",
-                    help="launch-shape knob passed to legion_set_tunable (measurement sweeps)")
+                    help="launch-shape knob passed to legion_set_tunable")
     ap.add_argument("--profile-only", action="store_true",
-                    help="set-up, warm-up and the timed steps only (for runs under a profiler); prints no bench line")
+                    help="set-up, warm-up and one timed window only (for runs under a profiler); prints no bench line")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.cache_frac is not None:
         cfg["cache_frac"] = args.cache_frac
-    cfg["cache_order"] = args.cache_order
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
@@ -415,97 +492,9 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     t_setup = time.perf_counter()
 
-    # ---- synthetic inputs -------------------------------------------------------------------
-    indptr, indices = make_graph(cfg, "cuda")
-    torch.cuda.empty_cache()
-    n, f = cfg["n_nodes"], cfg["feat_len"]
-    row_bytes = f * 4
-    n_edges = int(indices.numel())
-    labels, train, _, _ = synth.labels_and_split(n, cfg["classes"], max(cfg["train_frac"], 1e-6), device="cuda")
-    if cfg.get("zipf"):
-        train = zipf_batches(n, cfg["batch"], cfg["zipf_batches"], cfg["zipf"], world, rank)
-    mine = train[(train % world) == rank].contiguous()  # id % ngpu split, storage_management.cu:214-250
-    mine_labels = labels[mine.long()].contiguous()
-    table = host_table(cfg, "legion_b200_bench_features", rank, world, dev)
-
-    # ---- storage, cache, pool, runner ------------------------------------------------------------
-    g = L.GraphStorage(dev, indptr, indices)
-    fs = L.FeatureStorage(dev, n, row_bytes, table)
-    fs.set_split(L.TRAINMODE, mine, mine_labels)
-    order = torch.empty(n, dtype=torch.int32, device="cuda")
-    counts = None
-    if args.cache_order == "hotness":
-        # PreSc: one epoch of sampling only, every touched node counted; counts of all ranks added up
-        pre_pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, 2)
-        pre_pool.set_rng(0xC0FFEE + rank, 64)  # not the measured runs' stream: those batches must be new to the cache
-        pre = L.Runner(dev, g, fs, None, pre_pool, None)
-        counts = torch.zeros(n, dtype=torch.int32, device="cuda")
-        pre.presample(0, max(1, (int(mine.numel()) - 1) // cfg["batch"]), counts)
-        torch.cuda.synchronize()
-        pre.Finalize()
-        pre_pool.close()
-        if dist is not None:
-            dist.all_reduce(counts)
-        L.UnifiedCache.hotness_order(dev, counts, order)
-    else:
-        L.UnifiedCache.degree_order(dev, indptr, order)
-        if args.cache_order == "seeds_degree":
-            is_seed = torch.zeros(n, dtype=torch.bool, device="cuda")
-            is_seed[train.long()] = True
-            first = is_seed[order.long()]
-            order = torch.cat([order[first], order[~first]]).contiguous()
-            del is_seed, first
-    codec_name = cfg.get("codec", "raw")
-    codec = {"raw": L.CODEC_RAW, "int8": L.CODEC_INT8, "e4m3": L.CODEC_E4M3}[codec_name]
-    slot_bytes = row_bytes if codec == L.CODEC_RAW else (f + 4 + 15) // 16 * 16
-    budget = cap = min(n, int(n * cfg["cache_frac"] * row_bytes / slot_bytes))
-    replica_rows = 0
-    if cap * world >= n:
-        cap = (n + world - 1) // world
-    row_of = None
-    stored = None  # compressed copy of the host table (configs with host_codec)
-
     def barrier0():
         if dist is not None:
             dist.barrier()
-
-    lru_ways = cfg.get("lru_ways", 0)
-    if lru_ways:
-        # every GPU keeps its own LRU cache (no clique: the contents change every batch)
-        cap = cap // lru_ways * lru_ways
-        cache = L.UnifiedCache(dev, n, row_bytes, 0, lru=(cap // lru_ways, lru_ways))
-        cache.set_host_table(table)
-        args.host_layout = "id"
-    else:
-        if cfg.get("host_codec"):
-            stored = host_buffer(n * slot_bytes, "legion_b200_bench_codes", rank, world, dev).view(n, slot_bytes)
-            if rank == 0:
-                L.quantize_table(dev, codec, table, n, f, stored)
-            barrier0()
-        if world > 1 and not args.no_replicas:
-            from legion_ibp_b200 import server
-            mass = server.degree_mass(indptr, order) if counts is None else server.weight_mass(counts, order)
-            cap, replica_rows = server.plan_clique_cache(mass, n, budget, world)
-            del mass
-        cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank, codec=codec)
-        if args.host_layout == "seeds_first":
-            row_of = host_rows_seeds_first(order, train, cap * world)
-        if stored is not None:
-            cache.set_host_codec(codec)
-        cache.fill_static(order, table if stored is None else stored, row_of_id=row_of)
-        if replica_rows > 0:
-            cache.add_replicas(order, replica_rows, row_of_id=row_of)
-    del order, counts
-    share = None
-    if world > 1 and not lru_ways:
-        from legion_ibp_b200 import server
-        share = server.exchange_partitions(cache, rank, world, dist)
-    pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, args.pipes)
-    pool.set_rng(0x5EED + rank, 64)
-    runner = L.Runner(dev, g, fs, cache, pool, None)
-    n_iters = (int(mine.numel()) - 1) // cfg["batch"]
-    torch.cuda.synchronize()
-    setup_s = time.perf_counter() - t_setup
 
     def barrier():
         if dist is not None:
@@ -519,46 +508,217 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def sum_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t)
+        return float(t.item())
+
+    # ---- synthetic inputs -------------------------------------------------------------------
+    indptr, indices = make_graph(cfg, "cuda")
+    torch.cuda.empty_cache()
+    n, f = cfg["n_nodes"], cfg["feat_len"]
+    dtype, esz = elt_of(cfg)
+    row_bytes = f * esz
+    n_edges = int(indices.numel())
+    striped = cfg.get("table") == "striped"
+    lru_ways = cfg.get("lru_ways", 0)
+    if cfg.get("zipf"):
+        train = zipf_batches(n, cfg["batch"], cfg["zipf_batches"], cfg["zipf"], world, rank)
+        mine = train
+        mine_labels = (mine % cfg["classes"]).to(torch.int32).contiguous()
+    else:
+        labels, train, _, _ = synth.labels_and_split(n, cfg["classes"], max(cfg["train_frac"], 1e-6), device="cuda")
+        mine = train[(train % world) == rank].contiguous()  # id % ngpu split, storage_management.cu:214-250
+        mine_labels = labels[mine.long()].contiguous()
+        del labels
+
+    # ---- ranking and cache plan -----------------------------------------------------------------
+    codec_name = cfg.get("codec", "raw")
+    codec = {"raw": L.CODEC_RAW, "int8": L.CODEC_INT8, "e4m3": L.CODEC_E4M3}[codec_name]
+    slot_bytes = row_bytes if codec == L.CODEC_RAW else (f + 4 + 15) // 16 * 16
+    order = None
+    replica_rows = 0
+    if not lru_ways:
+        order = torch.empty(n, dtype=torch.int32, device="cuda")
+        L.UnifiedCache.degree_order(dev, indptr, order)
+    if striped:
+        cap = (n + world - 1) // world
+        need = cap * row_bytes + 8 * (n + 1) + 4 * n_edges + 4 * n
+        free_b, _ = torch.cuda.mem_get_info()
+        assert need < free_b + 4 * n, ("the table striped over %d GPU(s) needs %.0f GB per GPU next to the topology; "
+                                       "run this config on more GPUs" % (world, need / 1e9))
+    else:
+        budget = cap = min(n, int(n * cfg["cache_frac"] * row_bytes / slot_bytes))
+        if cap * world >= n:
+            cap = (n + world - 1) // world
+        if world > 1 and not args.no_replicas and not lru_ways:
+            from legion_ibp_b200 import server
+            mass = server.degree_mass(indptr, order)
+            cap, replica_rows = server.plan_clique_cache(mass, n, budget, world)
+            del mass
+
+    # ---- host table ----------------------------------------------------------------------------------
+    table = None           # [rows, row_bytes] uint8 view of the pinned host table
+    table_rows = 0
+    row_of = None
+    stored = None          # compressed copy of the host table (configs with host_codec)
+    host_layout = "none" if striped else ("id" if lru_ways else args.host_layout)
+    if not striped:
+        table_rows = n
+        whole = n * row_bytes
+        if whole > 0.8 * host_memory_bytes():
+            # the box cannot hold the table: a window of it stands in (row = id % rows), sized to half the memory
+            table_rows = int(host_memory_bytes() * 0.5) // row_bytes
+            assert lru_ways, "only the LRU cache addresses a window of the table (row = id % rows)"
+        node_of = None
+        if host_layout == "seeds_first":
+            row_of, node_of = host_rows_seeds_first(order, train, cap * world)
+        table = host_buffer(table_rows * row_bytes, "legion_b200_bench_features", rank, world, dev, barrier0)
+        private = getattr(table, "private", False)
+        table = table.view(table_rows, row_bytes)
+        fill_host_rows(table.view(dtype).view(table_rows, f), rank, world, barrier0, node_of, private)
+        del node_of
+
+    def expected_rows(ids_t):
+        """Rows that a gather of these node ids must return (device tensor [len, row_bytes] of bytes)."""
+        src = ids_t.long() if table_rows in (0, n) else ids_t.long() % table_rows
+        return synth.feature_rows(src, f, 0, dtype).view(torch.uint8).view(-1, row_bytes)
+
+    # ---- storage, cache, pool, runner ------------------------------------------------------------
+    g = L.GraphStorage(dev, indptr, indices)
+    fs = L.FeatureStorage(dev, table_rows if table_rows else n, row_bytes, table)
+    fs.set_split(L.TRAINMODE, mine, mine_labels)
+    if lru_ways:
+        # every GPU keeps its own LRU cache (no clique: the contents change every batch)
+        cap = cap // lru_ways * lru_ways
+        cache = L.UnifiedCache(dev, table_rows, row_bytes, 0, lru=(cap // lru_ways, lru_ways))
+        cache.set_host_table(table)
+    elif striped:
+        cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank, codec=codec)
+        cache.place_static(order)
+        chunk = 1 << 17
+        for s0 in range(0, cap, chunk):
+            s1 = min(cap, s0 + chunk)
+            t_idx = torch.arange(s0, s1, device="cuda", dtype=torch.int64) * world + rank
+            t_idx = t_idx[t_idx < n]
+            if t_idx.numel():
+                cache.write_partition_rows(s0, synth.feature_rows(order[t_idx], f, 0, dtype))
+        torch.cuda.synchronize()
+    else:
+        if cfg.get("host_codec"):
+            stored = host_buffer(n * slot_bytes, "legion_b200_bench_codes", rank, world, dev, barrier0)
+            own_copy = getattr(stored, "private", False)
+            stored = stored.view(n, slot_bytes)
+            if rank == 0 or own_copy:
+                L.quantize_table(dev, codec, table, n, f, stored)
+            barrier0()
+        cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank, codec=codec)
+        if stored is not None:
+            cache.set_host_codec(codec)
+        cache.fill_static(order, table if stored is None else stored, row_of_id=row_of)
+        if replica_rows > 0:
+            cache.add_replicas(order, replica_rows, row_of_id=row_of)
+    del order
+    share = None
+    if world > 1 and not lru_ways:
+        from legion_ibp_b200 import server
+        share = server.exchange_partitions(cache, rank, world, dist)
+    pipes = args.pipes or (2 if lru_ways else 4)
+    pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, pipes)
+    pool.set_rng(RNG_SEED + rank, 64)
+    runner = L.Runner(dev, g, fs, cache, pool, None)
+    n_iters = (int(mine.numel()) - 1) // cfg["batch"]
+    seeds_h = mine.cpu().numpy()
+    labels_h = mine_labels.cpu().numpy()
+    staging = None
+    if not args.no_seed_staging and hasattr(runner, "stage_seeds") and not lru_ways and not striped and codec == L.CODEC_RAW:
+        staging = {"list": runner.stage_seeds(L.TRAINMODE), "host": runner.register_host_seeds(seeds_h)}
+    torch.cuda.synchronize()
+    setup_s = time.perf_counter() - t_setup
+
+    # ---- full-size checks (outside every timed region) --------------------------------------------
+    O = load_oracle() if rank == 0 else None
+    h_indptr = h_indices = None
+    if rank == 0:
+        h_indptr, h_indices = indptr.cpu().numpy(), indices.cpu().numpy()
+
+    def check_batch(pipe, global_batch, it, what):
+        """The batch that sits in `pipe`: every gathered row against the table's generator on all ranks, and on
+        rank 0 ids, labels, both edge lists and both counter arrays against the CPU checker's batch."""
+        torch.cuda.synchronize()
+        nc = pool.read(L.BUF_NODE_COUNTER, pipe, 16, np.int32)
+        ec = pool.read(L.BUF_EDGE_COUNTER, pipe, 16, np.int32)
+        nn, ne = runner_counts(nc, ec)
+        ids_np = pool.read(L.BUF_IDS, pipe, nn, np.int32)
+        ids_t = torch.from_numpy(ids_np).cuda()
+        fptr, _ = pool.buffer(L.BUF_FEATURES, pipe)
+        got = torch.empty(nn * row_bytes, dtype=torch.uint8, device="cuda")
+        L._check(L.lib().legion_copy(ctypes.c_void_p(got.data_ptr()), ctypes.c_void_p(fptr), ctypes.c_int64(nn * row_bytes),
+                                     ctypes.c_int32(3)))
+        got = got.view(nn, row_bytes)
+        bad = 0
+        for r0 in range(0, nn, 1 << 17):
+            r1 = min(nn, r0 + (1 << 17))
+            want = expected_rows(ids_t[r0:r1])
+            if codec == L.CODEC_RAW:
+                bad += int((got[r0:r1] != want).any(dim=1).sum().item())
+            else:
+                # rows served by the compressed cache: |x - x^| <= absmax / 254 for int8 (half a code step); half an
+                # e4m3 step (2^-4 relative) of the scaled value for fp8; rows that missed are exact
+                w, x = want.view(torch.float32), got[r0:r1].view(torch.float32)
+                amax = w.abs().amax(dim=1, keepdim=True)
+                tol = amax / 254.0 * 1.001 if codec == L.CODEC_INT8 else torch.maximum(w.abs() / 16.0, amax / 448.0 / 1024.0) * 1.001
+                bad += int(((x - w).abs() > tol).any(dim=1).sum().item())
+        assert bad == 0, "%s: %d of %d gathered rows differ from the table" % (what, bad, nn)
+        res = {"rows_checked": nn}
+        if rank == 0:
+            ref = O.run_batch(h_indptr, h_indices, seeds_h, labels_h, cfg["batch"], it, cfg["fanout"], global_batch,
+                              RNG_SEED + rank)
+            assert np.array_equal(nc, ref["node_counter"]) and np.array_equal(ec, ref["edge_counter"]), what
+            assert np.array_equal(ids_np, ref["ids"]), what
+            assert np.array_equal(pool.read(L.BUF_LABELS, pipe, int(nc[9]), np.int32), ref["labels"]), what
+            assert np.array_equal(pool.read(L.BUF_AGG_SRC, pipe, ne, np.int32), ref["agg_src"]), what
+            assert np.array_equal(pool.read(L.BUF_AGG_DST, pipe, ne, np.int32), ref["agg_dst"]), what
+            res.update(ids=nn, edges=ne, against="CPU checker: ids, labels, agg_src, agg_dst, node_counter, edge_counter bit-exact")
+        return res
+
     # ---- value: inputs resident, device-timed ----------------------------------------------------
     step = 0
     for _ in range(args.warmup):
         runner.enqueue(step, L.TRAINMODE, step % n_iters)
         step += 1
     runner.sync()
-    # full-size spot check: gathered rows of the last warm-up batch are bit copies of their host rows
-    last_pipe = (step - 1) % args.pipes
-    nc_chk = pool.read(L.BUF_NODE_COUNTER, last_pipe, 16, np.int32)
-    n_chk = int(nc_chk[9 + int(nc_chk[8])])
-    ids_chk = torch.from_numpy(pool.read(L.BUF_IDS, last_pipe, n_chk, np.int32))
-    pick = torch.randint(0, n_chk, (min(2000, n_chk),))
-    fptr, _ = pool.buffer(L.BUF_FEATURES, last_pipe)
-    rows_chk = np.empty((n_chk, f), np.float32)
-    import ctypes
-    L._check(L.lib().legion_copy(ctypes.c_void_p(rows_chk.ctypes.data), ctypes.c_void_p(fptr), ctypes.c_int64(rows_chk.nbytes),
-                                 ctypes.c_int32(2)))
-    src_rows = ids_chk[pick].long() if row_of is None else row_of.cpu()[ids_chk[pick].long()].long()
-    want_rows = table[src_rows].numpy()
-    if codec == L.CODEC_RAW:
-        assert np.array_equal(rows_chk[pick.numpy()], want_rows), "gathered rows differ from the host table"
-    else:
-        # rows served by the compressed cache: |x - x^| <= absmax / 254 for int8 (half a code step);
-        # half an e4m3 step (2^-4 relative) of the scaled value for fp8
-        amax = np.abs(want_rows).max(axis=1, keepdims=True)
-        tol = amax / 254.0 * 1.001 if codec == L.CODEC_INT8 else np.maximum(np.abs(want_rows) / 16.0, amax / 448.0 / 1024.0) * 1.001
-        assert np.all(np.abs(rows_chk[pick.numpy()] - want_rows) <= tol), "dequantised rows out of tolerance"
-    del rows_chk
+    checks = {"value_path": check_batch((step - 1) % pipes, step - 1, (step - 1) % n_iters, "device-resident batch")}
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    for _ in range(args.steps):
-        runner.enqueue(step, L.TRAINMODE, step % n_iters)
-        step += 1
-    runner.sync()
-    barrier()
-    ms_total = max_over_ranks(runner.timing()["batch_ms"])
+    windows = []
+    timed_s, budget_s = 0.0, (0.0 if args.profile_only else 0.5)
+    while True:
+        barrier()
+        for _ in range(args.steps):
+            runner.enqueue(step, L.TRAINMODE, step % n_iters)
+            step += 1
+        runner.sync()
+        barrier()
+        ms = max_over_ranks(runner.timing()["batch_ms"])
+        windows.append(ms)
+        timed_s += ms * 1e-3
+        if timed_s >= budget_s or len(windows) >= 400:
+            break
+    wsorted = sorted(windows)
+    ms_total = wsorted[len(wsorted) // 2]
     value = args.steps * world / (ms_total * 1e-3)
     assert pool.device_error() == 0, "device-side error flag set"
+    if args.profile_only:
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"profile_only": True, "ms_per_step": ms_total / args.steps, "value": value}), flush=True)
+        runner.Finalize()
+        return
 
     # ---- kernel durations: the same graph replay with CUDA events around the gather launches, one
     # batch at a time (the events of a pipe's graph are overwritten by its next launch) ----------------
@@ -568,8 +728,10 @@ def main():
         step += 1
     runner.sync()
     stats0 = cache.stats()
+    staged0 = runner.staged_rows() if staging else 0
     tm = {"gather_ms": 0.0, "miss_ms": 0.0, "timed": 0}
-    for _ in range(args.steps):
+    k_steps = max(args.steps, 40)
+    for _ in range(k_steps):
         runner.enqueue(step, L.TRAINMODE, step % n_iters)
         step += 1
         runner.sync()
@@ -577,37 +739,30 @@ def main():
         for k in tm:
             tm[k] += t1[k]
     stats1 = cache.stats()
+    staged = (runner.staged_rows() - staged0) if staging else 0
     # the same events with batches in flight: how busy the host-link stream is in steady state
-    for _ in range(args.steps):
+    for _ in range(k_steps):
         runner.enqueue(step, L.TRAINMODE, step % n_iters)
         step += 1
     runner.sync()
     tp = runner.timing()
-    pipeline = {"window_ms_per_batch": tp["batch_ms"] / args.steps, "miss_ms_per_batch": tp["miss_ms"] / args.steps,
+    pipeline = {"window_ms_per_batch": tp["batch_ms"] / k_steps, "miss_ms_per_batch": tp["miss_ms"] / k_steps,
                 "miss_stream_busy_frac": tp["miss_ms"] / tp["batch_ms"] if tp["batch_ms"] > 0 else None}
     runner.set_options(use_graph=True, time_kernels=False)
-    # the timed region is a few milliseconds: the clock samples run on through the kernel-timing passes
-    # above, which replay the same batches
     clocks = sampler.stop() if rank == 0 else None
-    if args.profile_only:
-        if rank == 0:
-            print(json.dumps({"profile_only": True, "ms_per_step": ms_total / args.steps, "value": value}), flush=True)
-        runner.Finalize()
-        return
 
     # ---- roofline of the gather ---------------------------------------------------------------------
     # Algorithmic bytes per gathered row: the row read from its source + the row written + 4 B id +
-    # 4 B lookup-table entry.  Rows served from GPU memory are moved by the hit kernel (HBM bound);
-    # rows that miss the cache are moved by the miss kernel over the host link, for which the hit
-    # kernel still reads id + table entry and writes an 8-byte list entry.
+    # 4 B lookup-table entry.  Rows served from GPU memory are moved by the hit kernel (HBM bound; rows of
+    # uncached seeds that the copy engine staged in device memory count among them); rows that miss the cache
+    # are moved by the miss kernel over the host link, for which the hit kernel still reads id + table entry
+    # and writes an 8-byte list entry.
     d = {k: stats1[k] - stats0[k] for k in stats0}
-    hits = d["local_hits"] + d["peer_hits"]
+    hits = d["local_hits"] + d["peer_hits"] + staged
     rows = hits + d["misses"]
     gather_launches = tm["timed"]  # one lookup + gather launch per batch
-    # a hit reads its cache slot (the raw row; codes + scale; for the LRU cache also the keys of its set
-    # and one stamp) and writes the fp32 row
     hit_read = slot_bytes + (4 * lru_ways + 4 if lru_ways else 0)
-    hit_bytes = hits * (hit_read + row_bytes + 8) + d["misses"] * 16
+    hit_bytes = (hits - staged) * (hit_read + row_bytes + 8) + staged * (2 * row_bytes + 12) + d["misses"] * 16
     host_row_bytes = slot_bytes if stored is not None else row_bytes   # bytes a miss moves over the host link
     miss_bytes = d["misses"] * (host_row_bytes + row_bytes + 8)
     gather_s = tm["gather_ms"] * 1e-3
@@ -619,9 +774,6 @@ def main():
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = hit_bytes / gather_s / 1e9 if gather_s > 0 else 0.0
-    # DRAM bytes per launch: the full-size workload is too large for a multi-pass profiler capture, so the
-    # figure of the captured "mid" case (profiles/gather_kernels_mid_config.md: dram read + write bytes per
-    # row served from GPU memory) is scaled by the rows one launch serves here; raw 512-byte rows only
     traffic = traffic_source = None
     if codec == L.CODEC_RAW and not lru_ways and row_bytes == 512 and world == 1:
         traffic = NCU_DRAM_BYTES_PER_HIT_ROW * hits / max(1, gather_launches)
@@ -631,12 +783,13 @@ def main():
     kname = ("gather_lru_kernel (set probe + gather of rows held in the LRU cache)" if lru_ways else
              "gather_quant_kernel<%s> (cache lookup + gather with in-kernel dequantisation)" % codec_name
              if codec != L.CODEC_RAW else "gather_vec_kernel (cache lookup + gather of rows held in GPU memory)")
+    peer_frac = d["peer_hits"] / max(1, rows)
     roofline = {"bound": "hbm", "kernel": kname,
                 "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "peak_source": "of measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "of fallback 6650 GB/s",
                 "traffic": traffic, "traffic_source": traffic_source, "launches": gather_launches,
                 "avg_launch_ms": tm["gather_ms"] / max(1, gather_launches),
-                "rows_per_batch": rows / args.steps,
+                "rows_per_batch": rows / k_steps, "staged_seed_rows_per_batch": staged / k_steps,
                 "source_split": {k: d[k] / max(1, rows) for k in ("local_hits", "peer_hits", "misses")},
                 "measured": "CUDA events around each launch on its stream, %d batches run one at a time right "
                             "after the timed region" % tm["timed"]}
@@ -647,60 +800,53 @@ def main():
         nv = d["peer_hits"] * slot_bytes / gather_s / 1e9 if gather_s > 0 else 0.0
         roofline_nvlink = {"bound": "nvlink", "kernel": kname, "achieved": nv, "peak": 770.0, "unit": "GB/s",
                            "frac": nv / 770.0, "peak_source": "peer copy measured on this pool, per direction",
-                           "peer_rows_per_batch": d["peer_hits"] / args.steps}
+                           "peer_rows_per_batch": d["peer_hits"] / k_steps, "peer_row_frac": peer_frac}
+        if peer_frac > 0.5:
+            # most rows cross NVLink: that link, not HBM, bounds the launch
+            roofline = dict(roofline_nvlink, hbm=roofline, traffic=None, launches=gather_launches,
+                            avg_launch_ms=tm["gather_ms"] / max(1, gather_launches))
     # one rank at a time: the ranks' host links share the host's memory and root ports
     link_peak = 0.0
     for k in range(world):
         if k == rank:
-            link_peak = host_link_peak(table)
+            link_peak = copy_peak("h2d")
         barrier()
-    link_achieved = d["misses"] * host_row_bytes / miss_s / 1e9 if miss_s > 0 else 0.0
-    roofline_host = {"bound": "host_link", "kernel": "gather_miss_kernel (zero-copy fetch of missed rows)",
-                     "achieved": link_achieved, "peak": link_peak, "unit": "GB/s",
-                     "frac": link_achieved / link_peak if link_peak else None,
-                     "peak_source": "pinned host->device cudaMemcpy of 1 GiB measured in this run (the same kernel "
-                                    "alone reaches 50.6 GB/s on random rows of a 1 GB table and 26 GB/s over 48 GB)",
-                     "launches": tm["timed"], "avg_launch_ms": tm["miss_ms"] / max(1, tm["timed"]),
-                     "rows_per_batch": d["misses"] / args.steps, "algorithmic_bytes": miss_bytes}
+    roofline_host = None
+    if table is not None:
+        link_achieved = d["misses"] * host_row_bytes / miss_s / 1e9 if miss_s > 0 else 0.0
+        roofline_host = {"bound": "host_link", "kernel": "gather_miss_kernel (zero-copy fetch of missed rows)",
+                         "achieved": link_achieved, "peak": link_peak, "unit": "GB/s",
+                         "frac": link_achieved / link_peak if link_peak else None,
+                         "peak_source": "pinned host->device cudaMemcpy of 1 GiB measured in this run, one rank at a time",
+                         "launches": tm["timed"], "avg_launch_ms": tm["miss_ms"] / max(1, tm["timed"]),
+                         "rows_per_batch": d["misses"] / k_steps, "algorithmic_bytes": miss_bytes,
+                         "copy_engine_bytes_per_batch": staged * row_bytes / k_steps}
     # lower bound of the whole gather step: the slowest of the HBM side, the NVLink side and the host-link side
     t_lb = max(hit_bytes / (hbm_peak * 1e9), d["peer_hits"] * slot_bytes / 770e9,
-               d["misses"] * host_row_bytes / (link_peak * 1e9) if link_peak else 0.0)
-    roofline_path = {"lower_bound_ms_per_batch": t_lb / args.steps * 1e3,
+               (d["misses"] * host_row_bytes + staged * row_bytes) / (link_peak * 1e9) if link_peak else 0.0)
+    roofline_path = {"lower_bound_ms_per_batch": t_lb / k_steps * 1e3,
                      "gather_ms_per_batch": (tm["gather_ms"] + tm["miss_ms"]) / max(1, tm["timed"]),
                      "batch_ms": ms_total / args.steps}
 
     # ---- e2e: host buffers through the C ABI --------------------------------------------------------
     max_nodes, max_edges = bounds(cfg["batch"], cfg["fanout"])
-    seeds_h = mine.cpu().numpy()
-    labels_h = mine_labels.cpu().numpy()
-    # one set of page-locked output arrays per batch in flight; the batch itself writes into them
+    depth = pipes if lru_ways else pipes + 1   # static caches: one more batch may sample ahead of the pipes
     outs = [dict(ids=torch.empty(max_nodes, dtype=torch.int32).pin_memory().numpy(),
                  lab=torch.empty(cfg["batch"], dtype=torch.int32).pin_memory().numpy(),
                  src=torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy(),
-                 dst=torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy()) for _ in range(3)]
+                 dst=torch.empty(max_edges, dtype=torch.int32).pin_memory().numpy()) for _ in range(depth)]
     nc_o, ec_o = np.zeros(16, np.int32), np.zeros(16, np.int32)
     b = cfg["batch"]
 
-    mode = args.e2e_outputs
-
     def submit(i):
         it = i % n_iters
-        o = outs[i % 3]
-        if mode == "bound":
-            runner.submit_host_to(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i, o["ids"], o["lab"],
-                                  o["src"], o["dst"])
-        else:
-            runner.submit_host(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i)
+        o = outs[i % depth]
+        runner.submit_host_to(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i, o["ids"], o["lab"],
+                              o["src"], o["dst"])
 
     def collect():
-        if mode == "copy":
-            o = outs[0]
-            return runner.collect_host(o["ids"], o["lab"], o["src"], o["dst"], nc_o, ec_o, None)
         return runner.collect_host(None, None, None, None, nc_o, ec_o, None)
 
-    # two batches in flight plus, for static caches, a third that samples ahead (the API's limit); a
-    # batch counts as done when its collect returns
-    depth = 3 if (mode == "bound" and not lru_ways) else 2
     pipe0 = runner.current_pipe()
     for i in range(depth):
         submit(i)
@@ -709,18 +855,20 @@ def main():
         submit(i)
     for _ in range(depth):
         collect()
-    # the exported block structure of the last batch is what the device buffers hold
+    # the exported block structure of the last batch is what the device buffers hold, and that batch is right
     last = depth + 3
     nn_chk, ne_chk = runner_counts(nc_o, ec_o)
-    chk_pipe = (pipe0 + last) % 2
-    if mode != "none":
-        o_chk = outs[last % 3] if mode == "bound" else outs[0]
-        assert np.array_equal(o_chk["ids"][:nn_chk], pool.read(L.BUF_IDS, chk_pipe, nn_chk, np.int32))
-        assert np.array_equal(o_chk["src"][:ne_chk], pool.read(L.BUF_AGG_SRC, chk_pipe, ne_chk, np.int32))
-    # wall clock needs a longer window than the device-timed leg: 40 steps of 0.2 ms are 8 ms, which one
-    # descheduled rank out of eight distorts; the steps are the same steps
-    e2e_steps = max(args.steps, 200)
+    chk_pipe = (pipe0 + last) % pipes
+    o_chk = outs[last % depth]
+    assert np.array_equal(o_chk["ids"][:nn_chk], pool.read(L.BUF_IDS, chk_pipe, nn_chk, np.int32))
+    assert np.array_equal(o_chk["src"][:ne_chk], pool.read(L.BUF_AGG_SRC, chk_pipe, ne_chk, np.int32))
+    assert np.array_equal(o_chk["dst"][:ne_chk], pool.read(L.BUF_AGG_DST, chk_pipe, ne_chk, np.int32))
+    checks["host_buffer_path"] = check_batch(chk_pipe, last, last % n_iters, "host-buffer batch")
+    # wall clock needs a longer window than the device-timed leg: at least 0.5 s of steps
+    e2e_steps = max(args.steps, 200, int(0.6 / max(ms_total / args.steps * 1e-3, 1e-6)))
+    e2e_steps = min(e2e_steps, 20000)
     barrier()
+    staged_e2e0 = runner.staged_rows() if staging else 0
     t0 = time.perf_counter()
     d2h = 0
     for i in range(depth):
@@ -735,44 +883,61 @@ def main():
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
-    e2e = {"value": e2e_steps * world / e2e_s, "unit": "batches/s", "h2d_bytes_per_step": 8 * b,
-           "d2h_bytes_per_step": d2h // e2e_steps, "steps": e2e_steps,
-           "api": "legion_runner_submit_host%s / legion_runner_collect_host, %d batches in flight, outputs: %s" % (
-               "_to" if mode == "bound" else "", depth, mode),
-           "note": "seeds+labels copied in from host memory, ids/labels/edge lists/counters written to page-locked host "
-                   "memory every step; gathered rows stay in the device hand-off buffer where the trainer reads "
-                   "them; missed rows cross the host link inside the gather"}
+    staged_e2e = (runner.staged_rows() - staged_e2e0) if staging else 0
+    # floor of the export: every rank copies device -> pinned host at the same time
+    barrier()
+    d2h_peak = copy_peak("d2h")
+    barrier()
+    d2h_peak_min = -max_over_ranks(-d2h_peak)
+    e2e_value = e2e_steps * world / e2e_s
+    d2h_per_step = d2h // e2e_steps
+    floor_s = d2h_per_step / (d2h_peak_min * 1e9)
+    e2e = {"value": e2e_value, "unit": "batches/s", "h2d_bytes_per_step": 8 * b + staged_e2e * row_bytes // e2e_steps,
+           "d2h_bytes_per_step": d2h_per_step, "steps": e2e_steps,
+           "api": "legion_runner_submit_host_to / legion_runner_collect_host, %d batches in flight" % depth,
+           "note": "seeds+labels copied in from host memory (and, with seed staging, the rows of uncached seeds by the copy "
+                   "engine), ids/labels/edge lists/counters written to page-locked host memory every step; gathered rows "
+                   "stay in the device hand-off buffer where the trainer reads them; missed rows cross the host link "
+                   "inside the gather"}
+    roofline_e2e = {"bound": "host_link_d2h", "peak": d2h_peak_min, "unit": "GB/s",
+                    "peak_source": "device -> pinned host cudaMemcpy of 1 GiB, all ranks at the same time, slowest rank",
+                    "d2h_bytes_per_step": d2h_per_step, "floor_ms_per_step": floor_s * 1e3,
+                    "achieved_ms_per_step": e2e_s / e2e_steps * 1e3,
+                    "frac": floor_s / (e2e_s / e2e_steps) if e2e_s > 0 else None}
 
     # ---- CPU baseline on this box's cores (rank 0, N=1 only) ----------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        O = load_oracle()
         cores = O.num_threads()
-        nb = args.cpu_sample_batches or 2 * cores
-        h_indptr, h_indices = indptr.cpu().numpy(), indices.cpu().numpy()
-        tnp = table.numpy()
-        O.cpu_pipeline(h_indptr, h_indices, seeds_h, labels_h, b, 0, cores, cfg["fanout"], 1, tnp, cores)
-        t0 = time.perf_counter()
-        O.cpu_pipeline(h_indptr, h_indices, seeds_h, labels_h, b, cores, nb, cfg["fanout"], 1, tnp, cores)
-        dt = time.perf_counter() - t0
-        cpu = {"value": nb / dt, "unit": "batches/s", "cores": cores, "kind": "port",
-               "sample": "%d batches of the same workload (sample + relabel + gather), %d threads, %.1f s" %
-                         (nb, cores, dt)}
+        if table is not None and table_rows == n and row_of is None:
+            tnp = table.numpy()
+        else:
+            # the CPU pipeline reads a table in node-id order (a window of it when the box cannot hold it)
+            del table
+            tnp, _ = reference_table(cfg)
+        cpu = cpu_arms(O, h_indptr, h_indices, seeds_h, labels_h, b, cfg["fanout"], tnp, cores)
 
     if rank == 0:
         hops = len(cfg["fanout"])
+        per_batch = 1 + 4 * hops + 1 + (1 if not striped else 0) + (3 if lru_ways else 0)
         line = {"metric": "sampled+gathered mini-batches/sec", "value": value, "unit": "batches/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": dict(workload_config(cfg, world), host_table_layout=args.host_layout),
-                "e2e": e2e, "gpu_launches": args.steps * (1 + 4 * hops + 1 + 1 + (3 if lru_ways else 0)),
-                "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path, "roofline_nvlink": roofline_nvlink,
-                "pipeline": pipeline,
-                "cpu_baseline": cpu, "clocks": clocks,
+                "vs_baseline": None, "dtype": cfg.get("elt", "f32"), "data": "synthetic",
+                "config": workload_config(cfg, world), "host_table_layout": host_layout,
+                "host_table_rows": table_rows, "pipes": pipes,
+                "windows": {"count": len(windows), "timed_s": timed_s, "ms_per_step_min": wsorted[0] / args.steps,
+                            "ms_per_step_median": ms_total / args.steps, "ms_per_step_max": wsorted[-1] / args.steps},
+                "e2e": e2e, "gpu_launches": args.steps * per_batch,
+                "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
+                "roofline_nvlink": roofline_nvlink, "roofline_e2e": roofline_e2e,
+                "pipeline": pipeline, "full_size_checks": checks,
+                "cpu_baseline": cpu, "vs_cpu_baseline": {"value": value / cpu["value"], "e2e": e2e_value / cpu["value"]} if cpu else None,
+                "clocks": clocks,
                 "graph": {"nodes": n, "directed_edges": n_edges, "train_seeds_this_rank": int(mine.numel()),
                           "cache_rows_per_gpu": cap, "replica_rows_per_gpu": replica_rows,
-                          "peer_mapping": share}, "setup_s": setup_s, "tunables": args.tunable or None}
+                          "peer_mapping": share, "seed_staging": bool(staging)},
+                "setup_s": setup_s, "tunables": args.tunable or None}
         print(json.dumps(line), flush=True)
     runner.Finalize()
     if dist is not None:

@@ -32,6 +32,7 @@ extern "C" {
 #define LEGION_MAX_DEVICE 8      /* include/system_config.cuh:50 */
 #define LEGION_INTERBATCH_CON 2  /* include/system_config.cuh:47 */
 #define LEGION_INTRABATCH_CON 3  /* include/system_config.cuh:48 */
+#define LEGION_MAX_PIPES 4       /* batches a pool can hold in flight; the hand-off to trainers uses INTERBATCH_CON of them */
 #define LEGION_MEMORY_USAGE 7    /* include/system_config.cuh:51 */
 #define LEGION_TRAINMODE 0
 #define LEGION_VALIDMODE 1
@@ -161,6 +162,13 @@ int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n
  * uncached node. */
 int legion_cache_fill_static_rows(LegionCache *c, const int32_t *order_dev, int64_t n_order, const void *host_table,
                                   const int32_t *row_of_id_dev, void *stream);
+/* Placement without fill (InitPair + table insert, cache/cache_impl.cuh:104-109, cache/cache.cu:74-112,
+ * without FeatFillUp): builds the lookup table for `order` and leaves the rows to the caller, who writes
+ * row s of this GPU's partition (legion_cache_partition) with the row of node order[s * kg + ki].  For a
+ * table that exists nowhere as a whole: the MAG240M-shaped configuration spreads 375 GB over eight
+ * caches, each GPU loading (or generating) only its own stripe.  Uncompressed caches only; without a host
+ * table every node outside the clique's caches is a miss that nothing serves. */
+int legion_cache_place_static(LegionCache *c, const int32_t *order_dev, int64_t n_order, void *stream);
 /* Host table stored compressed ("IBP(M)" of the reference: compress_cpu_transfer_kernel,
  * comp_cache/static_cache.cu:656-772, with the int8 / e4m3 per-row codec in place of the absent
  * bit-packing): every row of the host table is feature_len one-byte codes + one fp32 scale, padded to
@@ -228,8 +236,9 @@ int legion_cache_destroy(LegionCache *c);
 
 /* MemoryPool + GPURunner::Initialize buffer allocation + IPCEnv::Initialize{Samples,Features}Buffer
  * (engine/server.cu:204-265, engine/ipc_service.cu:134-206).  Buffers are sized for the true
- * worst case of the fanout list.  `pipes` output sets (INTERBATCH_CON).  row_bytes_out is the
- * size of one gathered row. */
+ * worst case of the fanout list.  `pipes` output sets: INTERBATCH_CON (2) for a pool that is published to
+ * trainers, up to LEGION_MAX_PIPES for a consumer inside the process (more batches in flight hide more of
+ * the sampling kernels' latency).  row_bytes_out is the size of one gathered row. */
 int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batch_size, int32_t hop_num,
                        const int32_t *fanout, int32_t row_bytes_out, int32_t pipes);
 int legion_pool_destroy(LegionPool *p);
@@ -448,6 +457,27 @@ int legion_runner_current_pipe(LegionRunner *r);
  * training batches [first_batch, first_batch+count) without lookup or gather and counts every node they
  * touch in counts_dev (uint32 per node, zeroed by the caller). */
 int legion_runner_presample(LegionRunner *r, int32_t first_batch, int32_t count, uint32_t *counts_dev);
+/* Seed-row staging.  No counterpart in the reference, whose every missed row is read by zero-copy loads
+ * inside the gather kernel (cache/cache_impl.cuh:283-286).  On B200 a kernel that reads pinned host memory
+ * slows the HBM-bound kernels beside it by 2.4-3.6x while it runs, a copy-engine transfer does not; and
+ * seeds (random training nodes) are more than half of the rows that miss a degree-ordered cache.  The seed
+ * list of a mode is fixed for the run (engine/operator_impl.cu:28-56 slices it batch by batch), so the rows
+ * of its uncached nodes are copied once into a page-locked array in list order; the uncached seeds of one
+ * batch are then one contiguous block that the copy engine brings to the device while the batch samples,
+ * and the gather reads them from device memory.  Rows of sampled neighbours that miss keep the zero-copy
+ * path.  Static caches of uncompressed rows with a host table only (LEGION_E_ARG otherwise); call after the
+ * cache is filled (and replicas added): a later refill switches the staging off until it is rebuilt.
+ * Gathered rows do not change.  staged_rows_out (may be NULL): rows held in the page-locked array.
+ *   legion_runner_stage_seeds          the device-resident list of `mode` (batches of legion_runner_enqueue /
+ *                                      run_once / serve)
+ *   legion_runner_register_host_seeds  a list in the caller's host memory: a later legion_runner_submit_host[_to]
+ *                                      whose `seeds` pointer is a slice of [seeds_host, seeds_host + count) and
+ *                                      still holds what the list held now is recognised by address and staged;
+ *                                      any other batch takes the zero-copy path as before
+ *   legion_runner_staged_rows          rows that reached the device this way since the runner was created */
+int legion_runner_stage_seeds(LegionRunner *r, int32_t mode, int64_t *staged_rows_out);
+int legion_runner_register_host_seeds(LegionRunner *r, const int32_t *seeds_host, int32_t count, int64_t *staged_rows_out);
+int legion_runner_staged_rows(LegionRunner *r, int64_t *rows);
 /* use_graph (default 1): replay every batch as one CUDA graph per pipe instead of ~25 launches and
  * ~20 event calls from the host.  time_kernels (default 0): bracket the gather launches with CUDA
  * events on the streams they run on.  Call between batches; waits for the device. */

@@ -160,6 +160,19 @@ class UnifiedCache:
         _check(lib().legion_cache_fill_static_rows(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()),
                                                    _ptr(host_table), _ptr(row_of_id), _stream(stream)))
 
+    def place_static(self, order_dev, stream=None):
+        """Lookup table only; the caller writes row s of partition() with the row of node order[s * kg + ki]."""
+        _check(lib().legion_cache_place_static(self.h, _ptr(order_dev), C.c_int64(order_dev.numel()), _stream(stream)))
+
+    def write_partition_rows(self, first_row, rows_dev):
+        """Copies a device tensor of whole rows into this GPU's partition starting at row first_row."""
+        ptr, nbytes = self.partition()
+        n = rows_dev.numel() * rows_dev.element_size()
+        off = int(first_row) * self.row_bytes
+        if off < 0 or off + n > nbytes:
+            raise LegionError("write_partition_rows: rows [%d, +%d bytes) are outside the partition" % (first_row, n))
+        _check(lib().legion_copy(C.c_void_p(ptr + off), _ptr(rows_dev), C.c_int64(n), C.c_int32(3)))
+
     def set_host_codec(self, codec):
         """The host table holds compressed rows (codes + fp32 scale) of this cache's codec."""
         _check(lib().legion_cache_set_host_codec(self.h, C.c_int32(codec)))
@@ -449,6 +462,26 @@ class Runner:
     def presample(self, first_batch, count, counts_dev):
         """RunPreSc: sample only, count node accesses into counts_dev (uint32 per node)."""
         _check(lib().legion_runner_presample(self.h, C.c_int32(first_batch), C.c_int32(count), _ptr(counts_dev)))
+
+    def stage_seeds(self, mode=TRAINMODE):
+        """Rows of the uncached nodes of a mode's seed list into page-locked memory, in list order: the copy
+        engine then brings each batch's block in while the batch samples.  Returns the rows staged."""
+        n = C.c_int64()
+        _check(lib().legion_runner_stage_seeds(self.h, C.c_int32(mode), C.byref(n)))
+        return n.value
+
+    def register_host_seeds(self, seeds):
+        """The same for a seed list in host memory (numpy int32): submit_host[_to] calls that pass a slice
+        of this very array are staged.  The array must stay alive and unchanged."""
+        self._keep = self._keep + (seeds,)
+        n = C.c_int64()
+        _check(lib().legion_runner_register_host_seeds(self.h, _ptr(seeds), C.c_int32(len(seeds)), C.byref(n)))
+        return n.value
+
+    def staged_rows(self):
+        n = C.c_int64()
+        _check(lib().legion_runner_staged_rows(self.h, C.byref(n)))
+        return n.value
 
     def current_pipe(self):
         return lib().legion_runner_current_pipe(self.h)

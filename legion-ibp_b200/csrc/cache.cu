@@ -330,6 +330,11 @@ extern "C" int legion_cache_fill_static_rows(LegionCache *c, const int32_t *orde
     if (n_cached > 0) {
         static_place_kernel<<<grid_stride(n_cached, sms), 256, 0, s>>>(order_dev, n_cached, c->capacity, c->kg, c->lut);
         LG_LAUNCH_CHECK();
+        if (host_table == nullptr && c->fill_by_caller) {  // legion_cache_place_static: the caller writes the rows
+            LG_CUDA(cudaStreamSynchronize(s));
+            c->fill_gen += 1;
+            return LEGION_OK;
+        }
         LG_ARG(host_table != nullptr, "host_table is NULL");
         int64_t warps = c->capacity;
         int64_t g = (warps + 7) / 8;
@@ -355,6 +360,7 @@ extern "C" int legion_cache_fill_static_rows(LegionCache *c, const int32_t *orde
         LG_LAUNCH_CHECK();
     }
     LG_CUDA(cudaStreamSynchronize(s));
+    c->fill_gen += 1;
     return LEGION_OK;
 }
 
@@ -410,7 +416,22 @@ extern "C" int legion_cache_add_replicas(LegionCache *c, const int32_t *order_de
     }
     c->part[c->kg] = rep;
     c->replica_rows = (int32_t)n_rows;
+    c->fill_gen += 1;
     return LEGION_OK;
+}
+
+// Placement only (InitPair + Insert, cache/cache_impl.cuh:104-109, cache/cache.cu:74-112, without FeatFillUp):
+// builds the lookup table for `order`; the caller then writes the rows of this GPU's partition itself
+// (row s of legion_cache_partition holds node order[s * kg + ki]).  For tables that exist nowhere as a
+// whole, e.g. a table larger than host memory whose stripes are loaded or generated GPU by GPU.
+extern "C" int legion_cache_place_static(LegionCache *c, const int32_t *order_dev, int64_t n_order, void *stream)
+{
+    LG_ARG(c != nullptr && c->kind == 0, "not a static cache");
+    LG_ARG(c->codec == LEGION_CODEC_RAW, "rows written by the caller must be uncompressed");
+    c->fill_by_caller = 1;
+    int rc = legion_cache_fill_static_rows(c, order_dev, n_order, nullptr, nullptr, stream);
+    c->fill_by_caller = 0;
+    return rc;
 }
 
 extern "C" int legion_cache_fill_static(LegionCache *c, const int32_t *order_dev, int64_t n_order,

@@ -95,7 +95,7 @@ extern "C" int legion_pool_destroy(LegionPool *p)
 {
     if (p == nullptr) return LEGION_OK;
     cudaSetDevice(p->dev_id);
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
         cudaFree(p->ids[i]); cudaFree(p->features[i]); cudaFree(p->labels[i]); cudaFree(p->agg_src[i]);
         cudaFree(p->agg_dst[i]); cudaFree(p->node_counter[i]); cudaFree(p->edge_counter[i]);
         cudaFree(p->miss_rows[i]); cudaFree(p->miss_count[i]);
@@ -117,7 +117,7 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
     LG_ARG(hop_num >= 0 && hop_num <= LEGION_MAX_HOPS, "hop_num must be 0..3");
     LG_ARG(hop_num == 0 || fanout != nullptr, "fanout is NULL");
     LG_ARG(row_bytes_out > 0 && row_bytes_out % 4 == 0, "row_bytes_out must be a positive multiple of 4");
-    LG_ARG(pipes >= 1 && pipes <= LEGION_INTERBATCH_CON, "pipes must be 1 or 2");
+    LG_ARG(pipes >= 1 && pipes <= LEGION_MAX_PIPES, "pipes must be 1..4");
     for (int h = 0; h < hop_num; ++h)
         LG_ARG(fanout[h] >= 1 && fanout[h] <= LEGION_MAX_FANOUT, "fanout must be 1..32");
     LG_CUDA(cudaSetDevice(dev_id));

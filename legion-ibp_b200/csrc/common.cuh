@@ -4,6 +4,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string>
+#include <string.h>
 
 #include "../../include/legion_b200.h"
 
@@ -151,6 +152,8 @@ struct LegionCache {
     int32_t *lut;                      // n_nodes entries, global index or CACHEMISS
     void *part[LEGION_MAX_DEVICE + 1]; // part[ki] is owned; part[kg] = private copies of hot rows that peers hold
     int32_t replica_rows;              // rows of part[kg] (legion_cache_add_replicas)
+    int32_t fill_by_caller;            // set while legion_cache_place_static builds the table without copying rows
+    int64_t fill_gen;                  // counts the changes of the lookup table (fill, replicas)
     legion::VmmBlock own_block;        // set when part[ki] is shareable memory (clique of more than one GPU)
     legion::VmmBlock peer_block[LEGION_MAX_DEVICE];  // partitions mapped from other processes
     // lru
@@ -165,6 +168,26 @@ struct LegionCache {
     unsigned long long *stats;  // 4 counters on the device
 };
 
+namespace legion {
+// Rows of a seed list's uncached nodes in page-locked host memory, in list order (stage.cu).
+struct SeedStage {
+    int32_t valid;
+    int32_t count;               // entries of the list
+    const int32_t *ids_dev;      // the list on the device
+    int32_t *own_ids_dev;        // owned device copy of a list that was registered from host memory, or nullptr
+    const int32_t *host_base;    // where the registered host list lives in the caller's memory, or nullptr
+    int32_t *host_copy;          // what it held at registration (batches are compared against it)
+    int32_t *pos_dev;            // count + 1 entries: uncached entries before each list position
+    int32_t *pos;                // the same on the host
+    uint8_t *rows_host;          // pos[count] rows
+    int64_t rows;
+    int64_t fill_gen;            // generation of the cache's contents the staging was built for
+    LegionCache *cache;
+};
+int stage_build(LegionCache *c, const int32_t *ids_dev, int32_t count, int sm_count, SeedStage *st);
+void stage_free(SeedStage *st);
+}  // namespace legion
+
 struct LegionPool {
     int32_t dev_id;
     int32_t batch_size, hop_num;
@@ -175,29 +198,33 @@ struct LegionPool {
     int64_t input_tiles;  // entries of tile_sum / tile_off reserved for the counting kernels (edge tiles follow)
     int64_t feat_rows;
     // per pipe outputs
-    int32_t *ids[LEGION_INTERBATCH_CON];
-    void *features[LEGION_INTERBATCH_CON];
-    int32_t *labels[LEGION_INTERBATCH_CON];
-    int32_t *agg_src[LEGION_INTERBATCH_CON];
-    int32_t *agg_dst[LEGION_INTERBATCH_CON];
-    int32_t *node_counter[LEGION_INTERBATCH_CON];
-    int32_t *edge_counter[LEGION_INTERBATCH_CON];
+    int32_t *ids[LEGION_MAX_PIPES];
+    void *features[LEGION_MAX_PIPES];
+    int32_t *labels[LEGION_MAX_PIPES];
+    int32_t *agg_src[LEGION_MAX_PIPES];
+    int32_t *agg_dst[LEGION_MAX_PIPES];
+    int32_t *node_counter[LEGION_MAX_PIPES];
+    int32_t *edge_counter[LEGION_MAX_PIPES];
     // per pipe scratch (two batches may be in flight)
-    int64_t *cache_index[LEGION_INTERBATCH_CON];      // one entry per node of the batch
-    int32_t *src_global[LEGION_INTERBATCH_CON];       // sampled neighbour ids, all hops
-    legion::MapSlot *map[LEGION_INTERBATCH_CON];      // batch-local id map
+    int64_t *cache_index[LEGION_MAX_PIPES];      // one entry per node of the batch
+    int32_t *src_global[LEGION_MAX_PIPES];       // sampled neighbour ids, all hops
+    legion::MapSlot *map[LEGION_MAX_PIPES];      // batch-local id map
     uint32_t map_mask;        // back region of the id map: slots - 1
     uint32_t map_front_mask;  // front region: slots - 1
-    legion::NodeRec *node_rec[LEGION_INTERBATCH_CON];
-    int32_t *tile_sum[LEGION_INTERBATCH_CON], *tile_off[LEGION_INTERBATCH_CON];
-    int32_t *eslot[LEGION_INTERBATCH_CON], *erank[LEGION_INTERBATCH_CON];
-    int64_t *lru_victim[LEGION_INTERBATCH_CON];       // per node: way chosen for insertion, or -1
-    int2 *miss_rows[LEGION_INTERBATCH_CON];           // (row, node id) to fetch from the host table
-    int32_t *miss_count[LEGION_INTERBATCH_CON];       // [0] entries, [4] ticket
-    int32_t *ctl[LEGION_INTERBATCH_CON];
-    legion::BatchCtl *bctl[LEGION_INTERBATCH_CON];
-    int32_t *seed_stage[LEGION_INTERBATCH_CON], *label_stage[LEGION_INTERBATCH_CON];  // device staging for host-provided seeds
-    int32_t *h_stage[LEGION_INTERBATCH_CON];  // pinned host staging: seeds, labels, then both counter arrays
+    legion::NodeRec *node_rec[LEGION_MAX_PIPES];
+    int32_t *tile_sum[LEGION_MAX_PIPES], *tile_off[LEGION_MAX_PIPES];
+    int32_t *eslot[LEGION_MAX_PIPES], *erank[LEGION_MAX_PIPES];
+    int64_t *lru_victim[LEGION_MAX_PIPES];       // per node: way chosen for insertion, or -1
+    int2 *miss_rows[LEGION_MAX_PIPES];           // (row, node id) to fetch from the host table
+    int32_t *miss_count[LEGION_MAX_PIPES];       // [0] entries, [4] ticket
+    int32_t *ctl[LEGION_MAX_PIPES];
+    legion::BatchCtl *bctl[LEGION_MAX_PIPES];
+    int32_t *seed_stage[LEGION_MAX_PIPES], *label_stage[LEGION_MAX_PIPES];  // device staging for host-provided seeds
+    int32_t *h_stage[LEGION_MAX_PIPES];  // pinned host staging: seeds, labels, then both counter arrays
+    // seed rows that the copy engine staged for the batch about to be gathered (set by the runner, else null)
+    const uint8_t *stage_rows;
+    const int32_t *stage_pos;
+    int32_t stage_base, stage_n;
     // batch state
     int32_t iter, mode, pipe;
     uint32_t global_batch;

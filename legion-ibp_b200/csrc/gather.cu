@@ -39,7 +39,22 @@ struct GatherParams {
     int2 *miss_rows;     // (position in ids, host table row) of rows whose source is the host table
     int32_t *miss_count; // [0] number of entries
     int32_t *err;        // device error word of the pipe (sticky), or nullptr
+    // rows of uncached seeds that the copy engine staged in device memory for this batch: entry r < stage_n of the
+    // id list, when it misses the cache, is row stage_pos[r] - stage_base of stage_rows (nullptr: no staging)
+    const uint8_t *stage_rows;
+    const int32_t *stage_pos;
+    int32_t stage_base, stage_n;
 };
+
+// A missed row that sits in the batch's staging area is served from there like a cached row; `where` 4 keeps
+// it out of the hit / miss counters and off the miss list.
+__device__ __forceinline__ void use_staged(const GatherParams &p, int index, int &where, const uint8_t *&src)
+{
+    if (where == 2 && p.stage_rows != nullptr && index < p.stage_n) {
+        src = p.stage_rows + (int64_t)(__ldg(&p.stage_pos[index]) - p.stage_base) * p.row_bytes;
+        where = 4;
+    }
+}
 
 __device__ __forceinline__ const uint8_t *shfl_ptr(const uint8_t *p, int src)
 {
@@ -193,6 +208,7 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
         int where;
         const uint8_t *src = decode_raw(p, id, raw, gidx, where, host_row);
         if (r < n) p.cache_index[off + r] = gidx;
+        use_staged(p, off + r, where, src);
         add_stats(p.stats, where, lane);
         defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
         const int rows_here = min(32, n - c * 32);
@@ -351,6 +367,7 @@ __global__ void __launch_bounds__(256) gather_word_kernel(GatherParams p)
         int where;
         const uint8_t *src = resolve(p, id, gidx, where, host_row);
         if (r < n) p.cache_index[off + r] = gidx;
+        use_staged(p, off + r, where, src);
         add_stats(p.stats, where, lane);
         defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
         const int rows_here = min(32, n - c * 32);
@@ -855,6 +872,13 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
     gp.miss_rows = p->miss_rows[pipe];
     gp.miss_count = p->miss_count[pipe];
     gp.err = p->ctl[pipe] + CTL_ERROR;
+    // staged seed rows are only meaningful for a launch that starts at the seeds, over uncompressed rows
+    const bool staged = p->stage_rows != nullptr && (op_id == kOpGatherAll || op_id == 1) && c != nullptr &&
+                        c->codec == LEGION_CODEC_RAW && g_gather_engine == 0;
+    gp.stage_rows = staged ? p->stage_rows : nullptr;
+    gp.stage_pos = staged ? p->stage_pos : nullptr;
+    gp.stage_base = staged ? p->stage_base : 0;
+    gp.stage_n = staged ? p->stage_n : 0;
 
     // the bulk-copy engine has only ever read this GPU's own memory: a clique of more than one GPU keeps the register path
     if (g_gather_engine == 1 && gp.kg == 1 && (c == nullptr || c->codec == LEGION_CODEC_RAW) && row_bytes % 16 == 0 &&
@@ -1067,6 +1091,9 @@ extern "C" int legion_gather_rows_noalloc(void *stream, int32_t dev_id, const in
     gp.cache_index = reinterpret_cast<int32_t *>(scratch + kNaCacheIndex);
     gp.stats = nullptr;
     gp.err = nullptr;
+    gp.stage_rows = nullptr;
+    gp.stage_pos = nullptr;
+    gp.stage_base = gp.stage_n = 0;
     gp.row_bytes = row_bytes;
     gp.slot_bytes = row_bytes;
     gp.feature_len = row_bytes / 4;

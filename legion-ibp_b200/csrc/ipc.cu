@@ -228,6 +228,7 @@ extern "C" int legion_ipc_publish_pool(LegionIpcEnv *e, LegionPool *pool, int32_
 {
     LG_ARG(e != nullptr && pool != nullptr, "NULL handle");
     LG_ARG(dev_id >= 0 && dev_id < LEGION_MAX_DEVICE, "dev_id out of range");
+    LG_ARG(pool->pipes <= LEGION_INTERBATCH_CON, "the hand-off segment has two slots per device: create the pool with at most 2 pipes");
     LG_CUDA(cudaSetDevice(pool->dev_id));
     for (int i = 0; i < pool->pipes; ++i) {
         void *bufs[LEGION_MEMORY_USAGE] = { pool->ids[i], pool->features[i], pool->labels[i], pool->agg_src[i],

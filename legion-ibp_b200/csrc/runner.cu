@@ -66,13 +66,13 @@ struct LegionRunner {
     LegionPool *pool;
     LegionIpcEnv *env;
     cudaStream_t s_sample, s_gather, s_miss;
-    cudaStream_t s_launch[LEGION_INTERBATCH_CON];
-    cudaEvent_t hit_done[LEGION_INTERBATCH_CON];   // lookup + gather of the pipe's batch is over
-    cudaEvent_t pipe_done[LEGION_INTERBATCH_CON];
-    bool pipe_busy[LEGION_INTERBATCH_CON];
+    cudaStream_t s_launch[LEGION_MAX_PIPES];
+    cudaEvent_t hit_done[LEGION_MAX_PIPES];   // lookup + gather of the pipe's batch is over
+    cudaEvent_t pipe_done[LEGION_MAX_PIPES];
+    bool pipe_busy[LEGION_MAX_PIPES];
     int current_pipe, last_pipe;
     bool use_graph, time_kernels;
-    PipeGraph pg[LEGION_INTERBATCH_CON];
+    PipeGraph pg[LEGION_MAX_PIPES];
     // timing of the batches enqueued since the last sync
     cudaEvent_t t_begin, t_end;
     bool open_window;
@@ -85,19 +85,29 @@ struct LegionRunner {
     long long served;
     double served_us;
     // host-buffer batches submitted and not yet collected (oldest first)
-    int host_fifo[LEGION_INTERBATCH_CON + 1];
-    int32_t host_seeds[LEGION_INTERBATCH_CON + 1];
+    int host_fifo[LEGION_MAX_PIPES + 1];
+    int32_t host_seeds[LEGION_MAX_PIPES + 1];
     int host_pending;
     cudaStream_t s_copy;
     // pinned host buffers that the batch on a pipe exports its block structure into (submit_host_to)
-    HostOut host_out[LEGION_INTERBATCH_CON + 1];   // of the submitted batches, oldest first (parallel to host_fifo)
-    int64_t host_spec_nodes[LEGION_INTERBATCH_CON + 1], host_spec_edges[LEGION_INTERBATCH_CON + 1];  // elements copied ahead
-    bool host_exported[LEGION_INTERBATCH_CON + 1];  // every element of the block structure is on the host
+    HostOut host_out[LEGION_MAX_PIPES + 1];   // of the submitted batches, oldest first (parallel to host_fifo)
+    int64_t host_spec_nodes[LEGION_MAX_PIPES + 1], host_spec_edges[LEGION_MAX_PIPES + 1];  // elements copied ahead
+    bool host_exported[LEGION_MAX_PIPES + 1];  // every element of the block structure is on the host
     int64_t spec_nodes, spec_edges;                 // sizes to copy ahead: the largest batch seen so far plus a margin
-    bool host_bound[LEGION_INTERBATCH_CON + 1];  // of the submitted batches, oldest first (parallel to host_fifo)
+    bool host_bound[LEGION_MAX_PIPES + 1];  // of the submitted batches, oldest first (parallel to host_fifo)
     bool host_deferred;                          // the newest submitted batch still lacks its back half
     bool host_released;                          // ... and the batch that held its pipe has been collected
-    cudaEvent_t sampled[LEGION_INTERBATCH_CON], exported[LEGION_INTERBATCH_CON];
+    cudaEvent_t sampled[LEGION_MAX_PIPES], exported[LEGION_MAX_PIPES];
+    // seed-row staging (stage.cu): one staging per mode's device-resident list, one for a registered host list
+    legion::SeedStage stage[4];
+    uint8_t *seed_rows[LEGION_MAX_PIPES];   // device: the staged rows of the batch on each pipe
+    cudaStream_t s_h2d;                     // copy-engine transfers of staged rows
+    cudaEvent_t staged_ev[LEGION_MAX_PIPES];
+    bool hit_recorded[LEGION_MAX_PIPES];    // hit_done[pipe] has been recorded at least once
+    const legion::SeedStage *pipe_stage[LEGION_MAX_PIPES];  // staging used by the batch on the pipe, or nullptr
+    int64_t pipe_stage_first[LEGION_MAX_PIPES];
+    int32_t pipe_stage_n[LEGION_MAX_PIPES];
+    long long staged_rows;
 };
 
 using namespace legion;
@@ -135,6 +145,7 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
                                     LegionCache *cache, LegionPool *pool, LegionIpcEnv *env)
 {
     LG_ARG(out != nullptr && graph != nullptr && feature != nullptr && pool != nullptr, "NULL handle");
+    LG_ARG(env == nullptr || pool->pipes <= LEGION_INTERBATCH_CON, "a runner that serves trainers needs a pool of at most 2 pipes");
     LG_CUDA(cudaSetDevice(dev_id));
     LegionRunner *r = new LegionRunner();
     r->dev_id = dev_id;
@@ -155,7 +166,7 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     r->served_us = 0.0;
     r->host_pending = 0;
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_copy, cudaStreamNonBlocking));
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
         LG_CUDA(cudaEventCreateWithFlags(&r->sampled[i], cudaEventDisableTiming));
         LG_CUDA(cudaEventCreateWithFlags(&r->exported[i], cudaEventDisableTiming));
         r->host_bound[i] = false;
@@ -163,6 +174,15 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     r->host_deferred = false;
     r->host_released = false;
     r->spec_nodes = r->spec_edges = 0;
+    memset(r->stage, 0, sizeof(r->stage));
+    r->staged_rows = 0;
+    LG_CUDA(cudaStreamCreateWithFlags(&r->s_h2d, cudaStreamNonBlocking));
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
+        r->seed_rows[i] = nullptr;
+        r->hit_recorded[i] = false;
+        r->pipe_stage[i] = nullptr;
+        LG_CUDA(cudaEventCreateWithFlags(&r->staged_ev[i], cudaEventDisableTiming));
+    }
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_sample, cudaStreamNonBlocking));
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_gather, cudaStreamNonBlocking));
     {
@@ -172,9 +192,9 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
         LG_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
         LG_CUDA(cudaStreamCreateWithPriority(&r->s_miss, cudaStreamNonBlocking, hi));
     }
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i)
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i)
         LG_CUDA(cudaEventCreateWithFlags(&r->hit_done[i], cudaEventDisableTiming));
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
         LG_CUDA(cudaStreamCreateWithFlags(&r->s_launch[i], cudaStreamNonBlocking));
         LG_CUDA(cudaEventCreateWithFlags(&r->pipe_done[i], cudaEventDisableTiming));
         r->pipe_busy[i] = false;
@@ -188,7 +208,7 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
 
 static void drop_graphs(LegionRunner *r)
 {
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
         if (r->pg[i].valid) {
             cudaGraphExecDestroy(r->pg[i].exec);
             cudaGraphDestroy(r->pg[i].graph);
@@ -332,12 +352,31 @@ static int capture_pipe(LegionRunner *r, int pipe, const BatchCtl &v)
 // buffer.  enqueue_ctl issues both at once.  A host-buffer batch with bound outputs may be submitted
 // while both pipes still hold uncollected batches: its front half runs at once, its back half is issued
 // when the older batch on its pipe has been collected (its features released).
-static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, const HostOut *bound, bool pipe_is_held)
+static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, const HostOut *bound, bool pipe_is_held,
+                       const SeedStage *st = nullptr, int64_t st_first = 0)
 {
     LegionPool *p = r->pool;
     LegionCache *c = r->cache;
     const int pipe = r->current_pipe;
     int rc;
+    // Rows of this batch's uncached seeds: one contiguous block of the staging array, brought in by the copy
+    // engine while the batch samples.  The pipe's staging area was last read by the gather of the batch that
+    // used this pipe before (hit_done).
+    r->pipe_stage[pipe] = nullptr;
+    if (st != nullptr && st->valid && c != nullptr && st->cache == c && st->fill_gen == c->fill_gen && v.size > 0 &&
+        st_first >= 0 && st_first + v.size <= st->count && r->seed_rows[pipe] != nullptr) {
+        const int64_t lo = st->pos[st_first], hi = st->pos[st_first + v.size];
+        if (hi > lo) {
+            if (r->hit_recorded[pipe]) LG_CUDA(cudaStreamWaitEvent(r->s_h2d, r->hit_done[pipe], 0));
+            LG_CUDA(cudaMemcpyAsync(r->seed_rows[pipe], st->rows_host + lo * (int64_t)c->row_bytes,
+                                    (size_t)(hi - lo) * c->row_bytes, cudaMemcpyHostToDevice, r->s_h2d));
+        }
+        LG_CUDA(cudaEventRecord(r->staged_ev[pipe], r->s_h2d));
+        r->pipe_stage[pipe] = st;
+        r->pipe_stage_first[pipe] = st_first;
+        r->pipe_stage_n[pipe] = v.size;
+        r->staged_rows += hi - lo;
+    }
     const bool lru = c != nullptr && c->kind == 1;
     cudaStream_t front = r->use_graph ? r->s_launch[pipe] : r->s_sample;
     if (!r->open_window) {
@@ -423,7 +462,17 @@ static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound,
     const bool early_sampling = !lru && host_seeds == 0;
     p->pipe = pipe;
     if (early_sampling && r->pipe_busy[pipe] && !pipe_was_synced) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
+    if (r->pipe_stage[pipe] != nullptr) {
+        const SeedStage *st = r->pipe_stage[pipe];
+        LG_CUDA(cudaStreamWaitEvent(front, r->staged_ev[pipe], 0));
+        p->stage_rows = r->seed_rows[pipe];
+        p->stage_pos = st->pos_dev + r->pipe_stage_first[pipe];
+        p->stage_base = st->pos[r->pipe_stage_first[pipe]];
+        p->stage_n = r->pipe_stage_n[pipe];
+    }
     rc = issue_gather(r, front);
+    p->stage_rows = nullptr;
+    p->stage_pos = nullptr;
     if (rc != LEGION_OK) return rc;
     if (host_seeds > 0 || r->env != nullptr) {
         // the counters are final once the lookup has left its snapshot words; copied on this stream so
@@ -433,6 +482,7 @@ static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound,
         LG_CUDA(cudaMemcpyAsync(hc + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, front));
     }
     LG_CUDA(cudaEventRecord(r->hit_done[pipe], front));
+    r->hit_recorded[pipe] = true;
     LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->hit_done[pipe], 0));
     rc = issue_back(r);
     if (rc != LEGION_OK) return rc;
@@ -445,10 +495,11 @@ static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound,
     return LEGION_OK;
 }
 
-static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, const HostOut *bound = nullptr)
+static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, const HostOut *bound = nullptr,
+                       const SeedStage *st = nullptr, int64_t st_first = 0)
 {
     const int pipe = r->current_pipe;
-    int rc = issue_front(r, v, host_seeds, bound, false);
+    int rc = issue_front(r, v, host_seeds, bound, false, st, st_first);
     if (rc != LEGION_OK) return rc;
     return issue_rest(r, pipe, host_seeds, bound != nullptr, false);
 }
@@ -474,8 +525,10 @@ extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, i
     const int64_t first = (int64_t)bs * local_batch_id;
     int64_t size = ((int64_t)bs * (local_batch_id + 1) >= total_cap) ? (total_cap - first) : bs;  // operator_impl.cu:162
     if (size < 0) size = 0;
+    const SeedStage *st = (r->stage[mode].valid && r->stage[mode].ids_dev == r->feature->ids[mode] &&
+                           r->stage[mode].count == total_cap) ? &r->stage[mode] : nullptr;
     return enqueue_ctl(r, make_batch_ctl(p, r->cache, r->feature->ids[mode], r->feature->labels[mode], total_cap, first,
-                                         (int32_t)size, r->graph->n_nodes), 0);
+                                         (int32_t)size, r->graph->n_nodes), 0, nullptr, st, first);
 }
 
 // Host-buffer interface with batches in flight.  submit copies the seeds in and starts the batch;
@@ -599,11 +652,20 @@ static int submit_host_impl(LegionRunner *r, const int32_t *seeds, const int32_t
     const BatchCtl v = make_batch_ctl(p, r->cache, p->seed_stage[pipe], p->label_stage[pipe], n_seeds, 0, n_seeds,
                                       r->graph->n_nodes);
     const int64_t spec_n = r->spec_nodes, spec_e = r->spec_edges;  // what issue_front copies ahead
+    // a batch that is a slice of the registered host list (by address, and still holding what the list held
+    // at registration) gets the rows of its uncached seeds by the copy engine
+    const SeedStage *st = nullptr;
+    int64_t st_first = 0;
+    const SeedStage &hs = r->stage[3];
+    if (hs.valid && hs.host_base != nullptr && seeds >= hs.host_base && seeds + n_seeds <= hs.host_base + hs.count) {
+        st_first = seeds - hs.host_base;
+        if (memcmp(seeds, hs.host_copy + st_first, sizeof(int32_t) * (size_t)n_seeds) == 0) st = &hs;
+    }
     if (extra) {
-        rc = issue_front(r, v, n_seeds, bound, true);
+        rc = issue_front(r, v, n_seeds, bound, true, st, st_first);
         if (rc == LEGION_OK) r->host_deferred = true;
     } else {
-        rc = enqueue_ctl(r, v, n_seeds, bound);
+        rc = enqueue_ctl(r, v, n_seeds, bound, st, st_first);
     }
     if (rc != LEGION_OK) return rc;
     r->host_bound[r->host_pending] = bound != nullptr;
@@ -692,7 +754,8 @@ extern "C" int legion_runner_sync(LegionRunner *r)
     LG_CUDA(cudaStreamSynchronize(r->s_sample));
     LG_CUDA(cudaStreamSynchronize(r->s_gather));
     LG_CUDA(cudaStreamSynchronize(r->s_miss));
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) LG_CUDA(cudaStreamSynchronize(r->s_launch[i]));
+    LG_CUDA(cudaStreamSynchronize(r->s_h2d));
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) LG_CUDA(cudaStreamSynchronize(r->s_launch[i]));
     if (r->open_window) {
         float ms = 0.0f, g = 0.0f, m = 0.0f;
         int timed = 0;
@@ -740,7 +803,7 @@ extern "C" int legion_runner_sync(LegionRunner *r)
         r->last_timed = timed;
         r->open_window = false;
     }
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
         r->pipe_busy[i] = false;
         r->pg[i].launched = false;
     }
@@ -863,6 +926,70 @@ extern "C" int legion_runner_presample(LegionRunner *r, int32_t first_batch, int
     return LEGION_OK;
 }
 
+// ---- seed-row staging ------------------------------------------------------------------------------------
+
+static int stage_prepare(LegionRunner *r, SeedStage *st)
+{
+    LG_ARG(r->cache != nullptr, "the runner has no cache");
+    LG_CUDA(cudaSetDevice(r->dev_id));
+    int rc = legion_runner_sync(r);
+    if (rc != LEGION_OK) return rc;
+    stage_free(st);
+    for (int i = 0; i < r->pool->pipes; ++i) {
+        if (r->seed_rows[i] == nullptr)
+            LG_CUDA(cudaMalloc(reinterpret_cast<void **>(&r->seed_rows[i]), (size_t)r->pool->batch_size * r->pool->row_bytes_out));
+    }
+    return LEGION_OK;
+}
+
+extern "C" int legion_runner_stage_seeds(LegionRunner *r, int32_t mode, int64_t *staged_rows_out)
+{
+    LG_ARG(r != nullptr && mode >= 0 && mode <= 2, "bad argument");
+    LG_ARG(r->feature->ids[mode] != nullptr && r->feature->count[mode] > 0, "no seed list for this mode");
+    LG_ARG(r->host_pending == 0, "host-buffer batches are waiting to be collected");
+    SeedStage *st = &r->stage[mode];
+    int rc = stage_prepare(r, st);
+    if (rc != LEGION_OK) return rc;
+    rc = stage_build(r->cache, r->feature->ids[mode], r->feature->count[mode], r->pool->sm_count, st);
+    if (rc == LEGION_OK && staged_rows_out != nullptr) *staged_rows_out = st->rows;
+    return rc;
+}
+
+extern "C" int legion_runner_register_host_seeds(LegionRunner *r, const int32_t *seeds_host, int32_t count,
+                                                 int64_t *staged_rows_out)
+{
+    LG_ARG(r != nullptr && seeds_host != nullptr && count > 0, "bad argument");
+    LG_ARG(r->host_pending == 0, "host-buffer batches are waiting to be collected");
+    SeedStage *st = &r->stage[3];
+    int rc = stage_prepare(r, st);
+    if (rc != LEGION_OK) return rc;
+    int32_t *dev = nullptr;
+    LG_CUDA(cudaMalloc(reinterpret_cast<void **>(&dev), sizeof(int32_t) * (size_t)count));
+    cudaError_t e = cudaMemcpy(dev, seeds_host, sizeof(int32_t) * (size_t)count, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(dev);
+        LG_CUDA(e);
+    }
+    rc = stage_build(r->cache, dev, count, r->pool->sm_count, st);
+    if (rc != LEGION_OK) {
+        cudaFree(dev);
+        return rc;
+    }
+    st->own_ids_dev = dev;
+    st->host_base = seeds_host;
+    st->host_copy = new int32_t[(size_t)count];
+    memcpy(st->host_copy, seeds_host, sizeof(int32_t) * (size_t)count);
+    if (staged_rows_out != nullptr) *staged_rows_out = st->rows;
+    return LEGION_OK;
+}
+
+extern "C" int legion_runner_staged_rows(LegionRunner *r, int64_t *rows)
+{
+    LG_ARG(r != nullptr && rows != nullptr, "NULL pointer");
+    *rows = r->staged_rows;
+    return LEGION_OK;
+}
+
 extern "C" int legion_runner_destroy(LegionRunner *r)
 {
     if (r == nullptr) return LEGION_OK;
@@ -873,8 +1000,8 @@ extern "C" int legion_runner_destroy(LegionRunner *r)
     for (auto &pr : r->miss_ev) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
     for (auto &pr : r->sample_ev) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
     for (auto e : r->ev_free) cudaEventDestroy(e);
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) cudaEventDestroy(r->hit_done[i]);
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) {
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) cudaEventDestroy(r->hit_done[i]);
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
         cudaEventDestroy(r->pipe_done[i]);
         cudaStreamDestroy(r->s_launch[i]);
     }
@@ -884,7 +1011,10 @@ extern "C" int legion_runner_destroy(LegionRunner *r)
     cudaStreamDestroy(r->s_gather);
     cudaStreamDestroy(r->s_miss);
     cudaStreamDestroy(r->s_copy);
-    for (int i = 0; i < LEGION_INTERBATCH_CON; ++i) { cudaEventDestroy(r->sampled[i]); cudaEventDestroy(r->exported[i]); }
+    cudaStreamDestroy(r->s_h2d);
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) { cudaEventDestroy(r->sampled[i]); cudaEventDestroy(r->exported[i]); }
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) { cudaEventDestroy(r->staged_ev[i]); cudaFree(r->seed_rows[i]); }
+    for (int i = 0; i < 4; ++i) stage_free(&r->stage[i]);
     delete r;
     return LEGION_OK;
 }

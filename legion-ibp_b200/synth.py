@@ -2,7 +2,8 @@
 
 R-MAT topology (a=.57, b=.19, c=.19, d=.05), symmetrised, self loops dropped, duplicate edges
 merged, CSR with int64 offsets and int32 indices as the reference stores it
-(sampling_server/src/include/buildinfo.h:60-61); N(0,1) feature rows; uniform labels; random
+(sampling_server/src/include/buildinfo.h:60-61); bell-shaped feature rows of mean 0 and variance 1 that
+are a pure function of the node id; uniform labels; random
 seed split (dataset/gen_sets.py:62-76).  They stand in for the OGB datasets of
 dataset_info.py:3-18,75-82, which are not available offline.  torch does the generation (on the
 GPU for the large graphs); it is data synthesis, not part of the sampling path.
@@ -63,16 +64,40 @@ def _coprime_multiplier(n):
     return m
 
 
-def features_into(out, seed=0, chunk_rows=1 << 20):
-    """Fills a [N, F] tensor (pinned host or device) with N(0,1) values, chunk by chunk."""
-    n = out.shape[0]
+_M32 = 0xFFFFFFFF
+
+
+def _mix32(h):
+    """murmur3 finaliser on the low 32 bits of an int64 tensor."""
+    h = h ^ (h >> 16)
+    h = (h * 0x85EBCA6B) & _M32
+    h = h ^ (h >> 13)
+    h = (h * 0xC2B2AE35) & _M32
+    return h ^ (h >> 16)
+
+
+def feature_rows(ids, feat_len, seed=0, dtype=torch.float32):
+    """Feature rows of the given node ids, [len(ids), feat_len]: a pure function of (seed, id, column), so
+    that any row of a table of any size can be made again on demand, on the host or on the device, with
+    the same bits.  Every value is the standardised sum of four uniform bytes of a 32-bit hash (mean 0,
+    variance 1, bell-shaped): the stand-in for the N(0,1) features of the benchmark configurations."""
+    x = _mix32((ids.to(torch.int64) ^ ((seed * 0x9E3779B1 + 0x7F4A7C15) & _M32)) & _M32)
+    col = (torch.arange(feat_len, device=ids.device, dtype=torch.int64) * 0x9E3779B9) & _M32
+    h = _mix32((x[:, None] + col[None, :]) & _M32)
+    s = (h & 255) + ((h >> 8) & 255) + ((h >> 16) & 255) + (h >> 24)
+    # sum of four uniform bytes: mean 510, variance 4 * (256^2 - 1) / 12
+    return ((s - 510).to(torch.float32) * (1.0 / 147.80054127)).to(dtype)
+
+
+def features_into(out, seed=0, chunk_rows=1 << 18, row_ids=None, first=0, last=None):
+    """Fills rows [first, last) of a [N, F] tensor (pinned host or device): row r holds the features of
+    node r, or of node row_ids[r] for a table that is not stored in node-id order."""
+    n = out.shape[0] if last is None else last
     dev = "cuda" if torch.cuda.is_available() else "cpu"
-    g = torch.Generator(device=dev)
-    g.manual_seed(seed)
-    for r0 in range(0, n, chunk_rows):
+    for r0 in range(first, n, chunk_rows):
         r1 = min(n, r0 + chunk_rows)
-        blk = torch.randn(r1 - r0, out.shape[1], device=dev, generator=g, dtype=torch.float32).to(out.dtype)
-        out[r0:r1].copy_(blk, non_blocking=False)
+        ids = torch.arange(r0, r1, device=dev) if row_ids is None else row_ids[r0:r1].to(dev)
+        out[r0:r1].copy_(feature_rows(ids, out.shape[1], seed, out.dtype), non_blocking=False)
     return out
 
 

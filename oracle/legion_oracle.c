@@ -671,3 +671,110 @@ int64_t orc_cpu_pipeline(const int64_t *indptr, const int32_t *indices,
     }
     return total;
 }
+
+/* ------------------------------------------------------------------------------------
+ * The same timed CPU baseline with a sampler written for a CPU, not a replay of the GPU's
+ * lock-step algorithm: what a CPU library does for training_backend/dgl_graphsage.py:189-204
+ * (uniform neighbour sampling without replacement, to_block relabelling, index-select).
+ * Per hop the inputs are all nodes found so far, as above.  Picks: the whole list when
+ * deg <= fanout, else Floyd's algorithm (fanout draws, distinct by construction) with a
+ * splitmix64 stream per (batch, hop, input).  Relabelling: one open-addressing map per thread,
+ * sized once and emptied through the list of touched slots.  NOT bit-comparable with the GPU
+ * path (another random stream); it exists to be timed.  Returns the nodes gathered.
+ * ---------------------------------------------------------------------------------- */
+static inline uint64_t orc_splitmix(uint64_t *s)
+{
+    uint64_t z = (*s += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+int64_t orc_cpu_pipeline_native(const int64_t *indptr, const int32_t *indices,
+                                const int32_t *all_ids, const int32_t *all_labels, int32_t total_cap,
+                                int32_t batch_size, int32_t first_iter, int32_t n_batches, int32_t hop_num,
+                                const int32_t *fanout, uint64_t seed, const uint8_t *host_table,
+                                int64_t total_nodes, int64_t row_bytes, int64_t max_nodes, int64_t max_edges,
+                                int32_t threads, uint8_t *features_out,
+                                int32_t *scratch /* threads * (max_nodes + 2*max_edges + batch + 3*map_slots) */,
+                                int64_t map_slots /* power of two >= 2 * max_nodes */)
+{
+    int64_t total = 0;
+    const int64_t per_thread = max_nodes + 2 * max_edges + batch_size + 3 * map_slots;
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+#endif
+#pragma omp parallel reduction(+ : total)
+    {
+        int tid = 0;
+#ifdef _OPENMP
+        tid = omp_get_thread_num();
+#endif
+        int32_t *base = scratch + per_thread * tid;
+        int32_t *ids = base;
+        int32_t *agg_src = ids + max_nodes;
+        int32_t *agg_dst = agg_src + max_edges;
+        int32_t *labels = agg_dst + max_edges;
+        int32_t *mkey = labels + batch_size;
+        int32_t *mval = mkey + map_slots;
+        int32_t *touched = mval + map_slots;
+        const uint32_t mask = (uint32_t)(map_slots - 1);
+        for (int64_t i = 0; i < map_slots; ++i) mkey[i] = -1;
+        uint8_t *out = features_out + (int64_t)tid * max_nodes * row_bytes;
+#pragma omp for schedule(dynamic, 1)
+        for (int32_t b = 0; b < n_batches; ++b) {
+            const int64_t first = (int64_t)batch_size * (first_iter + b);
+            int64_t size = first + batch_size >= total_cap ? total_cap - first : batch_size;
+            if (size <= 0) continue;
+            int64_t n_nodes = 0, n_edges = 0, n_touched = 0;
+            for (int64_t i = 0; i < size; ++i) {
+                const int32_t v = all_ids[first + i];
+                labels[i] = all_labels[first + i];
+                uint32_t s = orc_mix((uint32_t)v) & mask;
+                while (mkey[s] != -1 && mkey[s] != v) s = (s + 1) & mask;
+                if (mkey[s] == -1) { mkey[s] = v; mval[s] = (int32_t)n_nodes; touched[n_touched++] = (int32_t)s; }
+                ids[n_nodes++] = v;
+            }
+            for (int32_t h = 0; h < hop_num; ++h) {
+                const int64_t n_in = n_nodes;
+                const int32_t k = fanout[h];
+                for (int64_t i = 0; i < n_in; ++i) {
+                    const int32_t v = ids[i];
+                    if (v < 0) continue;
+                    const int64_t s0 = indptr[v];
+                    const int64_t deg = indptr[v + 1] - s0;
+                    int32_t pick[ORC_MAX_FANOUT];
+                    int32_t m = 0;
+                    if (deg <= k) {
+                        for (int64_t j = 0; j < deg; ++j) pick[m++] = (int32_t)j;
+                    } else {
+                        uint64_t st = seed ^ ((uint64_t)(first_iter + b) << 40) ^ ((uint64_t)h << 34) ^ (uint64_t)i;
+                        for (int64_t j = deg - k; j < deg; ++j) {  /* Floyd: k distinct values of [0, deg) */
+                            int32_t t = (int32_t)(orc_splitmix(&st) % (uint64_t)(j + 1));
+                            int dup = 0;
+                            for (int32_t q = 0; q < m; ++q) if (pick[q] == t) { dup = 1; break; }
+                            pick[m++] = dup ? (int32_t)j : t;
+                        }
+                    }
+                    for (int32_t q = 0; q < m; ++q) {
+                        const int32_t u = indices[s0 + pick[q]];
+                        uint32_t s = orc_mix((uint32_t)u) & mask;
+                        while (mkey[s] != -1 && mkey[s] != u) s = (s + 1) & mask;
+                        if (mkey[s] == -1) {
+                            mkey[s] = u; mval[s] = (int32_t)n_nodes; touched[n_touched++] = (int32_t)s;
+                            ids[n_nodes++] = u;
+                        }
+                        agg_src[n_edges] = mval[s];
+                        agg_dst[n_edges] = (int32_t)i;
+                        ++n_edges;
+                    }
+                }
+            }
+            for (int64_t r = 0; r < n_nodes; ++r)
+                memcpy(out + r * row_bytes, host_table + ((int64_t)ids[r] % total_nodes) * row_bytes, (size_t)row_bytes);
+            for (int64_t t = 0; t < n_touched; ++t) mkey[touched[t]] = -1;
+            total += n_nodes;
+        }
+    }
+    return total;
+}

@@ -44,6 +44,7 @@ def lib():
         _lib.orc_float_to_e4m3.argtypes = [C.c_float]
         _lib.orc_lru_insert.restype = C.c_int64
         _lib.orc_cpu_pipeline.restype = C.c_int64
+        _lib.orc_cpu_pipeline_native.restype = C.c_int64
         _lib.orc_num_threads.restype = C.c_int
     return _lib
 
@@ -286,3 +287,27 @@ def cpu_pipeline(indptr, indices, all_ids, all_labels, batch_size, first_iter, n
                                       _p(host_table), C.c_int64(host_table.shape[0]), C.c_int64(row_bytes),
                                       C.c_int64(max_nodes), C.c_int64(max_edges), C.c_int32(t), _p(feat),
                                       _p(scratch)))
+
+
+def cpu_pipeline_native(indptr, indices, all_ids, all_labels, batch_size, first_iter, n_batches, fanout, seed,
+                        host_table, threads=0):
+    """Timed CPU baseline with a sampler written for a CPU (Floyd's algorithm, a reusable relabelling map
+    per thread); another random stream than the GPU path, so it is timed, not compared.  Returns nodes gathered."""
+    indptr, indices = _i64(indptr), _i32(indices)
+    all_ids, all_labels = _i32(all_ids), _i32(all_labels)
+    fan = _i32(fanout)
+    host_table = np.ascontiguousarray(host_table)
+    row_bytes = host_table.strides[0]
+    t = threads if threads > 0 else num_threads()
+    max_nodes, max_edges = batch_bounds(batch_size, list(fanout))
+    slots = 1024
+    while slots < 2 * max_nodes:
+        slots *= 2
+    feat = np.empty(t * max_nodes * row_bytes, dtype=np.uint8)
+    scratch = np.empty(t * (max_nodes + 2 * max_edges + batch_size + 3 * slots), dtype=np.int32)
+    return int(lib().orc_cpu_pipeline_native(_p(indptr), _p(indices), _p(all_ids), _p(all_labels),
+                                             C.c_int32(len(all_ids)), C.c_int32(batch_size), C.c_int32(first_iter),
+                                             C.c_int32(n_batches), C.c_int32(len(fan)), _p(fan), C.c_uint64(seed),
+                                             _p(host_table), C.c_int64(host_table.shape[0]), C.c_int64(row_bytes),
+                                             C.c_int64(max_nodes), C.c_int64(max_edges), C.c_int32(t), _p(feat),
+                                             _p(scratch), C.c_int64(slots)))

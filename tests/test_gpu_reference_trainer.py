@@ -27,16 +27,20 @@ pytestmark = pytest.mark.gpu
 EXT = os.path.join(ROOT, "oracle", "_ref", "ipc_service.so")
 
 TRAINER = r'''
-import importlib.util, sys, numpy as np, torch
+import faulthandler, importlib.util, sys, numpy as np, torch
+faulthandler.enable()
 ext_path, feat_len, total, out_path = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
 torch.cuda.set_device(0)
 torch.zeros(1, device="cuda")          # the extension expects a live context on the trainer's device
 spec = importlib.util.spec_from_file_location("ipc_service", ext_path)
 ipc_service = importlib.util.module_from_spec(spec)
 spec.loader.exec_module(ipc_service)
+print("initialize", flush=True)
 ipc_service.initialize()
+print("initialized", flush=True)
 res = {"steps": np.array(ipc_service.get_steps(), np.int32)}
 for b in range(total):
+    print("get_next", b, flush=True)
     t = ipc_service.get_next(feat_len)          # ids, features, labels, then (src, dst) per hop, last hop first
     res["blocks%d" % b] = np.array(ipc_service.get_block_size(), np.int32)
     res["n%d" % b] = np.array([len(t)], np.int32)

@@ -670,3 +670,108 @@ def test_partition_without_shareable_memory_needs_peer_access(oracle_mod, monkey
         assert rc == 0                 # peer access of device 1 to device 0 is on now
         assert L.lib().legion_enable_peer_access(1, 0) == 0   # already enabled is not an error
     c.close()
+
+
+@pytest.mark.parametrize("use_graph", [True, False])
+def test_seed_rows_staged_by_the_copy_engine_give_the_same_batches(oracle_mod, use_graph):
+    """With seed staging the rows of uncached seeds arrive by a copy-engine transfer from a page-locked
+    array in list order instead of zero-copy loads; every output must stay bit-identical, the staged rows
+    must no longer be counted (or fetched) as misses, and the last, shorter batch of the list must work."""
+    w = _world(oracle_mod, seed=21)
+    r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], None)
+    r.set_options(use_graph=use_graph)
+    lut = oracle_mod.static_cache_lut(oracle_mod.degree_order(w["indptr"]), int(w["n"] * 0.3), 1)
+    uncached_seed = lut[w["train"]] < 0
+    staged_total = r.stage_seeds(L.TRAINMODE)
+    assert staged_total == int(uncached_seed.sum()) and staged_total > 0
+    n_batches = (len(w["train"]) + w["batch"] - 1) // w["batch"]      # includes the shorter last batch
+    s0 = w["cache"].stats()
+    want_staged = 0
+    for it in range(0, n_batches - 1, 2):
+        r.enqueue(it, L.TRAINMODE, it)
+        r.enqueue(it + 1, L.TRAINMODE, it + 1)
+        r.sync()
+        _check_pipe(oracle_mod, w, 0, it, it)
+        _check_pipe(oracle_mod, w, 1, it + 1, it + 1)
+        want_staged += int(uncached_seed[it * w["batch"]:(it + 2) * w["batch"]].sum())
+    assert r.staged_rows() == want_staged
+    # the tail batch (5 seeds)
+    r.RunOnce(40, L.TRAINMODE, n_batches - 1)
+    ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], w["batch"], n_batches - 1, w["fanout"], 40, 99)
+    for pipe in (0, 1):
+        nc = w["pool"].read(L.BUF_NODE_COUNTER, pipe, 16, np.int32)
+        if np.array_equal(nc, ref["node_counter"]):
+            feat = w["pool"].read(L.BUF_FEATURES, pipe, len(ref["ids"]) * 128, np.float32).reshape(-1, 128)
+            np.testing.assert_array_equal(feat, w["table"][ref["ids"]])
+            break
+    else:
+        raise AssertionError("the tail batch is in neither pipe")
+    # staged rows are neither hits nor misses in the cache's counters: fewer misses than uncached rows
+    s1 = w["cache"].stats()
+    assert s1["misses"] - s0["misses"] > 0
+    assert w["pool"].device_error() == 0
+    # a refill invalidates the staging: batches still come out right, nothing is staged any more
+    w["cache"].fill_static(w["d_order"], w["h_table"])
+    before = r.staged_rows()
+    r.enqueue(50, L.TRAINMODE, 1)
+    r.sync()
+    assert r.staged_rows() == before
+    r.Finalize()
+
+
+def test_registered_host_seed_list_is_staged_by_address(oracle_mod):
+    """submit_host[_to] with a slice of a registered host list: staged; the same call with a copy of the
+    slice, or after the caller changed the list, takes the zero-copy path; the results are identical."""
+    w = _world(oracle_mod, seed=22)
+    r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], None)
+    b, f = w["batch"], w["table"].shape[1]
+    seeds = w["train"].copy()
+    labels = w["labels"].copy()
+    r.register_host_seeds(seeds)
+    mn, me = w["pool"].max_nodes, w["pool"].max_edges
+
+    def run(seed_arr, it, gb):
+        ids, lab = np.empty(mn, np.int32), np.empty(b, np.int32)
+        src, dst = np.empty(me, np.int32), np.empty(me, np.int32)
+        nc, ec = np.zeros(16, np.int32), np.zeros(16, np.int32)
+        feat = np.zeros((mn, f), np.float32)
+        r.submit_host(seed_arr, labels[it * b:(it + 1) * b], gb)
+        nn, ne = r.collect_host(ids, lab, src, dst, nc, ec, feat)
+        ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], b, it, w["fanout"], gb, 99)
+        np.testing.assert_array_equal(ids[:nn], ref["ids"])
+        np.testing.assert_array_equal(src[:ne], ref["agg_src"])
+        np.testing.assert_array_equal(dst[:ne], ref["agg_dst"])
+        np.testing.assert_array_equal(nc, ref["node_counter"])
+        np.testing.assert_array_equal(feat[:nn], w["table"][ref["ids"]])
+
+    n0 = r.staged_rows()
+    run(seeds[2 * b:3 * b], 2, 7)                 # a slice of the registered array
+    n1 = r.staged_rows()
+    assert n1 > n0
+    run(seeds[2 * b:3 * b].copy(), 2, 7)          # the same ids somewhere else in memory
+    assert r.staged_rows() == n1
+    # three staged batches in flight
+    mn_ids = [np.empty(mn, np.int32) for _ in range(2)]
+    for k in range(2):
+        r.submit_host(seeds[k * b:(k + 1) * b], labels[k * b:(k + 1) * b], 20 + k)
+    nc, ec = np.zeros(16, np.int32), np.zeros(16, np.int32)
+    for k in range(2):
+        feat = np.zeros((mn, f), np.float32)
+        nn, ne = r.collect_host(mn_ids[k], None, None, None, nc, ec, feat)
+        ref = oracle_mod.run_batch(w["indptr"], w["indices"], w["train"], w["labels"], b, k, w["fanout"], 20 + k, 99)
+        np.testing.assert_array_equal(mn_ids[k][:nn], ref["ids"])
+        np.testing.assert_array_equal(feat[:nn], w["table"][ref["ids"]])
+    assert r.staged_rows() > n1
+    # the caller overwrites a seed inside the registered array: that slice no longer matches the staging
+    n2 = r.staged_rows()
+    old = seeds[4 * b + 3]
+    seeds[4 * b + 3] = seeds[0]
+    ids, nc, ec = np.empty(mn, np.int32), np.zeros(16, np.int32), np.zeros(16, np.int32)
+    feat = np.zeros((mn, f), np.float32)
+    r.submit_host(seeds[4 * b:5 * b], labels[4 * b:5 * b], 30)
+    nn, _ = r.collect_host(ids, None, None, None, nc, ec, feat)
+    assert r.staged_rows() == n2
+    np.testing.assert_array_equal(feat[:nn], w["table"][ids[:nn]])
+    seeds[4 * b + 3] = old
+    assert w["pool"].device_error() == 0
+    r.Finalize()
