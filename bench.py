@@ -869,6 +869,7 @@ def main():
     e2e_steps = min(e2e_steps, 20000)
     barrier()
     staged_e2e0 = runner.staged_rows() if staging else 0
+    runner.host_times()
     t0 = time.perf_counter()
     d2h = 0
     for i in range(depth):
@@ -882,6 +883,7 @@ def main():
         d2h += 4 * nn + 8 * ne + 4 * b + 128
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
+    ht = runner.host_times()
     barrier()
     staged_e2e = (runner.staged_rows() - staged_e2e0) if staging else 0
     # floor of the export: every rank copies device -> pinned host at the same time
@@ -895,6 +897,9 @@ def main():
     e2e = {"value": e2e_value, "unit": "batches/s", "h2d_bytes_per_step": 8 * b + staged_e2e * row_bytes // e2e_steps,
            "d2h_bytes_per_step": d2h_per_step, "steps": e2e_steps,
            "api": "legion_runner_submit_host_to / legion_runner_collect_host, %d batches in flight" % depth,
+           "host_us_per_step": {"submit": ht["submit_us"] / max(1.0, ht["batches"]), "collect": ht["collect_us"] / max(1.0, ht["batches"]),
+                                "of_which_waiting_for_the_device": ht["collect_wait_us"] / max(1.0, ht["batches"]),
+                                "wall": e2e_s / e2e_steps * 1e6},
            "note": "seeds+labels copied in from host memory (and, with seed staging, the rows of uncached seeds by the copy "
                    "engine), ids/labels/edge lists/counters written to page-locked host memory every step; gathered rows "
                    "stay in the device hand-off buffer where the trainer reads them; missed rows cross the host link "

@@ -66,7 +66,8 @@ int legion_host_register(int32_t dev_id, void *ptr, int64_t bytes);
 /* Launch-shape knobs for measurements (the reference hard-codes its grids, e.g. cache/cache.cu:746-752).
  * "miss_ctas": CTAs of the host-link fetch kernel, 0 = one per SM. */
 int legion_set_tunable(const char *name, int32_t value);
-/* Names: "miss_ctas", "miss_threads" (launch shape of the host-link fetch); "gather_ctas_per_sm",
+/* Names: "miss_ctas", "miss_threads", "miss_rows" (launch shape of the host-link fetch and the rows a warp keeps
+ * in flight: 1, 2, 4 or 8); "gather_ctas_per_sm",
  * "gather_rows_in_flight" (2/4/8/16, register path); "gather_engine" 0 = rows move through registers,
  * 1 = rows move by bulk asynchronous copies through shared memory (start value from the environment
  * variable LEGION_GATHER_ENGINE); "pdl" 1 = the sampling kernels of a batch are launched as programmatic
@@ -452,6 +453,10 @@ int legion_runner_submit_host_to(LegionRunner *r, const int32_t *seeds, const in
 int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
                                int32_t *agg_dst_out, int32_t node_counter_out[16], int32_t edge_counter_out[16],
                                void *features_out);
+/* Host time spent inside submit / collect since the last call of this function (microseconds): out[0]
+ * submit, out[1] collect, out[2] the part of collect spent waiting for the device, out[3] batches submitted
+ * (the per-op times of the reference's MONITOR build, engine/server.cu:346-395, for the host side). */
+int legion_runner_host_times(LegionRunner *r, double out[4]);
 int legion_runner_current_pipe(LegionRunner *r);
 /* The presampling epoch (GPUServer::PreSc / GPURunner::RunPreSc, engine/server.cu:94-122,313-328): samples
  * training batches [first_batch, first_batch+count) without lookup or gather and counts every node they

@@ -483,6 +483,12 @@ class Runner:
         _check(lib().legion_runner_staged_rows(self.h, C.byref(n)))
         return n.value
 
+    def host_times(self):
+        """Host microseconds inside submit / collect since the last call: dict(submit, collect, collect_wait, batches)."""
+        a = (C.c_double * 4)()
+        _check(lib().legion_runner_host_times(self.h, a))
+        return dict(submit_us=a[0], collect_us=a[1], collect_wait_us=a[2], batches=a[3])
+
     def current_pipe(self):
         return lib().legion_runner_current_pipe(self.h)
 

@@ -935,6 +935,7 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
 
 int g_miss_ctas = 0;     // 0 = default; see legion_set_tunable
 int g_miss_threads = 0;  // 0 = default
+int g_miss_rows = 0;     // rows a warp of the fetch keeps in flight (0 = default, 4)
 
 // The rows the hit kernels listed so far, fetched from the pinned host table; empties the list.
 // No-op without a host table.
@@ -960,6 +961,9 @@ int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c)
     int grid = (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
     if (c->host_codec == LEGION_CODEC_INT8) gather_miss_quant_kernel<LEGION_CODEC_INT8, 8><<<grid, threads, 0, s>>>(mp);
     else if (c->host_codec == LEGION_CODEC_E4M3) gather_miss_quant_kernel<LEGION_CODEC_E4M3, 8><<<grid, threads, 0, s>>>(mp);
+    else if (g_miss_rows == 1) gather_miss_kernel<1><<<grid, threads, 0, s>>>(mp);
+    else if (g_miss_rows == 2) gather_miss_kernel<2><<<grid, threads, 0, s>>>(mp);
+    else if (g_miss_rows == 8) gather_miss_kernel<8><<<grid, threads, 0, s>>>(mp);
     else gather_miss_kernel<4><<<grid, threads, 0, s>>>(mp);
     LG_LAUNCH_CHECK();
     return LEGION_OK;
@@ -1147,6 +1151,11 @@ extern "C" int legion_set_tunable(const char *name, int32_t value)
     if (strcmp(name, "miss_threads") == 0) {
         LG_ARG(value == 0 || (value >= 32 && value <= 1024 && value % 32 == 0), "miss_threads must be a multiple of 32 up to 1024");
         g_miss_threads = value;
+        return LEGION_OK;
+    }
+    if (strcmp(name, "miss_rows") == 0) {
+        LG_ARG(value == 0 || value == 1 || value == 2 || value == 4 || value == 8, "miss_rows must be 0, 1, 2, 4 or 8");
+        g_miss_rows = value;
         return LEGION_OK;
     }
     if (strcmp(name, "map_front_shift") == 0) {

@@ -108,7 +108,17 @@ struct LegionRunner {
     int64_t pipe_stage_first[LEGION_MAX_PIPES];
     int32_t pipe_stage_n[LEGION_MAX_PIPES];
     long long staged_rows;
+    // host time spent inside submit / collect since the last reset (us): [0] submit, [1] collect, [2] of which waiting
+    // for the device, [3] calls
+    double host_us[4];
 };
+
+static inline double now_us()
+{
+    struct timespec t;
+    clock_gettime(CLOCK_MONOTONIC, &t);
+    return t.tv_sec * 1e6 + t.tv_nsec * 1e-3;
+}
 
 using namespace legion;
 
@@ -176,6 +186,7 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     r->spec_nodes = r->spec_edges = 0;
     memset(r->stage, 0, sizeof(r->stage));
     r->staged_rows = 0;
+    r->host_us[0] = r->host_us[1] = r->host_us[2] = r->host_us[3] = 0.0;
     LG_CUDA(cudaStreamCreateWithFlags(&r->s_h2d, cudaStreamNonBlocking));
     for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
         r->seed_rows[i] = nullptr;
@@ -543,7 +554,11 @@ static int finish_export(LegionRunner *r, int i)
     if (!r->host_bound[i] || r->host_exported[i]) return LEGION_OK;
     LegionPool *p = r->pool;
     const int pipe = r->host_fifo[i];
-    LG_CUDA(cudaEventSynchronize(r->exported[pipe]));
+    {
+        const double w0 = now_us();
+        LG_CUDA(cudaEventSynchronize(r->exported[pipe]));
+        r->host_us[2] += now_us() - w0;
+    }
     const int32_t *early = p->h_stage[pipe] + 2 * (size_t)p->batch_size + 32;
     const int hops = early[LEGION_INTRABATCH_CON * 3 - 1];
     const int64_t n_nodes = early[LEGION_INTRABATCH_CON * 3 + hops];
@@ -616,7 +631,22 @@ extern "C" int legion_runner_submit_host_to(LegionRunner *r, const int32_t *seed
     return submit_host_impl(r, seeds, labels, n_seeds, global_batch_id, &b);
 }
 
+static int submit_host_body(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                            int32_t global_batch_id, const HostOut *bound);
+
 static int submit_host_impl(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
+                            int32_t global_batch_id, const HostOut *bound)
+{
+    const double t0 = now_us();
+    int rc = submit_host_body(r, seeds, labels, n_seeds, global_batch_id, bound);
+    if (r != nullptr) {
+        r->host_us[0] += now_us() - t0;
+        r->host_us[3] += 1.0;
+    }
+    return rc;
+}
+
+static int submit_host_body(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
                             int32_t global_batch_id, const HostOut *bound)
 {
     LG_ARG(r != nullptr && seeds != nullptr && labels != nullptr, "NULL pointer");
@@ -679,9 +709,36 @@ static int submit_host_impl(LegionRunner *r, const int32_t *seeds, const int32_t
     return LEGION_OK;
 }
 
+static int collect_host_body(LegionRunner *r, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
+                             int32_t *agg_dst_out, int32_t node_counter_out[16], int32_t edge_counter_out[16],
+                             void *features_out);
+
 extern "C" int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
                                           int32_t *agg_dst_out, int32_t node_counter_out[16],
                                           int32_t edge_counter_out[16], void *features_out)
+{
+    const double t0 = now_us();
+    int rc = collect_host_body(r, ids_out, labels_out, agg_src_out, agg_dst_out, node_counter_out, edge_counter_out, features_out);
+    if (r != nullptr) r->host_us[1] += now_us() - t0;
+    return rc;
+}
+
+// Host time inside legion_runner_submit_host[_to] and legion_runner_collect_host since the last call of this
+// function, in microseconds: out[0] submit, out[1] collect, out[2] the part of collect spent waiting for the
+// device, out[3] batches submitted.  Tells a host-bound hand-off from a device-bound one.
+extern "C" int legion_runner_host_times(LegionRunner *r, double out[4])
+{
+    LG_ARG(r != nullptr && out != nullptr, "NULL pointer");
+    for (int i = 0; i < 4; ++i) {
+        out[i] = r->host_us[i];
+        r->host_us[i] = 0.0;
+    }
+    return LEGION_OK;
+}
+
+static int collect_host_body(LegionRunner *r, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
+                             int32_t *agg_dst_out, int32_t node_counter_out[16], int32_t edge_counter_out[16],
+                             void *features_out)
 {
     LG_ARG(r != nullptr && node_counter_out != nullptr && edge_counter_out != nullptr, "NULL pointer");
     if (r->host_pending == 0) {
@@ -715,7 +772,11 @@ extern "C" int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int
         r->host_exported[i - 1] = r->host_exported[i];
     }
     r->host_pending -= 1;
-    LG_CUDA(cudaEventSynchronize(r->pipe_done[pipe]));
+    {
+        const double w0 = now_us();
+        LG_CUDA(cudaEventSynchronize(r->pipe_done[pipe]));
+        r->host_us[2] += now_us() - w0;
+    }
     const int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
     memcpy(node_counter_out, hc, 64);
     memcpy(edge_counter_out, hc + 16, 64);

@@ -5,7 +5,9 @@
 //
 // reads ./meta_config (written by legion_server.py:45-46), loads the Legion-format dataset, runs one
 // host thread per GPU, builds the caches (presampled hotness order like the reference; set
-// LEGION_ORDER=degree for the degree order), publishes the hand-off buffers, prints
+// LEGION_ORDER=degree for the degree order; with more than one GPU the per-GPU budget is planned into a
+// stripe of the clique's cache plus private copies of the hottest peer rows), stages the rows of uncached
+// seeds in page-locked memory for the copy engine, publishes the hand-off buffers, prints
 // "System is ready for serving" (engine/server.cu:121; scripts/wait_file.sh waits for that line) and
 // serves every batch of the schedule to the trainers.  cache_agg_mode is accepted and ignored: an
 // NVSwitch box is one clique.  dyn_flags: bit 3 (DYN_COMP, comp_cache/cache_helper.cuh:34-45) selects
@@ -72,6 +74,8 @@ int main(int argc, char **argv)
     const char *seed_env = getenv("LEGION_SEED");
     const uint64_t seed = seed_env ? strtoull(seed_env, nullptr, 0) : 0;
     const int timeout_ms = getenv("LEGION_TIMEOUT_MS") ? atoi(getenv("LEGION_TIMEOUT_MS")) : -1;
+    const bool stripe_only = getenv("LEGION_STRIPE_ONLY") != nullptr && getenv("LEGION_STRIPE_ONLY")[0] == '1';
+    const bool no_staging = getenv("LEGION_NO_SEED_STAGING") != nullptr && getenv("LEGION_NO_SEED_STAGING")[0] == '1';
     if (ngpu < 1 || ngpu > LEGION_MAX_DEVICE) {
         fprintf(stderr, "ngpu must be 1..%d\n", LEGION_MAX_DEVICE);
         return 1;
@@ -119,6 +123,7 @@ int main(int argc, char **argv)
         }
     int64_t cap64 = meta.cache_memory / row_bytes;  // rows per GPU
     if (cap64 > n) cap64 = n;
+    const int64_t budget_rows = cap64;
     if (cap64 * ngpu >= n) cap64 = (n + ngpu - 1) / ngpu;
     const int32_t capacity = (int32_t)cap64;
     const int max_step = legion_ipc_max_step(env);
@@ -187,8 +192,26 @@ int main(int argc, char **argv)
             CHECK(legion_cache_set_host_table(r.cache, features));
         } else {
             int codec = (dyn_flags & 8) ? LEGION_CODEC_INT8 : LEGION_CODEC_RAW;
-            CHECK(legion_cache_create(&r.cache, g, n, row_bytes, ngpu, g, capacity, codec));
+            // The per-GPU budget is split into this GPU's stripe of the clique's cache and private copies of
+            // the hottest rows that the striping gave to peers (the capacity split of the reference's cost
+            // model, cache/cache.cu:449-557, for one process-wide clique); LEGION_STRIPE_ONLY=1 keeps the
+            // reference's placement.  Every thread computes the same plan.
+            int64_t stripe = capacity, replicas = 0;
+            if (ngpu > 1 && !stripe_only) {
+                const int64_t *ip_dev = r.d_indptr;
+                int64_t *tmp_ip = nullptr;
+                if (ip_dev == nullptr) {
+                    CUCHECK(cudaMalloc(&tmp_ip, 8 * (size_t)(n + 1)));
+                    CUCHECK(cudaMemcpy(tmp_ip, indptr, 8 * (size_t)(n + 1), cudaMemcpyHostToDevice));
+                    ip_dev = tmp_ip;
+                }
+                CHECK(legion_cache_plan(g, order, ip_dev, nullptr, n, budget_rows, ngpu, nullptr, &stripe, &replicas, nullptr));
+                if (tmp_ip) cudaFree(tmp_ip);
+            }
+            CHECK(legion_cache_create(&r.cache, g, n, row_bytes, ngpu, g, (int32_t)stripe, codec));
             CHECK(legion_cache_fill_static(r.cache, order, n, features, nullptr));
+            if (replicas > 0) CHECK(legion_cache_add_replicas(r.cache, order, n, replicas, nullptr, nullptr));
+            if (g == 0) printf("Cache rows per GPU: %lld striped + %lld private copies\n", (long long)stripe, (long long)replicas);
         }
         cudaFree(order);
         pthread_barrier_wait(&g_barrier);
@@ -204,6 +227,15 @@ int main(int argc, char **argv)
         }
         CHECK(legion_ipc_publish_pool(env, r.pool, g));
         CHECK(legion_runner_create(&r.runner, g, r.graph, r.feature, r.cache, r.pool, env));
+        if (!(dyn_flags & 1) && !(dyn_flags & 8) && !no_staging) {
+            // rows of the uncached seeds of every list into page-locked memory, in list order: the copy engine
+            // then brings each batch's block in while the batch samples
+            for (int m = 0; m < 3; ++m) {
+                int64_t staged = 0;
+                if (r.count[m] > 0) CHECK(legion_runner_stage_seeds(r.runner, m, &staged));
+                if (g == 0 && r.count[m] > 0) printf("Seed rows staged in host memory, mode %d: %lld\n", m, (long long)staged);
+            }
+        }
         pthread_barrier_wait(&g_barrier);
         if (g == 0) {
             printf("System is ready for serving\n");

@@ -20,6 +20,11 @@ def main():
     for s in sources:
         if not os.path.exists(s):
             raise SystemExit("missing reference source: " + s)
+    # the distribution's own compiler: objects made by another g++ wrapper on PATH crashed in iostream
+    # code (std::cout << int) once loaded next to torch
+    if os.path.exists("/usr/bin/g++") and os.path.exists("/usr/bin/gcc"):
+        os.environ["CXX"] = "/usr/bin/g++"
+        os.environ["CC"] = "/usr/bin/gcc"
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     os.environ.setdefault("CUDA_HOME", "/usr/local/cuda")
     os.environ.setdefault("MAX_JOBS", "4")
@@ -28,6 +33,7 @@ def main():
     os.makedirs(build_dir, exist_ok=True)
     load(name="ipc_service", sources=sources, build_directory=build_dir, verbose=False, is_python_module=False)
     shutil.copy2(os.path.join(build_dir, "ipc_service.so"), os.path.join(out, "ipc_service.so"))
+    shutil.rmtree(build_dir, ignore_errors=True)
     print("built", os.path.join(out, "ipc_service.so"))
 
 
