@@ -457,6 +457,9 @@ def main():
                          "of planning private copies of the hottest peer rows")
     ap.add_argument("--no-seed-staging", action="store_true",
                     help="fetch the rows of uncached seeds like any other miss instead of staging them by the copy engine")
+    ap.add_argument("--topology", default="device", choices=["device", "host"],
+                    help="where the CSR lives: in this GPU's memory (default), or in pinned host memory read in place by "
+                         "zero-copy loads (what a graph that does not fit beside the cache falls back to)")
     ap.add_argument("--tunable", action="append", default=[], metavar="NAME=VALUE",
                     help="launch-shape knob passed to legion_set_tunable")
     ap.add_argument("--profile-only", action="store_true",
@@ -587,7 +590,11 @@ def main():
         return synth.feature_rows(src, f, 0, dtype).view(torch.uint8).view(-1, row_bytes)
 
     # ---- storage, cache, pool, runner ------------------------------------------------------------
-    g = L.GraphStorage(dev, indptr, indices)
+    if args.topology == "host":
+        topo = (indptr.cpu().pin_memory(), indices.cpu().pin_memory())
+        g = L.GraphStorage(dev, topo[0], topo[1])
+    else:
+        g = L.GraphStorage(dev, indptr, indices)
     fs = L.FeatureStorage(dev, table_rows if table_rows else n, row_bytes, table)
     fs.set_split(L.TRAINMODE, mine, mine_labels)
     if lru_ways:
@@ -930,7 +937,7 @@ def main():
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": cfg.get("elt", "f32"), "data": "synthetic",
                 "config": workload_config(cfg, world), "host_table_layout": host_layout,
-                "host_table_rows": table_rows, "pipes": pipes,
+                "host_table_rows": table_rows, "pipes": pipes, "topology": args.topology,
                 "windows": {"count": len(windows), "timed_s": timed_s, "ms_per_step_min": wsorted[0] / args.steps,
                             "ms_per_step_median": ms_total / args.steps, "ms_per_step_max": wsorted[-1] / args.steps},
                 "e2e": e2e, "gpu_launches": args.steps * per_batch,

@@ -67,7 +67,8 @@ int legion_host_register(int32_t dev_id, void *ptr, int64_t bytes);
  * "miss_ctas": CTAs of the host-link fetch kernel, 0 = one per SM. */
 int legion_set_tunable(const char *name, int32_t value);
 /* Names: "miss_ctas", "miss_threads", "miss_rows" (launch shape of the host-link fetch and the rows a warp keeps
- * in flight: 1, 2, 4 or 8); "gather_ctas_per_sm",
+ * in flight: 1, 2, 4 or 8); "gather_rows_per_warp" (32, 16 or 8 rows looked up and copied per warp and chunk of
+ * the 512-byte-class gather); "gather_ctas_per_sm",
  * "gather_rows_in_flight" (2/4/8/16, register path); "gather_engine" 0 = rows move through registers,
  * 1 = rows move by bulk asynchronous copies through shared memory (start value from the environment
  * variable LEGION_GATHER_ENGINE); "pdl" 1 = the sampling kernels of a batch are launched as programmatic

@@ -190,31 +190,35 @@ __device__ __forceinline__ const uint8_t *decode_raw(const GatherParams &p, int3
 // lane, then copies their rows R at a time; while the first rows of a chunk are in flight it already
 // fetches the id and the table entry of its next chunk, so that only the first lookup of a warp is
 // exposed.
-template <int VPL, int R>
+template <int VPL, int R, int RPW = 32>
 __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
 {
+    // RPW = rows one warp looks up and copies per chunk (32: one per lane; 16 or 8: the upper lanes idle during
+    // the lookup, but a warp's life is shorter, so the last wave of CTAs costs less)
+    static_assert(RPW == 32 || RPW == 16 || RPW == 8, "rows per warp");
+    static_assert(RPW >= R, "a chunk holds at least one round of rows");
     int off, n;
     segment_of(p.nc, p.op_id, off, n);
     const int lane = threadIdx.x & 31;
     const int n_warps = (gridDim.x * blockDim.x) >> 5;
     const int row_vec = p.row_bytes >> 4;
     int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (c * 32 >= n) return;
-    int32_t id = (c * 32 + lane < n) ? __ldg(&p.ids[off + c * 32 + lane]) : -1;
+    if (c * RPW >= n) return;
+    int32_t id = (lane < RPW && c * RPW + lane < n) ? __ldg(&p.ids[off + c * RPW + lane]) : -1;
     int32_t raw = lookup_raw(p, id);
-    for (; c * 32 < n; c += n_warps) {
-        const int r = c * 32 + lane;
+    for (; c * RPW < n; c += n_warps) {
+        const int r = c * RPW + lane;
         int32_t gidx, host_row;
         int where;
         const uint8_t *src = decode_raw(p, id, raw, gidx, where, host_row);
-        if (r < n) p.cache_index[off + r] = gidx;
+        if (lane < RPW && r < n) p.cache_index[off + r] = gidx;
         use_staged(p, off + r, where, src);
         add_stats(p.stats, where, lane);
         defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
-        const int rows_here = min(32, n - c * 32);
-        uint8_t *dst_base = p.dst + (int64_t)(off + c * 32) * p.row_bytes;
-        const int rn = (c + n_warps) * 32 + lane;
-        id = (rn < n) ? __ldg(&p.ids[off + rn]) : -1;
+        const int rows_here = min(RPW, n - c * RPW);
+        uint8_t *dst_base = p.dst + (int64_t)(off + c * RPW) * p.row_bytes;
+        const int rn = (c + n_warps) * RPW + lane;
+        id = (lane < RPW && rn < n) ? __ldg(&p.ids[off + rn]) : -1;
         for (int j0 = 0; j0 < rows_here; j0 += R) {
             uint4 v[R][VPL];
             const uint8_t *sp[R];
@@ -775,10 +779,10 @@ __global__ void lru_claim_reset_kernel(const int64_t *__restrict__ victim, const
 
 // ---- launchers ------------------------------------------------------------------------------------------
 
-template <int VPL, int R>
+template <int VPL, int R, int RPW = 32>
 static void launch_vec(int grid, cudaStream_t s, const GatherParams &gp)
 {
-    gather_vec_kernel<VPL, R><<<grid, 256, 0, s>>>(gp);
+    gather_vec_kernel<VPL, R, RPW><<<grid, 256, 0, s>>>(gp);
 }
 template <int VPL, int R>
 static void launch_lru(int grid, cudaStream_t s, const LruParams &lp)
@@ -797,7 +801,9 @@ int g_gather_engine = gather_engine_from_env();
 int g_gather_cps = 0;  // CTAs per SM of the hit gathers (0 = default); see legion_set_tunable
 int g_gather_rows = 0; // rows in flight per warp for 512-byte-class rows (0 = default)
 
-static int segment_grid(const LegionPool *p, int32_t op_id, int64_t *rows_out)
+int g_gather_rpw = 0;  // rows per warp and chunk of the 512-byte-class gather (0 = default); see legion_set_tunable
+
+static int segment_grid(const LegionPool *p, int32_t op_id, int64_t *rows_out, int rows_per_warp = 32)
 {
     // worst-case rows of this segment: the seeds, or the new nodes of hop (op_id / 3), or all nodes
     int hop = op_id / LEGION_INTRABATCH_CON;  // 0 = seeds
@@ -806,9 +812,9 @@ static int segment_grid(const LegionPool *p, int32_t op_id, int64_t *rows_out)
     for (int h = 0; h < hop; ++h) { rows = nodes * p->fanout[h]; nodes += rows; }
     if (op_id == kOpGatherAll) rows = p->max_nodes;
     if (rows_out) *rows_out = rows;
-    int64_t chunks = (rows + 31) / 32;
+    int64_t chunks = (rows + rows_per_warp - 1) / rows_per_warp;
     int64_t g64 = (chunks + 7) / 8;
-    int cap = p->sm_count * (g_gather_cps > 0 ? g_gather_cps : 8);
+    int cap = p->sm_count * (g_gather_cps > 0 ? g_gather_cps : 8) * (32 / rows_per_warp);
     return (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
 }
 
@@ -916,7 +922,9 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
         case 1:
             // 8 rows (4 KB) in flight per warp measured best on 512-byte rows (2: 0.47-0.55 of the copy
             // peak, 4: 0.55-0.57, 8: 0.58-0.61, 16: 0.52-0.55, over 2-8 CTAs per SM)
-            if (g_gather_rows == 4) launch_vec<1, 4>(grid, s, gp);
+            if (g_gather_rpw == 16) launch_vec<1, 8, 16>(segment_grid(p, op_id, nullptr, 16), s, gp);
+            else if (g_gather_rpw == 8) launch_vec<1, 8, 8>(segment_grid(p, op_id, nullptr, 8), s, gp);
+            else if (g_gather_rows == 4) launch_vec<1, 4>(grid, s, gp);
             else if (g_gather_rows == 16) launch_vec<1, 16>(grid, s, gp);
             else if (g_gather_rows == 2) launch_vec<1, 2>(grid, s, gp);
             else launch_vec<1, 8>(grid, s, gp);
@@ -1176,6 +1184,11 @@ extern "C" int legion_set_tunable(const char *name, int32_t value)
     if (strcmp(name, "gather_ctas_per_sm") == 0) {
         LG_ARG(value >= 0 && value <= 16, "gather_ctas_per_sm out of range");
         g_gather_cps = value;
+        return LEGION_OK;
+    }
+    if (strcmp(name, "gather_rows_per_warp") == 0) {
+        LG_ARG(value == 0 || value == 8 || value == 16 || value == 32, "gather_rows_per_warp must be 0, 8, 16 or 32");
+        g_gather_rpw = value == 32 ? 0 : value;
         return LEGION_OK;
     }
     if (strcmp(name, "gather_rows_in_flight") == 0) {
