@@ -19,6 +19,7 @@ void set_error(const char *fmt, ...);
         if (_e != cudaSuccess) {                                                           \
             legion::set_error("%s:%d: %s -> %s", __FILE__, __LINE__, #call,                \
                               cudaGetErrorString(_e));                                     \
+            cudaGetLastError(); /* reported here: it must not surface again at a later launch check */ \
             return LEGION_E_CUDA;                                                          \
         }                                                                                  \
     } while (0)

@@ -93,6 +93,8 @@ struct LegionRunner {
     HostOut host_out[LEGION_MAX_PIPES + 1];   // of the submitted batches, oldest first (parallel to host_fifo)
     int64_t host_spec_nodes[LEGION_MAX_PIPES + 1], host_spec_edges[LEGION_MAX_PIPES + 1];  // elements copied ahead
     bool host_exported[LEGION_MAX_PIPES + 1];  // every element of the block structure is on the host
+    int32_t host_nc[LEGION_MAX_PIPES + 1][32]; // final counters of an exported batch (the pipe's mirror may already
+                                               // belong to the batch that samples ahead on the same pipe)
     int64_t spec_nodes, spec_edges;                 // sizes to copy ahead: the largest batch seen so far plus a margin
     bool host_bound[LEGION_MAX_PIPES + 1];  // of the submitted batches, oldest first (parallel to host_fifo)
     bool host_deferred;                          // the newest submitted batch still lacks its back half
@@ -130,10 +132,29 @@ extern "C" int legion_ipc_local_batch_id(LegionIpcEnv *e, int32_t global_batch_i
 extern "C" int legion_ipc_publish_counters(LegionIpcEnv *e, int32_t dev_id, int32_t pipe, const int32_t *node_counter,
                                            const int32_t *edge_counter);
 
+// Counter words of the finished batch on `pipe`, in the pipe's page-locked staging area.  With at least one hop
+// the last sampling kernel has stored both arrays there itself; the lookup + gather over all nodes only adds the
+// two snapshot words of the last lookup (nc[2], nc[3] = offset and size of the last hop's nodes,
+// operator_impl.cu:85-87), which are a function of the cumulative counts.  Call after the batch has finished.
+static const int32_t *final_counters(LegionRunner *r, int pipe)
+{
+    LegionPool *p = r->pool;
+    int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
+    if (p->hop_num > 0) {
+        memcpy(hc, hc + 32, 128);
+        const int hops = hc[LEGION_INTRABATCH_CON * 3 - 1];
+        const int n = hc[LEGION_INTRABATCH_CON * 3 + hops];
+        const int last = hops > 0 ? hc[LEGION_INTRABATCH_CON * 3 + hops - 1] : 0;
+        hc[2] = last;
+        hc[3] = n - last;
+    }
+    return hc;
+}
+
 // The finished batch of `pipe` goes to the consumer: counters into the host segment, then the post.
 static int post_batch(LegionRunner *r, int pipe)
 {
-    const int32_t *hc = r->pool->h_stage[pipe] + 2 * (size_t)r->pool->batch_size;
+    const int32_t *hc = final_counters(r, pipe);
     int rc = legion_ipc_publish_counters(r->env, r->dev_id, pipe, hc, hc + 16);
     if (rc != LEGION_OK) return rc;
     return legion_ipc_post(r->env, r->dev_id, pipe);
@@ -445,10 +466,12 @@ static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
         int32_t *early = p->h_stage[pipe] + 2 * (size_t)p->batch_size + 32;
         LG_CUDA(cudaEventRecord(r->sampled[pipe], front));
         LG_CUDA(cudaStreamWaitEvent(r->s_copy, r->sampled[pipe], 0));
-        LG_CUDA(cudaMemcpyAsync(early, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_copy));
-        LG_CUDA(cudaMemcpyAsync(early + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_copy));
-        if (bound->labels)
-            LG_CUDA(cudaMemcpyAsync(bound->labels, p->labels[pipe], 4 * (size_t)host_seeds, cudaMemcpyDeviceToHost, r->s_copy));
+        if (p->hop_num == 0) {  // no sampling kernel has stored the counters on the host
+            LG_CUDA(cudaMemcpyAsync(early, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_copy));
+            LG_CUDA(cudaMemcpyAsync(early + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, r->s_copy));
+        }
+        // the labels of a host-provided batch are the labels that came in
+        if (bound->labels) memcpy(bound->labels, p->h_stage[pipe] + p->batch_size, 4 * (size_t)host_seeds);
         if (bound->ids && r->spec_nodes > 0)
             LG_CUDA(cudaMemcpyAsync(bound->ids, p->ids[pipe], 4 * (size_t)r->spec_nodes, cudaMemcpyDeviceToHost, r->s_copy));
         if (bound->agg_src && r->spec_edges > 0)
@@ -485,9 +508,9 @@ static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound,
     p->stage_rows = nullptr;
     p->stage_pos = nullptr;
     if (rc != LEGION_OK) return rc;
-    if (host_seeds > 0 || r->env != nullptr) {
-        // the counters are final once the lookup has left its snapshot words; copied on this stream so
-        // that the next sampling on this pipe, which resets them, is ordered behind the copy
+    if ((host_seeds > 0 || r->env != nullptr) && p->hop_num == 0) {
+        // without a sampling kernel nothing has stored the counters on the host (final_counters): copied on this
+        // stream so that the next batch on this pipe, which resets them, is ordered behind the copy
         int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
         LG_CUDA(cudaMemcpyAsync(hc, p->node_counter[pipe], 64, cudaMemcpyDeviceToHost, front));
         LG_CUDA(cudaMemcpyAsync(hc + 16, p->edge_counter[pipe], 64, cudaMemcpyDeviceToHost, front));
@@ -497,7 +520,8 @@ static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound,
     LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->hit_done[pipe], 0));
     rc = issue_back(r);
     if (rc != LEGION_OK) return rc;
-    if (bound) LG_CUDA(cudaStreamWaitEvent(r->s_miss, r->exported[pipe], 0));
+    // (the export of a bound batch is waited for where it matters -- by collect, and by the batch that samples
+    // ahead on this pipe -- not here: the fetch stream is shared by all batches and must not idle behind a copy)
     LG_CUDA(cudaEventRecord(r->pipe_done[pipe], r->s_miss));
     if (lru) c->clock += 1;
     r->pipe_busy[pipe] = true;
@@ -560,6 +584,15 @@ static int finish_export(LegionRunner *r, int i)
         r->host_us[2] += now_us() - w0;
     }
     const int32_t *early = p->h_stage[pipe] + 2 * (size_t)p->batch_size + 32;
+    {
+        // the batch's final counters: what sampling left plus the snapshot words of the last lookup (final_counters)
+        int32_t *nc = r->host_nc[i];
+        memcpy(nc, early, 128);
+        const int h = nc[LEGION_INTRABATCH_CON * 3 - 1];
+        const int last = h > 0 ? nc[LEGION_INTRABATCH_CON * 3 + h - 1] : 0;
+        nc[2] = last;
+        nc[3] = nc[LEGION_INTRABATCH_CON * 3 + h] - last;
+    }
     const int hops = early[LEGION_INTRABATCH_CON * 3 - 1];
     const int64_t n_nodes = early[LEGION_INTRABATCH_CON * 3 + hops];
     const int64_t n_edges = (int64_t)early[16] + early[17];
@@ -762,6 +795,8 @@ static int collect_host_body(LegionRunner *r, int32_t *ids_out, int32_t *labels_
         int frc = finish_export(r, 0);
         if (frc != LEGION_OK) return frc;
     }
+    int32_t kept[32];
+    memcpy(kept, r->host_nc[0], sizeof(kept));  // this batch's, if it was exported (taken before the fifo moves)
     for (int i = 1; i < r->host_pending; ++i) {
         r->host_fifo[i - 1] = r->host_fifo[i];
         r->host_seeds[i - 1] = r->host_seeds[i];
@@ -770,6 +805,7 @@ static int collect_host_body(LegionRunner *r, int32_t *ids_out, int32_t *labels_
         r->host_spec_nodes[i - 1] = r->host_spec_nodes[i];
         r->host_spec_edges[i - 1] = r->host_spec_edges[i];
         r->host_exported[i - 1] = r->host_exported[i];
+        memcpy(r->host_nc[i - 1], r->host_nc[i], sizeof(r->host_nc[0]));
     }
     r->host_pending -= 1;
     {
@@ -777,7 +813,7 @@ static int collect_host_body(LegionRunner *r, int32_t *ids_out, int32_t *labels_
         LG_CUDA(cudaEventSynchronize(r->pipe_done[pipe]));
         r->host_us[2] += now_us() - w0;
     }
-    const int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
+    const int32_t *hc = (bound && p->hop_num > 0) ? kept : final_counters(r, pipe);
     memcpy(node_counter_out, hc, 64);
     memcpy(edge_counter_out, hc + 16, 64);
     // the caller reads this batch's rows from the pipe's feature buffer now; the batch that already
@@ -816,6 +852,7 @@ extern "C" int legion_runner_sync(LegionRunner *r)
     LG_CUDA(cudaStreamSynchronize(r->s_gather));
     LG_CUDA(cudaStreamSynchronize(r->s_miss));
     LG_CUDA(cudaStreamSynchronize(r->s_h2d));
+    LG_CUDA(cudaStreamSynchronize(r->s_copy));
     for (int i = 0; i < LEGION_MAX_PIPES; ++i) LG_CUDA(cudaStreamSynchronize(r->s_launch[i]));
     if (r->open_window) {
         float ms = 0.0f, g = 0.0f, m = 0.0f;

@@ -500,7 +500,7 @@ hop_flag_kernel(const int32_t *__restrict__ eslot, const MapSlot *map, int32_t *
 __global__ void hop_finish_kernel(const int32_t *__restrict__ erank, const int32_t *__restrict__ tile_off,
                                   const int32_t *__restrict__ eslot, const int32_t *__restrict__ src_global,
                                   int32_t *ids, MapSlot *map, int32_t *agg_src, int32_t *ctl, int32_t *nc, int32_t *ec,
-                                  int op_id)
+                                  int op_id, int32_t *host_mirror)
 {
     pdl_wait();
     pdl_trigger();
@@ -548,6 +548,16 @@ __global__ void hop_finish_kernel(const int32_t *__restrict__ erank, const int32
         ctl[CTL_E_HOP] = 0;
         ctl[CTL_C_HOP] = 0;
         ctl[CTL_TICKET_C] = 0;
+        // both counter arrays also go to page-locked host memory (32 posted stores): the host learns the
+        // sizes of the batch without a copy-engine transfer queued behind other batches' exports
+        if (host_mirror != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                host_mirror[i] = nc[i];
+                host_mirror[16 + i] = ec[i];
+            }
+            __threadfence_system();
+        }
     }
 }
 
@@ -660,7 +670,7 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
                        p->erank[pipe], tile_sum2, tile_off2, ctl, p->max_nodes));
     LG_CUDA(launch_dep(hop_finish_kernel, grid_for(edges, 256 * 4, cap), 256, s, p->erank[pipe], tile_off2, p->eslot[pipe],
                        p->src_global[pipe], p->ids[pipe], p->map[pipe], p->agg_src[pipe], ctl, p->node_counter[pipe],
-                       p->edge_counter[pipe], op_id));
+                       p->edge_counter[pipe], op_id, p->h_stage[pipe] + 2 * (size_t)p->batch_size + 32));
     return LEGION_OK;
 }
 

@@ -13,7 +13,7 @@ import math
 import torch
 
 
-def rmat_csr(n_nodes, n_pairs, seed=0, device="cpu", a=0.57, b=0.19, c=0.19, chunk=1 << 26):
+def rmat_csr(n_nodes, n_pairs, seed=0, device="cpu", a=0.57, b=0.19, c=0.19, chunk=1 << 26, max_sort=1 << 30):
     """Returns (indptr int64 [n+1], indices int32 [E]) of the symmetrised R-MAT graph."""
     g = torch.Generator(device=device)
     g.manual_seed(seed)
@@ -42,14 +42,30 @@ def rmat_csr(n_nodes, n_pairs, seed=0, device="cpu", a=0.57, b=0.19, c=0.19, chu
         keys.append(v * n_nodes + u)
         done += m
         del r, ubit, vbit, keep
-    key = torch.cat(keys)
+    total = sum(int(k.numel()) for k in keys)
+    # The sort behind torch.unique takes fewer than 2^31 keys: larger edge lists are sorted bucket by bucket,
+    # each bucket a range of source nodes (ids are scrambled, so the ranges hold about the same number of keys),
+    # and the sorted buckets follow one another.
+    n_buckets = max(1, -(-total // max_sort))
+    counts = torch.zeros(n_nodes, dtype=torch.int64, device=device)
+    parts = []
+    for b in range(n_buckets):
+        lo, hi = n_nodes * b // n_buckets, n_nodes * (b + 1) // n_buckets
+        if n_buckets == 1:
+            key = torch.cat(keys)
+            keys = []
+        else:
+            key = torch.cat([k[(k >= lo * n_nodes) & (k < hi * n_nodes)] for k in keys])
+        key = torch.unique(key)  # sorted, duplicates merged
+        src = torch.div(key, n_nodes, rounding_mode="floor")
+        parts.append((key - src * n_nodes).to(torch.int32))
+        del key
+        if src.numel():
+            counts[lo:hi] += torch.bincount(src - lo, minlength=hi - lo)
+        del src
     del keys
-    key = torch.unique(key)  # sorted, duplicates merged
-    src = torch.div(key, n_nodes, rounding_mode="floor")
-    indices = (key - src * n_nodes).to(torch.int32)
-    del key
-    counts = torch.bincount(src, minlength=n_nodes)
-    del src
+    indices = parts[0] if len(parts) == 1 else torch.cat(parts)
+    del parts
     indptr = torch.zeros(n_nodes + 1, dtype=torch.int64, device=device)
     torch.cumsum(counts, 0, out=indptr[1:])
     return indptr, indices
