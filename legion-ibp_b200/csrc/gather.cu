@@ -142,6 +142,43 @@ __device__ __forceinline__ void defer_misses(int2 *miss_rows, int32_t *miss_coun
     }
 }
 
+// The same in two halves, for a kernel that wants the row copies of the chunk in flight before it needs the
+// list position: the first half counts the chunk's misses, asks for their place in the list (the atomic's answer
+// travels while the rows do) and clears their source pointers; the second half writes the entries.
+struct MissTicket {
+    unsigned mask;
+    int base;
+};
+__device__ __forceinline__ MissTicket miss_begin(int32_t *miss_count, int where, const uint8_t *&src, int lane)
+{
+    MissTicket t;
+    t.mask = __ballot_sync(kFull, where == 2);
+    t.base = 0;
+    if (t.mask != 0u && lane == 0) t.base = atomicAdd(&miss_count[0], __popc(t.mask));
+    if (where == 2) src = nullptr;
+    return t;
+}
+__device__ __forceinline__ void miss_finish(int2 *miss_rows, const MissTicket &t, int row, int32_t id, int where, int lane)
+{
+    if (t.mask == 0u) return;
+    const int base = __shfl_sync(kFull, t.base, 0);
+    if (where == 2) miss_rows[base + __popc(t.mask & ((1u << lane) - 1u))] = make_int2(row, id);
+}
+
+// Hit / miss counters of a CTA, added to the cache's counters once per CTA (three atomics on three words that
+// every warp of every gather would otherwise hit).
+__device__ __forceinline__ void count_where(int *cta_counts, int where, int lane)
+{
+    unsigned m0 = __ballot_sync(kFull, where == 0);
+    unsigned m1 = __ballot_sync(kFull, where == 1);
+    unsigned m2 = __ballot_sync(kFull, where == 2);
+    if (lane == 0) {
+        if (m0) atomicAdd(&cta_counts[0], __popc(m0));
+        if (m1) atomicAdd(&cta_counts[1], __popc(m1));
+        if (m2) atomicAdd(&cta_counts[2], __popc(m2));
+    }
+}
+
 __device__ __forceinline__ void add_stats(unsigned long long *stats, int where, int lane)
 {
     unsigned m0 = __ballot_sync(kFull, where == 0);
@@ -197,13 +234,16 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
     // the lookup, but a warp's life is shorter, so the last wave of CTAs costs less)
     static_assert(RPW == 32 || RPW == 16 || RPW == 8, "rows per warp");
     static_assert(RPW >= R, "a chunk holds at least one round of rows");
+    __shared__ int cta_counts[3];
+    if (threadIdx.x < 3) cta_counts[threadIdx.x] = 0;
+    __syncthreads();
     int off, n;
     segment_of(p.nc, p.op_id, off, n);
     const int lane = threadIdx.x & 31;
     const int n_warps = (gridDim.x * blockDim.x) >> 5;
     const int row_vec = p.row_bytes >> 4;
     int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (c * RPW >= n) return;
+    if (blockIdx.x * (blockDim.x >> 5) * RPW >= n) return;  // the whole CTA is past the end
     int32_t id = (lane < RPW && c * RPW + lane < n) ? __ldg(&p.ids[off + c * RPW + lane]) : -1;
     int32_t raw = lookup_raw(p, id);
     for (; c * RPW < n; c += n_warps) {
@@ -213,8 +253,8 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
         const uint8_t *src = decode_raw(p, id, raw, gidx, where, host_row);
         if (lane < RPW && r < n) p.cache_index[off + r] = gidx;
         use_staged(p, off + r, where, src);
-        add_stats(p.stats, where, lane);
-        defer_misses(p.miss_rows, p.miss_count, off + r, host_row, where, src, lane);
+        if (p.stats != nullptr) count_where(cta_counts, where, lane);
+        const MissTicket ticket = miss_begin(p.miss_count, where, src, lane);
         const int rows_here = min(RPW, n - c * RPW);
         uint8_t *dst_base = p.dst + (int64_t)(off + c * RPW) * p.row_bytes;
         const int rn = (c + n_warps) * RPW + lane;
@@ -248,7 +288,11 @@ __global__ void __launch_bounds__(256) gather_vec_kernel(GatherParams p)
                 }
             }
         }
+        miss_finish(p.miss_rows, ticket, off + r, host_row, where, lane);
     }
+    __syncthreads();
+    if (p.stats != nullptr && threadIdx.x < 3 && cta_counts[threadIdx.x] != 0)
+        atomicAdd(&p.stats[threadIdx.x], (unsigned long long)cta_counts[threadIdx.x]);
 }
 
 // ---- the same gather with the copy engine of the SM (bulk asynchronous copies) -----------------------
@@ -960,18 +1004,23 @@ int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c)
     mp.dst = (uint8_t *)p->features[pipe];
     mp.row_bytes = p->row_bytes_out;
     mp.host_row_bytes = c->host_codec != LEGION_CODEC_RAW ? c->slot_bytes : p->row_bytes_out;
-    // 4 rows per warp and pass.  Shapes from 8 to 296 CTAs and 256 to 1024 threads were measured with
-    // batches in flight: fewer CTAs slow the fetch itself, none of them keeps co-running kernels from
-    // slowing down, and the batch rate stays within 10%; 148 x 256 was the best.
+
+    // A static cache behind seed staging leaves a few thousand scattered rows per batch, which arrive at the
+    // scattered-page rate of the link whatever is in flight, while every row in flight slows the kernels beside
+    // the fetch: one row per warp and four warps per CTA measured best (6.5 k batches/s against 6.1 k with four
+    // rows per warp and eight warps).  An LRU cache misses tens of thousands of rows per batch: its fetch
+    // keeps the wider shape.
+    const bool many = c->kind == 1;
     int64_t g64 = (p->max_nodes + 31) / 32;
     int cap = g_miss_ctas > 0 ? g_miss_ctas : kMissCtas;
-    int threads = g_miss_threads > 0 ? g_miss_threads : kMissThreads;
+    int threads = g_miss_threads > 0 ? g_miss_threads : (many ? kMissThreads : 128);
+    const int rows = g_miss_rows > 0 ? g_miss_rows : (many ? 4 : 1);
     int grid = (int)(g64 < 1 ? 1 : (g64 > cap ? cap : g64));
     if (c->host_codec == LEGION_CODEC_INT8) gather_miss_quant_kernel<LEGION_CODEC_INT8, 8><<<grid, threads, 0, s>>>(mp);
     else if (c->host_codec == LEGION_CODEC_E4M3) gather_miss_quant_kernel<LEGION_CODEC_E4M3, 8><<<grid, threads, 0, s>>>(mp);
-    else if (g_miss_rows == 1) gather_miss_kernel<1><<<grid, threads, 0, s>>>(mp);
-    else if (g_miss_rows == 2) gather_miss_kernel<2><<<grid, threads, 0, s>>>(mp);
-    else if (g_miss_rows == 8) gather_miss_kernel<8><<<grid, threads, 0, s>>>(mp);
+    else if (rows == 1) gather_miss_kernel<1><<<grid, threads, 0, s>>>(mp);
+    else if (rows == 2) gather_miss_kernel<2><<<grid, threads, 0, s>>>(mp);
+    else if (rows == 8) gather_miss_kernel<8><<<grid, threads, 0, s>>>(mp);
     else gather_miss_kernel<4><<<grid, threads, 0, s>>>(mp);
     LG_LAUNCH_CHECK();
     return LEGION_OK;
