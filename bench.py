@@ -335,17 +335,18 @@ def workload_config(cfg, n_gpus):
 
 
 def time_cpu(fn, cores, first_guess, target_s=3.0):
-    """Runs fn(first_batch, n_batches) once to warm up, once to estimate its rate, and once for about
-    target_s seconds; returns (batches/s, batches, seconds) of the last run."""
+    """Runs fn(first_batch, n_batches) once to warm up, then with growing batch counts until one run lasts
+    about target_s seconds; returns (batches/s, batches, seconds) of that run."""
     fn(0, cores)
-    t0 = time.perf_counter()
-    fn(cores, first_guess)
-    rate = first_guess / max(time.perf_counter() - t0, 1e-6)
-    nb = max(first_guess, int(rate * target_s) // cores * cores)
-    t0 = time.perf_counter()
-    fn(cores + first_guess, nb)
-    dt = time.perf_counter() - t0
-    return nb / dt, nb, dt
+    first, nb = cores, first_guess
+    while True:
+        t0 = time.perf_counter()
+        fn(first, nb)
+        dt = time.perf_counter() - t0
+        if dt >= 0.6 * target_s or nb >= (1 << 20):
+            return nb / dt, nb, dt
+        first += nb
+        nb = max(nb + cores, int(nb * target_s / max(dt, 1e-3)) // cores * cores)
 
 
 def cpu_arms(O, indptr, indices, seeds, labels, batch, fanout, table, cores, target_s=3.0):
@@ -355,8 +356,7 @@ def cpu_arms(O, indptr, indices, seeds, labels, batch, fanout, table, cores, tar
     n_iters = max(1, (len(seeds) - 1) // batch)
 
     def run(fn):
-        return lambda first, nb: fn(indptr, indices, seeds, labels, batch, first % max(1, n_iters - nb), nb, fanout, 1,
-                                    table, cores)
+        return lambda first, nb: fn(indptr, indices, seeds, labels, batch, first % n_iters, nb, fanout, 1, table, cores)
     native = time_cpu(run(O.cpu_pipeline_native), cores, 2 * cores, target_s)
     lockstep = time_cpu(run(O.cpu_pipeline), cores, 2 * cores, target_s / 2)
     best = max(native, lockstep, key=lambda r: r[0])

@@ -548,14 +548,14 @@ __global__ void hop_finish_kernel(const int32_t *__restrict__ erank, const int32
         ctl[CTL_E_HOP] = 0;
         ctl[CTL_C_HOP] = 0;
         ctl[CTL_TICKET_C] = 0;
-        // both counter arrays also go to page-locked host memory (32 posted stores): the host learns the
-        // sizes of the batch without a copy-engine transfer queued behind other batches' exports
-        if (host_mirror != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                host_mirror[i] = nc[i];
-                host_mirror[16 + i] = ec[i];
-            }
+    }
+    // After the last hop both counter arrays also go to page-locked host memory (one posted store per thread of
+    // a warp): the host learns the sizes of the batch without a copy-engine transfer queued behind other batches'
+    // exports.  s_flag is the same for every thread of the CTA.
+    if (s_flag && host_mirror != nullptr) {
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            host_mirror[threadIdx.x] = threadIdx.x < 16 ? nc[threadIdx.x] : ec[threadIdx.x - 16];
             __threadfence_system();
         }
     }
@@ -670,7 +670,8 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
                        p->erank[pipe], tile_sum2, tile_off2, ctl, p->max_nodes));
     LG_CUDA(launch_dep(hop_finish_kernel, grid_for(edges, 256 * 4, cap), 256, s, p->erank[pipe], tile_off2, p->eslot[pipe],
                        p->src_global[pipe], p->ids[pipe], p->map[pipe], p->agg_src[pipe], ctl, p->node_counter[pipe],
-                       p->edge_counter[pipe], op_id, p->h_stage[pipe] + 2 * (size_t)p->batch_size + 32));
+                       p->edge_counter[pipe], op_id,
+                       hop + 1 == p->hop_num ? p->h_stage[pipe] + 2 * (size_t)p->batch_size + 32 : (int32_t *)nullptr));
     return LEGION_OK;
 }
 

@@ -659,8 +659,10 @@ int64_t orc_cpu_pipeline(const int64_t *indptr, const int32_t *indices,
         int32_t *src_g = agg_dst + max_edges;
         int32_t *labels = src_g + max_edges;
         int32_t nc[16], ec[16];
+        /* the list is walked round and round: batch numbers past its end start over */
+        const int32_t whole = (total_cap - 1) / batch_size > 0 ? (total_cap - 1) / batch_size : 1;
         int64_t nn = orc_run_batch(indptr, indices, all_ids, all_labels, total_cap, batch_size,
-                                   first_iter + b, hop_num, fanout, (uint32_t)(first_iter + b), seed, 64,
+                                   (first_iter + b) % whole, hop_num, fanout, (uint32_t)(first_iter + b), seed, 64,
                                    ids, labels, agg_src, agg_dst, src_g, nc, ec);
         if (nn < 0) continue;
         uint8_t *out = features_out + (int64_t)tid * max_nodes * row_bytes;
@@ -723,7 +725,9 @@ int64_t orc_cpu_pipeline_native(const int64_t *indptr, const int32_t *indices,
         uint8_t *out = features_out + (int64_t)tid * max_nodes * row_bytes;
 #pragma omp for schedule(dynamic, 1)
         for (int32_t b = 0; b < n_batches; ++b) {
-            const int64_t first = (int64_t)batch_size * (first_iter + b);
+            /* the list is walked round and round: batch numbers past its end start over */
+            const int32_t whole = (total_cap - 1) / batch_size > 0 ? (total_cap - 1) / batch_size : 1;
+            const int64_t first = (int64_t)batch_size * ((first_iter + b) % whole);
             int64_t size = first + batch_size >= total_cap ? total_cap - first : batch_size;
             if (size <= 0) continue;
             int64_t n_nodes = 0, n_edges = 0, n_touched = 0;
