@@ -201,38 +201,41 @@ def host_memory_bytes():
 
 
 def host_buffer(n_bytes, shared_name, rank, world, dev=0, barrier=None):
-    """uint8 buffer in host memory that every rank's GPU can read: pinned (one rank) or one POSIX shared
-    segment that rank 0 creates and every rank maps and page-locks.  Not initialised."""
+    """uint8 buffer in host memory that every rank's GPU will read: pinned (one rank) or one POSIX shared
+    segment that rank 0 creates and every rank maps.  Not initialised; a shared segment is page-locked later,
+    by host_buffer_lock, once it has been filled (the driver may register a large range in pieces, and a copy
+    must not straddle two of them)."""
     import torch
     if world == 1:
         return torch.empty(n_bytes, dtype=torch.uint8, pin_memory=True)
-    L = load_pkg()
     path = "/dev/shm/" + shared_name
     if rank == 0:
         t = torch.from_file(path, shared=True, size=n_bytes, dtype=torch.uint8)
     barrier()
     if rank != 0:
         t = torch.from_file(path, shared=True, size=n_bytes, dtype=torch.uint8)
-    try:
-        L.host_register(dev, t)
-    except L.LegionError as e:
-        # the driver would not page-lock the shared segment: every rank keeps a pinned buffer of its own
-        print("rank %d: %s; falling back to a private pinned buffer" % (rank, e), file=sys.stderr, flush=True)
-        t = torch.empty(n_bytes, dtype=torch.uint8, pin_memory=True)
-        t.private = True
     barrier()
     if rank == 0:
         os.unlink(path)  # the mappings stay valid
     return t
 
 
-def fill_host_rows(table2d, rank, world, barrier, node_of_row=None, private=False):
-    """Every rank writes its share of the rows of a shared table (all rows of a private one): row r holds
-    the features of node r, or of node_of_row[r]."""
+def host_buffer_lock(t, rank, world, dev, barrier):
+    """Page-locks a filled shared segment for this rank's GPU."""
+    if world == 1:
+        return
+    L = load_pkg()
+    barrier()
+    L.host_register(dev, t)
+    barrier()
+
+
+def fill_host_rows(table2d, rank, world, barrier, node_of_row=None):
+    """Every rank writes its share of the rows of a shared table: row r holds the features of node r, or of
+    node_of_row[r]."""
     from legion_ibp_b200 import synth
     n = table2d.shape[0]
-    private = world == 1 or private
-    lo, hi = (0, n) if private else (n * rank // world, n * (rank + 1) // world)
+    lo, hi = n * rank // world, n * (rank + 1) // world
     synth.features_into(table2d, seed=0, row_ids=node_of_row, first=lo, last=hi)
     if barrier is not None:
         barrier()
@@ -579,9 +582,9 @@ def main():
         if host_layout == "seeds_first":
             row_of, node_of = host_rows_seeds_first(order, train, cap * world)
         table = host_buffer(table_rows * row_bytes, "legion_b200_bench_features", rank, world, dev, barrier0)
-        private = getattr(table, "private", False)
+        fill_host_rows(table.view(dtype).view(table_rows, f), rank, world, barrier0, node_of)
+        host_buffer_lock(table, rank, world, dev, barrier0)
         table = table.view(table_rows, row_bytes)
-        fill_host_rows(table.view(dtype).view(table_rows, f), rank, world, barrier0, node_of, private)
         del node_of
 
     def expected_rows(ids_t):
@@ -616,9 +619,9 @@ def main():
     else:
         if cfg.get("host_codec"):
             stored = host_buffer(n * slot_bytes, "legion_b200_bench_codes", rank, world, dev, barrier0)
-            own_copy = getattr(stored, "private", False)
+            host_buffer_lock(stored, rank, world, dev, barrier0)   # written in place by rank 0's kernel, row by row
             stored = stored.view(n, slot_bytes)
-            if rank == 0 or own_copy:
+            if rank == 0:
                 L.quantize_table(dev, codec, table, n, f, stored)
             barrier0()
         cache = L.UnifiedCache(dev, n, row_bytes, cap, kg=world, ki=rank, codec=codec)
