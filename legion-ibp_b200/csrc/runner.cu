@@ -429,12 +429,8 @@ static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
     }
     if (lru && r->last_pipe >= 0 && r->last_pipe != pipe && r->pipe_busy[r->last_pipe])
         LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[r->last_pipe], 0));
-    if (host_seeds > 0) {
-        int32_t *hs = p->h_stage[pipe];
-        // seeds and labels sit at [0, B) and [B, 2B) of both the pinned staging area and the device one
-        LG_CUDA(cudaMemcpyAsync(p->seed_stage[pipe], hs, sizeof(int32_t) * ((size_t)p->batch_size + host_seeds),
-                                cudaMemcpyHostToDevice, front));
-    }
+    // (the seeds and labels of a host-provided batch wait in the pipe's page-locked staging area, which the
+    // batch's first sampling kernel reads in place: 64 KB of zero-copy loads instead of one more transfer to issue)
     EvPair se = { nullptr, nullptr };
     if (r->time_kernels && r->sample_ev.size() < 8192) {
         se.a = take_event(r);
@@ -642,9 +638,25 @@ extern "C" int legion_runner_submit_host(LegionRunner *r, const int32_t *seeds, 
     return submit_host_impl(r, seeds, labels, n_seeds, global_batch_id, nullptr);
 }
 
+// Output arrays are checked once: the driver query costs as much as a launch, and a caller rotates a handful of
+// arrays.  (A stale entry cannot make a kernel fault: these arrays are only ever the target of copy-engine
+// transfers.)
+static bool device_can_write_query(const void *p);
+
 static bool device_can_write(const void *p)
 {
     if (p == nullptr) return true;
+    static thread_local const void *known[32];
+    static thread_local int n_known = 0;
+    for (int i = 0; i < n_known; ++i)
+        if (known[i] == p) return true;
+    if (!device_can_write_query(p)) return false;
+    known[n_known < 32 ? n_known++ : (n_known = 1, 0)] = p;
+    return true;
+}
+
+static bool device_can_write_query(const void *p)
+{
     cudaPointerAttributes a;
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
         cudaGetLastError();
@@ -712,7 +724,7 @@ static int submit_host_body(LegionRunner *r, const int32_t *seeds, const int32_t
     }
     memcpy(p->h_stage[pipe], seeds, sizeof(int32_t) * n_seeds);
     memcpy(p->h_stage[pipe] + p->batch_size, labels, sizeof(int32_t) * n_seeds);
-    const BatchCtl v = make_batch_ctl(p, r->cache, p->seed_stage[pipe], p->label_stage[pipe], n_seeds, 0, n_seeds,
+    const BatchCtl v = make_batch_ctl(p, r->cache, p->h_stage[pipe], p->h_stage[pipe] + p->batch_size, n_seeds, 0, n_seeds,
                                       r->graph->n_nodes);
     const int64_t spec_n = r->spec_nodes, spec_e = r->spec_edges;  // what issue_front copies ahead
     // a batch that is a slice of the registered host list (by address, and still holding what the list held
