@@ -452,6 +452,9 @@ def main():
     ap.add_argument("--pipes", type=int, default=0,
                     help="batches in flight on the device (0: 4 for static caches, 2 for the LRU cache; the hand-off to "
                          "trainer processes uses 2)")
+    ap.add_argument("--slots", type=int, default=2,
+                    help="hand-off buffer sets of the device-resident leg (the trainers' segment holds 2); pipes beyond "
+                         "them sample ahead into private buffers")
     ap.add_argument("--host-layout", default="seeds_first", choices=["id", "seeds_first"],
                     help="row order of the pinned host table: node-id order, or uncached seed nodes first and the "
                          "other uncached nodes by falling degree (shorter spans for the zero-copy misses)")
@@ -636,15 +639,25 @@ def main():
         from legion_ibp_b200 import server
         share = server.exchange_partitions(cache, rank, world, dist)
     pipes = args.pipes or (2 if lru_ways else 4)
-    pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, pipes)
+    # The device-resident leg leaves its batches in two hand-off slots, the number the trainers' segment holds;
+    # behind a static cache the other pipes sample ahead of them into private buffers.  The host-buffer leg has a
+    # pool of its own whose pipes are its slots (every batch in flight is exported to its own host arrays).
+    slots = min(pipes, args.slots) if not lru_ways else pipes
+    pool = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, pipes, slots=slots)
     pool.set_rng(RNG_SEED + rank, 64)
     runner = L.Runner(dev, g, fs, cache, pool, None)
+    if slots < pipes:
+        pool_h = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], row_bytes, pipes)
+        pool_h.set_rng(RNG_SEED + rank, 64)
+        runner_h = L.Runner(dev, g, fs, cache, pool_h, None)
+    else:
+        pool_h, runner_h = pool, runner
     n_iters = (int(mine.numel()) - 1) // cfg["batch"]
     seeds_h = mine.cpu().numpy()
     labels_h = mine_labels.cpu().numpy()
     staging = None
     if not args.no_seed_staging and hasattr(runner, "stage_seeds") and not lru_ways and not striped and codec == L.CODEC_RAW:
-        staging = {"list": runner.stage_seeds(L.TRAINMODE), "host": runner.register_host_seeds(seeds_h)}
+        staging = {"list": runner.stage_seeds(L.TRAINMODE), "host": runner_h.register_host_seeds(seeds_h)}
     torch.cuda.synchronize()
     setup_s = time.perf_counter() - t_setup
 
@@ -654,7 +667,7 @@ def main():
     if rank == 0:
         h_indptr, h_indices = indptr.cpu().numpy(), indices.cpu().numpy()
 
-    def check_batch(pipe, global_batch, it, what):
+    def check_batch(pipe, global_batch, it, what, pool=pool):
         """The batch that sits in `pipe`: every gathered row against the table's generator on all ranks, and on
         rank 0 ids, labels, both edge lists and both counter arrays against the CPU checker's batch."""
         torch.cuda.synchronize()
@@ -700,7 +713,7 @@ def main():
         runner.enqueue(step, L.TRAINMODE, step % n_iters)
         step += 1
     runner.sync()
-    checks = {"value_path": check_batch((step - 1) % pipes, step - 1, (step - 1) % n_iters, "device-resident batch")}
+    checks = {"value_path": check_batch((step - 1) % pipes % slots, step - 1, (step - 1) % n_iters, "device-resident batch")}
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -851,13 +864,13 @@ def main():
     def submit(i):
         it = i % n_iters
         o = outs[i % depth]
-        runner.submit_host_to(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i, o["ids"], o["lab"],
+        runner_h.submit_host_to(seeds_h[it * b:(it + 1) * b], labels_h[it * b:(it + 1) * b], i, o["ids"], o["lab"],
                               o["src"], o["dst"])
 
     def collect():
-        return runner.collect_host(None, None, None, None, nc_o, ec_o, None)
+        return runner_h.collect_host(None, None, None, None, nc_o, ec_o, None)
 
-    pipe0 = runner.current_pipe()
+    pipe0 = runner_h.current_pipe()
     for i in range(depth):
         submit(i)
     for i in range(depth, depth + 4):
@@ -870,16 +883,16 @@ def main():
     nn_chk, ne_chk = runner_counts(nc_o, ec_o)
     chk_pipe = (pipe0 + last) % pipes
     o_chk = outs[last % depth]
-    assert np.array_equal(o_chk["ids"][:nn_chk], pool.read(L.BUF_IDS, chk_pipe, nn_chk, np.int32))
-    assert np.array_equal(o_chk["src"][:ne_chk], pool.read(L.BUF_AGG_SRC, chk_pipe, ne_chk, np.int32))
-    assert np.array_equal(o_chk["dst"][:ne_chk], pool.read(L.BUF_AGG_DST, chk_pipe, ne_chk, np.int32))
-    checks["host_buffer_path"] = check_batch(chk_pipe, last, last % n_iters, "host-buffer batch")
+    assert np.array_equal(o_chk["ids"][:nn_chk], pool_h.read(L.BUF_IDS, chk_pipe, nn_chk, np.int32))
+    assert np.array_equal(o_chk["src"][:ne_chk], pool_h.read(L.BUF_AGG_SRC, chk_pipe, ne_chk, np.int32))
+    assert np.array_equal(o_chk["dst"][:ne_chk], pool_h.read(L.BUF_AGG_DST, chk_pipe, ne_chk, np.int32))
+    checks["host_buffer_path"] = check_batch(chk_pipe, last, last % n_iters, "host-buffer batch", pool_h)
     # wall clock needs a longer window than the device-timed leg: at least 0.5 s of steps
     e2e_steps = max(args.steps, 200, int(0.6 / max(ms_total / args.steps * 1e-3, 1e-6)))
     e2e_steps = min(e2e_steps, 20000)
     barrier()
-    staged_e2e0 = runner.staged_rows() if staging else 0
-    runner.host_times()
+    staged_e2e0 = runner_h.staged_rows() if staging else 0
+    runner_h.host_times()
     t0 = time.perf_counter()
     d2h = 0
     for i in range(depth):
@@ -893,9 +906,9 @@ def main():
         d2h += 4 * nn + 8 * ne + 4 * b + 128
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
-    ht = runner.host_times()
+    ht = runner_h.host_times()
     barrier()
-    staged_e2e = (runner.staged_rows() - staged_e2e0) if staging else 0
+    staged_e2e = (runner_h.staged_rows() - staged_e2e0) if staging else 0
     # floor of the export: every rank copies device -> pinned host at the same time
     barrier()
     d2h_peak = copy_peak("d2h")
@@ -940,7 +953,7 @@ def main():
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": cfg.get("elt", "f32"), "data": "synthetic",
                 "config": workload_config(cfg, world), "host_table_layout": host_layout,
-                "host_table_rows": table_rows, "pipes": pipes, "topology": args.topology,
+                "host_table_rows": table_rows, "pipes": pipes, "handoff_slots": slots, "topology": args.topology,
                 "windows": {"count": len(windows), "timed_s": timed_s, "ms_per_step_min": wsorted[0] / args.steps,
                             "ms_per_step_median": ms_total / args.steps, "ms_per_step_max": wsorted[-1] / args.steps},
                 "e2e": e2e, "gpu_launches": args.steps * per_batch,
@@ -954,6 +967,9 @@ def main():
                           "peer_mapping": share, "seed_staging": bool(staging)},
                 "setup_s": setup_s, "tunables": args.tunable or None}
         print(json.dumps(line), flush=True)
+    assert pool_h.device_error() == 0, "device-side error flag set"
+    if runner_h is not runner:
+        runner_h.Finalize()
     runner.Finalize()
     if dist is not None:
         dist.barrier()

@@ -243,6 +243,16 @@ int legion_cache_destroy(LegionCache *c);
  * the sampling kernels' latency).  row_bytes_out is the size of one gathered row. */
 int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batch_size, int32_t hop_num,
                        const int32_t *fanout, int32_t row_bytes_out, int32_t pipes);
+/* A pool that samples AHEAD of the hand-off: `slots` (<= 2 when it is published to trainers) sets of the seven
+ * hand-off buffers, and `pipes` (a multiple of slots, <= LEGION_MAX_PIPES) sets of sampling buffers and scratch.
+ * Batches are sampled into private buffers while the consumer still holds the slots; when a batch's slot
+ * (pipe % slots) is free its block structure is copied in (~3 MB) and its rows are gathered into the slot's
+ * feature buffer.  The reference samples into the hand-off buffers themselves (engine/server.cu:237-265,
+ * engine/ipc_service.cu:134-206), so it can only overlap INTERBATCH_CON batches.  For legion_runner_enqueue /
+ * run_once / serve; the per-operator entry points and the host-buffer calls need slots == pipes.
+ * legion_pool_buffer numbers the seven hand-off buffers by slot. */
+int legion_pool_create_ahead(LegionPool **out, int32_t dev_id, int32_t batch_size, int32_t hop_num,
+                             const int32_t *fanout, int32_t row_bytes_out, int32_t slots, int32_t pipes);
 int legion_pool_destroy(LegionPool *p);
 #define LEGION_BUF_IDS 0          /* slot order of engine/ipc_service.cu:163-169 */
 #define LEGION_BUF_FEATURES 1

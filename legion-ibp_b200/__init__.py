@@ -243,13 +243,16 @@ def quantize_table(dev_id, codec, rows, n_rows, feature_len, out_rows, stream=No
 class MemoryPool:
     """Scratch and double-buffered outputs of one GPU (engine/memorypool.cuh:20-221)."""
 
-    def __init__(self, dev_id, batch_size, fanout, row_bytes_out, pipes=2):
+    def __init__(self, dev_id, batch_size, fanout, row_bytes_out, pipes=2, slots=None):
+        """slots < pipes: batches are sampled ahead of the hand-off into private buffers (legion_pool_create_ahead)."""
         self.dev_id, self.batch_size, self.fanout = dev_id, int(batch_size), list(fanout)
         self.row_bytes_out, self.pipes = int(row_bytes_out), pipes
+        self.slots = pipes if slots is None else slots
         fan = (C.c_int32 * max(1, len(fanout)))(*fanout)
         self.h = C.c_void_p()
-        _check(lib().legion_pool_create(C.byref(self.h), C.c_int32(dev_id), C.c_int32(batch_size),
-                                        C.c_int32(len(fanout)), fan, C.c_int32(row_bytes_out), C.c_int32(pipes)))
+        _check(lib().legion_pool_create_ahead(C.byref(self.h), C.c_int32(dev_id), C.c_int32(batch_size),
+                                              C.c_int32(len(fanout)), fan, C.c_int32(row_bytes_out),
+                                              C.c_int32(self.slots), C.c_int32(pipes)))
         mn, me = C.c_int64(), C.c_int64()
         _check(lib().legion_pool_limits(self.h, C.byref(mn), C.byref(me)))
         self.max_nodes, self.max_edges = mn.value, me.value

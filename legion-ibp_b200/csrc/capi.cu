@@ -96,6 +96,11 @@ extern "C" int legion_pool_destroy(LegionPool *p)
     if (p == nullptr) return LEGION_OK;
     cudaSetDevice(p->dev_id);
     for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
+        if (p->slots < p->pipes) {  // separate hand-off buffers; feature buffers exist once per slot
+            cudaFree(p->pub_ids[i]); cudaFree(p->pub_labels[i]); cudaFree(p->pub_agg_src[i]); cudaFree(p->pub_agg_dst[i]);
+            cudaFree(p->pub_nc[i]); cudaFree(p->pub_ec[i]);
+            if (i >= p->slots) p->features[i] = nullptr;
+        }
         cudaFree(p->ids[i]); cudaFree(p->features[i]); cudaFree(p->labels[i]); cudaFree(p->agg_src[i]);
         cudaFree(p->agg_dst[i]); cudaFree(p->node_counter[i]); cudaFree(p->edge_counter[i]);
         cudaFree(p->miss_rows[i]); cudaFree(p->miss_count[i]);
@@ -112,7 +117,14 @@ extern "C" int legion_pool_destroy(LegionPool *p)
 extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batch_size, int32_t hop_num,
                                   const int32_t *fanout, int32_t row_bytes_out, int32_t pipes)
 {
+    return legion_pool_create_ahead(out, dev_id, batch_size, hop_num, fanout, row_bytes_out, pipes, pipes);
+}
+
+extern "C" int legion_pool_create_ahead(LegionPool **out, int32_t dev_id, int32_t batch_size, int32_t hop_num,
+                                        const int32_t *fanout, int32_t row_bytes_out, int32_t slots, int32_t pipes)
+{
     LG_ARG(out != nullptr, "out is NULL");
+    LG_ARG(slots >= 1 && slots <= pipes && pipes % slots == 0, "pipes must be a multiple of slots");
     LG_ARG(batch_size > 0, "batch_size must be positive");
     LG_ARG(hop_num >= 0 && hop_num <= LEGION_MAX_HOPS, "hop_num must be 0..3");
     LG_ARG(hop_num == 0 || fanout != nullptr, "fanout is NULL");
@@ -129,6 +141,7 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
     p->hop_num = hop_num;
     p->row_bytes_out = row_bytes_out;
     p->pipes = pipes;
+    p->slots = slots;
     // True worst case: every hop samples all nodes found so far (the reference sizes its buffers
     // as B*(1+f1+f1*f2), engine/server.cu:204-216, which is below it).
     int64_t nodes = batch_size, edges = 0, max_hop_edges = 0, max_inputs = batch_size;
@@ -193,7 +206,10 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
     cudaError_t e = cudaSuccess;
     for (int i = 0; i < pipes && e == cudaSuccess; ++i) {
         e = dmalloc(&p->ids[i], pad_nodes);
-        if (e == cudaSuccess) e = cudaMalloc(&p->features[i], (size_t)(nodes * (int64_t)row_bytes_out));
+        if (e == cudaSuccess) {
+            if (i < slots) e = cudaMalloc(&p->features[i], (size_t)(nodes * (int64_t)row_bytes_out));
+            else p->features[i] = p->features[i % slots];
+        }
         if (e == cudaSuccess) e = dmalloc(&p->labels[i], batch_size);
         if (e == cudaSuccess) e = dmalloc(&p->agg_src[i], pad_edges);
         if (e == cudaSuccess) e = dmalloc(&p->agg_dst[i], pad_edges);
@@ -228,7 +244,22 @@ extern "C" int legion_pool_create(LegionPool **out, int32_t dev_id, int32_t batc
         if (e == cudaSuccess) e = dmalloc(&p->seed_stage[i], 2 * (int64_t)batch_size);
         if (e == cudaSuccess) p->label_stage[i] = p->seed_stage[i] + batch_size;
         if (e == cudaSuccess)
-            e = cudaMallocHost(reinterpret_cast<void **>(&p->h_stage[i]), sizeof(int32_t) * (2 * (size_t)batch_size + 64));
+            e = cudaMallocHost(reinterpret_cast<void **>(&p->h_stage[i]), sizeof(int32_t) * (2 * (size_t)batch_size + 128));
+    }
+    for (int i = 0; i < slots && e == cudaSuccess; ++i) {
+        if (slots == pipes) {
+            p->pub_ids[i] = p->ids[i]; p->pub_labels[i] = p->labels[i]; p->pub_agg_src[i] = p->agg_src[i];
+            p->pub_agg_dst[i] = p->agg_dst[i]; p->pub_nc[i] = p->node_counter[i]; p->pub_ec[i] = p->edge_counter[i];
+            continue;
+        }
+        e = dmalloc(&p->pub_ids[i], pad_nodes);
+        if (e == cudaSuccess) e = dmalloc(&p->pub_labels[i], batch_size);
+        if (e == cudaSuccess) e = dmalloc(&p->pub_agg_src[i], pad_edges);
+        if (e == cudaSuccess) e = dmalloc(&p->pub_agg_dst[i], pad_edges);
+        if (e == cudaSuccess) e = dmalloc(&p->pub_nc[i], 16);
+        if (e == cudaSuccess) e = dmalloc(&p->pub_ec[i], 16);
+        if (e == cudaSuccess) e = cudaMemset(p->pub_nc[i], 0, 64);
+        if (e == cudaSuccess) e = cudaMemset(p->pub_ec[i], 0, 64);
     }
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
@@ -244,16 +275,17 @@ extern "C" int legion_pool_buffer(LegionPool *p, int32_t which, int32_t pipe, vo
 {
     LG_ARG(p != nullptr && ptr != nullptr, "NULL pointer");
     LG_ARG(pipe >= 0 && pipe < p->pipes, "pipe out of range");
+    if (which <= LEGION_BUF_EDGE_COUNTER) LG_ARG(pipe < p->slots, "the hand-off buffers are numbered by slot");
     int64_t b = 0;
     void *q = nullptr;
     switch (which) {
-    case LEGION_BUF_IDS: q = p->ids[pipe]; b = p->max_nodes * 4; break;
+    case LEGION_BUF_IDS: q = p->pub_ids[pipe]; b = p->max_nodes * 4; break;
     case LEGION_BUF_FEATURES: q = p->features[pipe]; b = p->feat_rows * (int64_t)p->row_bytes_out; break;
-    case LEGION_BUF_LABELS: q = p->labels[pipe]; b = (int64_t)p->batch_size * 4; break;
-    case LEGION_BUF_AGG_SRC: q = p->agg_src[pipe]; b = p->max_edges * 4; break;
-    case LEGION_BUF_AGG_DST: q = p->agg_dst[pipe]; b = p->max_edges * 4; break;
-    case LEGION_BUF_NODE_COUNTER: q = p->node_counter[pipe]; b = 64; break;
-    case LEGION_BUF_EDGE_COUNTER: q = p->edge_counter[pipe]; b = 64; break;
+    case LEGION_BUF_LABELS: q = p->pub_labels[pipe]; b = (int64_t)p->batch_size * 4; break;
+    case LEGION_BUF_AGG_SRC: q = p->pub_agg_src[pipe]; b = p->max_edges * 4; break;
+    case LEGION_BUF_AGG_DST: q = p->pub_agg_dst[pipe]; b = p->max_edges * 4; break;
+    case LEGION_BUF_NODE_COUNTER: q = p->pub_nc[pipe]; b = 64; break;
+    case LEGION_BUF_EDGE_COUNTER: q = p->pub_ec[pipe]; b = 64; break;
     case LEGION_BUF_CACHE_INDEX: q = p->cache_index[pipe]; b = p->max_nodes * 8; break;
     case LEGION_BUF_SRC_GLOBAL: q = p->src_global[pipe]; b = p->max_edges * 4; break;
     default: LG_ARG(false, "unknown buffer");

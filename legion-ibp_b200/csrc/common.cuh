@@ -105,6 +105,7 @@ struct BatchCtl {
     uint32_t k0, k1;            // RNG key
     int32_t max_rounds;
     int32_t clock;              // LRU batch clock
+    int32_t *mirror;            // page-locked host words that receive both counter arrays after the last hop
     int32_t n_nodes;            // ids outside [0, n_nodes) are skipped and raise DERR_BAD_ID
 };
 
@@ -198,6 +199,15 @@ struct LegionPool {
     int64_t max_nodes, max_edges, max_hop_edges, max_inputs;
     int64_t input_tiles;  // entries of tile_sum / tile_off reserved for the counting kernels (edge tiles follow)
     int64_t feat_rows;
+    // Hand-off buffers, `slots` sets: what a consumer reads (the seven buffers that are published to trainers).
+    // With slots == pipes they ARE the pipes' own output buffers below.  With fewer slots than pipes
+    // (legion_pool_create_ahead) every pipe samples into private buffers, ahead of the hand-off, and the block
+    // structure is copied into the slot (pipe % slots) when the batch's gather is issued; features[pipe] is the
+    // slot's feature buffer either way.
+    int32_t slots;
+    int32_t mirror_flip[LEGION_MAX_PIPES];  // which of a pipe's two counter mirrors the next batch on it writes (sampling ahead only)
+    int32_t *pub_ids[LEGION_MAX_PIPES], *pub_labels[LEGION_MAX_PIPES], *pub_agg_src[LEGION_MAX_PIPES],
+        *pub_agg_dst[LEGION_MAX_PIPES], *pub_nc[LEGION_MAX_PIPES], *pub_ec[LEGION_MAX_PIPES];
     // per pipe outputs
     int32_t *ids[LEGION_MAX_PIPES];
     void *features[LEGION_MAX_PIPES];
@@ -245,6 +255,7 @@ const void *map_clear_kernel_address();
 int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32_t fanout, int32_t hop,
                       int32_t op_id, bool seeds_pending = false);
 int launch_gather(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
+int launch_publish(cudaStream_t s, LegionPool *p);
 int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op_id);
 int launch_gather_misses(cudaStream_t s, LegionPool *p, LegionCache *c);
 int launch_lru_insert(cudaStream_t s, LegionPool *p, LegionCache *c);

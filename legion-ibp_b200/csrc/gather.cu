@@ -874,7 +874,7 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
         LG_ARG(c->row_bytes == row_bytes && row_bytes % 16 == 0, "lru cache rows must be a multiple of 16 bytes");
         LruParams lp;
         lp.ids = p->ids[pipe];
-        lp.nc = p->node_counter[pipe];
+        lp.nc = p->pub_nc[pipe % p->slots];  // the hand-off slot's counters (the pipe's own unless it samples ahead)
         lp.op_id = op_id;
         lp.keys = c->keys;
         lp.stamps = c->stamps;
@@ -904,7 +904,7 @@ int launch_gather_hits(cudaStream_t s, LegionPool *p, LegionCache *c, int32_t op
 
     GatherParams gp;
     gp.ids = p->ids[pipe];
-    gp.nc = p->node_counter[pipe];
+    gp.nc = p->pub_nc[pipe % p->slots];  // the hand-off slot's counters (the pipe's own unless it samples ahead)
     gp.op_id = op_id;
     gp.lut = c ? c->lut : nullptr;
     gp.capacity = c ? (c->capacity > 0 ? c->capacity : 1) : 1;

@@ -228,18 +228,18 @@ extern "C" int legion_ipc_publish_pool(LegionIpcEnv *e, LegionPool *pool, int32_
 {
     LG_ARG(e != nullptr && pool != nullptr, "NULL handle");
     LG_ARG(dev_id >= 0 && dev_id < LEGION_MAX_DEVICE, "dev_id out of range");
-    LG_ARG(pool->pipes <= LEGION_INTERBATCH_CON, "the hand-off segment has two slots per device: create the pool with at most 2 pipes");
+    LG_ARG(pool->slots <= LEGION_INTERBATCH_CON, "the hand-off segment has two slots per device: create the pool with at most 2 slots");
     LG_CUDA(cudaSetDevice(pool->dev_id));
-    for (int i = 0; i < pool->pipes; ++i) {
-        void *bufs[LEGION_MEMORY_USAGE] = { pool->ids[i], pool->features[i], pool->labels[i], pool->agg_src[i],
-                                            pool->agg_dst[i], pool->node_counter[i], pool->edge_counter[i] };
+    for (int i = 0; i < pool->slots; ++i) {
+        void *bufs[LEGION_MEMORY_USAGE] = { pool->pub_ids[i], pool->features[i], pool->pub_labels[i], pool->pub_agg_src[i],
+                                            pool->pub_agg_dst[i], pool->pub_nc[i], pool->pub_ec[i] };
         for (int k = 0; k < LEGION_MEMORY_USAGE; ++k) {
             cudaIpcMemHandle_t h;
             LG_CUDA(cudaIpcGetMemHandle(&h, bufs[k]));  // engine/ipc_service.cu:163-169,203
             memcpy((void *)&e->shm->memHandle[dev_id][i][k], &h, sizeof(h));
         }
     }
-    return legion_ipc_open_semaphores(e, dev_id, pool->pipes);
+    return legion_ipc_open_semaphores(e, dev_id, pool->slots);
 }
 
 extern "C" int legion_ipc_wait(LegionIpcEnv *e, int32_t dev_id, int32_t pipe, int32_t timeout_ms)

@@ -110,6 +110,11 @@ struct LegionRunner {
     int64_t pipe_stage_first[LEGION_MAX_PIPES];
     int32_t pipe_stage_n[LEGION_MAX_PIPES];
     long long staged_rows;
+    // sampling ahead of the hand-off (a pool with fewer slots than pipes)
+    cudaEvent_t slot_done[LEGION_MAX_PIPES];   // the batch that used the slot has left it (its fetch is over)
+    bool slot_busy[LEGION_MAX_PIPES];
+    int32_t *mirror_front[LEGION_MAX_PIPES];   // counter mirror of the batch last sampled on the pipe ...
+    int32_t *mirror_back[LEGION_MAX_PIPES];    // ... and of the batch whose gather was issued last
     // host time spent inside submit / collect since the last reset (us): [0] submit, [1] collect, [2] of which waiting
     // for the device, [3] calls
     double host_us[4];
@@ -141,7 +146,7 @@ static const int32_t *final_counters(LegionRunner *r, int pipe)
     LegionPool *p = r->pool;
     int32_t *hc = p->h_stage[pipe] + 2 * (size_t)p->batch_size;
     if (p->hop_num > 0) {
-        memcpy(hc, hc + 32, 128);
+        memcpy(hc, r->mirror_back[pipe] != nullptr ? r->mirror_back[pipe] : hc + 32, 128);
         const int hops = hc[LEGION_INTRABATCH_CON * 3 - 1];
         const int n = hc[LEGION_INTRABATCH_CON * 3 + hops];
         const int last = hops > 0 ? hc[LEGION_INTRABATCH_CON * 3 + hops - 1] : 0;
@@ -155,9 +160,10 @@ static const int32_t *final_counters(LegionRunner *r, int pipe)
 static int post_batch(LegionRunner *r, int pipe)
 {
     const int32_t *hc = final_counters(r, pipe);
-    int rc = legion_ipc_publish_counters(r->env, r->dev_id, pipe, hc, hc + 16);
+    const int slot = pipe % r->pool->slots;
+    int rc = legion_ipc_publish_counters(r->env, r->dev_id, slot, hc, hc + 16);
     if (rc != LEGION_OK) return rc;
-    return legion_ipc_post(r->env, r->dev_id, pipe);
+    return legion_ipc_post(r->env, r->dev_id, slot);
 }
 
 static cudaEvent_t take_event(LegionRunner *r)
@@ -176,7 +182,9 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
                                     LegionCache *cache, LegionPool *pool, LegionIpcEnv *env)
 {
     LG_ARG(out != nullptr && graph != nullptr && feature != nullptr && pool != nullptr, "NULL handle");
-    LG_ARG(env == nullptr || pool->pipes <= LEGION_INTERBATCH_CON, "a runner that serves trainers needs a pool of at most 2 pipes");
+    LG_ARG(env == nullptr || pool->slots <= LEGION_INTERBATCH_CON, "a runner that serves trainers needs a pool of at most 2 hand-off slots");
+    LG_ARG(cache == nullptr || cache->kind != 1 || pool->slots == pool->pipes,
+           "an LRU cache keeps whole batches in order: it needs a pool whose pipes are its hand-off slots");
     LG_CUDA(cudaSetDevice(dev_id));
     LegionRunner *r = new LegionRunner();
     r->dev_id = dev_id;
@@ -212,6 +220,9 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
         r->seed_rows[i] = nullptr;
         r->hit_recorded[i] = false;
+        r->slot_busy[i] = false;
+        r->mirror_front[i] = r->mirror_back[i] = nullptr;
+        LG_CUDA(cudaEventCreateWithFlags(&r->slot_done[i], cudaEventDisableTiming));
         r->pipe_stage[i] = nullptr;
         LG_CUDA(cudaEventCreateWithFlags(&r->staged_ev[i], cudaEventDisableTiming));
     }
@@ -476,6 +487,7 @@ static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
             LG_CUDA(cudaMemcpyAsync(bound->agg_dst, p->agg_dst[pipe], 4 * (size_t)r->spec_edges, cudaMemcpyDeviceToHost, r->s_copy));
         LG_CUDA(cudaEventRecord(r->exported[pipe], r->s_copy));
     }
+    r->mirror_front[pipe] = v.mirror;
     r->current_pipe = (pipe + 1) % p->pipes;  // engine/server.cu:398-399
     return LEGION_OK;
 }
@@ -492,6 +504,15 @@ static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound,
     const bool early_sampling = !lru && host_seeds == 0;
     p->pipe = pipe;
     if (early_sampling && r->pipe_busy[pipe] && !pipe_was_synced) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
+    r->mirror_back[pipe] = r->mirror_front[pipe];
+    const int slot = pipe % p->slots;
+    if (p->slots < p->pipes) {
+        // the batch was sampled ahead into the pipe's private buffers: once the batch that used the hand-off slot
+        // before has left it, the block structure is copied into the slot, and the gather fills the slot's rows
+        if (r->slot_busy[slot] && !pipe_was_synced) LG_CUDA(cudaStreamWaitEvent(front, r->slot_done[slot], 0));
+        rc = launch_publish(front, p);
+        if (rc != LEGION_OK) return rc;
+    }
     if (r->pipe_stage[pipe] != nullptr) {
         const SeedStage *st = r->pipe_stage[pipe];
         LG_CUDA(cudaStreamWaitEvent(front, r->staged_ev[pipe], 0));
@@ -519,6 +540,10 @@ static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound,
     // (the export of a bound batch is waited for where it matters -- by collect, and by the batch that samples
     // ahead on this pipe -- not here: the fetch stream is shared by all batches and must not idle behind a copy)
     LG_CUDA(cudaEventRecord(r->pipe_done[pipe], r->s_miss));
+    if (p->slots < p->pipes) {
+        LG_CUDA(cudaEventRecord(r->slot_done[slot], r->s_miss));
+        r->slot_busy[slot] = true;
+    }
     if (lru) c->clock += 1;
     r->pipe_busy[pipe] = true;
     r->last_pipe = pipe;
@@ -535,7 +560,16 @@ static int enqueue_ctl(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
     return issue_rest(r, pipe, host_seeds, bound != nullptr, false);
 }
 
+static int enqueue_impl(LegionRunner *r, int32_t global_batch_id, int32_t mode, int32_t local_batch_id, bool front_only);
+
 extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, int32_t mode, int32_t local_batch_id)
+{
+    return enqueue_impl(r, global_batch_id, mode, local_batch_id, false);
+}
+
+// front_only: sampling (and the staging of seed rows) only; the caller issues the gather half with issue_rest
+// when the batch's hand-off slot is free.
+static int enqueue_impl(LegionRunner *r, int32_t global_batch_id, int32_t mode, int32_t local_batch_id, bool front_only)
 {
     LG_ARG(r != nullptr, "runner is NULL");
     LG_ARG(mode >= 0 && mode <= 2, "invalid mode");
@@ -545,6 +579,7 @@ extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, i
     const int pipe = r->current_pipe;
     int rc = legion_pool_set_batch(p, local_batch_id, mode, pipe, (uint32_t)global_batch_id);
     if (rc != LEGION_OK) return rc;
+    if (p->slots < p->pipes) p->mirror_flip[pipe] ^= 1;
     int32_t bs = p->batch_size;
     if (r->env != nullptr) {
         bs = legion_ipc_current_batchsize(r->env, r->dev_id, mode);
@@ -558,8 +593,10 @@ extern "C" int legion_runner_enqueue(LegionRunner *r, int32_t global_batch_id, i
     if (size < 0) size = 0;
     const SeedStage *st = (r->stage[mode].valid && r->stage[mode].ids_dev == r->feature->ids[mode] &&
                            r->stage[mode].count == total_cap) ? &r->stage[mode] : nullptr;
-    return enqueue_ctl(r, make_batch_ctl(p, r->cache, r->feature->ids[mode], r->feature->labels[mode], total_cap, first,
-                                         (int32_t)size, r->graph->n_nodes), 0, nullptr, st, first);
+    const BatchCtl v = make_batch_ctl(p, r->cache, r->feature->ids[mode], r->feature->labels[mode], total_cap, first,
+                                      (int32_t)size, r->graph->n_nodes);
+    if (front_only) return issue_front(r, v, 0, nullptr, false, st, first);
+    return enqueue_ctl(r, v, 0, nullptr, st, first);
 }
 
 // Host-buffer interface with batches in flight.  submit copies the seeds in and starts the batch;
@@ -697,6 +734,7 @@ static int submit_host_body(LegionRunner *r, const int32_t *seeds, const int32_t
     LG_ARG(r != nullptr && seeds != nullptr && labels != nullptr, "NULL pointer");
     LegionPool *p = r->pool;
     LG_ARG(n_seeds > 0 && n_seeds <= p->batch_size, "n_seeds above the pool's batch size");
+    LG_ARG(p->slots == p->pipes, "the host-buffer calls need a pool whose pipes are its hand-off slots (legion_pool_create)");
     LG_CUDA(cudaSetDevice(r->dev_id));
     {
         int frc = flush_deferred(r);
@@ -915,6 +953,7 @@ extern "C" int legion_runner_sync(LegionRunner *r)
     }
     for (int i = 0; i < LEGION_MAX_PIPES; ++i) {
         r->pipe_busy[i] = false;
+        r->slot_busy[i] = false;
         r->pg[i].launched = false;
     }
     return LEGION_OK;
@@ -952,7 +991,7 @@ extern "C" int legion_runner_run_once(LegionRunner *r, int32_t global_batch_id, 
     LG_ARG(r != nullptr, "runner is NULL");
     const int pipe = r->current_pipe;
     if (r->env != nullptr) {
-        int rc = legion_ipc_wait(r->env, r->dev_id, pipe, timeout_ms);  // engine/server.cu:337
+        int rc = legion_ipc_wait(r->env, r->dev_id, pipe % r->pool->slots, timeout_ms);  // engine/server.cu:337
         if (rc != LEGION_OK) return rc;
     }
     struct timespec t0, t1;
@@ -984,6 +1023,42 @@ extern "C" int legion_runner_serve(LegionRunner *r, int32_t first_global_batch, 
 {
     LG_ARG(r != nullptr && r->env != nullptr, "runner has no IPC environment");
     int prev_pipe = -1;
+    LegionPool *p = r->pool;
+    if (p->slots < p->pipes) {
+        // Sampling ahead of the hand-off: the pool has more pipes than the segment has slots, so up to `pipes`
+        // batches are sampled (into private buffers) while the trainer still holds the slots; the gather half of
+        // batch b is issued when the trainer has released b's slot, batch b - 1 is posted once it has finished.
+        LG_ARG(r->host_pending == 0, "host-buffer batches are waiting to be collected");
+        const int32_t end = first_global_batch + count;
+        const int pipe0 = r->current_pipe;
+        int32_t nf = first_global_batch;
+        for (int32_t b = first_global_batch; b < end; ++b) {
+            int rc;
+            while (nf < end && nf < b + p->pipes) {
+                rc = enqueue_impl(r, nf, legion_ipc_current_mode(r->env, nf), legion_ipc_local_batch_id(r->env, nf), true);
+                if (rc != LEGION_OK) return rc;
+                ++nf;
+            }
+            const int pipe = (pipe0 + (b - first_global_batch)) % p->pipes;
+            rc = legion_ipc_wait(r->env, r->dev_id, pipe % p->slots, timeout_ms);
+            if (rc != LEGION_OK) return rc;
+            LG_CUDA(cudaSetDevice(r->dev_id));
+            rc = issue_rest(r, pipe, 0, false, false);
+            if (rc != LEGION_OK) return rc;
+            if (prev_pipe >= 0) {
+                LG_CUDA(cudaEventSynchronize(r->pipe_done[prev_pipe]));
+                rc = post_batch(r, prev_pipe);
+                if (rc != LEGION_OK) return rc;
+            }
+            prev_pipe = pipe;
+        }
+        if (prev_pipe >= 0) {
+            LG_CUDA(cudaEventSynchronize(r->pipe_done[prev_pipe]));
+            int rc = post_batch(r, prev_pipe);
+            if (rc != LEGION_OK) return rc;
+        }
+        return legion_runner_sync(r);
+    }
     for (int32_t b = first_global_batch; b < first_global_batch + count; ++b) {
         const int pipe = r->current_pipe;
         int rc = legion_ipc_wait(r->env, r->dev_id, pipe, timeout_ms);
@@ -1123,7 +1198,7 @@ extern "C" int legion_runner_destroy(LegionRunner *r)
     cudaStreamDestroy(r->s_copy);
     cudaStreamDestroy(r->s_h2d);
     for (int i = 0; i < LEGION_MAX_PIPES; ++i) { cudaEventDestroy(r->sampled[i]); cudaEventDestroy(r->exported[i]); }
-    for (int i = 0; i < LEGION_MAX_PIPES; ++i) { cudaEventDestroy(r->staged_ev[i]); cudaFree(r->seed_rows[i]); }
+    for (int i = 0; i < LEGION_MAX_PIPES; ++i) { cudaEventDestroy(r->staged_ev[i]); cudaEventDestroy(r->slot_done[i]); cudaFree(r->seed_rows[i]); }
     for (int i = 0; i < 4; ++i) stage_free(&r->stage[i]);
     delete r;
     return LEGION_OK;

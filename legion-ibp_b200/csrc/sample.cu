@@ -500,7 +500,7 @@ hop_flag_kernel(const int32_t *__restrict__ eslot, const MapSlot *map, int32_t *
 __global__ void hop_finish_kernel(const int32_t *__restrict__ erank, const int32_t *__restrict__ tile_off,
                                   const int32_t *__restrict__ eslot, const int32_t *__restrict__ src_global,
                                   int32_t *ids, MapSlot *map, int32_t *agg_src, int32_t *ctl, int32_t *nc, int32_t *ec,
-                                  int op_id, int32_t *host_mirror)
+                                  int op_id, const BatchCtl *__restrict__ b, int last_hop)
 {
     pdl_wait();
     pdl_trigger();
@@ -552,6 +552,7 @@ __global__ void hop_finish_kernel(const int32_t *__restrict__ erank, const int32
     // After the last hop both counter arrays also go to page-locked host memory (one posted store per thread of
     // a warp): the host learns the sizes of the batch without a copy-engine transfer queued behind other batches'
     // exports.  s_flag is the same for every thread of the CTA.
+    int32_t *host_mirror = last_hop ? b->mirror : nullptr;
     if (s_flag && host_mirror != nullptr) {
         __syncthreads();
         if (threadIdx.x < 32) {
@@ -617,6 +618,10 @@ BatchCtl make_batch_ctl(const LegionPool *p, const LegionCache *c, const int32_t
     v.max_rounds = p->max_rounds;
     v.clock = (c != nullptr && c->kind == 1) ? c->clock : 0;
     v.n_nodes = (n_nodes > 0 && n_nodes < 0x7FFFFFFF) ? (int32_t)n_nodes : 0x7FFFFFFF;
+    // two mirrors per pipe when batches are sampled ahead of the hand-off: the next batch on the pipe may finish its
+    // sampling before the host has read the counters of the one before
+    v.mirror = p->h_stage[p->pipe] + 2 * (size_t)p->batch_size + 32 +
+               (p->slots < p->pipes ? 32 * (p->mirror_flip[p->pipe] & 1) : 0);
     return v;
 }
 
@@ -670,8 +675,47 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
                        p->erank[pipe], tile_sum2, tile_off2, ctl, p->max_nodes));
     LG_CUDA(launch_dep(hop_finish_kernel, grid_for(edges, 256 * 4, cap), 256, s, p->erank[pipe], tile_off2, p->eslot[pipe],
                        p->src_global[pipe], p->ids[pipe], p->map[pipe], p->agg_src[pipe], ctl, p->node_counter[pipe],
-                       p->edge_counter[pipe], op_id,
-                       hop + 1 == p->hop_num ? p->h_stage[pipe] + 2 * (size_t)p->batch_size + 32 : (int32_t *)nullptr));
+                       p->edge_counter[pipe], op_id, p->bctl[pipe], hop + 1 == p->hop_num ? 1 : 0));
+    return LEGION_OK;
+}
+
+// ---- hand-off of a batch that was sampled ahead ------------------------------------------------------------------
+// A pool with fewer hand-off slots than pipes samples into private buffers; when the batch's turn comes, its
+// block structure (ids, labels, both edge lists, both counter arrays: ~3 MB for a paper100M-shaped batch) is
+// copied into the slot that the consumer reads (the buffers of engine/ipc_service.cu:163-169).  Sizes are read
+// from the counters on the device.
+__global__ void __launch_bounds__(256)
+publish_kernel(const int32_t *__restrict__ ids, const int32_t *__restrict__ labels, const int32_t *__restrict__ src,
+               const int32_t *__restrict__ dst, const int32_t *__restrict__ nc, const int32_t *__restrict__ ec,
+               int32_t *o_ids, int32_t *o_labels, int32_t *o_src, int32_t *o_dst, int32_t *o_nc, int32_t *o_ec)
+{
+    const int hops = nc[LEGION_INTRABATCH_CON * 3 - 1];
+    const int n = nc[LEGION_INTRABATCH_CON * 3 + hops];
+    const int n_lab = nc[LEGION_INTRABATCH_CON * 3];
+    const int e = ec[0] + ec[1];
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x, step = gridDim.x * blockDim.x;
+    // every array is padded to whole 1024-element tiles, so whole 16-byte vectors may be copied
+    for (int i = tid; i * 4 < n; i += step) reinterpret_cast<int4 *>(o_ids)[i] = reinterpret_cast<const int4 *>(ids)[i];
+    for (int i = tid; i * 4 < e; i += step) {
+        reinterpret_cast<int4 *>(o_src)[i] = reinterpret_cast<const int4 *>(src)[i];
+        reinterpret_cast<int4 *>(o_dst)[i] = reinterpret_cast<const int4 *>(dst)[i];
+    }
+    for (int i = tid; i < n_lab; i += step) o_labels[i] = labels[i];
+    if (blockIdx.x == 0 && threadIdx.x < 16) {
+        o_nc[threadIdx.x] = nc[threadIdx.x];
+        o_ec[threadIdx.x] = ec[threadIdx.x];
+    }
+}
+
+int launch_publish(cudaStream_t s, LegionPool *p)
+{
+    if (p->slots == p->pipes) return LEGION_OK;  // the pipe's buffers are the hand-off buffers
+    const int pipe = p->pipe, slot = pipe % p->slots;
+    publish_kernel<<<p->sm_count * 2, 256, 0, s>>>(p->ids[pipe], p->labels[pipe], p->agg_src[pipe], p->agg_dst[pipe],
+                                                   p->node_counter[pipe], p->edge_counter[pipe], p->pub_ids[slot],
+                                                   p->pub_labels[slot], p->pub_agg_src[slot], p->pub_agg_dst[slot],
+                                                   p->pub_nc[slot], p->pub_ec[slot]);
+    LG_LAUNCH_CHECK();
     return LEGION_OK;
 }
 

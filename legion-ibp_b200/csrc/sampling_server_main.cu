@@ -74,6 +74,7 @@ int main(int argc, char **argv)
     const char *seed_env = getenv("LEGION_SEED");
     const uint64_t seed = seed_env ? strtoull(seed_env, nullptr, 0) : 0;
     const int timeout_ms = getenv("LEGION_TIMEOUT_MS") ? atoi(getenv("LEGION_TIMEOUT_MS")) : -1;
+    const int pipes = (getenv("LEGION_PIPES") && atoi(getenv("LEGION_PIPES")) == 2) ? 2 : LEGION_MAX_PIPES;
     const bool stripe_only = getenv("LEGION_STRIPE_ONLY") != nullptr && getenv("LEGION_STRIPE_ONLY")[0] == '1';
     const bool no_staging = getenv("LEGION_NO_SEED_STAGING") != nullptr && getenv("LEGION_NO_SEED_STAGING")[0] == '1';
     if (ngpu < 1 || ngpu > LEGION_MAX_DEVICE) {
@@ -159,7 +160,10 @@ int main(int argc, char **argv)
             CUCHECK(cudaMemcpy(r.d_labels[m], lab.data(), 4 * (size_t)cnt, cudaMemcpyHostToDevice));
             CHECK(legion_features_set_split(r.feature, m, r.d_ids[m], r.d_labels[m], cnt));
         }
-        CHECK(legion_pool_create(&r.pool, g, max_bs, (int32_t)fanout.size(), fanout.data(), row_bytes, LEGION_INTERBATCH_CON));
+        // two hand-off slots (what the trainers' segment holds); behind a static cache up to four batches are
+        // sampled ahead of them into private buffers (LEGION_PIPES=2 samples into the slots like the reference)
+        CHECK(legion_pool_create_ahead(&r.pool, g, max_bs, (int32_t)fanout.size(), fanout.data(), row_bytes,
+                                       LEGION_INTERBATCH_CON, (dyn_flags & 1) ? LEGION_INTERBATCH_CON : pipes));
         CHECK(legion_pool_set_rng(r.pool, seed + (uint64_t)g, 64));
 
         // PreSc (engine/server.cu:94-122): rank the nodes, fill the cache

@@ -13,7 +13,8 @@ from conftest import ROOT, small_graph
 pytestmark = pytest.mark.gpu
 
 
-def _world(oracle_mod, n=5000, pairs=70000, feat_len=128, batch=96, fanout=(25, 10), cached_frac=0.3, seed=0):
+def _world(oracle_mod, n=5000, pairs=70000, feat_len=128, batch=96, fanout=(25, 10), cached_frac=0.3, seed=0, pipes=2,
+           slots=None):
     import torch
     rng = np.random.default_rng(seed)
     indptr, indices = small_graph(n, pairs, seed)
@@ -35,7 +36,7 @@ def _world(oracle_mod, n=5000, pairs=70000, feat_len=128, batch=96, fanout=(25, 
     w["cache"] = L.UnifiedCache(0, n, feat_len * 4, cap)
     w["d_order"] = torch.from_numpy(order).cuda()
     w["cache"].fill_static(w["d_order"], w["h_table"])
-    w["pool"] = L.MemoryPool(0, batch, list(fanout), feat_len * 4, 2)
+    w["pool"] = L.MemoryPool(0, batch, list(fanout), feat_len * 4, pipes, slots=slots)
     w["pool"].set_rng(99, 64)
     return w
 
@@ -513,10 +514,13 @@ np.savez(out_path, **res)
 '''
 
 
-def test_client_api_consumes_batches(oracle_mod, tmp_path):
+@pytest.mark.parametrize("pipes", [2, 4])
+def test_client_api_consumes_batches(oracle_mod, tmp_path, pipes):
     """The trainer-side C-ABI client (initialize / get_next / get_block_size / get_steps / synchronize /
-    finalize) in a second process, fed by legion_runner_serve."""
-    w = _world(oracle_mod, seed=6)
+    finalize) in a second process, fed by legion_runner_serve.  With four pipes behind the two hand-off slots
+    the server samples up to four batches ahead of the trainer into private buffers and copies each block
+    structure into its slot when the slot is free; what the trainer sees must not change."""
+    w = _world(oracle_mod, seed=6, pipes=pipes, slots=2)
     shm = "legion_b200_cli_%d" % os.getpid()
     env = L.IPCEnv(1, shm)
     env.Coordinate([len(w["train"])], [1], [1], w["batch"], 1)
@@ -524,10 +528,12 @@ def test_client_api_consumes_batches(oracle_mod, tmp_path):
     script = tmp_path / "client.py"
     script.write_text(CLIENT)
     out = tmp_path / "client.npz"
-    n_batches = 4
+    n_batches = 6
     proc = subprocess.Popen([sys.executable, str(script), ROOT, shm, str(n_batches), str(w["table"].shape[1]), str(out)],
                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
     r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], env)
+    if pipes == 4:
+        r.stage_seeds(L.TRAINMODE)
     try:
         r.serve(0, n_batches, timeout_ms=120000)
         stdout, _ = proc.communicate(timeout=120)
@@ -774,4 +780,35 @@ def test_registered_host_seed_list_is_staged_by_address(oracle_mod):
     np.testing.assert_array_equal(feat[:nn], w["table"][ids[:nn]])
     seeds[4 * b + 3] = old
     assert w["pool"].device_error() == 0
+    r.Finalize()
+
+
+@pytest.mark.parametrize("use_graph", [True, False])
+def test_batches_sampled_ahead_of_two_handoff_slots(oracle_mod, use_graph):
+    """A pool with four pipes behind two hand-off slots: batches are sampled into private buffers and published
+    into slot (batch % 2) when their gather is issued.  Whatever is enqueued, the two slots hold the last two
+    batches, bit for bit what the host replay gives, and the per-operator and host-buffer calls refuse such a pool."""
+    w = _world(oracle_mod, seed=31, pipes=4, slots=2)
+    r = L.Runner(0, w["g"], w["f"], w["cache"], w["pool"], None)
+    r.set_options(use_graph=use_graph)
+    r.stage_seeds(L.TRAINMODE)
+    for it in range(6):
+        r.enqueue(it, L.TRAINMODE, it)
+    r.sync()
+    _check_pipe(oracle_mod, w, 0, 4, 4)
+    _check_pipe(oracle_mod, w, 1, 5, 5)
+    r.enqueue(6, L.TRAINMODE, 0)
+    r.sync()
+    _check_pipe(oracle_mod, w, 0, 0, 6)      # batch 6 ran on pipe 2 and was published into slot 0
+    _check_pipe(oracle_mod, w, 1, 5, 5)      # slot 1 is untouched
+    for it in range(7, 16):
+        r.enqueue(it, L.TRAINMODE, it % 6)
+    r.sync()
+    _check_pipe(oracle_mod, w, 0, 14 % 6, 14)
+    _check_pipe(oracle_mod, w, 1, 15 % 6, 15)
+    assert w["pool"].device_error() == 0
+    with pytest.raises(L.LegionError, match="hand-off slots"):
+        r.submit_host(w["train"][:w["batch"]], w["labels"][:w["batch"]], 1)
+    with pytest.raises(L.LegionError, match="numbered by slot"):
+        w["pool"].buffer(L.BUF_IDS, 3)
     r.Finalize()
