@@ -455,9 +455,11 @@ def main():
     ap.add_argument("--slots", type=int, default=2,
                     help="hand-off buffer sets of the device-resident leg (the trainers' segment holds 2); pipes beyond "
                          "them sample ahead into private buffers")
-    ap.add_argument("--host-layout", default="seeds_first", choices=["id", "seeds_first"],
-                    help="row order of the pinned host table: node-id order, or uncached seed nodes first and the "
-                         "other uncached nodes by falling degree (shorter spans for the zero-copy misses)")
+    ap.add_argument("--host-layout", default="packed", choices=["id", "packed", "seeds_first"],
+                    help="row order of the pinned host table: node-id order (the feature file's); packed = the rows of "
+                         "uncached nodes by falling degree, cached rows last (what the sampling_server binary does at "
+                         "load time: the likeliest misses next to each other); seeds_first = uncached seed nodes, then "
+                         "packed (only matters without seed staging)")
     ap.add_argument("--no-replicas", action="store_true",
                     help="N > 1: stripe the whole per-GPU budget over the clique (the reference's placement) instead "
                          "of planning private copies of the hottest peer rows")
@@ -584,6 +586,11 @@ def main():
         node_of = None
         if host_layout == "seeds_first":
             row_of, node_of = host_rows_seeds_first(order, train, cap * world)
+        elif host_layout == "packed":
+            n_cached = min(n, cap * world)
+            row_of = torch.empty(n, dtype=torch.int32, device="cuda")
+            L.UnifiedCache.pack_order(dev, order, n_cached, row_of)
+            node_of = torch.cat([order[n_cached:], order[:n_cached]])
         table = host_buffer(table_rows * row_bytes, "legion_b200_bench_features", rank, world, dev, barrier0)
         fill_host_rows(table.view(dtype).view(table_rows, f), rank, world, barrier0, node_of)
         host_buffer_lock(table, rank, world, dev, barrier0)

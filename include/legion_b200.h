@@ -129,6 +129,16 @@ int legion_dataset_arrays(LegionDataset *d, const int64_t **indptr, const int32_
  * present, else id % partition_count.  ids_out == NULL returns the count only. */
 int legion_dataset_split(LegionDataset *d, int32_t mode, int32_t partition_count, int32_t part_id, int32_t *ids_out,
                          int32_t *labels_out, int32_t *count_out);
+/* Host table packed by rank.  The reference keeps the table in node-id order (cache/cache_impl.cuh:283-286,
+ * storage/storage_management.cu:160-175); random zero-copy reads of widely scattered host pages are slow on this
+ * platform, and the better a node's rank, the more often its row is asked for.  Packed order: the rows of the
+ * nodes that the clique's caches do not hold (rank >= n_cached) by rising rank, then the rows of the cached
+ * nodes.  legion_dataset_pack_features rewrites the loaded table in that order (a second page-locked copy exists
+ * while it runs; legion_dataset_arrays returns the new table afterwards); legion_cache_pack_order gives every
+ * GPU the matching row_of_id array for legion_cache_fill_static_rows / legion_cache_add_replicas. */
+int legion_dataset_pack_features(LegionDataset *d, int32_t dev_id, const int32_t *order_dev, int64_t n_cached);
+int legion_cache_pack_order(int32_t dev_id, const int32_t *order_dev, int64_t n_nodes, int64_t n_cached,
+                            int32_t *row_of_dev, void *stream);
 int legion_dataset_destroy(LegionDataset *d);
 
 /* ---- cache ----------------------------------------------------------------------- */

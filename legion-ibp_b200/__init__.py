@@ -144,6 +144,12 @@ class UnifiedCache:
                                                 _ptr(order_out), _stream(stream)))
 
     @staticmethod
+    def pack_order(dev_id, order_dev, n_cached, row_of_out, stream=None):
+        """row_of[id] of a host table in packed order (Dataset.pack_features): rank t -> t - n_cached, cached ranks last."""
+        _check(lib().legion_cache_pack_order(C.c_int32(dev_id), _ptr(order_dev), C.c_int64(_numel(order_dev)),
+                                             C.c_int64(n_cached), _ptr(row_of_out), _stream(stream)))
+
+    @staticmethod
     def plan(dev_id, order_dev, n_nodes, budget_rows, world, indptr=None, counts=None, cost=None, stream=None):
         """(stripe_rows, replica_rows) of a per-GPU row budget; weights from degrees or presampled counts."""
         a, b = C.c_int64(), C.c_int64()
@@ -557,6 +563,17 @@ class Dataset:
         self.indices = view(ix, e, C.c_int32, np.int32)
         self.features = view(ft, n * f, C.c_float, np.float32).reshape(-1, f) if load_features else None
         self.labels = view(lb, n, C.c_int32, np.int32)
+        self.features_ptr = ft.value
+
+    def pack_features(self, dev_id, order_dev, n_cached):
+        """Rewrites the loaded table in packed order: rows of the nodes of rank >= n_cached by rising rank, then
+        the rows of the cached nodes.  The features view and pointer are those of the new table afterwards."""
+        import numpy as np
+        _check(lib().legion_dataset_pack_features(self.h, C.c_int32(dev_id), _ptr(order_dev), C.c_int64(n_cached)))
+        ft = C.c_void_p()
+        _check(lib().legion_dataset_arrays(self.h, None, None, C.byref(ft), None))
+        n, f = self.meta.node_num, self.meta.float_feature_len
+        self.features = np.ctypeslib.as_array(C.cast(ft, C.POINTER(C.c_float)), shape=(n * f,)).view(np.float32).reshape(-1, f)
         self.features_ptr = ft.value
 
     def split(self, mode, partition_count, part_id):

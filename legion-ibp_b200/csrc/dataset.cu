@@ -212,6 +212,74 @@ extern "C" int legion_dataset_arrays(LegionDataset *d, const int64_t **indptr, c
     return LEGION_OK;
 }
 
+// ---- host table packed by rank -------------------------------------------------------------------------------
+// The reference keeps the feature table in node-id order (cpu_float_features[id * F], cache/cache_impl.cuh:283-286;
+// loaded by storage/storage_management.cu:160-175).  Random zero-copy reads of widely scattered host pages are
+// slow on this platform, and the rows that miss a ranked cache are not spread evenly: the better a node's rank,
+// the more often it is asked for.  Packed order: the rows of the nodes that the clique's caches do NOT hold, by
+// rising rank (the likeliest misses next to each other), followed by the rows of the cached nodes (read once, at
+// fill time).  row of rank t = t - n_cached for t >= n_cached, n - n_cached + t otherwise.
+__global__ void pack_row_of_kernel(const int32_t *__restrict__ order, int64_t n, int64_t n_cached, int32_t *row_of)
+{
+    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x)
+        row_of[order[t]] = (int32_t)(t >= n_cached ? t - n_cached : n - n_cached + t);
+}
+
+// one warp per destination row; source and destination are page-locked host memory
+__global__ void __launch_bounds__(256)
+pack_rows_kernel(const uint8_t *__restrict__ src, uint8_t *dst, const int32_t *__restrict__ order, int64_t n, int64_t n_cached,
+                 int64_t row_bytes)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n; r += n_warps) {
+        const int64_t t = r < n - n_cached ? r + n_cached : r - (n - n_cached);
+        const uint32_t *s4 = reinterpret_cast<const uint32_t *>(src + (int64_t)order[t] * row_bytes);
+        uint32_t *d4 = reinterpret_cast<uint32_t *>(dst + r * row_bytes);
+        for (int64_t w = lane; w < (row_bytes >> 2); w += 32) d4[w] = s4[w];
+    }
+}
+
+extern "C" int legion_cache_pack_order(int32_t dev_id, const int32_t *order_dev, int64_t n_nodes, int64_t n_cached,
+                                       int32_t *row_of_dev, void *stream)
+{
+    LG_ARG(order_dev != nullptr && row_of_dev != nullptr, "NULL pointer");
+    LG_ARG(n_nodes > 0 && n_nodes < (1ll << 31) && n_cached >= 0 && n_cached <= n_nodes, "bad counts");
+    LG_CUDA(cudaSetDevice(dev_id));
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_id);
+    pack_row_of_kernel<<<sms * 8, 256, 0, (cudaStream_t)stream>>>(order_dev, n_nodes, n_cached, row_of_dev);
+    LG_LAUNCH_CHECK();
+    LG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return LEGION_OK;
+}
+
+extern "C" int legion_dataset_pack_features(LegionDataset *d, int32_t dev_id, const int32_t *order_dev, int64_t n_cached)
+{
+    LG_ARG(d != nullptr && d->features != nullptr && d->pinned, "the dataset needs its features in page-locked memory");
+    LG_ARG(order_dev != nullptr && n_cached >= 0 && n_cached <= d->meta.node_num, "bad order or count");
+    LG_CUDA(cudaSetDevice(dev_id));
+    const int64_t n = d->meta.node_num, row_bytes = 4ll * d->meta.float_feature_len;
+    float *packed = (float *)host_alloc(n * row_bytes, 1);
+    if (packed == nullptr) {
+        set_error("legion_dataset_pack_features: no page-locked memory for a second copy of the table (%lld bytes)",
+                  (long long)(n * row_bytes));
+        return LEGION_E_NOMEM;
+    }
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_id);
+    pack_rows_kernel<<<sms * 8, 256>>>((const uint8_t *)d->features, (uint8_t *)packed, order_dev, n, n_cached, row_bytes);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        host_free(packed, 1);
+        LG_CUDA(e);
+    }
+    host_free(d->features, 1);
+    d->features = packed;
+    return LEGION_OK;
+}
+
 // The seeds of one GPU for one mode (storage_management.cu:214-250): owner = partition[id] when a
 // partition file exists (training set only, as in the reference), else id % partition_count.  List
 // order is kept.  Call with ids_out == NULL to get the count.

@@ -7,7 +7,8 @@
 // host thread per GPU, builds the caches (presampled hotness order like the reference; set
 // LEGION_ORDER=degree for the degree order; with more than one GPU the per-GPU budget is planned into a
 // stripe of the clique's cache plus private copies of the hottest peer rows), stages the rows of uncached
-// seeds in page-locked memory for the copy engine, publishes the hand-off buffers, prints
+// seeds in page-locked memory for the copy engine, rewrites the host table in packed order (uncached rows by
+// rising rank; LEGION_HOST_LAYOUT=id keeps the file's order), publishes the hand-off buffers, prints
 // "System is ready for serving" (engine/server.cu:121; scripts/wait_file.sh waits for that line) and
 // serves every batch of the schedule to the trainers.  cache_agg_mode is accepted and ignored: an
 // NVSwitch box is one clique.  dyn_flags: bit 3 (DYN_COMP, comp_cache/cache_helper.cuh:34-45) selects
@@ -56,6 +57,8 @@ struct Rank {
 };
 
 static pthread_barrier_t g_barrier;
+static pthread_mutex_t g_sum_lock = PTHREAD_MUTEX_INITIALIZER;
+static std::vector<uint32_t> g_total_counts;  // presampled access counts of all GPUs, added up
 
 int main(int argc, char **argv)
 {
@@ -75,6 +78,7 @@ int main(int argc, char **argv)
     const uint64_t seed = seed_env ? strtoull(seed_env, nullptr, 0) : 0;
     const int timeout_ms = getenv("LEGION_TIMEOUT_MS") ? atoi(getenv("LEGION_TIMEOUT_MS")) : -1;
     const int pipes = (getenv("LEGION_PIPES") && atoi(getenv("LEGION_PIPES")) == 2) ? 2 : LEGION_MAX_PIPES;
+    const bool packed_layout = !(getenv("LEGION_HOST_LAYOUT") != nullptr && strcmp(getenv("LEGION_HOST_LAYOUT"), "id") == 0);
     const bool stripe_only = getenv("LEGION_STRIPE_ONLY") != nullptr && getenv("LEGION_STRIPE_ONLY")[0] == '1';
     const bool no_staging = getenv("LEGION_NO_SEED_STAGING") != nullptr && getenv("LEGION_NO_SEED_STAGING")[0] == '1';
     if (ngpu < 1 || ngpu > LEGION_MAX_DEVICE) {
@@ -187,6 +191,19 @@ int main(int argc, char **argv)
             CHECK(legion_runner_create(&pre, g, r.graph, r.feature, nullptr, r.pool, nullptr));
             CHECK(legion_runner_presample(pre, 0, steps[0], counts));
             CHECK(legion_runner_destroy(pre));
+            if (ngpu > 1) {
+                // The clique shares ONE ranking (rank t lives on GPU t % ngpu for every member), so the access
+                // counts of all GPUs are added up before any of them ranks (the reference merges the per-GPU
+                // counters of a clique in CandidateSelection, cache/cache.cu:354-447).
+                std::vector<uint32_t> mine((size_t)n);
+                CUCHECK(cudaMemcpy(mine.data(), counts, 4 * (size_t)n, cudaMemcpyDeviceToHost));
+                pthread_mutex_lock(&g_sum_lock);
+                if (g_total_counts.empty()) g_total_counts.assign((size_t)n, 0u);
+                for (int64_t i = 0; i < n; ++i) g_total_counts[(size_t)i] += mine[(size_t)i];
+                pthread_mutex_unlock(&g_sum_lock);
+                pthread_barrier_wait(&g_barrier);
+                CUCHECK(cudaMemcpy(counts, g_total_counts.data(), 4 * (size_t)n, cudaMemcpyHostToDevice));
+            }
             CHECK(legion_cache_hotness_order(g, counts, n, order, nullptr));
             cudaFree(counts);
         }
@@ -213,8 +230,23 @@ int main(int argc, char **argv)
                 if (tmp_ip) cudaFree(tmp_ip);
             }
             CHECK(legion_cache_create(&r.cache, g, n, row_bytes, ngpu, g, (int32_t)stripe, codec));
-            CHECK(legion_cache_fill_static(r.cache, order, n, features, nullptr));
-            if (replicas > 0) CHECK(legion_cache_add_replicas(r.cache, order, n, replicas, nullptr, nullptr));
+            // The host table is rewritten once in packed order: uncached rows by rising rank, cached rows last
+            // (LEGION_HOST_LAYOUT=id keeps the node-id order of the feature file).  Thread 0 moves the rows, every
+            // GPU gets the matching row-of-id array.
+            int32_t *row_of = nullptr;
+            const float *table = features;
+            if (packed_layout) {
+                int64_t n_cached = stripe * ngpu < n ? stripe * ngpu : n;
+                CUCHECK(cudaMalloc(&row_of, 4 * (size_t)n));
+                CHECK(legion_cache_pack_order(g, order, n, n_cached, row_of, nullptr));
+                pthread_barrier_wait(&g_barrier);
+                if (g == 0) CHECK(legion_dataset_pack_features(ds, g, order, n_cached));
+                pthread_barrier_wait(&g_barrier);
+                CHECK(legion_dataset_arrays(ds, nullptr, nullptr, &table, nullptr));
+            }
+            CHECK(legion_cache_fill_static_rows(r.cache, order, n, table, row_of, nullptr));
+            if (replicas > 0) CHECK(legion_cache_add_replicas(r.cache, order, n, replicas, row_of, nullptr));
+            if (row_of) cudaFree(row_of);
             if (g == 0) printf("Cache rows per GPU: %lld striped + %lld private copies\n", (long long)stripe, (long long)replicas);
         }
         cudaFree(order);

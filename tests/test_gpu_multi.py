@@ -134,7 +134,10 @@ def test_server_binary_on_two_gpus_plans_replicas_and_stages_seeds(oracle_mod, t
     meta.cache_memory = feat_len * 4 * 1500
     meta.write(str(tmp_path / "meta_config"))
     shm = "legion_b200_srv2_%d_%d" % (os.getpid(), int(no_vmm))
-    env = dict(os.environ, LEGION_SHM_NAME=shm, LEGION_ORDER="degree", LEGION_SEED=str(seed), LEGION_TIMEOUT_MS="120000")
+    # the run with plain allocations also ranks by presampled hotness (the reference's policy): every GPU must then
+    # rank by the access counts of ALL GPUs, or the members of the clique would disagree on where a row lives
+    env = dict(os.environ, LEGION_SHM_NAME=shm, LEGION_ORDER="hotness" if no_vmm else "degree", LEGION_SEED=str(seed),
+               LEGION_TIMEOUT_MS="120000")
     if no_vmm:
         env["LEGION_NO_VMM"] = "1"
     binary = os.path.join(ROOT, "legion-ibp_b200", "sampling_server")

@@ -812,3 +812,52 @@ def test_batches_sampled_ahead_of_two_handoff_slots(oracle_mod, use_graph):
     with pytest.raises(L.LegionError, match="numbered by slot"):
         w["pool"].buffer(L.BUF_IDS, 3)
     r.Finalize()
+
+
+def test_host_table_packed_by_rank_serves_the_same_batches(oracle_mod, tmp_path):
+    """The loader rewrites the feature table in packed order (uncached rows by rising rank, cached rows last)
+    and every GPU gets the matching row-of-id array: the table's rows move, the batches do not change, and the
+    staged seed rows are found through the same indirection."""
+    import torch
+    from test_dataset_cpu import meta_for, write_dataset
+    f = 32
+    ref = write_dataset(tmp_path / "ds", n=4000, f=f, seed=17)
+    meta = meta_for(tmp_path / "ds", ref, f=f)
+    ds = L.Dataset(meta, pin=True)
+    n = meta.node_num
+    d_ip = torch.from_numpy(np.ascontiguousarray(ds.indptr)).cuda()
+    d_ix = torch.from_numpy(np.ascontiguousarray(ds.indices)).cuda()
+    order = torch.empty(n, dtype=torch.int32, device="cuda")
+    L.UnifiedCache.degree_order(0, d_ip, order)
+    cap = n // 8
+    row_of = torch.empty(n, dtype=torch.int32, device="cuda")
+    L.UnifiedCache.pack_order(0, order, cap, row_of)
+    before = ds.features.copy()
+    ds.pack_features(0, order, cap)
+    h_order, h_row_of = order.cpu().numpy(), row_of.cpu().numpy()
+    np.testing.assert_array_equal(h_row_of[h_order[cap:]], np.arange(n - cap))          # uncached: by rising rank
+    np.testing.assert_array_equal(h_row_of[h_order[:cap]], n - cap + np.arange(cap))    # cached: last
+    np.testing.assert_array_equal(ds.features[h_row_of], before)                       # every row moved to its place
+    g = L.GraphStorage(0, d_ip, d_ix)
+    fs = L.FeatureStorage(0, n, f * 4, ds.features)
+    ids, lab = ds.split(L.TRAINMODE, 1, 0)
+    d_ids, d_lab = torch.from_numpy(ids).cuda(), torch.from_numpy(lab).cuda()
+    fs.set_split(L.TRAINMODE, d_ids, d_lab)
+    cache = L.UnifiedCache(0, n, f * 4, cap)
+    cache.fill_static(order, ds.features, row_of_id=row_of)
+    pool = L.MemoryPool(0, 48, [25, 10], f * 4, 2)
+    pool.set_rng(5, 64)
+    r = L.Runner(0, g, fs, cache, pool, None)
+    assert r.stage_seeds(L.TRAINMODE) > 0
+    for it in range(0, 4, 2):
+        r.enqueue(it, L.TRAINMODE, it)
+        r.enqueue(it + 1, L.TRAINMODE, it + 1)
+        r.sync()
+        for pipe in (0, 1):
+            b = oracle_mod.run_batch(ref["indptr"], ref["indices"], ids, lab, 48, it + pipe, [25, 10], it + pipe, 5)
+            np.testing.assert_array_equal(pool.read(L.BUF_IDS, pipe, len(b["ids"]), np.int32), b["ids"])
+            feat = pool.read(L.BUF_FEATURES, pipe, len(b["ids"]) * f, np.float32).reshape(-1, f)
+            np.testing.assert_array_equal(feat, ref["feats"][b["ids"]])
+    st = cache.stats()
+    assert st["local_hits"] > 0 and st["misses"] > 0 and r.staged_rows() > 0
+    r.Finalize(); pool.close(); cache.close(); fs.close(); g.close(); ds.close()
