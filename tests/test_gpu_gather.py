@@ -586,3 +586,55 @@ def test_native_cache_plan_matches_the_host_planner(oracle_mod, world):
             assert got == tuple(want) or abs(cost(mass, *got) - cost(mass, *want)) <= 1e-9 * max(1.0, cost(mass, *want))
     with pytest.raises(L.LegionError):
         L.UnifiedCache.plan(0, order, n, 10, 2)     # neither degrees nor counts
+
+
+@pytest.mark.parametrize("kg", [1, 4])
+def test_table_spread_over_the_clique_without_a_host_copy(oracle_mod, kg):
+    """The MAG240M-shaped layout: legion_cache_place_static builds the lookup table only, every member writes the
+    rows of its own stripe into its partition (row s = node order[s * kg + ki], made on the fly from the node id),
+    and there is no host table at all.  Every node is cached somewhere, so every row of a gather must come back,
+    local or from a peer, bit for bit; the clique is emulated on one GPU."""
+    import torch
+    from legion_ibp_b200 import synth
+    indptr, _ = small_graph(9000, 110000, 5)
+    n, f = len(indptr) - 1, 768
+    row_bytes = f * 2                                        # 768 x fp16 = 1536-byte rows
+    order = oracle_mod.degree_order(indptr)
+    d_order = torch.from_numpy(order).cuda()
+    cap = (n + kg - 1) // kg
+    rng = np.random.default_rng(kg)
+    ids_list = rng.integers(0, n, 6000).astype(np.int32)
+    d_ids = torch.from_numpy(ids_list).cuda()
+    caches = []
+    for ki in range(kg):
+        c = L.UnifiedCache(0, n, row_bytes, cap, kg=kg, ki=ki)
+        c.place_static(d_order)
+        t = torch.arange(cap, device="cuda", dtype=torch.int64) * kg + ki
+        t = t[t < n]
+        c.write_partition_rows(0, synth.feature_rows(d_order[t], f, 0, torch.float16))
+        with pytest.raises(L.LegionError, match="outside the partition"):
+            c.write_partition_rows(cap, synth.feature_rows(d_order[t[:1]], f, 0, torch.float16))
+        caches.append(c)
+    for a in range(kg):
+        for b in range(kg):
+            if a != b:
+                caches[a].set_peer(b, caches[b].partition()[0])
+    fs = L.FeatureStorage(0, n, row_bytes, None)
+    fs.set_split(L.TRAINMODE, d_ids, torch.zeros_like(d_ids))
+    want = synth.feature_rows(d_ids, f, 0, torch.float16).cpu().numpy().view(np.uint8).reshape(len(ids_list), row_bytes)
+    for ki in (0, kg - 1):
+        pool = L.MemoryPool(0, len(ids_list), [], row_bytes, 1)
+        pool.set_batch(0, L.TRAINMODE, 0, 0)
+        L.BatchGenerate(None, fs, caches[ki], pool, len(ids_list), 0, 0, 0, L.TRAINMODE, False, 0)
+        L.FeatureCacheLookup(None, caches[ki], pool, 1, 0)
+        got = pool.read(L.BUF_FEATURES, 0, len(ids_list) * row_bytes, np.uint8).reshape(len(ids_list), row_bytes)
+        np.testing.assert_array_equal(got, want)
+        ci = pool.read(L.BUF_CACHE_INDEX, 0, len(ids_list), np.int32)
+        np.testing.assert_array_equal(ci, oracle_mod.find_feat(ids_list, oracle_mod.static_cache_lut(order, cap, kg)))
+        assert (ci >= 0).all()
+        st = caches[ki].stats()
+        assert st["misses"] == 0 and (st["peer_hits"] > 0) == (kg > 1)
+        pool.close()
+    for c in caches:
+        c.close()
+    fs.close()
