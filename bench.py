@@ -448,6 +448,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--edge-counts", action="store_true",
+                    help="also time the host-buffer loop with per-destination edge counts in the place of agg_dst "
+                         "(extra key e2e_edge_counts)")
     ap.add_argument("--cache-frac", type=float, default=None, help="override the cached fraction of the table")
     ap.add_argument("--pipes", type=int, default=0,
                     help="batches in flight on the device (0: 4 for static caches, 2 for the LRU cache; the hand-off to "
@@ -897,24 +900,43 @@ def main():
     # wall clock needs a longer window than the device-timed leg: at least 0.5 s of steps
     e2e_steps = max(args.steps, 200, int(0.6 / max(ms_total / args.steps * 1e-3, 1e-6)))
     e2e_steps = min(e2e_steps, 20000)
+    def timed_e2e(counts):
+        """e2e_steps batches through the host-buffer calls; counts: per-destination edge counts (bytes) leave in
+        the place of agg_dst.  Returns (seconds, max over ranks; bytes device -> host; host times)."""
+        runner_h.set_edge_counts(counts)
+        for i in range(depth):          # a first round, untimed: sizes the copies that run ahead
+            submit(50 + i)
+        for _ in range(depth):
+            collect()
+        barrier()
+        runner_h.host_times()
+        t0 = time.perf_counter()
+        d2h = 0
+        hops_n = len(cfg["fanout"])
+
+        def out_bytes(nn, ne):
+            if counts:
+                return 4 * nn + 4 * ne + int(sum(nc_o[9 + h] for h in range(hops_n))) + 4 * b + 128
+            return 4 * nn + 8 * ne + 4 * b + 128
+        for i in range(depth):
+            submit(100 + i)
+        for i in range(depth, e2e_steps):
+            nn, ne = collect()
+            d2h += out_bytes(nn, ne)
+            submit(100 + i)
+        for _ in range(depth):
+            nn, ne = collect()
+            d2h += out_bytes(nn, ne)
+        torch.cuda.synchronize()
+        sec = max_over_ranks(time.perf_counter() - t0)
+        ht = runner_h.host_times()
+        barrier()
+        runner_h.set_edge_counts(False)
+        return sec, d2h, ht
+
     barrier()
     staged_e2e0 = runner_h.staged_rows() if staging else 0
-    runner_h.host_times()
-    t0 = time.perf_counter()
-    d2h = 0
-    for i in range(depth):
-        submit(100 + i)
-    for i in range(depth, e2e_steps):
-        nn, ne = collect()
-        d2h += 4 * nn + 8 * ne + 4 * b + 128
-        submit(100 + i)
-    for _ in range(depth):
-        nn, ne = collect()
-        d2h += 4 * nn + 8 * ne + 4 * b + 128
-    torch.cuda.synchronize()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
-    ht = runner_h.host_times()
-    barrier()
+    e2e_s, d2h, ht = timed_e2e(False)
     staged_e2e = (runner_h.staged_rows() - staged_e2e0) if staging else 0
     # floor of the export: every rank copies device -> pinned host at the same time
     barrier()
@@ -934,6 +956,33 @@ def main():
                    "engine), ids/labels/edge lists/counters written to page-locked host memory every step; gathered rows "
                    "stay in the device hand-off buffer where the trainer reads them; missed rows cross the host link "
                    "inside the gather"}
+    e2e_counts = None
+    if args.edge_counts:
+        # the same loop with the edge counts in the place of agg_dst, checked on its last batch first
+        runner_h.set_edge_counts(True)
+        cnt_bufs = [torch.empty(len(cfg["fanout"]) * max_nodes + 16, dtype=torch.uint8).pin_memory().numpy() for _ in range(depth)]
+        for o, cb in zip(outs, cnt_bufs):
+            o["dst_i32"], o["dst"] = o["dst"], cb
+        for i in range(depth):
+            submit(i)
+        for _ in range(depth):
+            collect()
+        nn_c, ne_c = runner_counts(nc_o, ec_o)
+        last_c = depth - 1
+        pipe_c = runner_h.current_pipe()
+        pipe_c = (pipe_c + pipes - 1) % pipes
+        n_cnt = int(sum(nc_o[9 + h] for h in range(len(cfg["fanout"]))))
+        dst_c = L.agg_dst_from_counts(outs[last_c % depth]["dst"][:n_cnt], nc_o)
+        assert np.array_equal(dst_c, pool_h.read(L.BUF_AGG_DST, pipe_c, ne_c, np.int32)), "edge counts do not give agg_dst"
+        sec_c, d2h_c, ht_c = timed_e2e(True)
+        e2e_counts = {"value": e2e_steps * world / sec_c, "unit": "batches/s", "d2h_bytes_per_step": d2h_c // e2e_steps,
+                      "steps": e2e_steps, "agg_dst_rebuilt_and_checked": True,
+                      "floor_ms_per_step": d2h_c / e2e_steps / (d2h_peak_min * 1e9) * 1e3,
+                      "achieved_ms_per_step": sec_c / e2e_steps * 1e3,
+                      "note": "legion_runner_set_edge_counts(1): one byte per destination and hop leaves in the place of "
+                              "agg_dst (4 bytes per edge); everything else as in e2e"}
+        for o in outs:
+            o["dst"] = o.pop("dst_i32")
     roofline_e2e = {"bound": "host_link_d2h", "peak": d2h_peak_min, "unit": "GB/s",
                     "peak_source": "device -> pinned host cudaMemcpy of 1 GiB, all ranks at the same time, slowest rank",
                     "d2h_bytes_per_step": d2h_per_step, "floor_ms_per_step": floor_s * 1e3,
@@ -965,7 +1014,7 @@ def main():
                             "ms_per_step_median": ms_total / args.steps, "ms_per_step_max": wsorted[-1] / args.steps},
                 "e2e": e2e, "gpu_launches": args.steps * per_batch,
                 "roofline": roofline, "roofline_host_link": roofline_host, "roofline_path": roofline_path,
-                "roofline_nvlink": roofline_nvlink, "roofline_e2e": roofline_e2e,
+                "roofline_nvlink": roofline_nvlink, "roofline_e2e": roofline_e2e, "e2e_edge_counts": e2e_counts,
                 "pipeline": pipeline, "full_size_checks": checks,
                 "cpu_baseline": cpu, "vs_cpu_baseline": {"value": value / cpu["value"], "e2e": e2e_value / cpu["value"]} if cpu else None,
                 "clocks": clocks,

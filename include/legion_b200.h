@@ -474,6 +474,17 @@ int legion_runner_submit_host_to(LegionRunner *r, const int32_t *seeds, const in
 int legion_runner_collect_host(LegionRunner *r, int32_t *ids_out, int32_t *labels_out, int32_t *agg_src_out,
                                int32_t *agg_dst_out, int32_t node_counter_out[16], int32_t edge_counter_out[16],
                                void *features_out);
+/* on = 1: the host-buffer calls of this runner deliver, in the place of agg_dst, the number of edges sampled
+ * for every destination, one byte each (fanout <= 32): for hop 0 the counts of the batch's seeds 0 .. n0-1,
+ * behind them for hop 1 the counts of all nodes known when hop 1 began (node_counter[9 + 1] of them), and so on;
+ * sum over h < hops of node_counter[9 + h] bytes in all.  Within a hop the destinations of the edge list are
+ * non-decreasing (engine/operator_impl.cu:178-301 appends the edges node by node here, in node order), so
+ * agg_dst of hop h is destination d repeated count[d] times and a CSC block (what
+ * training_backend/ipc_cuda_kernel.cu:194-240 hands to the model) needs only the running sum of the counts.
+ * The array passed as agg_dst_out is then written as bytes; it needs hops x max_nodes of them at most.  About a
+ * third of a batch's block structure no longer crosses the host link.  No counterpart in the reference; default
+ * off; call with no batch in flight (LEGION_E_STATE otherwise). */
+int legion_runner_set_edge_counts(LegionRunner *r, int32_t on);
 /* Host time spent inside submit / collect since the last call of this function (microseconds): out[0]
  * submit, out[1] collect, out[2] the part of collect spent waiting for the device, out[3] batches submitted
  * (the per-op times of the reference's MONITOR build, engine/server.cu:346-395, for the host side). */

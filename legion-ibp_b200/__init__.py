@@ -492,6 +492,10 @@ class Runner:
         _check(lib().legion_runner_staged_rows(self.h, C.byref(n)))
         return n.value
 
+    def set_edge_counts(self, on):
+        """The host-buffer calls deliver per-destination edge counts (bytes) in the place of agg_dst."""
+        _check(lib().legion_runner_set_edge_counts(self.h, C.c_int32(1 if on else 0)))
+
     def host_times(self):
         """Host microseconds inside submit / collect since the last call: dict(submit, collect, collect_wait, batches)."""
         a = (C.c_double * 4)()
@@ -642,3 +646,16 @@ class ipc_service:
         if self.h:
             lib().legion_client_close(self.h)
             self.h = C.c_void_p()
+
+
+def agg_dst_from_counts(counts, node_counter):
+    """agg_dst of a batch from its per-destination edge counts (Runner.set_edge_counts): within hop h the
+    destinations run 0 .. node_counter[9 + h] - 1, each repeated count times."""
+    import numpy as np
+    hops = int(node_counter[INTRABATCH_CON * 3 - 1])
+    out, pos = [], 0
+    for h in range(hops):
+        n = int(node_counter[INTRABATCH_CON * 3 + h])
+        out.append(np.repeat(np.arange(n, dtype=np.int32), counts[pos:pos + n]))
+        pos += n
+    return np.concatenate(out) if out else np.zeros(0, np.int32)

@@ -106,6 +106,7 @@ extern "C" int legion_pool_destroy(LegionPool *p)
         cudaFree(p->miss_rows[i]); cudaFree(p->miss_count[i]);
         cudaFree(p->cache_index[i]); cudaFree(p->src_global[i]); cudaFree(p->map[i]); cudaFree(p->node_rec[i]);
         cudaFree(p->tile_sum[i]); cudaFree(p->tile_off[i]); cudaFree(p->eslot[i]); cudaFree(p->erank[i]);
+        cudaFree(p->edge_cnt[i]);
         cudaFree(p->lru_victim[i]); cudaFree(p->ctl[i]); cudaFree(p->bctl[i]);
         cudaFree(p->seed_stage[i]);
         if (p->h_stage[i]) cudaFreeHost(p->h_stage[i]);
@@ -229,6 +230,7 @@ extern "C" int legion_pool_create_ahead(LegionPool **out, int32_t dev_id, int32_
         if (e == cudaSuccess) e = dmalloc(&p->tile_off[i], tiles);
         if (e == cudaSuccess) e = dmalloc(&p->eslot[i], pad_hop_edges);
         if (e == cudaSuccess) e = dmalloc(&p->erank[i], pad_hop_edges);
+        if (e == cudaSuccess) e = dmalloc(&p->edge_cnt[i], (hop_num > 0 ? hop_num : 1) * pad_nodes);
         if (e == cudaSuccess) e = dmalloc(&p->lru_victim[i], pad_nodes);
         if (e == cudaSuccess) e = dmalloc(&p->ctl[i], CTL_WORDS);
         if (e == cudaSuccess) e = dmalloc(&p->bctl[i], 1);

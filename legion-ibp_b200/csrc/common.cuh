@@ -225,6 +225,7 @@ struct LegionPool {
     legion::NodeRec *node_rec[LEGION_MAX_PIPES];
     int32_t *tile_sum[LEGION_MAX_PIPES], *tile_off[LEGION_MAX_PIPES];
     int32_t *eslot[LEGION_MAX_PIPES], *erank[LEGION_MAX_PIPES];
+    uint8_t *edge_cnt[LEGION_MAX_PIPES];         // edges sampled for every destination, hop after hop (one byte each)
     int64_t *lru_victim[LEGION_MAX_PIPES];       // per node: way chosen for insertion, or -1
     int2 *miss_rows[LEGION_MAX_PIPES];           // (row, node id) to fetch from the host table
     int32_t *miss_count[LEGION_MAX_PIPES];       // [0] entries, [4] ticket

@@ -96,6 +96,8 @@ struct LegionRunner {
     int32_t host_nc[LEGION_MAX_PIPES + 1][32]; // final counters of an exported batch (the pipe's mirror may already
                                                // belong to the batch that samples ahead on the same pipe)
     int64_t spec_nodes, spec_edges;                 // sizes to copy ahead: the largest batch seen so far plus a margin
+    int64_t spec_cnt, host_spec_cnt[LEGION_MAX_PIPES + 1];  // the same for the per-destination edge counts (bytes)
+    bool edge_counts;                               // bound batches export edge counts in the place of agg_dst
     bool host_bound[LEGION_MAX_PIPES + 1];  // of the submitted batches, oldest first (parallel to host_fifo)
     bool host_deferred;                          // the newest submitted batch still lacks its back half
     bool host_released;                          // ... and the batch that held its pipe has been collected
@@ -213,6 +215,8 @@ extern "C" int legion_runner_create(LegionRunner **out, int32_t dev_id, LegionGr
     r->host_deferred = false;
     r->host_released = false;
     r->spec_nodes = r->spec_edges = 0;
+    r->spec_cnt = 0;
+    r->edge_counts = false;
     memset(r->stage, 0, sizeof(r->stage));
     r->staged_rows = 0;
     r->host_us[0] = r->host_us[1] = r->host_us[2] = r->host_us[3] = 0.0;
@@ -483,8 +487,12 @@ static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
             LG_CUDA(cudaMemcpyAsync(bound->ids, p->ids[pipe], 4 * (size_t)r->spec_nodes, cudaMemcpyDeviceToHost, r->s_copy));
         if (bound->agg_src && r->spec_edges > 0)
             LG_CUDA(cudaMemcpyAsync(bound->agg_src, p->agg_src[pipe], 4 * (size_t)r->spec_edges, cudaMemcpyDeviceToHost, r->s_copy));
-        if (bound->agg_dst && r->spec_edges > 0)
+        if (bound->agg_dst && r->edge_counts) {
+            if (r->spec_cnt > 0)
+                LG_CUDA(cudaMemcpyAsync(bound->agg_dst, p->edge_cnt[pipe], (size_t)r->spec_cnt, cudaMemcpyDeviceToHost, r->s_copy));
+        } else if (bound->agg_dst && r->spec_edges > 0) {
             LG_CUDA(cudaMemcpyAsync(bound->agg_dst, p->agg_dst[pipe], 4 * (size_t)r->spec_edges, cudaMemcpyDeviceToHost, r->s_copy));
+        }
         LG_CUDA(cudaEventRecord(r->exported[pipe], r->s_copy));
     }
     r->mirror_front[pipe] = v.mirror;
@@ -640,7 +648,17 @@ static int finish_export(LegionRunner *r, int i)
         LG_CUDA(cudaMemcpyAsync(o.agg_src + se, p->agg_src[pipe] + se, 4 * (size_t)(n_edges - se), cudaMemcpyDeviceToHost, r->s_copy));
         tail = true;
     }
-    if (o.agg_dst && n_edges > se) {
+    // per-destination edge counts: one byte for every node known at the start of each hop
+    int64_t n_cnt = 0;
+    for (int h = 0; h < hops; ++h) n_cnt += early[LEGION_INTRABATCH_CON * 3 + h];
+    if (o.agg_dst && r->edge_counts) {
+        const int64_t sc = r->host_spec_cnt[i];
+        if (n_cnt > sc) {
+            LG_CUDA(cudaMemcpyAsync(reinterpret_cast<uint8_t *>(o.agg_dst) + sc, p->edge_cnt[pipe] + sc, (size_t)(n_cnt - sc),
+                                    cudaMemcpyDeviceToHost, r->s_copy));
+            tail = true;
+        }
+    } else if (o.agg_dst && n_edges > se) {
         LG_CUDA(cudaMemcpyAsync(o.agg_dst + se, p->agg_dst[pipe] + se, 4 * (size_t)(n_edges - se), cudaMemcpyDeviceToHost, r->s_copy));
         tail = true;
     }
@@ -652,6 +670,10 @@ static int finish_export(LegionRunner *r, int i)
     if (want_e > p->max_edges) want_e = p->max_edges;
     if (want_n > r->spec_nodes) r->spec_nodes = want_n;
     if (want_e > r->spec_edges) r->spec_edges = want_e;
+    int64_t want_c = (n_cnt + n_cnt / 16 + 255) / 256 * 256;
+    const int64_t cap_c = (int64_t)(p->hop_num > 0 ? p->hop_num : 1) * p->max_nodes;
+    if (want_c > cap_c) want_c = cap_c;
+    if (want_c > r->spec_cnt) r->spec_cnt = want_c;
     return LEGION_OK;
 }
 
@@ -700,6 +722,17 @@ static bool device_can_write_query(const void *p)
         return false;
     }
     return (a.type == cudaMemoryTypeHost || a.type == cudaMemoryTypeManaged) && ((uintptr_t)p & 15) == 0;
+}
+
+extern "C" int legion_runner_set_edge_counts(LegionRunner *r, int32_t on)
+{
+    LG_ARG(r != nullptr, "runner is NULL");
+    if (r->host_pending != 0) {
+        set_error("legion_runner_set_edge_counts: %d batches are waiting to be collected", r->host_pending);
+        return LEGION_E_STATE;
+    }
+    r->edge_counts = on != 0;
+    return LEGION_OK;
 }
 
 extern "C" int legion_runner_submit_host_to(LegionRunner *r, const int32_t *seeds, const int32_t *labels, int32_t n_seeds,
@@ -764,7 +797,7 @@ static int submit_host_body(LegionRunner *r, const int32_t *seeds, const int32_t
     memcpy(p->h_stage[pipe] + p->batch_size, labels, sizeof(int32_t) * n_seeds);
     const BatchCtl v = make_batch_ctl(p, r->cache, p->h_stage[pipe], p->h_stage[pipe] + p->batch_size, n_seeds, 0, n_seeds,
                                       r->graph->n_nodes);
-    const int64_t spec_n = r->spec_nodes, spec_e = r->spec_edges;  // what issue_front copies ahead
+    const int64_t spec_n = r->spec_nodes, spec_e = r->spec_edges, spec_c = r->spec_cnt;  // what issue_front copies ahead
     // a batch that is a slice of the registered host list (by address, and still holding what the list held
     // at registration) gets the rows of its uncached seeds by the copy engine
     const SeedStage *st = nullptr;
@@ -785,6 +818,7 @@ static int submit_host_body(LegionRunner *r, const int32_t *seeds, const int32_t
     r->host_out[r->host_pending] = bound != nullptr ? *bound : HostOut{ nullptr, nullptr, nullptr, nullptr };
     r->host_spec_nodes[r->host_pending] = spec_n;
     r->host_spec_edges[r->host_pending] = spec_e;
+    r->host_spec_cnt[r->host_pending] = spec_c;
     r->host_exported[r->host_pending] = false;
     r->host_fifo[r->host_pending] = pipe;
     r->host_seeds[r->host_pending] = n_seeds;
@@ -854,6 +888,7 @@ static int collect_host_body(LegionRunner *r, int32_t *ids_out, int32_t *labels_
         r->host_out[i - 1] = r->host_out[i];
         r->host_spec_nodes[i - 1] = r->host_spec_nodes[i];
         r->host_spec_edges[i - 1] = r->host_spec_edges[i];
+        r->host_spec_cnt[i - 1] = r->host_spec_cnt[i];
         r->host_exported[i - 1] = r->host_exported[i];
         memcpy(r->host_nc[i - 1], r->host_nc[i], sizeof(r->host_nc[0]));
     }
@@ -881,7 +916,13 @@ static int collect_host_body(LegionRunner *r, int32_t *ids_out, int32_t *labels_
     if (ids_out) LG_CUDA(cudaMemcpyAsync(ids_out, p->ids[pipe], 4 * n_nodes, cudaMemcpyDeviceToHost, s));
     if (labels_out) LG_CUDA(cudaMemcpyAsync(labels_out, p->labels[pipe], 4 * (int64_t)n_seeds, cudaMemcpyDeviceToHost, s));
     if (agg_src_out) LG_CUDA(cudaMemcpyAsync(agg_src_out, p->agg_src[pipe], 4 * n_edges, cudaMemcpyDeviceToHost, s));
-    if (agg_dst_out) LG_CUDA(cudaMemcpyAsync(agg_dst_out, p->agg_dst[pipe], 4 * n_edges, cudaMemcpyDeviceToHost, s));
+    if (agg_dst_out && r->edge_counts) {
+        int64_t n_cnt = 0;
+        for (int h = 0; h < hops; ++h) n_cnt += hc[LEGION_INTRABATCH_CON * 3 + h];
+        if (n_cnt > 0) LG_CUDA(cudaMemcpyAsync(agg_dst_out, p->edge_cnt[pipe], (size_t)n_cnt, cudaMemcpyDeviceToHost, s));
+    } else if (agg_dst_out) {
+        LG_CUDA(cudaMemcpyAsync(agg_dst_out, p->agg_dst[pipe], 4 * n_edges, cudaMemcpyDeviceToHost, s));
+    }
     if (features_out)
         LG_CUDA(cudaMemcpyAsync(features_out, p->features[pipe], n_nodes * (int64_t)p->row_bytes_out,
                                 cudaMemcpyDeviceToHost, s));

@@ -395,11 +395,16 @@ __global__ void __launch_bounds__(256)
 hop_sample_kernel(const int32_t *__restrict__ indices, const NodeRec *__restrict__ rec,
                   const int32_t *__restrict__ tile_off, int32_t fanout, uint32_t hop,
                   const BatchCtl *__restrict__ b, int32_t *src_global, int32_t *agg_dst,
-                  int32_t *eslot, MapSlot *map, MapDims mask, int32_t *ctl, int tile_shift)
+                  int32_t *eslot, MapSlot *map, MapDims mask, int32_t *ctl, int tile_shift,
+                  const int32_t *nc, uint8_t *edge_cnt)
 {
     pdl_wait();
     pdl_trigger();
     if (ctl[CTL_ERROR] != DERR_NONE) return;
+    // where this hop's per-destination edge counts start: behind those of the hops before it, whose destinations
+    // were the nodes known when each began (node_counter words 9 .. 9 + hop - 1)
+    int cnt_base = 0;
+    for (uint32_t h = 0; h < hop; ++h) cnt_base += nc[LEGION_INTRABATCH_CON * 3 + h];
     const uint32_t batch_id = b->global_batch, k0 = b->k0, k1 = b->k1;
     const int max_rounds = b->max_rounds;
     const int n = ctl[CTL_N_NODES];
@@ -411,6 +416,7 @@ hop_sample_kernel(const int32_t *__restrict__ indices, const NodeRec *__restrict
         int4 raw = __ldg(reinterpret_cast<const int4 *>(&rec[i]));
         NodeRec r = *reinterpret_cast<NodeRec *>(&raw);
         const uint32_t deg = (uint32_t)r.deg;
+        if (lane == 0) edge_cnt[cnt_base + i] = (uint8_t)min(deg, k);
         if (deg == 0) continue;
         const int eh0 = __ldg(&tile_off[i >> tile_shift]) + r.loff;  // tile of the counting kernel that ran before
         int out_slot = -1;   // slot of this lane's first edge, second edge in out_slot2
@@ -667,7 +673,8 @@ int launch_sample_hop(cudaStream_t s, LegionPool *p, const LegionGraph *g, int32
     }
     LG_CUDA(launch_dep(hop_sample_kernel, grid_for(inputs, 8, cap), 256, s, g->indices, p->node_rec[pipe], p->tile_off[pipe],
                        fanout, (uint32_t)hop, p->bctl[pipe], p->src_global[pipe], p->agg_dst[pipe], p->eslot[pipe],
-                       p->map[pipe], MapDims{ p->map_front_mask, p->map_mask }, ctl, seeds_pending ? 8 : 10));
+                       p->map[pipe], MapDims{ p->map_front_mask, p->map_mask }, ctl, seeds_pending ? 8 : 10,
+                       p->node_counter[pipe], p->edge_cnt[pipe]));
     static_assert(kScanThreads == 256 && kTile == 1024, "tile shifts above assume 256-thread scans over 1024-item tiles");
     int32_t *tile_sum2 = p->tile_sum[pipe] + p->input_tiles;
     int32_t *tile_off2 = p->tile_off[pipe] + p->input_tiles;

@@ -298,6 +298,67 @@ def test_submit_host_to_writes_pinned_buffers(oracle_mod, use_graph):
     r.Finalize()
 
 
+def test_edge_counts_in_the_place_of_agg_dst(oracle_mod):
+    """set_edge_counts: the array named as agg_dst receives one byte per destination and hop; expanding the
+    counts gives agg_dst of the replay, through bound buffers (batches of growing then shrinking size, so the
+    copy-ahead size is both too small and too large) and through a plain collect."""
+    import torch
+    w = _world(oracle_mod, seed=11)
+    pool = w["pool"]
+    r = L.Runner(0, w["g"], w["f"], w["cache"], pool, None)
+    b = w["batch"]
+    hops = len(w["fanout"])
+
+    def pinned(n, dt=torch.int32):
+        return torch.full((n,), -7, dtype=dt).pin_memory().numpy()
+    outs = [dict(ids=pinned(pool.max_nodes), lab=pinned(b), src=pinned(pool.max_edges),
+                 cnt=pinned(hops * pool.max_nodes + 16, torch.uint8)) for _ in range(2)]
+    nc = np.zeros(16, np.int32); ec = np.zeros(16, np.int32)
+    r.submit_host(w["train"][:b], w["labels"][:b], 30)
+    with pytest.raises(L.LegionError, match="waiting to be collected"):
+        r.set_edge_counts(True)
+    r.collect_host(None, None, None, None, nc, ec, None)
+    r.set_edge_counts(True)
+    sizes = [b // 4, b, b // 2, b, 3]
+
+    def seeds_of(it):
+        return w["train"][it * b:it * b + sizes[it]], w["labels"][it * b:it * b + sizes[it]]
+
+    def check(it, cnt):
+        sd, lb = seeds_of(it)
+        ref = oracle_mod.run_batch(w["indptr"], w["indices"], sd, lb, len(sd), 0, w["fanout"], 40 + it, 99)
+        np.testing.assert_array_equal(nc, ref["node_counter"])
+        n_cnt = int(sum(nc[9 + h] for h in range(hops)))
+        assert int(cnt[:n_cnt].astype(np.int64).sum()) == len(ref["agg_dst"])
+        np.testing.assert_array_equal(L.agg_dst_from_counts(cnt[:n_cnt], nc), ref["agg_dst"])
+        return ref
+
+    for it in range(len(sizes) + 1):
+        if it < len(sizes):
+            o = outs[it % 2]
+            sd, lb = seeds_of(it)
+            r.submit_host_to(sd, lb, 40 + it, o["ids"], o["lab"], o["src"], o["cnt"])
+        if it >= 1:
+            n_nodes, n_edges = r.collect_host(None, None, None, None, nc, ec, None)
+            o = outs[(it - 1) % 2]
+            ref = check(it - 1, o["cnt"])
+            np.testing.assert_array_equal(o["ids"][:n_nodes], ref["ids"])
+            np.testing.assert_array_equal(o["src"][:n_edges], ref["agg_src"])
+    # plain collect: the counts are copied out at collect time
+    sd, lb = seeds_of(1)
+    r.submit_host(sd, lb, 41)
+    cnt = np.zeros(hops * pool.max_nodes, np.uint8)
+    r.collect_host(None, None, None, cnt, nc, ec, None)
+    check(1, cnt)
+    r.set_edge_counts(False)
+    dst = np.zeros(pool.max_edges, np.int32)
+    r.submit_host(sd, lb, 41)
+    _, n_edges = r.collect_host(None, None, None, dst, nc, ec, None)
+    ref = oracle_mod.run_batch(w["indptr"], w["indices"], sd, lb, len(sd), 0, w["fanout"], 41, 99)
+    np.testing.assert_array_equal(dst[:n_edges], ref["agg_dst"])
+    r.Finalize()
+
+
 CONSUMER = r'''
 import ctypes as C, sys, os, mmap, numpy as np
 sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
