@@ -260,6 +260,24 @@ def copy_peak(kind, n_bytes=1 << 30):
     return 3 * n_bytes / (a.elapsed_time(b) * 1e-3) / 1e9
 
 
+def presampled_counts(dev, indptr, indices, n, row_bytes, cfg, seeds, seed_labels, rank, world):
+    """Visits per node (int32, device) over one presampling epoch of every rank's training batches."""
+    import torch.distributed as dist
+    g0 = L.GraphStorage(dev, indptr, indices)
+    f0 = L.FeatureStorage(dev, n, row_bytes, None)
+    f0.set_split(L.TRAINMODE, seeds, seed_labels)
+    pool0 = L.MemoryPool(dev, cfg["batch"], cfg["fanout"], 16, 1)   # rows are not gathered: a token row size
+    pool0.set_rng(RNG_SEED + 7919 * (rank + 1), 64)                  # not the stream of the timed batches
+    r0 = L.Runner(dev, g0, f0, None, pool0, None)
+    counts = torch.zeros(n, dtype=torch.int32, device="cuda")
+    r0.presample(0, (seeds.numel() + cfg["batch"] - 1) // cfg["batch"], counts)
+    torch.cuda.synchronize()
+    r0.Finalize(); pool0.close(); f0.close(); g0.close()
+    if world > 1:
+        dist.all_reduce(counts)
+    return counts
+
+
 def host_rows_seeds_first(order, seeds, n_cached):
     """(row_of[id], node_of[row]) for a host table that holds, in this order: the uncached seed nodes, the
     other uncached nodes by falling degree, and last the nodes whose rows live in the GPU caches (read
@@ -448,6 +466,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cache-order", choices=["degree", "hotness"], default="degree",
+                    help="ranking that fills the static caches: node degree, or the visits counted in a presampling "
+                         "epoch over the training batches (the reference's PreSc)")
     ap.add_argument("--edge-counts", action="store_true",
                     help="also time the host-buffer loop with per-destination edge counts in the place of agg_dst "
                          "(extra key e2e_edge_counts)")
@@ -554,9 +575,17 @@ def main():
     slot_bytes = row_bytes if codec == L.CODEC_RAW else (f + 4 + 15) // 16 * 16
     order = None
     replica_rows = 0
+    access_counts = None
     if not lru_ways:
         order = torch.empty(n, dtype=torch.int32, device="cuda")
-        L.UnifiedCache.degree_order(dev, indptr, order)
+        if args.cache_order == "hotness" and not striped:
+            # the reference's presampling epoch (GPUServer::PreSc, engine/server.cu:94-122): every training batch
+            # is sampled once with a random stream of its own, the visits of all ranks are added up
+            # (cache/cache.cu:354-447) and the nodes are ranked by them
+            access_counts = presampled_counts(dev, indptr, indices, n, row_bytes, cfg, mine, mine_labels, rank, world)
+            L.UnifiedCache.hotness_order(dev, access_counts, order)
+        else:
+            L.UnifiedCache.degree_order(dev, indptr, order)
     if striped:
         cap = (n + world - 1) // world
         need = cap * row_bytes + 8 * (n + 1) + 4 * n_edges + 4 * n
@@ -569,7 +598,7 @@ def main():
             cap = (n + world - 1) // world
         if world > 1 and not args.no_replicas and not lru_ways:
             from legion_ibp_b200 import server
-            mass = server.degree_mass(indptr, order)
+            mass = server.degree_mass(indptr, order) if access_counts is None else server.weight_mass(access_counts, order)
             cap, replica_rows = server.plan_clique_cache(mass, n, budget, world)
             del mass
 
@@ -643,7 +672,7 @@ def main():
         cache.fill_static(order, table if stored is None else stored, row_of_id=row_of)
         if replica_rows > 0:
             cache.add_replicas(order, replica_rows, row_of_id=row_of)
-    del order
+    del order, access_counts
     share = None
     if world > 1 and not lru_ways:
         from legion_ibp_b200 import server
@@ -1009,6 +1038,7 @@ def main():
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": cfg.get("elt", "f32"), "data": "synthetic",
                 "config": workload_config(cfg, world), "host_table_layout": host_layout,
+                "cache_order": ("none" if lru_ways else ("degree" if striped else args.cache_order)),
                 "host_table_rows": table_rows, "pipes": pipes, "handoff_slots": slots, "topology": args.topology,
                 "windows": {"count": len(windows), "timed_s": timed_s, "ms_per_step_min": wsorted[0] / args.steps,
                             "ms_per_step_median": ms_total / args.steps, "ms_per_step_max": wsorted[-1] / args.steps},
