@@ -193,6 +193,30 @@ def make_graph(cfg, device, seed=0):
     return synth.rmat_csr(cfg["n_nodes"], cfg["n_pairs"], seed=seed, device=device)
 
 
+def bind_near_gpu(gpu_index):
+    """Keeps this process on the CPUs next to its GPU (the driver library's affinity mask of the device), so
+    that the page-locked arrays it allocates are on the memory node that the GPU's host link is attached to:
+    with eight ranks on two sockets the copies of half of them otherwise cross the socket link.  Returns the
+    number of CPUs in the mask, 0 when it could not be applied (the process then stays where it was)."""
+    try:
+        import pynvml
+        import torch
+        pynvml.nvmlInit()
+        pr = torch.cuda.get_device_properties(gpu_index)
+        bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        n_cpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (n_cpu + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return 0
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return 0
+
+
 def host_memory_bytes():
     try:
         return os.sysconf("SC_PAGE_SIZE") * os.sysconf("SC_PHYS_PAGES")
@@ -260,8 +284,9 @@ def copy_peak(kind, n_bytes=1 << 30):
     return 3 * n_bytes / (a.elapsed_time(b) * 1e-3) / 1e9
 
 
-def presampled_counts(dev, indptr, indices, n, row_bytes, cfg, seeds, seed_labels, rank, world):
+def presampled_counts(L, dev, indptr, indices, n, row_bytes, cfg, seeds, seed_labels, rank, world):
     """Visits per node (int32, device) over one presampling epoch of every rank's training batches."""
+    import torch
     import torch.distributed as dist
     g0 = L.GraphStorage(dev, indptr, indices)
     f0 = L.FeatureStorage(dev, n, row_bytes, None)
@@ -301,21 +326,30 @@ def zipf_batches(n_nodes, batch, n_batches, s, world=1, rank=0):
     id % world == rank, made distinct inside every window of `batch` seeds (a mini-batch holds a node once)."""
     import torch
     from legion_ibp_b200 import synth
-    draws = synth.zipf_seeds(n_nodes, 4 * batch * n_batches * world, s=s, seed=0, device="cuda")
-    draws = draws[(draws % world) == rank]
-    assert draws.numel() >= 3 * batch * n_batches
-    draws = draws[:3 * batch * n_batches].view(n_batches, 3 * batch)
-    out = []
-    for i in range(n_batches):
-        row = draws[i]
-        uniq, first = None, None
-        srt, idx = torch.sort(row, stable=True)
-        keep = torch.ones_like(srt, dtype=torch.bool)
-        keep[1:] = srt[1:] != srt[:-1]
-        first = torch.sort(idx[keep]).values  # positions of first appearances, in draw order
-        uniq = row[first][:batch]
-        assert uniq.numel() == batch, "not enough distinct Zipf draws for a batch"
-        out.append(uniq.to(torch.int32))
+    # the hottest ids take a large share of the draws (of a rank's share all the more when the ranks split them), so
+    # the window that has to hold `batch` distinct ids is doubled until every batch finds them
+    mult = 1
+    while True:
+        draws = synth.zipf_seeds(n_nodes, 4 * mult * batch * n_batches * world, s=s, seed=0, device="cuda")
+        draws = draws[(draws % world) == rank]
+        win = 3 * mult * batch
+        assert draws.numel() >= win * n_batches
+        draws = draws[:win * n_batches].view(n_batches, win)
+        out = []
+        for i in range(n_batches):
+            row = draws[i]
+            srt, idx = torch.sort(row, stable=True)
+            keep = torch.ones_like(srt, dtype=torch.bool)
+            keep[1:] = srt[1:] != srt[:-1]
+            first = torch.sort(idx[keep]).values  # positions of first appearances, in draw order
+            uniq = row[first][:batch]
+            if uniq.numel() < batch:
+                break
+            out.append(uniq.to(torch.int32))
+        if len(out) == n_batches:
+            break
+        mult *= 2
+        assert mult <= 64, "not enough distinct Zipf draws for a batch"
     return torch.cat(out)
 
 
@@ -466,12 +500,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-binding", action="store_true",
+                    help="leave the process on whatever CPUs it was started on (default: the CPUs next to its GPU)")
     ap.add_argument("--cache-order", choices=["degree", "hotness"], default="degree",
                     help="ranking that fills the static caches: node degree, or the visits counted in a presampling "
                          "epoch over the training batches (the reference's PreSc)")
-    ap.add_argument("--edge-counts", action="store_true",
-                    help="also time the host-buffer loop with per-destination edge counts in the place of agg_dst "
-                         "(extra key e2e_edge_counts)")
+    ap.add_argument("--no-edge-counts", action="store_true",
+                    help="skip the second host-buffer loop, which delivers per-destination edge counts in the place of "
+                         "agg_dst (extra key e2e_edge_counts)")
+    ap.add_argument("--edge-counts", action="store_true", help=argparse.SUPPRESS)  # the loop runs by default
     ap.add_argument("--cache-frac", type=float, default=None, help="override the cached fraction of the table")
     ap.add_argument("--pipes", type=int, default=0,
                     help="batches in flight on the device (0: 4 for static caches, 2 for the LRU cache; the hand-off to "
@@ -519,6 +556,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, "--gpus must equal the number of launched ranks"
+    # (one rank keeps all CPUs: the CPU baseline of the same run uses every core)
+    near_cpus = 0 if (args.no_cpu_binding or world == 1) else bind_near_gpu(local_rank)
     torch.cuda.set_device(local_rank)
     dev = local_rank
     dist = None
@@ -582,7 +621,7 @@ def main():
             # the reference's presampling epoch (GPUServer::PreSc, engine/server.cu:94-122): every training batch
             # is sampled once with a random stream of its own, the visits of all ranks are added up
             # (cache/cache.cu:354-447) and the nodes are ranked by them
-            access_counts = presampled_counts(dev, indptr, indices, n, row_bytes, cfg, mine, mine_labels, rank, world)
+            access_counts = presampled_counts(L, dev, indptr, indices, n, row_bytes, cfg, mine, mine_labels, rank, world)
             L.UnifiedCache.hotness_order(dev, access_counts, order)
         else:
             L.UnifiedCache.degree_order(dev, indptr, order)
@@ -986,7 +1025,7 @@ def main():
                    "stay in the device hand-off buffer where the trainer reads them; missed rows cross the host link "
                    "inside the gather"}
     e2e_counts = None
-    if args.edge_counts:
+    if not args.no_edge_counts:
         # the same loop with the edge counts in the place of agg_dst, checked on its last batch first
         runner_h.set_edge_counts(True)
         cnt_bufs = [torch.empty(len(cfg["fanout"]) * max_nodes + 16, dtype=torch.uint8).pin_memory().numpy() for _ in range(depth)]
@@ -1037,7 +1076,7 @@ def main():
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": cfg.get("elt", "f32"), "data": "synthetic",
-                "config": workload_config(cfg, world), "host_table_layout": host_layout,
+                "config": workload_config(cfg, world), "host_table_layout": host_layout, "cpus_bound_near_gpu": near_cpus,
                 "cache_order": ("none" if lru_ways else ("degree" if striped else args.cache_order)),
                 "host_table_rows": table_rows, "pipes": pipes, "handoff_slots": slots, "topology": args.topology,
                 "windows": {"count": len(windows), "timed_s": timed_s, "ms_per_step_min": wsorted[0] / args.steps,
