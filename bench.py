@@ -321,7 +321,7 @@ def host_rows_seeds_first(order, seeds, n_cached):
     return row_of, node_of.to(torch.int32)
 
 
-def zipf_batches(n_nodes, batch, n_batches, s, world=1, rank=0):
+def zipf_batches(n_nodes, batch, n_batches, s, world=1, rank=0, device="cuda"):
     """Seed sequence of one rank for the LRU stress workload: Zipf(s) draws over node id, those with
     id % world == rank, made distinct inside every window of `batch` seeds (a mini-batch holds a node once)."""
     import torch
@@ -330,7 +330,7 @@ def zipf_batches(n_nodes, batch, n_batches, s, world=1, rank=0):
     # the window that has to hold `batch` distinct ids is doubled until every batch finds them
     mult = 1
     while True:
-        draws = synth.zipf_seeds(n_nodes, 4 * mult * batch * n_batches * world, s=s, seed=0, device="cuda")
+        draws = synth.zipf_seeds(n_nodes, 4 * mult * batch * n_batches * world, s=s, seed=0, device=device)
         draws = draws[(draws % world) == rank]
         win = 3 * mult * batch
         assert draws.numel() >= win * n_batches

@@ -39,3 +39,52 @@ def test_graph_generator_sorts_large_edge_lists_bucket_by_bucket():
     for v in (0, 17, 4999):      # adjacency lists are sorted, without self loops or duplicates
         adj = indices[indptr[v]:indptr[v + 1]]
         assert (np.diff(adj) > 0).all() and (adj != v).all()
+
+
+def _bench_module():
+    import importlib.util
+    import os
+    from conftest import ROOT
+    spec = importlib.util.spec_from_file_location("legion_bench", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_zipf_seed_batches_hold_distinct_ids_for_every_rank():
+    """The LRU stress workload's seeds: Zipf draws split by id % world; a rank whose share is dominated by
+    one hot id (rank 0 of eight: node 0) still gets whole batches of distinct ids, and one rank gets the
+    sequence it always got."""
+    bench = _bench_module()
+    for world, ranks in ((1, (0,)), (4, (0, 3)), (8, (0, 7))):
+        for rank in ranks:
+            t = bench.zipf_batches(50_000_000, 512, 6, 1.1, world, rank, device="cpu")
+            assert t.dtype == torch.int32 and t.numel() == 6 * 512
+            assert bool(((t % world) == rank).all())
+            for row in t.view(6, 512):
+                assert row.unique().numel() == 512
+    a = bench.zipf_batches(50_000_000, 512, 6, 1.1, 1, 0, device="cpu")
+    b = bench.zipf_batches(50_000_000, 512, 6, 1.1, 1, 0, device="cpu")
+    assert torch.equal(a, b)
+    # hot ids come up again and again across batches: that is what the LRU cache lives on
+    assert a.unique().numel() < 0.8 * a.numel()
+
+
+def test_edge_counts_expand_to_agg_dst(oracle_mod):
+    """agg_dst_from_counts: per-destination, per-hop edge counts (what legion_runner_set_edge_counts delivers)
+    give back the destination list of the checker's batch."""
+    import legion_ibp_b200 as L
+    from conftest import small_graph
+    indptr, indices = small_graph(3000, 30000, 5)
+    rng = np.random.default_rng(2)
+    train = rng.permutation(3000)[:200].astype(np.int32)
+    labels = rng.integers(0, 5, 200).astype(np.int32)
+    for fanout in ([25, 10], [5], [15, 10, 5]):
+        b = oracle_mod.run_batch(indptr, indices, train, labels, 64, 1, fanout, 9, 3)
+        nc, ec = b["node_counter"], b["edge_counter"]
+        counts, lo = [], 0
+        for h in range(len(fanout)):
+            e = int(ec[9 + h + 1])                       # edges of hop h
+            counts.append(np.bincount(b["agg_dst"][lo:lo + e], minlength=int(nc[9 + h])).astype(np.uint8))
+            lo += e
+        np.testing.assert_array_equal(L.agg_dst_from_counts(np.concatenate(counts), nc), b["agg_dst"])
