@@ -194,27 +194,46 @@ def make_graph(cfg, device, seed=0):
 
 
 def bind_near_gpu(gpu_index):
-    """Keeps this process on the CPUs next to its GPU (the driver library's affinity mask of the device), so
-    that the page-locked arrays it allocates are on the memory node that the GPU's host link is attached to:
-    with eight ranks on two sockets the copies of half of them otherwise cross the socket link.  Returns the
-    number of CPUs in the mask, 0 when it could not be applied (the process then stays where it was)."""
+    """Keeps this process next to its GPU: on the CPUs that the driver library reports for the device, and with
+    the memory node of the GPU's PCIe slot as the preferred node of its allocations (set_mempolicy), so that the
+    page-locked arrays it allocates are on the memory that the GPU's host link is attached to.  With eight ranks
+    on two sockets the copies of half of them otherwise cross the socket link, whatever CPUs the container
+    allows.  Returns (CPUs in the mask, preferred node); 0 / -1 for a part that could not be applied (the
+    process then stays as it was)."""
+    n_bound, node = 0, -1
     try:
-        import pynvml
         import torch
-        pynvml.nvmlInit()
         pr = torch.cuda.get_device_properties(gpu_index)
         bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+    except Exception:
+        return 0, -1
+    try:
+        import pynvml
+        pynvml.nvmlInit()
         h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
         n_cpu = os.cpu_count() or 1
         words = pynvml.nvmlDeviceGetCpuAffinity(h, (n_cpu + 63) // 64)
         cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
         cpus &= os.sched_getaffinity(0)
-        if not cpus:
-            return 0
-        os.sched_setaffinity(0, cpus)
-        return len(cpus)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            n_bound = len(cpus)
     except Exception:
-        return 0
+        pass
+    try:
+        import ctypes
+        with open("/sys/bus/pci/devices/%s/numa_node" % bus[-12:].lower()) as fh:
+            want = int(fh.read().strip())
+        if want >= 0:
+            mask = (ctypes.c_ulong * 16)()
+            mask[want // 64] = 1 << (want % 64)
+            libc = ctypes.CDLL(None, use_errno=True)
+            MPOL_PREFERRED, SYS_set_mempolicy = 1, 238        # x86-64
+            if os.uname().machine == "x86_64" and libc.syscall(SYS_set_mempolicy, MPOL_PREFERRED, mask, 16 * 64 + 1) == 0:
+                node = want
+    except Exception:
+        pass
+    return n_bound, node
 
 
 def host_memory_bytes():
@@ -557,7 +576,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, "--gpus must equal the number of launched ranks"
     # (one rank keeps all CPUs: the CPU baseline of the same run uses every core)
-    near_cpus = 0 if (args.no_cpu_binding or world == 1) else bind_near_gpu(local_rank)
+    near_cpus, near_node = (0, -1) if (args.no_cpu_binding or world == 1) else bind_near_gpu(local_rank)
     torch.cuda.set_device(local_rank)
     dev = local_rank
     dist = None
@@ -1076,7 +1095,7 @@ def main():
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": cfg.get("elt", "f32"), "data": "synthetic",
-                "config": workload_config(cfg, world), "host_table_layout": host_layout, "cpus_bound_near_gpu": near_cpus,
+                "config": workload_config(cfg, world), "host_table_layout": host_layout, "cpus_bound_near_gpu": near_cpus, "preferred_memory_node": near_node,
                 "cache_order": ("none" if lru_ways else ("degree" if striped else args.cache_order)),
                 "host_table_rows": table_rows, "pipes": pipes, "handoff_slots": slots, "topology": args.topology,
                 "windows": {"count": len(windows), "timed_s": timed_s, "ms_per_step_min": wsorted[0] / args.steps,
