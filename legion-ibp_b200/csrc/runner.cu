@@ -431,9 +431,9 @@ static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
         r->open_window = true;
         r->window_batches = 0;
     }
-    // An LRU cache has to see the previous batch's insertions before anything of this batch runs.
-    // Otherwise sampling only rewrites buffers that the last fetch on this pipe does not touch, so it
-    // starts at once; the wait for that fetch comes before the gather (issue_back).
+    // With a static cache sampling only rewrites buffers that the last fetch on this pipe does not touch, so it
+    // starts at once; the wait for that fetch comes before the gather (issue_rest).  The insertion kernels of
+    // an LRU cache read the pipe's ids, so there sampling waits for the pipe's own previous batch.
     const bool early_sampling = !lru && host_seeds == 0;
     if (pipe_is_held) {
         // the older batch on this pipe is still uncollected: its ids and edge lists have left for the
@@ -442,8 +442,9 @@ static int issue_front(LegionRunner *r, const BatchCtl &v, int32_t host_seeds, c
     } else if (!early_sampling && r->pipe_busy[pipe]) {
         LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
     }
-    if (lru && r->last_pipe >= 0 && r->last_pipe != pipe && r->pipe_busy[r->last_pipe])
-        LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[r->last_pipe], 0));
+    // (an LRU cache has to hold the previous batch's insertions before this batch looks anything up: that wait
+    // stands in front of the gather, issue_rest; sampling reads no cache state and runs beside the previous
+    // batch's fetch)
     // (the seeds and labels of a host-provided batch wait in the pipe's page-locked staging area, which the
     // batch's first sampling kernel reads in place: 64 KB of zero-copy loads instead of one more transfer to issue)
     EvPair se = { nullptr, nullptr };
@@ -512,6 +513,8 @@ static int issue_rest(LegionRunner *r, int pipe, int32_t host_seeds, bool bound,
     const bool early_sampling = !lru && host_seeds == 0;
     p->pipe = pipe;
     if (early_sampling && r->pipe_busy[pipe] && !pipe_was_synced) LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[pipe], 0));
+    if (lru && r->last_pipe >= 0 && r->last_pipe != pipe && r->pipe_busy[r->last_pipe])
+        LG_CUDA(cudaStreamWaitEvent(front, r->pipe_done[r->last_pipe], 0));
     r->mirror_back[pipe] = r->mirror_front[pipe];
     const int slot = pipe % p->slots;
     if (p->slots < p->pipes) {
