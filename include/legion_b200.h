@@ -458,7 +458,7 @@ int legion_runner_submit_host(LegionRunner *r, const int32_t *seeds, const int32
  * copied into these page-locked host buffers (cudaHostAlloc / cudaHostRegister, 16-byte aligned, sized
  * for the pool's limits; NULL skips one) as soon as the batch's sampling is over and while its rows are
  * still being gathered.  The sizes are only on the device at that point, so the copies are issued with
- * the size of the largest batch seen so far plus 1/16 (elements past the batch's own counts are
+ * the size of the largest batch seen so far plus 1/64 (elements past the batch's own counts are
  * scratch), and whatever a larger batch leaves behind is moved when it is collected.  The matching
  * legion_runner_collect_host only waits and returns the counters (its array arguments are ignored), so
  * the host never sits between "sizes known" and "copy issued".  The buffers belong to the batch until

@@ -667,13 +667,14 @@ static int finish_export(LegionRunner *r, int i)
     }
     if (tail) LG_CUDA(cudaStreamSynchronize(r->s_copy));
     r->host_exported[i] = true;
-    // batches of one workload differ by a few percent: 1/16 of headroom, rounded up to 256 elements
-    int64_t want_n = (n_nodes + n_nodes / 16 + 255) / 256 * 256, want_e = (n_edges + n_edges / 16 + 255) / 256 * 256;
+    // the sizes copied ahead follow the largest batch seen so far: 1/64 of headroom above it, rounded up to 256 elements
+    // (every byte of headroom crosses the host link for nothing)
+    int64_t want_n = (n_nodes + n_nodes / 64 + 255) / 256 * 256, want_e = (n_edges + n_edges / 64 + 255) / 256 * 256;
     if (want_n > p->max_nodes) want_n = p->max_nodes;
     if (want_e > p->max_edges) want_e = p->max_edges;
     if (want_n > r->spec_nodes) r->spec_nodes = want_n;
     if (want_e > r->spec_edges) r->spec_edges = want_e;
-    int64_t want_c = (n_cnt + n_cnt / 16 + 255) / 256 * 256;
+    int64_t want_c = (n_cnt + n_cnt / 64 + 255) / 256 * 256;
     const int64_t cap_c = (int64_t)(p->hop_num > 0 ? p->hop_num : 1) * p->max_nodes;
     if (want_c > cap_c) want_c = cap_c;
     if (want_c > r->spec_cnt) r->spec_cnt = want_c;
