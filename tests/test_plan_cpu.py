@@ -53,3 +53,44 @@ def test_degree_mass():
     order = torch.tensor([0, 3, 2, 1], dtype=torch.int32)
     mass = server.degree_mass(indptr, order)
     assert mass(0) == 0.0 and mass(1) == 0.5 and mass(2) == 0.9 and mass(4) == 1.0 and mass(99) == 1.0
+
+
+def _simulated_cost(w_by_rank, n, world, ki, stripe, rep, cost):
+    """Expected cost of one row access on member `ki`, from the placement itself: rank t of the clique's order
+    lives on member t % world while t < stripe * world; the `rep` hottest ranks that are not ki's own are
+    copied into ki's memory (what legion_cache_fill_static + legion_cache_add_replicas build)."""
+    c_l, c_p, c_h = cost
+    t = np.arange(n)
+    covered = t < stripe * world
+    own = covered & (t % world == ki)
+    foreign = np.flatnonzero(covered & ~own)[:rep]
+    local = own.copy()
+    local[foreign] = True
+    per_row = np.where(local, c_l, np.where(covered, c_p, c_h))
+    return float((w_by_rank * per_row).sum() / w_by_rank.sum())
+
+
+def test_plan_cost_formula_agrees_with_the_placement_and_the_choice_is_near_the_best():
+    """The planner's closed form against a row-by-row account of where every rank of the order ends up, and its
+    choice against every split of the budget on a fine grid."""
+    n = 60000
+    rng = np.random.default_rng(4)
+    w = np.sort(rng.pareto(1.3, n) + 1e-3)[::-1].copy()        # weights in rank order, heavy-tailed
+    mass = _mass_from_weights(w)
+    cost = server.ROW_COST
+    for world in (2, 4, 8):
+        budget = n // 8
+        stripe, rep = server.plan_clique_cache(mass, n, budget, world)
+        assert stripe + rep <= budget and rep <= stripe
+        c_l, c_p, c_h = cost
+        cov = min(n, stripe * world)
+        top = min(cov, rep * world // (world - 1))
+        formula = (c_h * (1 - mass(cov)) + c_p * (mass(cov) - mass(top)) * (world - 1) / world +
+                   c_l * (mass(top) + (mass(cov) - mass(top)) / world))
+        sims = [_simulated_cost(w, n, world, ki, stripe, rep, cost) for ki in range(world)]
+        # the closed form treats "one in `world` of the covered ranks is mine" as exact; per member it is not
+        assert abs(np.mean(sims) - formula) <= 0.02 * formula
+        best = min(np.mean([_simulated_cost(w, n, world, ki, budget - r, r, cost) for ki in (0, world - 1)])
+                   for r in range(0, budget // 2 + 1, max(1, budget // 200)))
+        assert np.mean(sims) <= 1.02 * best
+        assert np.mean(sims) <= np.mean([_simulated_cost(w, n, world, ki, budget, 0, cost) for ki in range(world)])
