@@ -401,10 +401,6 @@ hop_sample_kernel(const int32_t *__restrict__ indices, const NodeRec *__restrict
     pdl_wait();
     pdl_trigger();
     if (ctl[CTL_ERROR] != DERR_NONE) return;
-    // where this hop's per-destination edge counts start: behind those of the hops before it, whose destinations
-    // were the nodes known when each began (node_counter words 9 .. 9 + hop - 1)
-    int cnt_base = 0;
-    for (uint32_t h = 0; h < hop; ++h) cnt_base += nc[LEGION_INTRABATCH_CON * 3 + h];
     const uint32_t batch_id = b->global_batch, k0 = b->k0, k1 = b->k1;
     const int max_rounds = b->max_rounds;
     const int n = ctl[CTL_N_NODES];
@@ -416,7 +412,14 @@ hop_sample_kernel(const int32_t *__restrict__ indices, const NodeRec *__restrict
         int4 raw = __ldg(reinterpret_cast<const int4 *>(&rec[i]));
         NodeRec r = *reinterpret_cast<NodeRec *>(&raw);
         const uint32_t deg = (uint32_t)r.deg;
-        if (lane == 0) edge_cnt[cnt_base + i] = (uint8_t)min(deg, k);
+        if (lane == 0) {
+            // this hop's per-destination edge counts start behind those of the hops before it, whose destinations
+            // were the nodes known when each began (node_counter words 9 .. 9 + hop - 1; summed here, by one lane,
+            // rather than held in a register of every thread for the whole kernel)
+            int cnt_at = i;
+            for (uint32_t h = 0; h < hop; ++h) cnt_at += __ldg(&nc[LEGION_INTRABATCH_CON * 3 + h]);
+            edge_cnt[cnt_at] = (uint8_t)min(deg, k);
+        }
         if (deg == 0) continue;
         const int eh0 = __ldg(&tile_off[i >> tile_shift]) + r.loff;  // tile of the counting kernel that ran before
         int out_slot = -1;   // slot of this lane's first edge, second edge in out_slot2
